@@ -1,0 +1,217 @@
+/* ogle_cuda.h - C ABI of the B200 (sm_100a) backend for the OGLE graph runtime's
+ * data-parallel hot path: conv2d family with fused bias/BN/activation, gemm,
+ * pooling, elementwise, concat, layout conversion and the SSD box decoder and
+ * post-process.
+ *
+ * The reference runtime (kl456123/OGLE) has no foreign-function interface: each
+ * operator's Kernel::Compute binds OpenGL textures and draws. Every entry point
+ * below is what such a Compute (or a Context copy function) calls instead, and
+ * its comment cites the reference code it replaces, by path inside that project.
+ *
+ * Conventions
+ *  - All pointers are DEVICE pointers unless a name ends in _host.
+ *  - Activations use ONE layout: [N][H][W][Cs] fp32 with Cs = channel stride in
+ *    floats, Cs >= round_up(C,4) and Cs % 4 == 0. This is the byte layout of the
+ *    reference's NHWC4 textures and of its ANY4 textures for 4-D shapes
+ *    (ogl_runtime/opengl/core/tensor_format.cc:308-337). Lanes C..Cs-1 of a
+ *    tensor produced here are zero unless a wider stride was requested for an
+ *    in-place concat.
+ *  - Every function enqueues work on `stream` and returns immediately. None
+ *    allocates device memory, synchronises or aborts. Return value: OGLE_OK or
+ *    a negative OgleStatus.
+ *  - One host thread per device; calls for different streams/devices may run
+ *    concurrently from different threads.
+ */
+#ifndef OGLE_CUDA_H_
+#define OGLE_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* ogle_stream_t; /* == cudaStream_t */
+
+typedef enum {
+    OGLE_OK = 0,
+    OGLE_ERR_INVALID = -1,     /* bad argument (shape, stride, null pointer) */
+    OGLE_ERR_UNSUPPORTED = -2, /* outside what the reference defines          */
+    OGLE_ERR_CUDA = -3,        /* a CUDA runtime/driver call failed            */
+    OGLE_ERR_ALIGNMENT = -4,   /* pointer or stride not 16-byte aligned        */
+    OGLE_ERR_DEVICE = -5,      /* not an sm_100 device / no device             */
+    OGLE_ERR_TIMEOUT = -6      /* a bounded device-side wait gave up           */
+} OgleStatus;
+
+/* Arithmetic used by the dense contractions (conv2d general/pointwise, gemm). */
+typedef enum {
+    OGLE_MATH_FP32 = 0,   /* CUDA-core fp32 FMA                                         */
+    OGLE_MATH_TF32 = 1,   /* tcgen05 kind::tf32, one pass (10-bit mantissa operands)    */
+    OGLE_MATH_TF32X3 = 2  /* tcgen05 kind::tf32, 3-pass hi/lo split: fp32-grade results */
+} OgleMathMode;
+
+typedef enum { OGLE_ACT_NONE = 0, OGLE_ACT_CLIP = 1, OGLE_ACT_RELU = 2 } OgleActivation;
+
+const char* ogle_cuda_status_string(int status);
+/* Library version and the GPU architecture it was built for ("sm_100a"). */
+const char* ogle_cuda_build_info(void);
+/* Number of kernels this library has launched in this process (all streams). */
+uint64_t ogle_cuda_launch_count(void);
+/* Last CUDA error string seen by this library on the calling thread. */
+const char* ogle_cuda_last_error(void);
+
+/* ------------------------------------------------------------------ conv2d */
+/* Mirrors the uniform set of Conv2DKernel::Compute,
+ * ogl_runtime/opengl/nn/kernels/conv2d.cc:116-167, plus the output placement
+ * fields that let a producer write straight into a concat consumer. */
+typedef struct {
+    int N;
+    int in_hwc[3];   /* H, W, C of the input   */
+    int out_hwc[3];  /* Ho, Wo, K of the output */
+    int kernel, stride, pad, dilation, group;
+    int has_bias;
+    int act;         /* OgleActivation */
+    float min_value, max_value;
+    int in_channel_stride;   /* floats per input pixel; 0 = round_up(C,4)   */
+    int out_channel_stride;  /* floats per output pixel; 0 = round_up(K,4)  */
+    int out_channel_offset;  /* first output channel lands here (mult of 4) */
+    int math_mode;           /* OgleMathMode */
+} OgleConvParams;
+
+/* Output size rule of Conv2DKernel::InferOutputShape (conv2d.cc:169-195).
+ * Fills p->out_hwc from the other fields. */
+int ogle_cuda_conv2d_infer(OgleConvParams* p);
+
+/* Bytes of the device-side packed filter for these parameters. */
+size_t ogle_cuda_conv2d_filter_bytes(const OgleConvParams* p);
+
+/* Re-lays an OIHW filter [K][C/group][k][k] (device) into the layout the conv
+ * kernels read. Replaces the NCHW->HWN4C4 upload pass,
+ * ogl_runtime/opengl/core/context.cc:123-154 with nchw_to_hwn4c4.glsl. Run once
+ * per model, like the reference's "ready" pre-compute (fbo_session.cc:240-245). */
+int ogle_cuda_conv2d_prepack(const OgleConvParams* p, const float* w_oihw, void* packed,
+                             ogle_stream_t stream);
+
+/* y = act(conv(x, w) + bias). Variant choice follows Conv2DKernel::SelectKernel
+ * (conv2d.cc:19-51): pointwise, depthwise, grouped, general. Replaces
+ * conv2d.glsl, conv2d_pw.glsl, conv2d_dw.glsl, conv2d_grp.glsl and their _any4
+ * twins. bias: K floats (may be NULL when has_bias == 0). */
+int ogle_cuda_conv2d(const OgleConvParams* p, const float* x, const void* packed_filter,
+                     const float* bias, float* y, ogle_stream_t stream);
+
+/* -------------------------------------------------------------------- pool */
+/* PoolKernel::Compute, ogl_runtime/opengl/nn/kernels/pool.cc:55-79 + pool.glsl.
+ * type: 0 max (all-padding window gives 0), 1 average (divides by kernel^2,
+ * padding included), 2 global average (kernel := H, requires H == W). */
+typedef struct {
+    int N;
+    int in_hwc[3];
+    int out_hwc[3];
+    int kernel, stride, pad, type;
+    int in_channel_stride, out_channel_stride; /* 0 = round_up(C,4) */
+} OglePoolParams;
+int ogle_cuda_pool_infer(OglePoolParams* p);
+int ogle_cuda_pool(const OglePoolParams* p, const float* x, float* y, ogle_stream_t stream);
+
+/* ------------------------------------------------------------- elementwise */
+/* BatchNormKernel::Compute, nn/kernels/batchnorm.cc:30-78 + batchnorm.glsl:
+ * (x-mean)/sqrt(var+eps)*gamma+beta, params are C floats each. */
+int ogle_cuda_batchnorm(const float* x, const float* gamma, const float* beta, const float* mean,
+                        const float* var, float* y, long pixels, int C, int channel_stride,
+                        float eps, ogle_stream_t stream);
+/* relu.glsl / clip.glsl / binary.glsl over n floats (n % 4 == 0). */
+int ogle_cuda_relu(const float* x, float* y, long n, ogle_stream_t stream);
+int ogle_cuda_clip(const float* x, float* y, long n, float lo, float hi, ogle_stream_t stream);
+int ogle_cuda_add(const float* a, const float* b, float* y, long n, ogle_stream_t stream);
+
+/* -------------------------------------------------------------------- gemm */
+/* GemmKernel::Compute, nn/kernels/gemm.cc:25-65 + gemm.glsl:
+ * Y[M,N] = alpha*A[M,K]*(transB ? B[N,K]^T : B[K,N]) + beta*C.
+ * Row strides (lda, ldb, ldc, ldy, in floats) are round_up(cols,4) for the
+ * reference's ANY4 layout. bias_mode: 0 none, 1 C is [M,N] (ldc), 2 C is [N]
+ * broadcast over rows (the reference defines this only for M == 1). */
+typedef struct {
+    int M, K, N;
+    int transB;
+    float alpha, beta;
+    int bias_mode;
+    int lda, ldb, ldc, ldy;
+    int math_mode; /* OgleMathMode */
+} OgleGemmParams;
+int ogle_cuda_gemm(const OgleGemmParams* p, const float* A, const float* B, const float* C,
+                   float* Y, ogle_stream_t stream);
+
+/* ------------------------------------------------------------------ concat */
+/* ConcatKernel::Compute, nn/kernels/concat.cc:53-96 + concat_multi.glsl.
+ * Shapes are 4-D (left-padded with 1s, as AmendShape does); last dimension of
+ * every tensor is stored padded to a multiple of 4. One pass, each input read
+ * once and written once. */
+#define OGLE_MAX_CONCAT_INPUTS 16
+typedef struct {
+    int n_inputs;
+    int axis;                                   /* 0..3 */
+    int in_shapes[OGLE_MAX_CONCAT_INPUTS][4];
+} OgleConcatParams;
+int ogle_cuda_concat(const OgleConcatParams* p, const float* const* inputs_host_array,
+                     float* y, ogle_stream_t stream);
+
+/* -------------------------------------------------- layout / glue kernels */
+/* ANY -> ANY4 / NHWC -> NHWC4 upload conversion and back
+ * (Context::CopyCPUTensorToDevice / CopyDeviceTensorToCPU,
+ * ogl_runtime/opengl/core/context.cc:123-185; any_to_any4.glsl, any4_to_any.glsl):
+ * [rows][last] dense <-> [rows][stride] with zero fill. stride 0 = round_up(last,4). */
+int ogle_cuda_pad4(const float* dense, float* padded, long rows, int last, int stride,
+                   ogle_stream_t stream);
+int ogle_cuda_unpad4(const float* padded, float* dense, long rows, int last, int stride,
+                     ogle_stream_t stream);
+/* NCHW dense -> NHWC4 (for callers holding NCHW images). */
+int ogle_cuda_nchw_to_nhwc4(const float* nchw, float* nhwc4, int N, int C, int H, int W,
+                            ogle_stream_t stream);
+/* TransposeKernel (nn/kernels/transpose.cc:73-90 + transpose_any4.glsl): 4-D
+ * permute, out dim i = in dim perm[i]; both sides padded on their last dim. */
+int ogle_cuda_transpose(const float* x, float* y, const int in_shape[4], const int perm[4],
+                        ogle_stream_t stream);
+/* ReshapeKernel / FlattenKernel (nn/kernels/reshape.cc:30-46 + reshape_any4.glsl):
+ * same logical element order, different padded last dimension. */
+int ogle_cuda_reshape(const float* x, float* y, long n_elements, int in_last, int out_last,
+                      ogle_stream_t stream);
+
+/* --------------------------------------------------------------------- SSD */
+/* functor::SSDBBoxDecoder (ogl_runtime/opengl/core/functor.cc:96-143 +
+ * decoder.glsl): pred [N][A][4] deltas, anchors [A][4] (cx,cy,w,h) shared by all
+ * images, out [N][A][4] corners (xmin,ymin,xmax,ymax). */
+int ogle_cuda_ssd_decode(const float* pred, const float* anchors, float* out, int N, int A,
+                         const float variances[4], ogle_stream_t stream);
+
+/* Detector post-process (ogl_runtime/opengl/examples/ssd/detector.cc:114-228):
+ * the reference does this on the CPU after reading back boxes and logits.
+ * mode 0 (reference rule): softmax, best foreground class per anchor, keep
+ *   score > score_thr, top_k by score over the image (ties: lower anchor
+ *   first), then the reference's greedy NMS on integer pixel rectangles when
+ *   nms_thr > 0. Output rows per image: top_k.
+ * mode 1 (per-class, standard SSD): softmax, per foreground class keep
+ *   score > score_thr and the top_k by score. Output rows per image:
+ *   (C-1)*top_k. No NMS.
+ * logits [N][A][logit_stride] (logit_stride >= C); boxes [N][A][4] corners.
+ * Outputs (device): out_score [N][rows] (0 where empty), out_anchor [N][rows]
+ * (-1 where empty), out_class [N][rows], out_box [N][rows][4] (mode 0: integer
+ * pixel rect x,y,w,h as floats; mode 1: the corner box), out_count [N] (mode 0)
+ * or [N][C-1] (mode 1). */
+typedef struct {
+    int N, A, C;
+    int logit_stride;
+    int mode;
+    float score_thr;
+    int top_k;       /* <= 256 */
+    float nms_thr;   /* mode 0 only; <= 0 disables NMS */
+    int image_w, image_h; /* mode 0: scale to pixels */
+} OgleDetectParams;
+int ogle_cuda_ssd_detect(const OgleDetectParams* p, const float* logits, const float* boxes,
+                         float* out_score, int* out_anchor, int* out_class, float* out_box,
+                         int* out_count, ogle_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OGLE_CUDA_H_ */

@@ -1,0 +1,36 @@
+// Library-wide state and the small informational entry points of ogle_cuda.h.
+#include "common.cuh"
+
+namespace ogle {
+std::atomic<uint64_t> g_launch_count{0};
+static thread_local char g_last_error[256] = "";
+void set_last_error(cudaError_t e) {
+    const char* s = cudaGetErrorString(e);
+    int i = 0;
+    for (; s[i] && i < 255; ++i) g_last_error[i] = s[i];
+    g_last_error[i] = 0;
+}
+}  // namespace ogle
+
+extern "C" {
+
+const char* ogle_cuda_status_string(int status) {
+    switch (status) {
+        case OGLE_OK: return "ok";
+        case OGLE_ERR_INVALID: return "invalid argument";
+        case OGLE_ERR_UNSUPPORTED: return "unsupported (outside what the reference defines)";
+        case OGLE_ERR_CUDA: return "CUDA call failed";
+        case OGLE_ERR_ALIGNMENT: return "pointer or stride not 16-byte aligned";
+        case OGLE_ERR_DEVICE: return "no sm_100 device";
+        case OGLE_ERR_TIMEOUT: return "bounded device-side wait gave up";
+        default: return "unknown status";
+    }
+}
+
+const char* ogle_cuda_build_info(void) { return "ogle_cuda 0.1 sm_100a"; }
+
+uint64_t ogle_cuda_launch_count(void) { return ogle::g_launch_count.load(std::memory_order_relaxed); }
+
+const char* ogle_cuda_last_error(void) { return ogle::g_last_error; }
+
+}  // extern "C"

@@ -1,0 +1,157 @@
+// conv2d entry points: shape inference, filter packing and variant dispatch.
+#include "conv_args.cuh"
+
+namespace ogle {
+
+int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x,
+                   const float* w_hi, const float* w_lo, const float* bias, float* y, cudaStream_t s);
+bool conv_tc_supported(const ConvArgs& a, int variant);
+
+// Destination-indexed packing of an OIHW filter into the three sections of the
+// packed blob (see FilterLayout).
+__global__ void prepack_tap_major_kernel(const float* __restrict__ w, float* __restrict__ dst,
+                                         int K, int Cg, int kernel, int Cp, int Kp) {
+    const int taps = kernel * kernel;
+    const long total = (long)taps * Cp * Kp;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total;
+         i += (long)gridDim.x * blockDim.x) {
+        long t = i;
+        const int k = int(t % Kp); t /= Kp;
+        const int c = int(t % Cp); t /= Cp;
+        const int tap = int(t);
+        float v = 0.f;
+        if (k < K && c < Cg) v = w[((long)k * Cg + c) * taps + tap];
+        dst[i] = v;
+    }
+}
+
+__global__ void prepack_kmajor_kernel(const float* __restrict__ w, float* __restrict__ hi,
+                                      float* __restrict__ lo, int K, int Cg, int kernel,
+                                      int Kp128, int Cp32) {
+    const int taps = kernel * kernel;
+    const long total = (long)Kp128 * taps * Cp32;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total;
+         i += (long)gridDim.x * blockDim.x) {
+        long t = i;
+        const int c = int(t % Cp32); t /= Cp32;
+        const int tap = int(t % taps); t /= taps;
+        const int k = int(t);
+        float v = 0.f;
+        if (k < K && c < Cg) v = w[((long)k * Cg + c) * taps + tap];
+        // hi keeps the 10 mantissa bits a TF32 operand carries; lo is the exact
+        // remainder (itself later truncated to TF32 by the tensor core)
+        const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+        hi[i] = h;
+        lo[i] = v - h;
+    }
+}
+
+static int fill_args(const OgleConvParams* p, ConvArgs* a, int* variant) {
+    if (!p) return OGLE_ERR_INVALID;
+    const int H = p->in_hwc[0], W = p->in_hwc[1], C = p->in_hwc[2];
+    const int K = p->out_hwc[2];
+    int group = p->group <= 0 ? 1 : p->group;   // conv2d.cc:91-94
+    if (p->N <= 0 || H <= 0 || W <= 0 || C <= 0 || K <= 0) return OGLE_ERR_INVALID;
+    if (p->kernel <= 0 || p->stride <= 0 || p->pad < 0 || p->dilation <= 0) return OGLE_ERR_INVALID;
+    if (C % group || K % group) return OGLE_ERR_INVALID;
+    if (p->act < 0 || p->act > 2) return OGLE_ERR_INVALID;
+    const int eff = p->kernel * p->dilation - p->dilation + 1;   // conv2d.cc:191-194
+    const int Ho = (H - eff + 2 * p->pad) / p->stride + 1;
+    const int Wo = (W - eff + 2 * p->pad) / p->stride + 1;
+    if (Ho <= 0 || Wo <= 0) return OGLE_ERR_INVALID;
+    a->N = p->N; a->H = H; a->W = W; a->C = C;
+    a->Cs = p->in_channel_stride ? p->in_channel_stride : up4(C);
+    a->Ho = Ho; a->Wo = Wo; a->K = K;
+    a->Ks = p->out_channel_stride ? p->out_channel_stride : up4(K);
+    a->koff = p->out_channel_offset;
+    if (a->Cs < up4(C) || (a->Cs & 3) || (a->Ks & 3) || (a->koff & 3) || a->koff < 0 ||
+        a->koff + up4(K) > a->Ks)
+        return OGLE_ERR_INVALID;
+    a->kernel = p->kernel; a->stride = p->stride; a->pad = p->pad; a->dil = p->dilation; a->group = group;
+    // shader choice, conv2d.cc:35-50
+    if (p->kernel == 1 && group == 1 && p->dilation == 1 && p->stride == 1 && p->pad == 0) *variant = CONV_POINTWISE;
+    else if (group != 1) *variant = (group == C && group == K) ? CONV_DEPTHWISE : CONV_GROUPED;
+    else *variant = CONV_GENERAL;
+    a->Cp = (*variant == CONV_DEPTHWISE) ? 1 : up4(C / group);
+    a->Kp = up4(K);
+    a->has_bias = p->has_bias ? 1 : 0;
+    a->M = (long)p->N * Ho * Wo;
+    // activation, with the per-shader differences of the reference kept:
+    //   pointwise clip clamps to [0, max] (conv2d_pw.glsl:85);
+    //   grouped relu is max(min_value, v) (conv2d_grp.glsl:121).
+    a->act = p->act; a->lo = p->min_value; a->hi = p->max_value;
+    if (*variant == CONV_POINTWISE && p->act == OGLE_ACT_CLIP) a->lo = 0.f;
+    if (*variant == CONV_GROUPED && p->act == OGLE_ACT_RELU) {
+        a->act = OGLE_ACT_CLIP; a->lo = p->min_value; a->hi = __builtin_inff();
+    }
+    return OGLE_OK;
+}
+
+}  // namespace ogle
+
+using namespace ogle;
+
+extern "C" {
+
+int ogle_cuda_conv2d_infer(OgleConvParams* p) {
+    ConvArgs a; int variant;
+    int rc = fill_args(p, &a, &variant);
+    if (rc != OGLE_OK) return rc;
+    p->out_hwc[0] = a.Ho; p->out_hwc[1] = a.Wo;
+    return OGLE_OK;
+}
+
+size_t ogle_cuda_conv2d_filter_bytes(const OgleConvParams* p) {
+    ConvArgs a; int variant;
+    if (fill_args(p, &a, &variant) != OGLE_OK) return 0;
+    return filter_layout(a.K, a.C / a.group, a.kernel, a.group, a.Cp).total;
+}
+
+int ogle_cuda_conv2d_prepack(const OgleConvParams* p, const float* w_oihw, void* packed,
+                             ogle_stream_t stream) {
+    ConvArgs a; int variant;
+    int rc = fill_args(p, &a, &variant);
+    if (rc != OGLE_OK) return rc;
+    if (!w_oihw || !packed) return OGLE_ERR_INVALID;
+    if (!aligned16(packed)) return OGLE_ERR_ALIGNMENT;
+    const int Cg = a.C / a.group;
+    const FilterLayout L = filter_layout(a.K, Cg, a.kernel, a.group, a.Cp);
+    cudaStream_t s = (cudaStream_t)stream;
+    char* base = static_cast<char*>(packed);
+    const long n0 = (long)a.kernel * a.kernel * a.Cp * a.Kp;
+    prepack_tap_major_kernel<<<grid_for(n0, 256), 256, 0, s>>>(w_oihw, reinterpret_cast<float*>(base),
+                                                               a.K, Cg, a.kernel, a.Cp, a.Kp);
+    rc = finish_launch();
+    if (rc != OGLE_OK) return rc;
+    if (L.kmajor_bytes) {
+        const long n1 = (long)L.Kp128 * a.kernel * a.kernel * L.Cp32;
+        prepack_kmajor_kernel<<<grid_for(n1, 256), 256, 0, s>>>(
+            w_oihw, reinterpret_cast<float*>(base + L.off_hi), reinterpret_cast<float*>(base + L.off_lo),
+            a.K, Cg, a.kernel, L.Kp128, L.Cp32);
+        rc = finish_launch();
+    }
+    return rc;
+}
+
+int ogle_cuda_conv2d(const OgleConvParams* p, const float* x, const void* packed_filter,
+                     const float* bias, float* y, ogle_stream_t stream) {
+    ConvArgs a; int variant;
+    int rc = fill_args(p, &a, &variant);
+    if (rc != OGLE_OK) return rc;
+    if (a.Ho != p->out_hwc[0] || a.Wo != p->out_hwc[1]) return OGLE_ERR_INVALID;
+    if (!x || !packed_filter || !y || (a.has_bias && !bias)) return OGLE_ERR_INVALID;
+    if (!aligned16(x) || !aligned16(y) || !aligned16(packed_filter))
+        return OGLE_ERR_ALIGNMENT;
+    if (p->math_mode < OGLE_MATH_FP32 || p->math_mode > OGLE_MATH_TF32X3) return OGLE_ERR_INVALID;
+    const char* base = static_cast<const char*>(packed_filter);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (p->math_mode != OGLE_MATH_FP32 && (variant == CONV_GENERAL || variant == CONV_POINTWISE) &&
+        conv_tc_supported(a, variant)) {
+        const FilterLayout L = filter_layout(a.K, a.C / a.group, a.kernel, a.group, a.Cp);
+        return launch_conv_tc(a, variant, p->math_mode, x, reinterpret_cast<const float*>(base + L.off_hi),
+                              reinterpret_cast<const float*>(base + L.off_lo), bias, y, s);
+    }
+    return launch_conv_simt(a, variant, x, reinterpret_cast<const float*>(base), bias, y, s);
+}
+
+}  // extern "C"

@@ -1,0 +1,54 @@
+// Argument block and packed-filter layout shared by the conv2d kernels.
+#pragma once
+#include "common.cuh"
+
+namespace ogle {
+
+enum ConvVariant { CONV_GENERAL = 0, CONV_POINTWISE = 1, CONV_DEPTHWISE = 2, CONV_GROUPED = 3 };
+
+struct ConvArgs {
+    int N, H, W, C, Cs;        // input: channels and channel stride (floats per pixel)
+    int Ho, Wo, K, Ks, koff;   // output: channels, channel stride, first channel offset
+    int kernel, stride, pad, dil, group;
+    int Cp, Kp;                // packed filter extents: round_up(C/group,4), round_up(K,4)
+    int act;                   // effective activation after the per-variant quirks
+    float lo, hi;
+    int has_bias;
+    long M;                    // N*Ho*Wo output pixels
+};
+
+// Packed filter blob, in this order (all sections 256-byte aligned):
+//   section 0  "tap-major"  [kernel*kernel][Cp][Kp] fp32, zero padded: read by the
+//              CUDA-core kernels with the output channel fastest, so that a warp's
+//              weight loads are contiguous. For depthwise Cp == 1: [taps][Kp].
+//   section 1  "k-major hi" [Kp128][kernel*kernel][Cp32] fp32 with the low 13
+//              mantissa bits cleared: B operand of the tcgen05 path (TMA tiles of
+//              128 output channels x 32 reduction elements).
+//   section 2  "k-major lo" same shape: w - hi(w), for the 3-pass TF32 split.
+// Sections 1 and 2 exist only for group == 1.
+struct FilterLayout {
+    size_t tap_major_bytes, kmajor_bytes;   // one k-major section
+    size_t off_hi, off_lo, total;
+    int Kp128, Cp32;
+};
+
+inline size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+inline FilterLayout filter_layout(int K, int Cg, int kernel, int group, int Cp) {
+    FilterLayout L;
+    const int taps = kernel * kernel;
+    L.tap_major_bytes = align256(size_t(taps) * Cp * up4(K) * sizeof(float));
+    L.Kp128 = (K + 127) / 128 * 128;
+    L.Cp32 = (Cg + 31) / 32 * 32;
+    L.kmajor_bytes = group == 1 ? align256(size_t(L.Kp128) * taps * L.Cp32 * sizeof(float)) : 0;
+    L.off_hi = L.tap_major_bytes;
+    L.off_lo = L.off_hi + L.kmajor_bytes;
+    L.total = L.off_lo + L.kmajor_bytes;
+    return L;
+}
+
+// Entry points of the individual translation units.
+int launch_conv_simt(const ConvArgs& a, int variant, const float* x, const float* w_tap_major,
+                     const float* bias, float* y, cudaStream_t s);
+
+}  // namespace ogle

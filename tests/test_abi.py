@@ -1,0 +1,52 @@
+"""The C-ABI library loads without a GPU and exports every symbol the headers declare."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared(header, prefix):
+    text = open(os.path.join(ROOT, "include", header)).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(" + prefix + r"\w+)\s*\(", text)))
+
+
+def test_cuda_library_exports_every_declared_symbol():
+    from ogle_b200 import _lib
+    lib = _lib.cuda_lib()
+    names = _declared("ogle_cuda.h", "ogle_cuda_")
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(lib, n), n
+    assert set(names) == set(_lib.CUDA_SYMBOLS), set(names) ^ set(_lib.CUDA_SYMBOLS)
+    assert b"sm_100a" in lib.ogle_cuda_build_info()
+    assert lib.ogle_cuda_status_string(-2).startswith(b"unsupported")
+
+
+def test_shape_inference_needs_no_gpu():
+    """Output-size rule of conv2d.cc:191-194 and pool.cc:93-96."""
+    from ogle_b200 import ops
+    p = ops.conv_params(1, 300, 300, 3, 32, 3, stride=2, pad=1)
+    assert list(p.out_hwc) == [150, 150, 32]
+    p = ops.conv_params(1, 19, 19, 512, 24, 3, stride=1, pad=1)
+    assert list(p.out_hwc) == [19, 19, 24]
+    p = ops.conv_params(1, 10, 10, 8, 8, 3, stride=2, pad=1, dilation=2)
+    assert list(p.out_hwc) == [4, 4, 8]
+    q = ops.pool_params(32, 76, 76, 256, 3, 2, 1, 0)
+    assert list(q.out_hwc) == [38, 38, 256]
+    q = ops.pool_params(2, 7, 7, 512, 0, 0, 0, 2)
+    assert list(q.out_hwc) == [1, 1, 512] and q.kernel == 7
+
+
+def test_invalid_arguments_return_status_not_abort():
+    from ogle_b200 import _lib
+    lib = _lib.cuda_lib()
+    p = _lib.ConvParams()
+    assert lib.ogle_cuda_conv2d_infer(ctypes.byref(p)) == -1
+    assert lib.ogle_cuda_conv2d_filter_bytes(ctypes.byref(p)) == 0
+    assert lib.ogle_cuda_relu(None, None, 3, None) == -1      # n not a multiple of 4
+    assert lib.ogle_cuda_relu(None, None, 0, None) == 0       # empty input is a no-op
+    assert lib.ogle_cuda_pad4(None, None, 0, 5, 0, None) == 0

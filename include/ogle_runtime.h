@@ -1,0 +1,80 @@
+/* ogle_runtime.h - C ABI of the host runtime (libogle_rt.so): the graph session
+ * and the SSD detector, for callers that do not link the C++ classes.
+ *
+ * The reference runtime is a C++ library with no foreign-function interface;
+ * each entry point below names the C++ member it wraps, which in turn mirrors a
+ * member of the reference (cited by path inside kl456123/OGLE).
+ *
+ * Error behaviour: the reference aborts the process on any failed check. Here
+ * the same conditions come back as a negative return value and
+ * ogle_rt_last_error() holds the message for the calling thread.
+ */
+#ifndef OGLE_RUNTIME_H_
+#define OGLE_RUNTIME_H_
+#include <stddef.h>
+#include <stdint.h>
+#include "ogle_cuda.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct OgleSession OgleSession;
+typedef struct OgleDetector OgleDetector;
+
+/* dlxnet.TensorProto.DataFormat values (ogl_runtime/opengl/core/dlxnet.proto:8-29) */
+enum { OGLE_FMT_NCHW = 0, OGLE_FMT_NHWC = 1, OGLE_FMT_NHWC4 = 3, OGLE_FMT_HWN4C4 = 4, OGLE_FMT_ANY = 5, OGLE_FMT_ANY4 = 6 };
+
+const char* ogle_rt_last_error(void);
+/* Operator names in the kernel registry, '\n'-separated
+ * (REGISTER_KERNEL_WITH_NAME, ogl_runtime/opengl/core/kernel_registry.h:36-42). */
+const char* ogle_rt_registered_kernels(void);
+
+/* FBOSession(), ogl_runtime/opengl/core/fbo_session.h:13-15. device < 0 keeps the
+ * current CUDA device; stream NULL creates a private stream. */
+OgleSession* ogle_session_create(int device, ogle_stream_t stream);
+void ogle_session_destroy(OgleSession* s);
+/* "math_mode" (OgleMathMode), "use_graph" (0/1). Set before the first run. */
+int ogle_session_set_option(OgleSession* s, const char* key, int value);
+/* FBOSession::LoadGraph(path) / LoadGraph(ModelProto), fbo_session.cc:62-124. */
+int ogle_session_load_graph_file(OgleSession* s, const char* path);
+int ogle_session_load_graph_bytes(OgleSession* s, const void* data, size_t size);
+/* FBOSession::Run(NamedTensorList), fbo_session.cc:127-156. Each input is a dense
+ * host tensor (data, shape, rank, dformat). Asynchronous; host buffers must stay
+ * valid until ogle_session_synchronize or a get_output call. */
+int ogle_session_run(OgleSession* s, int n_inputs, const char* const* names, const float* const* data_host,
+                     const int* const* shapes, const int* ranks, const int* dformats);
+/* Same, with inputs already on the device in the padded NHWC4/ANY4 layout. */
+int ogle_session_run_device(OgleSession* s, int n_inputs, const char* const* names, const float* const* data_device);
+int ogle_session_synchronize(OgleSession* s);
+/* FBOSession::FindTensorByName: shape (up to 8 dims), rank, device data format, device pointer. */
+int ogle_session_tensor_info(OgleSession* s, const char* name, int* shape8, int* rank, int* dformat, void** device_ptr);
+/* FBOSession::GetOutputs for one tensor, fbo_session.cc:276-301. dformat is "NHWC",
+ * "NCHW", "ANY", "NHWC4", "ANY4" or "HWN4C4". Synchronises. */
+int ogle_session_get_output(OgleSession* s, const char* name, const char* dformat, float* out_host, size_t capacity_floats);
+int ogle_session_num_active_kernels(OgleSession* s);
+int ogle_session_graph_captured(OgleSession* s);
+size_t ogle_session_device_bytes(OgleSession* s);
+/* One eager pass with per-node timing; writes "name\ttype\tkernel\tms\n" rows into buf. */
+int ogle_session_profile(OgleSession* s, int n_inputs, const char* const* names, const float* const* data_host,
+                         const int* const* shapes, const int* ranks, const int* dformats, char* buf, size_t buf_size);
+
+/* Detector::Create / Detect, ogl_runtime/opengl/examples/ssd/detector.cc:24-47,275-295.
+ * mode 0: reference rule; mode 1: per-class top-k. Tensor names default to
+ * "input", "cls_logits", "box_preds", "anchors" when NULL. */
+OgleDetector* ogle_detector_create(int device, ogle_stream_t stream, const char* model_path, int mode, float score_thr,
+                                   int top_k, float nms_thr, int math_mode, const char* input_name,
+                                   const char* logits_name, const char* boxes_name, const char* anchors_name);
+void ogle_detector_destroy(OgleDetector* d);
+/* Enqueue upload + network + decode + post-process + copy-back for N preprocessed NHWC images. */
+int ogle_detector_detect_async(OgleDetector* d, const float* images_nhwc_host, int N, int H, int W);
+/* Wait for it and copy the results out. rows = top_k (mode 0) or (C-1)*top_k (mode 1).
+ * Any output pointer may be NULL. count holds N (mode 0) or N*(C-1) ints. */
+int ogle_detector_wait(OgleDetector* d, float* score, int* anchor, int* cls, float* box, int* count);
+int ogle_detector_info(OgleDetector* d, int* num_anchors, int* num_classes, int* rows, size_t* h2d_bytes, size_t* d2h_bytes);
+OgleSession* ogle_detector_session(OgleDetector* d);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OGLE_RUNTIME_H_ */

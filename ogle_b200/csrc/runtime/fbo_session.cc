@@ -1,0 +1,263 @@
+#include "fbo_session.h"
+
+#include <cuda_runtime.h>
+#include <cstdlib>
+
+#include "kernel_registry.h"
+
+namespace ogle {
+
+#define OGLE_RT_CUDA(call)                                                              \
+    do {                                                                                \
+        cudaError_t e_ = (call);                                                        \
+        if (e_ != cudaSuccess) OGLE_FATAL() << #call << ": " << cudaGetErrorString(e_); \
+    } while (0)
+
+FBOSession::FBOSession(Context* context) : context_(context) {
+    if (const char* g = std::getenv("OGLE_USE_GRAPH")) use_graph_ = std::atoi(g) != 0;
+}
+
+FBOSession::~FBOSession() {
+    context_->MakeCurrent();
+    DropGraph();
+}
+
+void FBOSession::DropGraph() {
+    if (graph_exec_) {
+        cudaGraphExecDestroy(reinterpret_cast<cudaGraphExec_t>(graph_exec_));
+        graph_exec_ = nullptr;
+    }
+}
+
+void FBOSession::set_use_graph(bool flag) {
+    use_graph_ = flag;
+    if (!flag) DropGraph();
+}
+
+void FBOSession::LoadGraph(const std::string& model_path) {
+    dlxnet::ModelProto model;
+    std::string err;
+    OGLE_CHECK(dlxnet::ReadModelFromFile(model_path, &model, &err)) << "Load Graph " << model_path << " Failed: " << err;
+    LoadGraph(model);
+}
+
+void FBOSession::LoadGraph(const dlxnet::ModelProto& model_proto) {
+    // fbo_session.cc:77-124
+    context_->MakeCurrent();
+    DropGraph();
+    model_ = model_proto;
+    kernels_.clear();
+    active_.clear();
+    total_tensors_.clear();
+    tensor_name_index_.clear();
+    default_input_sizes_.clear();
+    const dlxnet::GraphProto& graph = model_.graph;
+    total_tensors_.resize(graph.tensor_names.size());
+    for (size_t i = 0; i < graph.tensor_names.size(); ++i) tensor_name_index_[graph.tensor_names[i]] = int(i);
+
+    for (const dlxnet::NodeProto& node : graph.node) {
+        if (node.type == "Input") {
+            const auto& dims = node.attr.input_attr.dims;
+            OGLE_CHECK_GE(dims.size(), 2u);
+            for (size_t i = dims.size() - 2; i < dims.size(); ++i) default_input_sizes_.push_back(dims[i]);
+            continue;
+        }
+        Kernel* kernel = nullptr;
+        KernelRegistry::Global()->CreateKernel(node.type, &kernel, context_);
+        if (kernel == nullptr) OGLE_FATAL() << "unsupported kernel name " << node.type;
+        std::unique_ptr<Kernel> owned(kernel);
+        for (int64_t idx : node.input_index)
+            OGLE_CHECK(idx >= 0 && idx < int64_t(total_tensors_.size())) << "node " << node.name << " input index " << idx;
+        for (int64_t idx : node.output_index)
+            OGLE_CHECK(idx >= 0 && idx < int64_t(total_tensors_.size())) << "node " << node.name << " output index " << idx;
+        kernel->Setup(node, this);
+        kernels_.emplace_back(std::move(owned));
+    }
+    finalized_ = false;
+    graph_created_ = true;
+    eager_runs_ = 0;
+    device_bytes_ = 0;
+}
+
+void FBOSession::UploadInputs(const NamedTensorList& inputs_cpu) {
+    for (const auto& in : inputs_cpu) {
+        const Tensor* input_cpu = in.second;
+        auto iter = tensor_name_index_.find(in.first);
+        if (iter == tensor_name_index_.end()) OGLE_FATAL() << "tensor_name: " << in.first << " Cannot Find";
+        const int input_index = iter->second;
+        if (!finalized_) {
+            total_tensors_[input_index].reset(new Tensor(Tensor::DT_FLOAT, input_cpu->shape(), Tensor::DEVICE_TEXTURE,
+                                                         FormatToStride4(input_cpu->dformat())));
+            device_bytes_ += total_tensors_[input_index]->AllocatedSize();
+        }
+        context_->CopyCPUTensorToDevice(input_cpu, total_tensors_[input_index].get());
+    }
+}
+
+void FBOSession::Setup(const NamedTensorList& inputs_cpu) {
+    OGLE_CHECK(graph_created_) << "No Graph Loaded!";
+    context_->MakeCurrent();
+    UploadInputs(inputs_cpu);
+    if (!finalized_) Finalize();
+}
+
+void FBOSession::Finalize() {
+    // fbo_session.cc:196-252
+    ready_.assign(total_tensors_.size(), false);
+    active_.clear();
+    for (size_t i = 0; i < kernels_.size(); ++i) {
+        Kernel* kernel = kernels_[i].get();
+        kernel->input_tensors_.clear();
+        kernel->output_tensors_.clear();
+        for (int idx : kernel->input_tensor_indexes_) {
+            Tensor* t = total_tensors_[idx].get();
+            OGLE_CHECK(t != nullptr) << "input tensor is uninitialized of kernel index: " << i << " (" << kernel->kernel_name() << ")";
+            kernel->input_tensors_.push_back(t);
+        }
+        kernel->SelectKernel(kernel->input_tensors_);
+        TensorShapeList output_shapes;
+        kernel->InferOutputShape(kernel->input_tensors_, output_shapes);
+        OGLE_CHECK_GT(output_shapes.size(), 0u);
+        OGLE_CHECK_LE(output_shapes.size(), kernel->output_tensor_indexes_.size());
+        for (size_t j = 0; j < output_shapes.size(); ++j) {
+            const DataFormat dformat = kernel->GetOutputDFormat(int(j));
+            Tensor* out = nullptr;
+            if (kernel->IsNoOp()) {
+                // the output is the input's memory under a new shape
+                out = new Tensor(output_shapes[j], dformat, kernel->input_tensors_[0]->device<float>());
+            } else {
+                out = new Tensor(Tensor::DT_FLOAT, output_shapes[j], Tensor::DEVICE_TEXTURE, dformat);
+                device_bytes_ += out->AllocatedSize();
+            }
+            total_tensors_[kernel->output_tensor_indexes_[j]].reset(out);
+            kernel->output_tensors_.push_back(out);
+        }
+        if (CheckKernelReady(kernel)) {
+            // pre-compute: constants, weight re-layout, shape arithmetic
+            kernel->Compute();
+            UpdateKernelReady(kernel);
+        } else if (!kernel->IsNoOp()) {
+            active_.push_back(kernel);
+        }
+    }
+    context_->Synchronize();
+    finalized_ = true;
+}
+
+bool FBOSession::CheckKernelReady(const Kernel* kernel) {
+    if (kernel->ForceReady()) return true;
+    for (int id : kernel->input_tensor_indexes_)
+        if (!ready_[id]) return false;
+    return true;
+}
+
+void FBOSession::UpdateKernelReady(const Kernel* kernel) {
+    for (int id : kernel->output_tensor_indexes_) ready_[id] = true;
+}
+
+int FBOSession::num_active_kernels() const { return int(active_.size()); }
+
+void FBOSession::Execute() {
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(context_->stream());
+    if (graph_exec_) {
+        OGLE_RT_CUDA(cudaGraphLaunch(reinterpret_cast<cudaGraphExec_t>(graph_exec_), s));
+        return;
+    }
+    if (use_graph_ && eager_runs_ >= 1 && !active_.empty()) {
+        // Everything a node needs was created by the eager pass; this pass only records.
+        cudaGraph_t graph = nullptr;
+        OGLE_RT_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+        try {
+            for (Kernel* k : active_) k->Compute();
+        } catch (...) {
+            cudaStreamEndCapture(s, &graph);
+            if (graph) cudaGraphDestroy(graph);
+            throw;
+        }
+        OGLE_RT_CUDA(cudaStreamEndCapture(s, &graph));
+        cudaGraphExec_t exec = nullptr;
+        cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (e != cudaSuccess) OGLE_FATAL() << "cudaGraphInstantiate: " << cudaGetErrorString(e);
+        graph_exec_ = reinterpret_cast<CUgraphExec_st*>(exec);
+        OGLE_RT_CUDA(cudaGraphLaunch(exec, s));
+        return;
+    }
+    for (Kernel* k : active_) k->Compute();
+    ++eager_runs_;
+}
+
+void FBOSession::Run(const NamedTensorList& inputs_cpu) {
+    Setup(inputs_cpu);
+    OGLE_CHECK(finalized_) << "Please Setup Session First";
+    Execute();
+}
+
+void FBOSession::RunDevice(const std::vector<std::pair<std::string, const float*>>& inputs_device) {
+    OGLE_CHECK(finalized_) << "RunDevice needs a session that Run or Setup has finalized";
+    context_->MakeCurrent();
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(context_->stream());
+    for (const auto& in : inputs_device) {
+        Tensor* t = FindTensorByName(in.first);
+        OGLE_CHECK(t != nullptr && in.second != nullptr);
+        if (in.second != t->device<float>())
+            OGLE_RT_CUDA(cudaMemcpyAsync(t->device(), in.second, t->AllocatedSize(), cudaMemcpyDeviceToDevice, s));
+    }
+    Execute();
+}
+
+std::vector<NodeTiming> FBOSession::Profile(const NamedTensorList& inputs_cpu) {
+    Setup(inputs_cpu);
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(context_->stream());
+    std::vector<cudaEvent_t> ev(active_.size() + 1);
+    for (auto& e : ev) OGLE_RT_CUDA(cudaEventCreate(&e));
+    OGLE_RT_CUDA(cudaEventRecord(ev[0], s));
+    for (size_t i = 0; i < active_.size(); ++i) {
+        active_[i]->Compute();
+        OGLE_RT_CUDA(cudaEventRecord(ev[i + 1], s));
+    }
+    OGLE_RT_CUDA(cudaStreamSynchronize(s));
+    std::vector<NodeTiming> out;
+    for (size_t i = 0; i < active_.size(); ++i) {
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
+        out.push_back({active_[i]->kernel_name(), active_[i]->kernel_type(), active_[i]->kernel_fname(), ms});
+    }
+    for (auto& e : ev) cudaEventDestroy(e);
+    return out;
+}
+
+void FBOSession::GetOutputs(const TensorNameList& output_names, const StringList& output_dformats, TensorList* outputs) {
+    OGLE_CHECK_EQ(output_names.size(), output_dformats.size());
+    context_->MakeCurrent();
+    if (outputs->size() < output_names.size()) outputs->resize(output_names.size());
+    for (size_t i = 0; i < output_names.size(); ++i) {
+        Tensor* gpu_tensor = FindTensorByName(output_names[i]);
+        OGLE_CHECK(gpu_tensor != nullptr) << "tensor " << output_names[i] << " was never produced";
+        const DataFormat dformat = StrToFormat(output_dformats[i]);
+        if (outputs->at(i) == nullptr)
+            outputs->at(i) = new Tensor(Tensor::DT_FLOAT, gpu_tensor->shape(), Tensor::HOST_MEMORY, dformat);
+        context_->CopyDeviceTensorToCPU(gpu_tensor, outputs->at(i));
+    }
+}
+
+std::string FBOSession::DebugString() const {
+    std::ostringstream ss;
+    ss << "ModelProto: producer " << model_.producer_name << ", " << model_.graph.node.size() << " nodes, "
+       << model_.graph.tensor_names.size() << " tensors\n";
+    for (auto& k : kernels_) ss << k->DebugString() << "\n";
+    return ss.str();
+}
+
+Tensor* FBOSession::FindTensorByName(const std::string& name) {
+    auto iter = tensor_name_index_.find(name);
+    if (iter == tensor_name_index_.end()) OGLE_FATAL() << "tensor_name: " << name << " Cannot Find";
+    return FindTensorById(iter->second);
+}
+
+Tensor* FBOSession::FindTensorById(int id) {
+    OGLE_CHECK_LT(id, int(total_tensors_.size()));
+    return total_tensors_[id].get();
+}
+
+}  // namespace ogle

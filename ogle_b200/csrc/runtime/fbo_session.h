@@ -1,0 +1,95 @@
+// FBOSession: loads a dlx graph, instantiates one Kernel per node through the
+// registry, allocates every tensor once, pre-computes constant sub-graphs, and
+// runs the remaining nodes in file order. Same public surface as the reference's
+// ogl_runtime/opengl/core/fbo_session.h:11-90. The OpenGL framebuffer loop of
+// fbo_session.cc:127-156 is replaced by a CUDA graph: the first Run executes the
+// nodes eagerly, the next one captures them, later ones replay the capture.
+#ifndef OGLE_RUNTIME_FBO_SESSION_H_
+#define OGLE_RUNTIME_FBO_SESSION_H_
+#include "context.h"
+#include "kernel.h"
+#include "types.h"
+
+struct CUgraphExec_st;
+
+namespace ogle {
+
+struct NodeTiming {
+    std::string name, type, kernel;
+    float ms;
+};
+
+class FBOSession {
+public:
+    explicit FBOSession(Context* context);
+    FBOSession() : FBOSession(GetContext()) {}
+    virtual ~FBOSession();
+
+    // Allocates tensors on the first call (shapes follow from the inputs given
+    // then); uploads the inputs on every call.
+    void Setup(const NamedTensorList& inputs_cpu);
+    // Upload inputs, then run every node that is not pre-computed. Asynchronous:
+    // returns when the work is enqueued on context()->stream().
+    void Run(const NamedTensorList& inputs_cpu);
+    // Run, but with inputs that already live on the device in NHWC4/ANY4 layout
+    // (device-to-device copy into the session's input tensors).
+    void RunDevice(const std::vector<std::pair<std::string, const float*>>& inputs_device);
+
+    void LoadGraph(const dlxnet::ModelProto& model_proto);
+    void LoadGraph(const std::string& model_path);
+
+    // Reads named tensors back in the requested host formats ("NHWC", "NCHW",
+    // "ANY", "NHWC4", "ANY4", "HWN4C4"). Allocates (*outputs)[i] when null; the
+    // caller owns them. Synchronises.
+    void GetOutputs(const TensorNameList& output_names, const StringList& output_dformats, TensorList* outputs);
+
+    std::string DebugString() const;
+    Context* context() const { return context_; }
+    bool IsONNX() const { return model_.producer_name == "ONNX"; }
+    Tensor* FindTensorByName(const std::string& name);
+    Tensor* FindTensorById(int id);
+    // true once the tensor was produced by the setup pass (a model constant or derived from one)
+    bool IsTensorReady(int id) const { return id >= 0 && id < int(ready_.size()) && ready_[id]; }
+    bool allow_resized() const { return allow_resized_; }
+    void set_allow_resized(bool flag) { allow_resized_ = flag; }
+    const IntList& default_input_sizes() const { return default_input_sizes_; }
+
+    // CUDA-graph replay of the steady state (default on; OGLE_USE_GRAPH=0 disables).
+    void set_use_graph(bool flag);
+    bool graph_captured() const { return graph_exec_ != nullptr; }
+    // Nodes executed per Run (not pre-computed, not aliases).
+    int num_active_kernels() const;
+    // One eager pass with an event pair around every node; the per-node table the
+    // reference's profiler prints (nn/profiler/profiler.cc:10-46).
+    std::vector<NodeTiming> Profile(const NamedTensorList& inputs_cpu);
+    // Bytes of device memory held by tensors of this session.
+    size_t device_bytes() const { return device_bytes_; }
+
+private:
+    bool CheckKernelReady(const Kernel* kernel);
+    void UpdateKernelReady(const Kernel* kernel);
+    void UploadInputs(const NamedTensorList& inputs_cpu);
+    void Finalize();
+    void Execute();
+    void DropGraph();
+
+    Context* context_;
+    OwnedKernelList kernels_;
+    dlxnet::ModelProto model_;
+    OwnedTensorList total_tensors_;
+    bool finalized_ = false;
+    bool graph_created_ = false;
+    NamedIndex tensor_name_index_;
+    std::vector<bool> ready_;
+    std::vector<Kernel*> active_;       // the steady-state sequence
+    bool allow_resized_ = false;
+    IntList default_input_sizes_;
+    bool use_graph_ = true;
+    int eager_runs_ = 0;
+    CUgraphExec_st* graph_exec_ = nullptr;
+    size_t device_bytes_ = 0;
+    friend class Kernel;
+};
+
+}  // namespace ogle
+#endif

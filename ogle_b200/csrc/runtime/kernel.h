@@ -1,0 +1,64 @@
+// Kernel: the per-operator interface, as ogl_runtime/opengl/core/kernel.h:15-123.
+// A subclass parses its attributes (SetupAttr), picks a variant and output data
+// formats once input tensors are known (SelectKernel), infers output shapes
+// (InferOutputShape) and enqueues its work (Compute). Compute calls one entry
+// point of include/ogle_cuda.h on the session's stream; it never allocates or
+// synchronises, so the session can capture the whole sequence in a CUDA graph.
+#ifndef OGLE_RUNTIME_KERNEL_H_
+#define OGLE_RUNTIME_KERNEL_H_
+#include "context.h"
+#include "types.h"
+
+namespace ogle {
+
+class FBOSession;
+
+class Kernel {
+public:
+    explicit Kernel(Context* context) : context_(context) {}
+    virtual ~Kernel() {}
+
+    virtual void Compute(TensorList& inputs, TensorList& outputs) = 0;
+    virtual void SetupAttr(const dlxnet::Attribute& attr) = 0;
+    virtual void Setup(const dlxnet::NodeProto& node_proto, FBOSession* session);
+    void Compute() { Compute(input_tensors_, output_tensors_); }
+
+    DataFormat GetOutputDFormat(int i) const;
+    std::string DebugString() const;
+
+    virtual void InferOutputShape(TensorShapeList& inputs, TensorShapeList& outputs) = 0;
+    // some ops need input values or data formats (Reshape, Pool, Concat)
+    virtual void InferOutputShape(const TensorList& inputs, TensorShapeList& output_shapes);
+
+    void set_kernel_name(const std::string& n) { kernel_name_ = n; }
+    void set_kernel_type(const std::string& n) { kernel_type_ = n; }
+    const std::string& kernel_name() const { return kernel_name_; }
+    const std::string& kernel_type() const { return kernel_type_; }
+    void set_session(FBOSession* s) { session_ = s; }
+    FBOSession* session() const { return session_; }
+
+    // Shape-like kernels run at setup whatever their inputs' state (kernel.h:80).
+    virtual bool ForceReady() const { return false; }
+    // Name of the device kernel family chosen by SelectKernel (the reference
+    // stores a shader file name here).
+    const std::string& kernel_fname() const { return kernel_fname_; }
+    virtual void SelectKernel(const TensorList& inputs) {}
+    // True when Compute only aliases/keeps memory and launches nothing.
+    virtual bool IsNoOp() const { return false; }
+
+protected:
+    Context* context_;
+    std::string kernel_fname_;
+    std::vector<Tensor*> input_tensors_;    // not owned
+    std::vector<Tensor*> output_tensors_;   // not owned
+    std::vector<int> input_tensor_indexes_;
+    std::vector<int> output_tensor_indexes_;
+    std::vector<DataFormat> output_tensor_dformats_;
+    friend class FBOSession;
+    std::string kernel_name_;
+    std::string kernel_type_;
+    FBOSession* session_ = nullptr;
+};
+
+}  // namespace ogle
+#endif

@@ -1,0 +1,687 @@
+// The operator kernels: one class per reference kernel under
+// ogl_runtime/opengl/nn/kernels/, registered under the same ONNX operator names.
+// Attribute parsing, variant selection, shape inference and the checks follow
+// the reference; Compute calls include/ogle_cuda.h instead of drawing.
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstring>
+
+#include "fbo_session.h"
+#include "kernel.h"
+#include "kernel_registry.h"
+#include "ogle_cuda.h"
+
+namespace ogle {
+namespace {
+
+using TP = dlxnet::TensorProto;
+
+bool IsPadded4(const Tensor* t) { return t->dformat() == TP::NHWC4 || t->dformat() == TP::ANY4; }
+
+IntList AmendShape(const IntList& shape) {
+    // left-pad to 4-D with 1s (ogl_runtime/opengl/utils/util.cc:44-59)
+    OGLE_CHECK_LE(shape.size(), 4u);
+    IntList s(4 - shape.size(), 1);
+    s.insert(s.end(), shape.begin(), shape.end());
+    return s;
+}
+
+long Rows(const Tensor* t) { return t->shape().empty() ? 1 : long(t->num_elements() / size_t(t->last_stride())); }
+
+// Square kernel / equal strides / four equal pads, as conv2d.cc:67-88 and pool.cc:38-54.
+void ParseWindow(const std::vector<int64_t>& kernel_shape, const std::vector<int64_t>& strides,
+                 const std::vector<int64_t>& pads, int* kernel, int* stride, int* pad) {
+    OGLE_CHECK_EQ(pads.size(), 4u);
+    for (int64_t p : pads) OGLE_CHECK_EQ(pads[0], p);
+    *pad = int(pads[0]);
+    OGLE_CHECK_EQ(strides.size(), 2u);
+    OGLE_CHECK_EQ(strides[0], strides[1]);
+    *stride = int(strides[0]);
+    OGLE_CHECK_EQ(kernel_shape.size(), 2u);
+    OGLE_CHECK_EQ(kernel_shape[0], kernel_shape[1]);
+    *kernel = int(kernel_shape[0]);
+}
+
+// ------------------------------------------------------------------- Const
+// nn/kernels/const.cc:7-66
+class ConstKernel : public Kernel {
+public:
+    explicit ConstKernel(Context* c) : Kernel(c) {}
+    void SetupAttr(const dlxnet::Attribute& attr) override {
+        OGLE_CHECK(!tensor_);
+        tensor_.reset(new Tensor(attr.const_attr.value));
+        output_tensor_dformats_.push_back(attr.const_attr.value.target_data_format);
+        kernel_fname_ = "upload";
+    }
+    void Compute(TensorList& inputs, TensorList& outputs) override {
+        OGLE_CHECK(inputs.empty()) << "Input should be empty in ConstKernel";
+        context_->CopyCPUTensorToDevice(tensor_.get(), outputs[0]);
+    }
+    void InferOutputShape(TensorShapeList& inputs, TensorShapeList& outputs) override {
+        OGLE_CHECK(inputs.empty()) << "Input should be empty in ConstKernel";
+        const DataFormat f = output_tensor_dformats_[0];
+        OGLE_CHECK(f == TP::ANY4 || f == TP::HWN4C4) << "unsupported dformat " << int(f) << " in Const Kernel " << kernel_name_;
+        outputs.push_back(tensor_->shape());
+    }
+private:
+    std::unique_ptr<Tensor> tensor_;
+};
+REGISTER_KERNEL_WITH_NAME(ConstKernel, "Const");
+REGISTER_KERNEL_WITH_NAME(ConstKernel, "Constant");
+
+// -------------------------------------------------------------------- Conv
+// nn/kernels/conv2d.cc:19-197
+class Conv2DKernel : public Kernel {
+public:
+    explicit Conv2DKernel(Context* c) : Kernel(c) {}
+    ~Conv2DKernel() override { if (packed_) cudaFree(packed_); }
+
+    void SetupAttr(const dlxnet::Attribute& attr) override {
+        const auto& p = attr.conv2d_attr;
+        ParseWindow(p.kernel_shape, p.strides, p.pads, &kernel_size_, &stride_, &padding_);
+        group_size_ = int(p.group);
+        if (group_size_ == 0) group_size_ = 1;
+        if (p.dilations.size() == 2) {
+            OGLE_CHECK_EQ(p.dilations[0], p.dilations[1]);
+            dilation_ = int(p.dilations[0]);
+        } else if (p.dilations.size() == 1) {
+            dilation_ = int(p.dilations[0]);
+        } else {
+            dilation_ = 1;
+        }
+        activation_type_ = p.activation_type;
+        min_ = p.min;
+        max_ = p.max;
+    }
+
+    void SelectKernel(const TensorList& inputs) override {
+        OGLE_CHECK(inputs.size() == 2 || inputs.size() == 3);
+        OGLE_CHECK(IsPadded4(inputs[0])) << "conv input must be NHWC4 or ANY4";
+        OGLE_CHECK_EQ(inputs[0]->shape().size(), 4u);
+        const bool pw = kernel_size_ == 1 && group_size_ == 1 && dilation_ == 1 && stride_ == 1 && padding_ == 0;
+        if (pw) kernel_fname_ = "conv2d_pw";
+        else if (group_size_ != 1)
+            kernel_fname_ = (group_size_ == inputs[0]->shape()[3] && group_size_ == inputs[1]->shape()[0]) ? "conv2d_dw" : "conv2d_grp";
+        else kernel_fname_ = "conv2d";
+        output_tensor_dformats_.push_back(inputs[0]->dformat());
+    }
+
+    void InferOutputShape(const TensorList& inputs, TensorShapeList& output_shapes) override {
+        Kernel::InferOutputShape(inputs, output_shapes);
+        // the filter is re-laid out once when it is a model constant (the reference does
+        // this in its upload pass); otherwise before every launch
+        const size_t bytes = ogle_cuda_conv2d_filter_bytes(&params_);
+        OGLE_CHECK_GT(bytes, 0u);
+        if (packed_) cudaFree(packed_);
+        cudaError_t e = cudaMalloc(&packed_, bytes);
+        OGLE_CHECK(e == cudaSuccess) << "cudaMalloc(" << bytes << "): " << cudaGetErrorString(e);
+        filter_is_constant_ = session_ && session_->IsTensorReady(input_tensor_indexes_[1]);
+        if (filter_is_constant_)
+            OGLE_CUDA_OK(ogle_cuda_conv2d_prepack(&params_, inputs[1]->device<float>(), packed_, context_->stream()));
+    }
+
+    void InferOutputShape(TensorShapeList& input_shapes, TensorShapeList& output_shapes) override {
+        OGLE_CHECK(input_shapes.size() == 3 || input_shapes.size() == 2);
+        output_shapes.clear();
+        output_shapes.resize(1);
+        const IntList& image_shape = input_shapes[0];
+        const IntList& filter_shape = input_shapes[1];
+        OGLE_CHECK_EQ(image_shape.size(), 4u);
+        OGLE_CHECK_EQ(filter_shape.size(), 4u);
+        OGLE_CHECK_EQ(filter_shape[2], kernel_size_);
+        OGLE_CHECK_EQ(filter_shape[3], kernel_size_);
+        OGLE_CHECK_EQ(filter_shape[1] * group_size_, image_shape[3]);
+        std::memset(&params_, 0, sizeof(params_));
+        params_.N = image_shape[0];
+        params_.in_hwc[0] = image_shape[1]; params_.in_hwc[1] = image_shape[2]; params_.in_hwc[2] = image_shape[3];
+        params_.out_hwc[2] = filter_shape[0];
+        params_.kernel = kernel_size_; params_.stride = stride_; params_.pad = padding_;
+        params_.dilation = dilation_; params_.group = group_size_;
+        params_.has_bias = input_shapes.size() > 2;
+        params_.act = activation_type_ == "Clip" ? OGLE_ACT_CLIP : (activation_type_ == "Relu" ? OGLE_ACT_RELU : OGLE_ACT_NONE);
+        if (!activation_type_.empty() && params_.act == OGLE_ACT_NONE) params_.act = OGLE_ACT_RELU;  // conv2d.cc:137-143
+        params_.min_value = min_; params_.max_value = max_;
+        params_.math_mode = context_->math_mode();
+        OGLE_CUDA_OK(ogle_cuda_conv2d_infer(&params_));
+        output_shapes[0] = {image_shape[0], params_.out_hwc[0], params_.out_hwc[1], filter_shape[0]};
+    }
+
+    void Compute(TensorList& inputs, TensorList& outputs) override {
+        if (!filter_is_constant_)
+            OGLE_CUDA_OK(ogle_cuda_conv2d_prepack(&params_, inputs[1]->device<float>(), packed_, context_->stream()));
+        const float* bias = inputs.size() > 2 ? inputs[2]->device<float>() : nullptr;
+        OGLE_CUDA_OK(ogle_cuda_conv2d(&params_, inputs[0]->device<float>(), packed_, bias, outputs[0]->device<float>(),
+                                      context_->stream()));
+    }
+
+private:
+    int padding_ = 0, stride_ = 1, kernel_size_ = 1, group_size_ = 1, dilation_ = 1;
+    std::string activation_type_;
+    float min_ = 0.f, max_ = 0.f;
+    OgleConvParams params_;
+    void* packed_ = nullptr;
+    bool filter_is_constant_ = false;
+};
+REGISTER_KERNEL_WITH_NAME(Conv2DKernel, "Conv");
+
+// ------------------------------------------------------ BatchNormalization
+// nn/kernels/batchnorm.cc:14-95
+class BatchNormKernel : public Kernel {
+public:
+    explicit BatchNormKernel(Context* c) : Kernel(c) { kernel_fname_ = "batchnorm"; }
+    void SetupAttr(const dlxnet::Attribute& attr) override {
+        momentum_ = attr.batchnorm_attr.momentum;
+        eps_ = attr.batchnorm_attr.epsilon;
+    }
+    void SelectKernel(const TensorList& inputs) override {
+        OGLE_CHECK(IsPadded4(inputs[0]));
+        output_tensor_dformats_.push_back(inputs[0]->dformat());
+    }
+    void InferOutputShape(TensorShapeList& in, TensorShapeList& out) override {
+        OGLE_CHECK_EQ(in.size(), 5u);
+        for (int i = 1; i < 5; ++i) {
+            OGLE_CHECK_EQ(in[i].size(), 1u);
+            OGLE_CHECK_EQ(in[i][0], in[0].back());
+        }
+        out.assign(1, in[0]);
+    }
+    void Compute(TensorList& in, TensorList& out) override {
+        OGLE_CUDA_OK(ogle_cuda_batchnorm(in[0]->device<float>(), in[1]->device<float>(), in[2]->device<float>(),
+                                         in[3]->device<float>(), in[4]->device<float>(), out[0]->device<float>(),
+                                         Rows(in[0]), in[0]->last_stride(), 0, eps_, context_->stream()));
+    }
+private:
+    float momentum_ = 0.f, eps_ = 0.f;
+};
+REGISTER_KERNEL_WITH_NAME(BatchNormKernel, "BatchNormalization");
+
+// ------------------------------------------------------- Relu / Clip / Add
+// nn/kernels/relu.cc, clip.cc, binary.cc
+class ReluKernel : public Kernel {
+public:
+    explicit ReluKernel(Context* c) : Kernel(c) { kernel_fname_ = "relu"; }
+    void SetupAttr(const dlxnet::Attribute&) override {}
+    void SelectKernel(const TensorList& inputs) override {
+        OGLE_CHECK(IsPadded4(inputs[0]));
+        output_tensor_dformats_.push_back(inputs[0]->dformat());
+    }
+    void InferOutputShape(TensorShapeList& in, TensorShapeList& out) override {
+        OGLE_CHECK_EQ(in.size(), 1u);
+        out.assign(1, in[0]);
+    }
+    void Compute(TensorList& in, TensorList& out) override {
+        OGLE_CUDA_OK(ogle_cuda_relu(in[0]->device<float>(), out[0]->device<float>(), long(in[0]->AllocatedElements()),
+                                    context_->stream()));
+    }
+};
+REGISTER_KERNEL_WITH_NAME(ReluKernel, "Relu");
+
+class ClipKernel : public Kernel {
+public:
+    explicit ClipKernel(Context* c) : Kernel(c) { kernel_fname_ = "clip"; }
+    void SetupAttr(const dlxnet::Attribute& attr) override {
+        min_ = attr.clip_attr.min;
+        max_ = attr.clip_attr.max;
+    }
+    void SelectKernel(const TensorList& inputs) override {
+        OGLE_CHECK(IsPadded4(inputs[0]));
+        output_tensor_dformats_.push_back(inputs[0]->dformat());
+    }
+    void InferOutputShape(TensorShapeList& in, TensorShapeList& out) override {
+        OGLE_CHECK_EQ(in.size(), 1u);
+        out.assign(1, in[0]);
+    }
+    void Compute(TensorList& in, TensorList& out) override {
+        OGLE_CUDA_OK(ogle_cuda_clip(in[0]->device<float>(), out[0]->device<float>(), long(in[0]->AllocatedElements()),
+                                    min_, max_, context_->stream()));
+    }
+private:
+    float min_ = 0.f, max_ = 0.f;
+};
+REGISTER_KERNEL_WITH_NAME(ClipKernel, "Clip");
+
+class BinaryKernel : public Kernel {
+public:
+    explicit BinaryKernel(Context* c) : Kernel(c) { kernel_fname_ = "binary_add"; }
+    void SetupAttr(const dlxnet::Attribute&) override {}
+    void SelectKernel(const TensorList& inputs) override {
+        OGLE_CHECK(IsPadded4(inputs[0]));
+        output_tensor_dformats_.push_back(inputs[0]->dformat());
+    }
+    void InferOutputShape(TensorShapeList& in, TensorShapeList& out) override {
+        // same-shape operands only; the reference has no broadcast (binary.cc:55-63)
+        OGLE_CHECK_EQ(in.size(), 2u);
+        OGLE_CHECK_EQ(in[0].size(), in[1].size());
+        for (size_t i = 0; i < in[0].size(); ++i) OGLE_CHECK_EQ(in[0][i], in[1][i]);
+        out.assign(1, in[0]);
+    }
+    void Compute(TensorList& in, TensorList& out) override {
+        OGLE_CUDA_OK(ogle_cuda_add(in[0]->device<float>(), in[1]->device<float>(), out[0]->device<float>(),
+                                   long(in[0]->AllocatedElements()), context_->stream()));
+    }
+};
+REGISTER_KERNEL_WITH_NAME(BinaryKernel, "Add");
+
+// -------------------------------------------------------------------- Pool
+// nn/kernels/pool.cc:26-129
+enum PoolType { MaxPool = 0, AveragePool = 1, GlobalAveragePool = 2 };
+template <PoolType pool_type>
+class PoolKernel : public Kernel {
+public:
+    explicit PoolKernel(Context* c) : Kernel(c) { kernel_fname_ = pool_type == MaxPool ? "pool_max" : "pool_avg"; }
+    void SetupAttr(const dlxnet::Attribute& attr) override {
+        if (pool_type == GlobalAveragePool) return;
+        // both MaxPool and AveragePool read maxpool_attr (pool.cc:32)
+        const auto& p = attr.maxpool_attr;
+        ParseWindow(p.kernel_shape, p.strides, p.pads, &kernel_size_, &stride_, &padding_);
+    }
+    void SelectKernel(const TensorList& inputs) override {
+        OGLE_CHECK(IsPadded4(inputs[0]));
+        output_tensor_dformats_.push_back(inputs[0]->dformat());
+    }
+    void InferOutputShape(TensorShapeList& in, TensorShapeList& out) override {
+        OGLE_CHECK_EQ(in.size(), 1u);
+        OGLE_CHECK_EQ(in[0].size(), 4u);
+        std::memset(&params_, 0, sizeof(params_));
+        params_.N = in[0][0];
+        params_.in_hwc[0] = in[0][1]; params_.in_hwc[1] = in[0][2]; params_.in_hwc[2] = in[0][3];
+        params_.kernel = kernel_size_; params_.stride = stride_; params_.pad = padding_;
+        params_.type = int(pool_type);
+        if (pool_type == GlobalAveragePool) OGLE_CHECK_EQ(in[0][1], in[0][2]);  // pool.cc:88
+        OGLE_CUDA_OK(ogle_cuda_pool_infer(&params_));
+        out.assign(1, IntList{in[0][0], params_.out_hwc[0], params_.out_hwc[1], in[0][3]});
+    }
+    void Compute(TensorList& in, TensorList& out) override {
+        OGLE_CUDA_OK(ogle_cuda_pool(&params_, in[0]->device<float>(), out[0]->device<float>(), context_->stream()));
+    }
+private:
+    int kernel_size_ = 1, stride_ = 1, padding_ = 0;
+    OglePoolParams params_;
+};
+REGISTER_KERNEL_WITH_NAME(PoolKernel<MaxPool>, "MaxPool");
+REGISTER_KERNEL_WITH_NAME(PoolKernel<AveragePool>, "AveragePool");
+REGISTER_KERNEL_WITH_NAME(PoolKernel<GlobalAveragePool>, "GlobalAveragePool");
+
+// -------------------------------------------------------------------- Gemm
+// nn/kernels/gemm.cc:16-108
+class GemmKernel : public Kernel {
+public:
+    explicit GemmKernel(Context* c) : Kernel(c) { kernel_fname_ = "gemm"; }
+    void SetupAttr(const dlxnet::Attribute& attr) override {
+        alpha_ = attr.gemm_attr.alpha;
+        beta_ = attr.gemm_attr.beta;
+        transB_ = attr.gemm_attr.transb;
+        output_tensor_dformats_.push_back(TP::ANY4);
+    }
+    void InferOutputShape(TensorShapeList& in, TensorShapeList& out) override {
+        out.clear();
+        out.resize(1);
+        OGLE_CHECK_GE(in.size(), 2u);
+        OGLE_CHECK_EQ(in[0].size(), 2u);
+        OGLE_CHECK_EQ(in[1].size(), 2u);
+        if (transB_) {
+            OGLE_CHECK_EQ(in[1][1], in[0][1]);
+            out[0] = {in[0][0], in[1][0]};
+        } else {
+            OGLE_CHECK_EQ(in[1][0], in[0][1]);
+            out[0] = {in[0][0], in[1][1]};
+        }
+        std::memset(&params_, 0, sizeof(params_));
+        params_.M = out[0][0]; params_.K = in[0][1]; params_.N = out[0][1];
+        params_.transB = transB_; params_.alpha = alpha_; params_.beta = beta_;
+        params_.math_mode = context_->math_mode();
+        if (in.size() > 2) {
+            if (in[2].size() == 2) {
+                OGLE_CHECK_EQ(out[0][0], in[2][0]);
+                OGLE_CHECK_EQ(out[0][1], in[2][1]);
+                params_.bias_mode = 1;
+            } else {
+                // a [N] bias is broadcast over rows (ONNX); the reference's shader is
+                // only correct for M == 1 here (gemm.glsl:92-94)
+                OGLE_CHECK_EQ(in[2].size(), 1u);
+                OGLE_CHECK_EQ(out[0][1], in[2][0]);
+                params_.bias_mode = 2;
+            }
+        }
+    }
+    void Compute(TensorList& in, TensorList& out) override {
+        OGLE_CHECK_EQ(in[0]->dformat(), TP::ANY4);
+        OGLE_CHECK_EQ(in[1]->dformat(), TP::ANY4);
+        const float* c = in.size() > 2 ? in[2]->device<float>() : nullptr;
+        OGLE_CUDA_OK(ogle_cuda_gemm(&params_, in[0]->device<float>(), in[1]->device<float>(), c, out[0]->device<float>(),
+                                    context_->stream()));
+    }
+private:
+    float alpha_ = 1.f, beta_ = 1.f;
+    int transB_ = 0;
+    OgleGemmParams params_;
+};
+REGISTER_KERNEL_WITH_NAME(GemmKernel, "Gemm");
+
+// ------------------------------------------------------------------ Concat
+// nn/kernels/concat.cc:32-133
+class ConcatKernel : public Kernel {
+public:
+    explicit ConcatKernel(Context* c) : Kernel(c) { kernel_fname_ = "concat"; }
+    void SetupAttr(const dlxnet::Attribute& attr) override { axis_ = attr.concat_attr.axis; }
+    void SelectKernel(const TensorList& inputs) override {
+        // The reference accepts ANY4 inputs only (concat.cc:33). NHWC4 has the same
+        // bytes in linear memory, so it is accepted too, with the ONNX (NCHW) axis
+        // mapped onto the stored NHWC order as concat.cc:42-45 does.
+        for (auto t : inputs) OGLE_CHECK(IsPadded4(t)) << "concat inputs must be ANY4 or NHWC4";
+        output_tensor_dformats_.push_back(TP::ANY4);
+        if (session_ && session_->IsONNX() && inputs[0]->dformat() == TP::NHWC4 && axis_ >= 0) {
+            static const int mapping[4] = {0, 3, 1, 2};
+            OGLE_CHECK_LT(axis_, 4);
+            axis_ = mapping[axis_];
+        }
+    }
+    void InferOutputShape(TensorShapeList& in, TensorShapeList& out) override {
+        if (axis_ < 0) axis_ += int(in[0].size());   // concat.cc:101-103 handles -1
+        OGLE_CHECK_GE(in.size(), 2u);
+        OGLE_CHECK_LE(in.size(), size_t(OGLE_MAX_CONCAT_INPUTS));
+        OGLE_CHECK(axis_ >= 0 && axis_ < int(in[0].size()));
+        out.assign(1, in[0]);
+        out[0][axis_] = 0;
+        for (auto& s : in) {
+            OGLE_CHECK_EQ(out[0].size(), s.size());
+            for (size_t i = 0; i < s.size(); ++i) {
+                if (int(i) != axis_) OGLE_CHECK_EQ(s[i], out[0][i]);
+                else out[0][i] += s[i];
+            }
+        }
+        std::memset(&params_, 0, sizeof(params_));
+        params_.n_inputs = int(in.size());
+        params_.axis = axis_ + 4 - int(in[0].size());   // concat.cc:61
+        for (size_t i = 0; i < in.size(); ++i) {
+            const IntList s4 = AmendShape(in[i]);
+            for (int d = 0; d < 4; ++d) params_.in_shapes[i][d] = s4[d];
+        }
+    }
+    void Compute(TensorList& in, TensorList& out) override {
+        const float* ptrs[OGLE_MAX_CONCAT_INPUTS];
+        for (size_t i = 0; i < in.size(); ++i) ptrs[i] = in[i]->device<float>();
+        OGLE_CUDA_OK(ogle_cuda_concat(&params_, ptrs, out[0]->device<float>(), context_->stream()));
+    }
+private:
+    int axis_ = 0;
+    OgleConcatParams params_;
+};
+REGISTER_KERNEL_WITH_NAME(ConcatKernel, "Concat");
+
+// --------------------------------------------------------------- Transpose
+// nn/kernels/transpose.cc:34-105
+class TransposeKernel : public Kernel {
+public:
+    explicit TransposeKernel(Context* c) : Kernel(c) { kernel_fname_ = "transpose"; }
+    void SetupAttr(const dlxnet::Attribute& attr) override {
+        for (int p : attr.transpose_attr.perm) perm_.push_back(p);
+    }
+    void SelectKernel(const TensorList& inputs) override {
+        OGLE_CHECK(IsPadded4(inputs[0]));
+        output_tensor_dformats_.push_back(TP::ANY4);
+        if (session_ && session_->IsONNX() && inputs[0]->dformat() == TP::NHWC4) {
+            // the stored order is NHWC while perm is in ONNX (NCHW) terms
+            OGLE_CHECK_EQ(perm_.size(), 4u);
+            static const int mapping[4] = {0, 3, 1, 2};
+            for (int& p : perm_) p = mapping[p];
+        }
+        identity_ = true;
+        for (size_t i = 0; i < perm_.size(); ++i) identity_ = identity_ && perm_[i] == int(i);
+    }
+    void InferOutputShape(TensorShapeList& in, TensorShapeList& out) override {
+        OGLE_CHECK_EQ(in.size(), 1u);
+        OGLE_CHECK_LE(perm_.size(), in[0].size());
+        out.assign(1, IntList());
+        for (int p : perm_) out[0].push_back(in[0][p]);
+        for (size_t i = perm_.size(); i < in[0].size(); ++i) out[0].push_back(in[0][i]);
+        in_shape4_ = AmendShape(in[0]);
+        // AmendPerm, transpose.cc:12-21
+        perm4_.clear();
+        for (size_t i = 0; i < 4 - perm_.size(); ++i) perm4_.push_back(int(i));
+        for (int p : perm_) perm4_.push_back(p + 4 - int(perm_.size()));
+    }
+    bool IsNoOp() const override { return identity_; }
+    void Compute(TensorList& in, TensorList& out) override {
+        if (identity_) return;
+        OGLE_CUDA_OK(ogle_cuda_transpose(in[0]->device<float>(), out[0]->device<float>(), in_shape4_.data(), perm4_.data(),
+                                         context_->stream()));
+    }
+private:
+    IntList perm_, perm4_, in_shape4_;
+    bool identity_ = false;
+};
+REGISTER_KERNEL_WITH_NAME(TransposeKernel, "Transpose");
+
+// ----------------------------------------------------------------- Reshape
+// nn/kernels/reshape.cc:18-97
+class ReshapeKernel : public Kernel {
+public:
+    explicit ReshapeKernel(Context* c) : Kernel(c) { kernel_fname_ = "reshape"; }
+    void SetupAttr(const dlxnet::Attribute&) override {}
+    void SelectKernel(const TensorList& inputs) override {
+        OGLE_CHECK(IsPadded4(inputs[0]));
+        output_tensor_dformats_.push_back(TP::ANY4);
+    }
+    void InferOutputShape(TensorShapeList&, TensorShapeList&) override {
+        OGLE_FATAL() << "Reshape needs the value of its shape input";
+    }
+    void InferOutputShape(const TensorList& inputs, TensorShapeList& out) override {
+        out.clear();
+        out.resize(1);
+        OGLE_CHECK_EQ(inputs.size(), 2u);
+        // the target shape is a (float-valued) device tensor computed at setup
+        Tensor cpu(Tensor::DT_FLOAT, inputs[1]->shape(), Tensor::HOST_MEMORY, TP::ANY);
+        context_->CopyDeviceTensorToCPU(inputs[1], &cpu);
+        IntList& shape = out[0];
+        for (size_t i = 0; i < cpu.num_elements(); ++i) shape.push_back(int(std::lround(cpu.host<float>()[i])));
+        const IntList& in_shape = inputs[0]->shape();
+        const long n = long(inputs[0]->num_elements());
+        long remain = 1;
+        for (size_t i = 0; i < shape.size(); ++i) {
+            if (shape[i] == 0) {
+                OGLE_CHECK_LT(i, in_shape.size());
+                shape[i] = in_shape[i];
+            }
+            if (shape[i] != -1) remain *= shape[i];
+        }
+        bool seen = false;
+        for (int& d : shape) {
+            if (d == -1) {
+                OGLE_CHECK(!seen) << "more than one -1 in a reshape target";
+                OGLE_CHECK(remain > 0 && n % remain == 0);
+                d = int(n / remain);
+                seen = true;
+            }
+        }
+        long total = 1;
+        for (int d : shape) total *= d;
+        OGLE_CHECK_EQ(total, n) << "reshape changes the element count";
+        OGLE_CHECK_LE(shape.size(), 4u);
+        n_ = n;
+        in_last_ = inputs[0]->last_stride();
+        out_last_ = shape.empty() ? 1 : shape.back();
+        // same bytes when neither side pads, or the padded row is unchanged
+        alias_ = (in_last_ == out_last_) || (in_last_ % 4 == 0 && out_last_ % 4 == 0);
+    }
+    bool IsNoOp() const override { return alias_; }
+    void Compute(TensorList& in, TensorList& out) override {
+        if (alias_) return;
+        OGLE_CUDA_OK(ogle_cuda_reshape(in[0]->device<float>(), out[0]->device<float>(), n_, in_last_, out_last_,
+                                       context_->stream()));
+    }
+private:
+    long n_ = 0;
+    int in_last_ = 1, out_last_ = 1;
+    bool alias_ = false;
+};
+REGISTER_KERNEL_WITH_NAME(ReshapeKernel, "Reshape");
+
+// ----------------------------------------------------------------- Flatten
+// nn/kernels/flatten.cc:16-96. Elements keep the stored (NHWC) order. For an
+// NHWC4 input the ONNX axis is mapped onto the stored order as the reference does;
+// where that leaves leading 1-sized dims (global-pool output [N,1,1,C], axis 1 ->
+// 3) they are dropped so that the result is the 2-D [N, C] a following Gemm needs.
+class FlattenKernel : public Kernel {
+public:
+    explicit FlattenKernel(Context* c) : Kernel(c) { kernel_fname_ = "reshape"; }
+    void SetupAttr(const dlxnet::Attribute& attr) override { axis_ = attr.flatten_attr.axis; }
+    void SelectKernel(const TensorList& inputs) override {
+        OGLE_CHECK(IsPadded4(inputs[0]));
+        nhwc_input_ = session_ && session_->IsONNX() && inputs[0]->dformat() == TP::NHWC4;
+        output_tensor_dformats_.push_back(TP::ANY4);
+    }
+    void InferOutputShape(TensorShapeList& in, TensorShapeList& out) override {
+        OGLE_CHECK_EQ(in.size(), 1u);
+        const IntList& s = in[0];
+        OGLE_CHECK(axis_ >= 0 && axis_ <= int(s.size()));
+        out.assign(1, IntList());
+        long tail = 1;
+        if (nhwc_input_) {
+            OGLE_CHECK_EQ(s.size(), 4u);
+            // ONNX dims [N,C,H,W]: everything from `axis_` on is flattened; in stored order
+            // that is a contiguous tail only for axis 1 (all of H,W,C) or axis 0
+            OGLE_CHECK(axis_ <= 1) << "Flatten of an NHWC4 tensor supports axis 0 or 1";
+            if (axis_ == 1) out[0].push_back(s[0]);
+            for (size_t i = size_t(axis_); i < 4; ++i) tail *= s[i];
+        } else {
+            for (int i = 0; i < axis_; ++i) out[0].push_back(s[i]);
+            for (size_t i = size_t(axis_); i < s.size(); ++i) tail *= s[i];
+        }
+        out[0].push_back(int(tail));
+        n_ = 1;
+        for (int d : s) n_ *= d;
+        in_last_ = s.back();
+        out_last_ = int(tail);
+        alias_ = (in_last_ == out_last_) || (in_last_ % 4 == 0 && out_last_ % 4 == 0);
+    }
+    bool IsNoOp() const override { return alias_; }
+    void Compute(TensorList& in, TensorList& out) override {
+        if (alias_) return;
+        OGLE_CUDA_OK(ogle_cuda_reshape(in[0]->device<float>(), out[0]->device<float>(), n_, in_last_, out_last_,
+                                       context_->stream()));
+    }
+private:
+    int axis_ = 1;
+    bool nhwc_input_ = false, alias_ = false;
+    long n_ = 0;
+    int in_last_ = 1, out_last_ = 1;
+};
+REGISTER_KERNEL_WITH_NAME(FlattenKernel, "Flatten");
+
+// ------------------------------------------------ Shape / Gather / Unsqueeze
+// Shape arithmetic of exported graphs (Shape -> Gather -> Unsqueeze -> Concat ->
+// Reshape). These only ever run in the setup pass; they go through the host.
+class ShapeKernel : public Kernel {
+public:
+    explicit ShapeKernel(Context* c) : Kernel(c) { kernel_fname_ = "shape"; }
+    void SetupAttr(const dlxnet::Attribute&) override {}
+    bool ForceReady() const override { return true; }   // nn/kernels/shape.h
+    void InferOutputShape(TensorShapeList& in, TensorShapeList& out) override {
+        output_tensor_dformats_.push_back(TP::ANY4);
+        OGLE_CHECK_EQ(in.size(), 1u);
+        const int dims = int(in[0].size());
+        out.assign(1, IntList{dims});
+        tensor_.reset(new Tensor(Tensor::DT_FLOAT, IntList{dims}, Tensor::HOST_MEMORY, TP::ANY));
+        for (int i = 0; i < dims; ++i) tensor_->host<float>()[i] = float(in[0][i]);
+    }
+    void Compute(TensorList& in, TensorList& out) override {
+        OGLE_CHECK_EQ(in.size(), 1u);
+        context_->CopyCPUTensorToDevice(tensor_.get(), out[0]);
+        context_->Synchronize();
+    }
+private:
+    std::unique_ptr<Tensor> tensor_;
+};
+REGISTER_KERNEL_WITH_NAME(ShapeKernel, "Shape");
+
+class GatherKernel : public Kernel {
+public:
+    explicit GatherKernel(Context* c) : Kernel(c) { kernel_fname_ = "gather"; }
+    void SetupAttr(const dlxnet::Attribute& attr) override { axis_ = attr.gather_attr.axis; }
+    void InferOutputShape(TensorShapeList& in, TensorShapeList& out) override {
+        output_tensor_dformats_.push_back(TP::ANY4);
+        OGLE_CHECK_EQ(in.size(), 2u);
+        out.assign(1, in[1]);
+    }
+    void Compute(TensorList& in, TensorList& out) override {
+        // gather.glsl:7-18: a scalar index into a 4-element shape tensor, with the ONNX
+        // (NCHW) index mapped onto the stored NHWC order: 0->0, 1->3, 2->1, 3->2
+        Tensor data(Tensor::DT_FLOAT, in[0]->shape(), Tensor::HOST_MEMORY, TP::ANY);
+        Tensor index(Tensor::DT_FLOAT, in[1]->shape(), Tensor::HOST_MEMORY, TP::ANY);
+        context_->CopyDeviceTensorToCPU(in[0], &data);
+        context_->CopyDeviceTensorToCPU(in[1], &index);
+        OGLE_CHECK_GE(data.num_elements(), 1u);
+        const int sel = int(index.host<float>()[0]);
+        static const int lane[4] = {0, 3, 1, 2};
+        const int src = lane[sel >= 0 && sel < 3 ? sel : 3];
+        Tensor result(Tensor::DT_FLOAT, out[0]->shape(), Tensor::HOST_MEMORY, TP::ANY);
+        std::memset(result.host(), 0, result.AllocatedSize());
+        result.host<float>()[0] = size_t(src) < data.num_elements() ? data.host<float>()[src] : 0.f;
+        context_->CopyCPUTensorToDevice(&result, out[0]);
+        context_->Synchronize();
+    }
+private:
+    int axis_ = 0;
+};
+REGISTER_KERNEL_WITH_NAME(GatherKernel, "Gather");
+
+class UnsqueezeKernel : public Kernel {
+public:
+    explicit UnsqueezeKernel(Context* c) : Kernel(c) { kernel_fname_ = "unsqueeze"; }
+    void SetupAttr(const dlxnet::Attribute& attr) override {
+        for (int a : attr.unsqueeze_attr.axes) axes_.push_back(a);
+        OGLE_CHECK_EQ(axes_.size(), 1u);   // unsqueeze.cc:22-24
+    }
+    void InferOutputShape(TensorShapeList& in, TensorShapeList& out) override {
+        output_tensor_dformats_.push_back(TP::ANY4);
+        OGLE_CHECK_EQ(in.size(), 1u);
+        out.assign(1, in[0]);
+        OGLE_CHECK(axes_[0] >= 0 && axes_[0] <= int(in[0].size()));
+        out[0].insert(out[0].begin() + axes_[0], 1);
+        // inserting anywhere but after the last dim keeps the padded rows as they are
+        alias_ = axes_[0] < int(in[0].size()) || in[0].empty();
+        OGLE_CHECK(alias_) << "Unsqueeze: appending a trailing dim is not supported (unsqueeze.cc:55)";
+    }
+    bool IsNoOp() const override { return alias_; }
+    void Compute(TensorList&, TensorList&) override {}
+private:
+    IntList axes_;
+    bool alias_ = true;
+};
+REGISTER_KERNEL_WITH_NAME(UnsqueezeKernel, "Unsqueeze");
+
+// ----------------------------------------------------------------- Decoder
+// nn/kernels/decoder.cc:12-97: prediction [N,A,4] ANY4, anchors [N,h,w,4].
+class DecoderKernel : public Kernel {
+public:
+    explicit DecoderKernel(Context* c) : Kernel(c) { kernel_fname_ = "ssd_decode"; }
+    void SetupAttr(const dlxnet::Attribute&) override {}
+    void SelectKernel(const TensorList& inputs) override {
+        OGLE_CHECK_EQ(inputs.size(), 2u);
+        OGLE_CHECK_EQ(inputs[0]->dformat(), TP::ANY4);
+        output_tensor_dformats_.push_back(TP::ANY4);
+    }
+    void InferOutputShape(TensorShapeList& in, TensorShapeList& out) override {
+        OGLE_CHECK_GE(in.size(), 2u);
+        OGLE_CHECK_EQ(in[0].size(), 3u);
+        OGLE_CHECK_EQ(in[0][2], 4);
+        OGLE_CHECK_EQ(in[1].size(), 4u);
+        OGLE_CHECK_EQ(in[1][0], in[0][0]);
+        OGLE_CHECK_EQ(in[1][1] * in[1][2], in[0][1]);
+        OGLE_CHECK_EQ(in[1][3], 4);
+        // the reference reads anchors at the prediction's own index, i.e. one image
+        OGLE_CHECK_EQ(in[0][0], 1) << "Decoder kernel is defined for batch 1; use functor::SSDBBoxDecoder for batches";
+        out.assign(1, IntList{in[0][0], in[0][1], 4});
+    }
+    void Compute(TensorList& in, TensorList& out) override {
+        const float var[4] = {0.1f, 0.1f, 0.2f, 0.2f};   // decoder.cc:18
+        OGLE_CUDA_OK(ogle_cuda_ssd_decode(in[0]->device<float>(), in[1]->device<float>(), out[0]->device<float>(),
+                                          in[0]->shape()[0], in[0]->shape()[1], var, context_->stream()));
+    }
+};
+REGISTER_KERNEL_WITH_NAME(DecoderKernel, "Decoder");
+
+}  // namespace
+}  // namespace ogle

@@ -68,6 +68,10 @@ OgleDetector* ogle_detector_create(int device, ogle_stream_t stream, const char*
 void ogle_detector_destroy(OgleDetector* d);
 /* Enqueue upload + network + decode + post-process + copy-back for N preprocessed NHWC images. */
 int ogle_detector_detect_async(OgleDetector* d, const float* images_nhwc_host, int N, int H, int W);
+/* Same for images already on the device as [N][H][W][4] floats (channel 3 zero).
+ * The session must have been sized by one ogle_detector_detect_async call of the
+ * same shape. copy_back 0 leaves the detections on the device. */
+int ogle_detector_detect_device_async(OgleDetector* d, const float* images_nhwc4_device, int N, int H, int W, int copy_back);
 /* Wait for it and copy the results out. rows = top_k (mode 0) or (C-1)*top_k (mode 1).
  * Any output pointer may be NULL. count holds N (mode 0) or N*(C-1) ints. */
 int ogle_detector_wait(OgleDetector* d, float* score, int* anchor, int* cls, float* box, int* count);

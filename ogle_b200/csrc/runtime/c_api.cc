@@ -215,6 +215,11 @@ int ogle_detector_detect_async(OgleDetector* d, const float* images, int N, int 
     return guarded([&] { d->detector->DetectAsync(images, N, H, W); });
 }
 
+int ogle_detector_detect_device_async(OgleDetector* d, const float* images, int N, int H, int W, int copy_back) {
+    if (!d || !images || N <= 0) return -1;
+    return guarded([&] { d->detector->DetectDeviceAsync(images, N, H, W, copy_back != 0); });
+}
+
 int ogle_detector_wait(OgleDetector* d, float* score, int* anchor, int* cls, float* box, int* count) {
     if (!d) return -1;
     return guarded([&] {

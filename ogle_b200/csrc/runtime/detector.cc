@@ -51,6 +51,20 @@ void Detector::DetectAsync(const float* images_nhwc, int N, int H, int W) {
     Tensor input(Tensor::DT_FLOAT, IntList{N, H, W, 3}, const_cast<float*>(images_nhwc), dlxnet::TensorProto::NHWC);
     session_->Run({{options_.input_names[0], &input}});          // detector.cc:235-240
     h2d_bytes_ = input.num_elements() * sizeof(float);
+    PostProcess(N, H, W, true);
+}
+
+void Detector::DetectDeviceAsync(const float* images_nhwc4_device, int N, int H, int W, bool copy_back) {
+    context_->MakeCurrent();
+    Tensor* in = session_->FindTensorByName(options_.input_names[0]);
+    OGLE_CHECK(in != nullptr) << "run DetectAsync once before DetectDeviceAsync (it sizes the session)";
+    OGLE_CHECK(in->shape() == (IntList{N, H, W, 3})) << "device input does not match the session's input shape";
+    session_->RunDevice({{options_.input_names[0], images_nhwc4_device}});
+    h2d_bytes_ = 0;
+    PostProcess(N, H, W, copy_back);
+}
+
+void Detector::PostProcess(int N, int H, int W, bool copy_back) {
     Tensor* cls_logits = session_->FindTensorByName(options_.output_names[0]);
     Tensor* box_preds = session_->FindTensorByName(options_.output_names[1]);
     Tensor* anchors = session_->FindTensorByName(options_.output_names[2]);
@@ -82,9 +96,12 @@ void Detector::DetectAsync(const float* images_nhwc, int N, int H, int W) {
                                       reinterpret_cast<int*>(d + off_anchor_), reinterpret_cast<int*>(d + off_cls_),
                                       reinterpret_cast<float*>(d + off_box_), reinterpret_cast<int*>(d + off_count_),
                                       context_->stream()));
-    OGLE_RT_CUDA(cudaMemcpyAsync(out_host_, out_dev_, out_bytes_, cudaMemcpyDeviceToHost,
-                                 reinterpret_cast<cudaStream_t>(context_->stream())));
-    d2h_bytes_ = out_bytes_;
+    d2h_bytes_ = 0;
+    if (copy_back) {
+        OGLE_RT_CUDA(cudaMemcpyAsync(out_host_, out_dev_, out_bytes_, cudaMemcpyDeviceToHost,
+                                     reinterpret_cast<cudaStream_t>(context_->stream())));
+        d2h_bytes_ = out_bytes_;
+    }
 }
 
 const DetectionBatch& Detector::Wait() {

@@ -40,6 +40,9 @@ public:
     // upload, the network, decode and post-process, and the copies of the results
     // into pinned staging; Wait() then exposes them.
     void DetectAsync(const float* images_nhwc, int N, int H, int W);
+    // Same, for images that already sit on the device in the padded NHWC4 layout
+    // [N][H][W][4]; copy_back = false leaves the detections on the device.
+    void DetectDeviceAsync(const float* images_nhwc4_device, int N, int H, int W, bool copy_back);
     // Blocks until the last DetectAsync finished; results are valid until the next call.
     const DetectionBatch& Wait();
     FBOSession* session() { return session_.get(); }
@@ -53,6 +56,7 @@ public:
 
 private:
     void AllocateOutputs(int N);
+    void PostProcess(int N, int H, int W, bool copy_back);
     DetectorOptions options_;
     Context* context_;
     std::unique_ptr<FBOSession> session_;

@@ -37,6 +37,7 @@ RT_SYMBOLS = {
     "ogle_detector_create": (_vp, [C.c_int, _vp, _cp, C.c_int, C.c_float, C.c_int, C.c_float, C.c_int, _cp, _cp, _cp, _cp]),
     "ogle_detector_destroy": (None, [_vp]),
     "ogle_detector_detect_async": (C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int]),
+    "ogle_detector_detect_device_async": (C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int]),
     "ogle_detector_wait": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "ogle_detector_info": (C.c_int, [_vp, _ip, _ip, _ip, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "ogle_detector_session": (_vp, [_vp]),
@@ -213,6 +214,12 @@ class Detector:
     def detect_async(self, images_ptr, N, H, W):
         """images_ptr: address of N*H*W*3 host floats (NHWC, preprocessed); pinned memory makes the copy asynchronous."""
         _check(self._lib.ogle_detector_detect_async(self._h, images_ptr, N, H, W), "detect_async")
+        self._shape = N
+
+    def detect_device_async(self, images_dev_ptr, N, H, W, copy_back=False):
+        """images_dev_ptr: device address of [N,H,W,4] floats (padded NHWC4)."""
+        _check(self._lib.ogle_detector_detect_device_async(self._h, images_dev_ptr, N, H, W, int(copy_back)),
+               "detect_device_async")
         self._shape = N
 
     def info(self):

@@ -60,6 +60,11 @@ const char* ogle_cuda_build_info(void);
 uint64_t ogle_cuda_launch_count(void);
 /* Last CUDA error string seen by this library on the calling thread. */
 const char* ogle_cuda_last_error(void);
+/* Device-side status word of the tensor-core kernels: 0, or the code of the first
+ * bounded wait that gave up (the launch then produced no valid output). Reading
+ * synchronises the device; clear resets it. */
+int ogle_cuda_device_status(void);
+int ogle_cuda_clear_device_status(void);
 
 /* ------------------------------------------------------------------ conv2d */
 /* Mirrors the uniform set of Conv2DKernel::Compute,
@@ -141,6 +146,17 @@ typedef struct {
 } OgleGemmParams;
 int ogle_cuda_gemm(const OgleGemmParams* p, const float* A, const float* B, const float* C,
                    float* Y, ogle_stream_t stream);
+
+/* B operand re-laid for the tensor-core path: K-major [round_up(N,128)][round_up(K,32)]
+ * split into hi (10 mantissa bits) and lo (remainder) halves. Like the conv filter
+ * packing, it is done once for a constant B (the usual case: Gemm weights are model
+ * constants) and replaces the ANY -> ANY4 upload pass of context.cc:135-141. */
+size_t ogle_cuda_gemm_packed_b_bytes(const OgleGemmParams* p);
+int ogle_cuda_gemm_pack_b(const OgleGemmParams* p, const float* B, void* packed, ogle_stream_t stream);
+/* ogle_cuda_gemm with B given in packed form (math_mode TF32 or TF32X3; FP32 is
+ * served from the raw B by ogle_cuda_gemm). */
+int ogle_cuda_gemm_packed(const OgleGemmParams* p, const float* A, const void* packed_b, const float* C,
+                          float* Y, ogle_stream_t stream);
 
 /* ------------------------------------------------------------------ concat */
 /* ConcatKernel::Compute, nn/kernels/concat.cc:53-96 + concat_multi.glsl.

@@ -2,6 +2,8 @@
 #include "common.cuh"
 
 namespace ogle {
+int read_tc_error();
+int clear_tc_error();
 std::atomic<uint64_t> g_launch_count{0};
 static thread_local char g_last_error[256] = "";
 void set_last_error(cudaError_t e) {
@@ -32,5 +34,13 @@ const char* ogle_cuda_build_info(void) { return "ogle_cuda 0.1 sm_100a"; }
 uint64_t ogle_cuda_launch_count(void) { return ogle::g_launch_count.load(std::memory_order_relaxed); }
 
 const char* ogle_cuda_last_error(void) { return ogle::g_last_error; }
+
+int ogle_cuda_device_status(void) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return OGLE_ERR_CUDA;
+    const int v = ogle::read_tc_error();
+    return v == 0 ? OGLE_OK : (v < 0 ? OGLE_ERR_CUDA : OGLE_ERR_TIMEOUT);
+}
+
+int ogle_cuda_clear_device_status(void) { return ogle::clear_tc_error() == 0 ? OGLE_OK : OGLE_ERR_CUDA; }
 
 }  // extern "C"

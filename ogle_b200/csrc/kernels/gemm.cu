@@ -8,6 +8,23 @@ namespace ogle {
 int launch_gemm_tc(const OgleGemmParams& p, const float* A, const float* B, const float* C,
                    float* Y, cudaStream_t s);
 bool gemm_tc_supported(const OgleGemmParams& p, const float* A, const float* B);
+int launch_gemm_tc_packed(const OgleGemmParams& p, const float* A, const float* Bhi, const float* Blo,
+                          const float* C, float* Y, cudaStream_t s);
+
+// B [K][ldb] (or [N][ldb] when transB) -> hi / lo, each [round_up(N,128)][round_up(K,32)], K-major.
+__global__ void gemm_pack_b_kernel(const float* __restrict__ B, float* __restrict__ hi, float* __restrict__ lo,
+                                   int K, int N, int ldb, int transB, int Kp32, int Np128) {
+    const long total = (long)Np128 * Kp32;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total;
+         i += (long)gridDim.x * blockDim.x) {
+        const int k = int(i % Kp32), n = int(i / Kp32);
+        float v = 0.f;
+        if (k < K && n < N) v = transB ? B[(long)n * ldb + k] : B[(long)k * ldb + n];
+        const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+        hi[i] = h;
+        lo[i] = v - h;
+    }
+}
 
 template <bool TRANSB>
 __global__ void __launch_bounds__(256)
@@ -129,21 +146,67 @@ gemm_simt_kernel(const float* __restrict__ A, const float* __restrict__ B, const
 
 using namespace ogle;
 
+static int normalize_gemm(OgleGemmParams* p) {
+    if (p->M <= 0 || p->K <= 0 || p->N <= 0) return OGLE_ERR_INVALID;
+    if (p->lda == 0) p->lda = up4(p->K);
+    if (p->ldb == 0) p->ldb = p->transB ? up4(p->K) : up4(p->N);
+    if (p->ldy == 0) p->ldy = up4(p->N);
+    if (p->ldc == 0) p->ldc = up4(p->N);
+    if (p->lda < p->K || p->ldy < p->N || p->ldb < (p->transB ? p->K : p->N)) return OGLE_ERR_INVALID;
+    if ((p->lda & 3) || (p->ldb & 3) || (p->ldy & 3)) return OGLE_ERR_ALIGNMENT;
+    if (p->bias_mode < 0 || p->bias_mode > 2) return OGLE_ERR_INVALID;
+    if (p->bias_mode == 1 && p->ldc < p->N) return OGLE_ERR_INVALID;
+    if (p->math_mode < OGLE_MATH_FP32 || p->math_mode > OGLE_MATH_TF32X3) return OGLE_ERR_INVALID;
+    return OGLE_OK;
+}
+
+extern "C" size_t ogle_cuda_gemm_packed_b_bytes(const OgleGemmParams* pp) {
+    if (!pp) return 0;
+    OgleGemmParams p = *pp;
+    if (normalize_gemm(&p) != OGLE_OK) return 0;
+    const size_t half = size_t((p.N + 127) / 128 * 128) * size_t((p.K + 31) / 32 * 32) * sizeof(float);
+    return 2 * ((half + 255) / 256 * 256);
+}
+
+extern "C" int ogle_cuda_gemm_pack_b(const OgleGemmParams* pp, const float* B, void* packed, ogle_stream_t stream) {
+    if (!pp || !B || !packed) return OGLE_ERR_INVALID;
+    OgleGemmParams p = *pp;
+    int rc = normalize_gemm(&p);
+    if (rc != OGLE_OK) return rc;
+    if (!aligned16(packed)) return OGLE_ERR_ALIGNMENT;
+    const int Kp32 = (p.K + 31) / 32 * 32, Np128 = (p.N + 127) / 128 * 128;
+    const size_t half = (size_t(Np128) * Kp32 * sizeof(float) + 255) / 256 * 256;
+    float* hi = static_cast<float*>(packed);
+    float* lo = reinterpret_cast<float*>(static_cast<char*>(packed) + half);
+    gemm_pack_b_kernel<<<grid_for((long)Np128 * Kp32, 256), 256, 0, (cudaStream_t)stream>>>(B, hi, lo, p.K, p.N, p.ldb,
+                                                                                            p.transB, Kp32, Np128);
+    return finish_launch();
+}
+
+extern "C" int ogle_cuda_gemm_packed(const OgleGemmParams* pp, const float* A, const void* packed_b, const float* C,
+                                     float* Y, ogle_stream_t stream) {
+    if (!pp || !A || !packed_b || !Y) return OGLE_ERR_INVALID;
+    OgleGemmParams p = *pp;
+    int rc = normalize_gemm(&p);
+    if (rc != OGLE_OK) return rc;
+    if (p.bias_mode && !C) return OGLE_ERR_INVALID;
+    if (p.math_mode == OGLE_MATH_FP32) return OGLE_ERR_INVALID;
+    if (!aligned16(A) || !aligned16(Y) || !aligned16(packed_b)) return OGLE_ERR_ALIGNMENT;
+    const int Kp32 = (p.K + 31) / 32 * 32, Np128 = (p.N + 127) / 128 * 128;
+    const size_t half = (size_t(Np128) * Kp32 * sizeof(float) + 255) / 256 * 256;
+    const float* hi = static_cast<const float*>(packed_b);
+    const float* lo = reinterpret_cast<const float*>(static_cast<const char*>(packed_b) + half);
+    return launch_gemm_tc_packed(p, A, hi, lo, C, Y, (cudaStream_t)stream);
+}
+
 extern "C" int ogle_cuda_gemm(const OgleGemmParams* pp, const float* A, const float* B, const float* C,
                               float* Y, ogle_stream_t stream) {
     if (!pp || !A || !B || !Y) return OGLE_ERR_INVALID;
     OgleGemmParams p = *pp;
-    if (p.M <= 0 || p.K <= 0 || p.N <= 0) return OGLE_ERR_INVALID;
-    if (p.lda == 0) p.lda = up4(p.K);
-    if (p.ldb == 0) p.ldb = p.transB ? up4(p.K) : up4(p.N);
-    if (p.ldy == 0) p.ldy = up4(p.N);
-    if (p.ldc == 0) p.ldc = up4(p.N);
-    if (p.lda < p.K || p.ldy < p.N || p.ldb < (p.transB ? p.K : p.N)) return OGLE_ERR_INVALID;
-    if ((p.lda & 3) || (p.ldb & 3)) return OGLE_ERR_ALIGNMENT;
-    if (p.bias_mode < 0 || p.bias_mode > 2 || (p.bias_mode && !C)) return OGLE_ERR_INVALID;
-    if (p.bias_mode == 1 && p.ldc < p.N) return OGLE_ERR_INVALID;
+    int rc0 = normalize_gemm(&p);
+    if (rc0 != OGLE_OK) return rc0;
+    if (p.bias_mode && !C) return OGLE_ERR_INVALID;
     if (!aligned16(A) || !aligned16(B) || !aligned16(Y)) return OGLE_ERR_ALIGNMENT;
-    if (p.math_mode < OGLE_MATH_FP32 || p.math_mode > OGLE_MATH_TF32X3) return OGLE_ERR_INVALID;
     cudaStream_t s = (cudaStream_t)stream;
     if (p.math_mode != OGLE_MATH_FP32 && gemm_tc_supported(p, A, B)) return launch_gemm_tc(p, A, B, C, Y, s);
     dim3 grid(div_up(p.M, 128), div_up(p.ldy, 64));

@@ -324,6 +324,7 @@ def main():
         builder = lambda n: models.mobilenet_v1_ssd(batch=n, num_classes=args.classes, seed=0, weight_std=0.02)
         cpu = cpu_baseline(builder, args.classes, args.cpu_seconds)
 
+    graph_captured = sess.graph_captured()
     det.close()
     if world > 1:
         dist.barrier()
@@ -338,7 +339,7 @@ def main():
                                % (args.classes, B, "per-class top-200 (thr 0.01)" if args.mode == 1 else "reference Detector rule"),
                    "global_batch": B * world, "math_mode": args.math, "gflop_per_image": info["flops_per_image"] / 1e9,
                    "l2": "inputs larger than L2 (%.0f MB per step, two batches alternated)" % (B * 300 * 300 * 16 / 1e6),
-                   "parallelism": "image-sharded x%d, no collective" % world, "cuda_graph": sess.graph_captured()},
+                   "parallelism": "image-sharded x%d, no collective" % world, "cuda_graph": graph_captured},
         "e2e": e2e, "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step,
         "clocks": clocks, "roofline": roof, "cpu_baseline": cpu}), flush=True)
 

@@ -23,106 +23,26 @@
 // issue, warps 2-5 = operand split (3-pass mode) then epilogue. All waits on
 // mbarriers are bounded: a wait that gives up records an error code, and every
 // role falls through to the common teardown that frees tensor memory.
-#include <cuda.h>
+#include <cstdlib>
 
-#include "conv_args.cuh"
+#include "tc_common.cuh"
 
 namespace ogle {
+
+int launch_tc_v2(tc::TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, const CUtensorMap& mBlo,
+                 const CUtensorMap& mY, long m_tiles, const float* bias, int* err_flag, cudaStream_t s);
 
 __device__ int g_tc_error = 0;   // first error seen by any block (0 = none)
 
 namespace {
 
+using namespace tc;
 constexpr int kThreads = 192;
-constexpr int kTileM = 128;
-constexpr int kChunk = 32;              // reduction elements per pipeline stage (128 bytes)
-constexpr int kABytes = kTileM * 128;   // one A tile
-constexpr uint32_t kSpinLimit = 1u << 22;
-
-struct TcArgs {
-    int flat;                 // 1: rows are a flat range of pixels (pointwise / gemm)
-    int tn, th, tw;           // output pixels per tile along n, h, w (tn*th*tw <= 128)
-    int tiles_w, tiles_h;     // tile grid along w and h (n follows)
-    int N, Ho, Wo;            // output extent (flat: rows = Wo)
-    int stride, pad, dil, kernel;
-    int chunks_per_tap, Cp32;
-    int K, Kp, Ks, koff;      // output channels, padded to 4, row stride, first channel
-    int BN, n_tiles;          // N tile and how many cover Kp
-    int act;
-    float lo, hi;
-    float alpha, beta;
-    int bias_mode;            // 0 none, 1 full matrix C[m][ldc], 2 per-column vector
-    int ldc;
-    int passes;               // 1 (TF32) or 3 (hi/lo split)
-    int stages;
-    int tmem_cols;
-};
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Bounded wait for the phase with the given parity. false = gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    const uint32_t addr = smem_u32(bar);
-    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint64_t* bar,
-                                            int c0, int c1, int c2, int c3) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-        ::"r"(dst), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
-}
-
-// K-major operand tile, 128-byte rows, 128-byte swizzle, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
-    uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);   // start address, bits [0,14)
-    d |= (uint64_t)1 << 16;                              // leading byte offset (unused with swizzle), bits [16,30)
-    d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset, bits [32,46)
-    d |= (uint64_t)1 << 46;                              // descriptor version for sm_100
-    d |= (uint64_t)2 << 61;                              // SWIZZLE_128B
-    return d;
-}
-
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ void record_error(int code) { atomicCAS(&g_tc_error, 0, code); }
 
 __global__ void __launch_bounds__(kThreads)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmBhi,
                const __grid_constant__ CUtensorMap tmBlo, const float* __restrict__ bias, float* __restrict__ y,
-               const TcArgs a) {
+               const TcArgs a, int* err_flag) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[4], bar_xf[4], bar_empty[4], bar_accum;
     __shared__ uint32_t tmem_slot;
@@ -183,7 +103,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int it = 0; it < total && ok; ++it) {
                 const int s = it % a.stages, j = it / a.stages;
                 if (j > 0) ok = mbar_wait(&bar_empty[s], (uint32_t)((j - 1) & 1));
-                if (!ok) { record_error(1); break; }
+                if (!ok) { record_error(err_flag, 1); break; }
                 const int tap = it / a.chunks_per_tap;
                 const int c0 = (it - tap * a.chunks_per_tap) * kChunk;
                 const int ky = tap / a.kernel, kx = tap - ky * a.kernel;
@@ -212,7 +132,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const int s = it % a.stages;
                 const uint32_t ph = (uint32_t)((it / a.stages) & 1);
                 ok = mbar_wait(split ? &bar_xf[s] : &bar_full[s], ph);
-                if (!ok) { record_error(2); s_abort = 1; break; }
+                if (!ok) { record_error(err_flag, 2); s_abort = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int k = 0; k < kChunk / 8; ++k) {
@@ -236,7 +156,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const int s = it % a.stages;
                 const uint32_t ph = (uint32_t)((it / a.stages) & 1);
                 ok = mbar_wait(&bar_full[s], ph);
-                if (!ok) { record_error(3); break; }
+                if (!ok) { record_error(err_flag, 3); break; }
                 float4* pa = reinterpret_cast<float4*>(base_ptr + (size_t)s * stage_bytes);
                 float4* pl = pa + kABytes / 16;
 #pragma unroll
@@ -256,7 +176,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
         }
         if (ok) ok = mbar_wait(&bar_accum, 0);
-        if (!ok) record_error(4);
+        if (!ok) record_error(err_flag, 4);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (ok && !s_abort) {
             const int q = warp & 3;                       // TMEM lane quarter this warp may read
@@ -345,6 +265,21 @@ bool make_map(CUtensorMap* m, const void* ptr, int rank, const cuuint64_t* dims,
     return r == CUDA_SUCCESS;
 }
 
+int* error_flag_ptr() {
+    // per-device address of the status word
+    static thread_local int* ptr = nullptr;
+    static thread_local int ptr_device = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (ptr_device != dev) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_tc_error) != cudaSuccess) return nullptr;
+        ptr = static_cast<int*>(p);
+        ptr_device = dev;
+    }
+    return ptr;
+}
+
 int next_pow2(int v) { int p = 32; while (p < v) p <<= 1; return p; }
 
 // Picks N tiling, stage count and shared memory; launches.
@@ -370,8 +305,30 @@ int launch_tc(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, const C
     }
     const long blocks = m_tiles * t.n_tiles;
     if (blocks <= 0 || blocks > 0x7fffffffL) return OGLE_ERR_UNSUPPORTED;
-    conv_tc_kernel<<<(unsigned)blocks, kThreads, smem, s>>>(mA, mBhi, mBlo, bias, y, t);
+    conv_tc_kernel<<<(unsigned)blocks, kThreads, smem, s>>>(mA, mBhi, mBlo, bias, y, t, error_flag_ptr());
     return finish_launch();
+}
+
+// 2 = persistent kernel (default), 1 = one tile per block. OGLE_TC_VARIANT overrides.
+int tc_variant() {
+    static int v = [] {
+        const char* e = getenv("OGLE_TC_VARIANT");
+        return (e && e[0] == '1') ? 1 : 2;
+    }();
+    return v;
+}
+
+// N tiling of the persistent kernel: multiples of 32 columns (one staging slab each);
+// narrower tiles when there would otherwise be fewer tiles than SMs.
+void choose_n_tiling_v2(int Kp, long m_tiles, TcArgs* t) {
+    int bn = (Kp + 31) / 32 * 32;
+    if (bn > 256) {
+        const int parts = (Kp + 255) / 256;
+        bn = ((Kp + parts - 1) / parts + 31) / 32 * 32;
+    }
+    while (bn > 32 && m_tiles * ((Kp + bn - 1) / bn) < kNumSMs) bn = (bn / 2 + 31) / 32 * 32;
+    t->BN = bn;
+    t->n_tiles = (Kp + bn - 1) / bn;
 }
 
 void choose_n_tiling(int Kp, TcArgs* t) {
@@ -390,7 +347,7 @@ void choose_n_tiling(int Kp, TcArgs* t) {
 bool conv_tc_supported(const ConvArgs& a, int variant) {
     if (variant != CONV_GENERAL && variant != CONV_POINTWISE) return false;
     if (a.group != 1) return false;
-    if (a.kernel * a.kernel * a.Cp < 64) return false;      // reduction too short: the RGB stem stays on CUDA cores
+    if (a.kernel * a.kernel * a.Cp < 32) return false;      // reduction too short: the RGB stem stays on CUDA cores
     if (a.kernel > 7) return false;
     if (!encode_fn()) return false;
     if (variant == CONV_GENERAL) {
@@ -411,9 +368,9 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
     t.act = a.act; t.lo = a.lo; t.hi = a.hi;
     t.alpha = 1.f; t.beta = 1.f; t.bias_mode = a.has_bias ? 2 : 0; t.ldc = 0;
     t.passes = math_mode == OGLE_MATH_TF32X3 ? 3 : 1;
-    choose_n_tiling(a.Kp, &t);
+    const bool v2 = tc_variant() == 2;
 
-    CUtensorMap mA, mBhi, mBlo;
+    CUtensorMap mA, mBhi, mBlo, mY;
     long m_tiles;
     if (variant == CONV_POINTWISE) {
         t.flat = 1;
@@ -425,6 +382,11 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
         const cuuint32_t box[4] = {kChunk, kTileM, 1, 1};
         const cuuint32_t es[4] = {1, 1, 1, 1};
         if (!make_map(&mA, x, 4, dims, str, box, es)) return OGLE_ERR_CUDA;
+        if (v2) {
+            const cuuint64_t yd[4] = {(cuuint64_t)a.Kp, (cuuint64_t)a.M, 1, 1};
+            const cuuint64_t ys[3] = {(cuuint64_t)a.Ks * 4, (cuuint64_t)a.Ks * 4 * (cuuint64_t)a.M, (cuuint64_t)a.Ks * 4 * (cuuint64_t)a.M};
+            if (!make_map(&mY, y + a.koff, 4, yd, ys, box, es)) return OGLE_ERR_CUDA;
+        }
     } else {
         t.flat = 0;
         t.N = a.N; t.Ho = a.Ho; t.Wo = a.Wo;
@@ -447,7 +409,16 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
                                    (cuuint32_t)t.tn};
         const cuuint32_t es[4] = {1, (cuuint32_t)a.stride, (cuuint32_t)a.stride, 1};
         if (!make_map(&mA, x, 4, dims, str, box, es)) return OGLE_ERR_CUDA;
+        if (v2) {
+            const cuuint64_t yd[4] = {(cuuint64_t)a.Kp, (cuuint64_t)a.Wo, (cuuint64_t)a.Ho, (cuuint64_t)a.N};
+            const cuuint64_t ys[3] = {(cuuint64_t)a.Ks * 4, (cuuint64_t)a.Ks * 4 * a.Wo, (cuuint64_t)a.Ks * 4 * a.Wo * a.Ho};
+            const cuuint32_t yb[4] = {kChunk, (cuuint32_t)t.tw, (cuuint32_t)t.th, (cuuint32_t)t.tn};
+            const cuuint32_t ye[4] = {1, 1, 1, 1};
+            if (!make_map(&mY, y + a.koff, 4, yd, ys, yb, ye)) return OGLE_ERR_CUDA;
+        }
     }
+    if (v2) choose_n_tiling_v2(a.Kp, m_tiles, &t);
+    else choose_n_tiling(a.Kp, &t);
     const int Kp128 = (a.K + 127) / 128 * 128;
     const cuuint64_t bdims[2] = {(cuuint64_t)taps * t.Cp32, (cuuint64_t)Kp128};
     const cuuint64_t bstr[1] = {(cuuint64_t)taps * t.Cp32 * 4};
@@ -455,6 +426,7 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
     const cuuint32_t bes[2] = {1, 1};
     if (!make_map(&mBhi, w_hi, 2, bdims, bstr, bbox, bes)) return OGLE_ERR_CUDA;
     if (!make_map(&mBlo, w_lo, 2, bdims, bstr, bbox, bes)) return OGLE_ERR_CUDA;
+    if (v2) return launch_tc_v2(t, mA, mBhi, mBlo, mY, m_tiles, bias, error_flag_ptr(), s);
     return launch_tc(t, mA, mBhi, mBlo, m_tiles, bias, y, s);
 }
 
@@ -477,8 +449,11 @@ static int launch_gemm_common(const OgleGemmParams& p, const float* A, const flo
     t.act = OGLE_ACT_NONE;
     t.alpha = p.alpha; t.beta = p.beta; t.bias_mode = p.bias_mode; t.ldc = p.ldc;
     t.passes = passes;
-    choose_n_tiling(t.Kp, &t);
-    CUtensorMap mA, mBhi, mBlo;
+    const bool v2 = tc_variant() == 2;
+    const long m_tiles = (p.M + kTileM - 1) / kTileM;
+    if (v2) choose_n_tiling_v2(t.Kp, m_tiles, &t);
+    else choose_n_tiling(t.Kp, &t);
+    CUtensorMap mA, mBhi, mBlo, mY;
     const cuuint64_t dims[4] = {(cuuint64_t)p.K, (cuuint64_t)p.M, 1, 1};
     const cuuint64_t str[3] = {(cuuint64_t)p.lda * 4, (cuuint64_t)p.lda * 4 * (cuuint64_t)p.M, (cuuint64_t)p.lda * 4 * (cuuint64_t)p.M};
     const cuuint32_t box[4] = {kChunk, kTileM, 1, 1};
@@ -490,7 +465,13 @@ static int launch_gemm_common(const OgleGemmParams& p, const float* A, const flo
     const cuuint32_t bes[2] = {1, 1};
     if (!make_map(&mBhi, Bhi, 2, bdims, bstr, bbox, bes)) return OGLE_ERR_CUDA;
     if (!make_map(&mBlo, Blo ? Blo : Bhi, 2, bdims, bstr, bbox, bes)) return OGLE_ERR_CUDA;
-    return launch_tc(t, mA, mBhi, mBlo, (p.M + kTileM - 1) / kTileM, C, Y, s);
+    if (v2) {
+        const cuuint64_t yd[4] = {(cuuint64_t)t.Kp, (cuuint64_t)p.M, 1, 1};
+        const cuuint64_t ys[3] = {(cuuint64_t)p.ldy * 4, (cuuint64_t)p.ldy * 4 * (cuuint64_t)p.M, (cuuint64_t)p.ldy * 4 * (cuuint64_t)p.M};
+        if (!make_map(&mY, Y, 4, yd, ys, box, es)) return OGLE_ERR_CUDA;
+        return launch_tc_v2(t, mA, mBhi, mBlo, mY, m_tiles, C, error_flag_ptr(), s);
+    }
+    return launch_tc(t, mA, mBhi, mBlo, m_tiles, C, Y, s);
 }
 
 int launch_gemm_tc(const OgleGemmParams& p, const float* A, const float* B, const float* C, float* Y, cudaStream_t s) {

@@ -1,0 +1,353 @@
+// Persistent tcgen05 kernel for the dense contractions (conv2d general/pointwise
+// as implicit GEMM, gemm): the same arithmetic as conv_tc.cu, restructured so that
+// one block per SM walks a list of output tiles and every stage of the pipeline
+// overlaps with the others ACROSS tiles:
+//
+//   warp 0      TMA producer: keeps a ring of operand stages full, running ahead
+//               into the next tile while the current one is still being multiplied;
+//   warp 1      MMA issuer: accumulates tile i into one half of tensor memory while
+//               the epilogue drains tile i-1 from the other half;
+//   warps 2-5   epilogue: tcgen05.ld -> bias / activation -> shared-memory staging in
+//               the 128-byte swizzle -> TMA tensor store (fully coalesced, clipped at
+//               the tensor edge by the hardware);
+//   warps 6-9   operand split for the 3-pass TF32 mode (idle in one-pass mode).
+//
+// HBM traffic per tile is the algorithmic minimum: the activation tile is read
+// once, the output tile written once; filters come from L2.
+// All mbarrier waits are bounded and abort the block cleanly (status word set,
+// in-flight copies drained, tensor memory freed).
+#include "tc_common.cuh"
+
+namespace ogle {
+namespace {
+
+using namespace tc;
+
+constexpr int kThreads2 = 320;
+constexpr int kMaxStages = 8;
+constexpr int kStagingBytes = kTileM * 128;   // one 128-row x 32-column fp32 slab
+
+// Bounded wait that also gives up early when another role of the block has aborted.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if ((spin & 255u) == 255u && *abort_flag) return false;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
+struct TileCoord { int n_tile, n0, h0, w0; };
+
+__device__ __forceinline__ TileCoord tile_coord(const TcArgs& a, int tile) {
+    TileCoord c;
+    c.n_tile = tile % a.n_tiles;
+    const int m_tile = tile / a.n_tiles;
+    c.n0 = 0; c.h0 = 0;
+    if (a.flat) {
+        c.w0 = m_tile * kTileM;
+    } else {
+        const int tw_i = m_tile % a.tiles_w;
+        const int t = m_tile / a.tiles_w;
+        c.w0 = tw_i * a.tw;
+        c.h0 = (t % a.tiles_h) * a.th;
+        c.n0 = (t / a.tiles_h) * a.tn;
+    }
+    return c;
+}
+
+__global__ void __launch_bounds__(kThreads2, 1)
+conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmBhi,
+                const __grid_constant__ CUtensorMap tmBlo, const __grid_constant__ CUtensorMap tmY,
+                const float* __restrict__ bias, const TcArgs a, int* err_flag) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[kMaxStages], bar_xf[kMaxStages], bar_empty[kMaxStages];
+    __shared__ __align__(8) uint64_t bar_acc_full[2], bar_acc_empty[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int s_abort;
+    __shared__ float s_bias[256];
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool split = a.passes == 3;
+    const uint32_t b_bytes = (uint32_t)a.BN * 128u;
+    const uint32_t stage_bytes = (split ? 2u : 1u) * (kABytes + b_bytes);
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    // ring of operand stages (A | A_lo | B_hi | B_lo), then two output staging slabs
+    auto sA = [&](int s) { return base + (uint32_t)s * stage_bytes; };
+    auto sAlo = [&](int s) { return sA(s) + kABytes; };
+    auto sBhi = [&](int s) { return sA(s) + (split ? 2u : 1u) * kABytes; };
+    auto sBlo = [&](int s) { return sBhi(s) + b_bytes; };
+    const uint32_t staging_off = (uint32_t)a.stages * stage_bytes;
+
+    const int chunks = a.kernel * a.kernel * a.chunks_per_tap;
+    const int rows_in_tile = a.flat ? kTileM : a.tn * a.th * a.tw;
+    volatile int* abort_flag = &s_abort;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_xf[s], 128);
+            mbar_init(&bar_empty[s], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bar_acc_full[i], 1);
+            mbar_init(&bar_acc_empty[i], 128);
+        }
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"((uint32_t)a.tmem_cols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            const uint32_t tx = (uint32_t)rows_in_tile * 128u + (split ? 2u : 1u) * b_bytes;
+            long g = 0;          // chunks issued so far, over all tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x) {
+                const TileCoord tc_ = tile_coord(a, tile);
+                for (int it = 0; it < chunks; ++it, ++g) {
+                    const int s = (int)(g % a.stages);
+                    const long j = g / a.stages;
+                    if (j > 0) ok = wait_or_abort(&bar_empty[s], (uint32_t)((j - 1) & 1), abort_flag);
+                    if (!ok) { record_error(err_flag, 1); break; }
+                    const int tap = it / a.chunks_per_tap;
+                    const int c0 = (it - tap * a.chunks_per_tap) * kChunk;
+                    const int ky = tap / a.kernel, kx = tap - ky * a.kernel;
+                    mbar_expect_tx(&bar_full[s], tx);
+                    if (a.flat) tma_load_4d(sA(s), &tmA, &bar_full[s], c0, tc_.w0, 0, 0);
+                    else tma_load_4d(sA(s), &tmA, &bar_full[s], c0, tc_.w0 * a.stride - a.pad + kx * a.dil,
+                                     tc_.h0 * a.stride - a.pad + ky * a.dil, tc_.n0);
+                    tma_load_2d(sBhi(s), &tmBhi, &bar_full[s], tap * a.Cp32 + c0, tc_.n_tile * a.BN);
+                    if (split) tma_load_2d(sBlo(s), &tmBlo, &bar_full[s], tap * a.Cp32 + c0, tc_.n_tile * a.BN);
+                }
+            }
+            if (!ok) {
+                // let the copies already in flight land before the block retires
+                s_abort = 1;
+                for (long i = (g > a.stages ? g - a.stages : 0); i < g; ++i)
+                    mbar_wait(&bar_full[i % a.stages], (uint32_t)((i / a.stages) & 1));
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(a.BN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+            long g = 0;
+            bool ok = true;
+            int ti = 0;
+            for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x, ++ti) {
+                const int as = ti & 1, use = ti >> 1;
+                if (use > 0) ok = wait_or_abort(&bar_acc_empty[as], (uint32_t)((use - 1) & 1), abort_flag);
+                if (!ok) { record_error(err_flag, 5); s_abort = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d = tmem_d + (uint32_t)(as * a.BN);
+                for (int it = 0; it < chunks; ++it, ++g) {
+                    const int s = (int)(g % a.stages);
+                    const uint32_t ph = (uint32_t)((g / a.stages) & 1);
+                    ok = wait_or_abort(split ? &bar_xf[s] : &bar_full[s], ph, abort_flag);
+                    if (!ok) { record_error(err_flag, 2); s_abort = 1; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                    for (int k = 0; k < kChunk / 8; ++k) {
+                        const uint64_t ad = umma_desc(sA(s) + k * 32), bd = umma_desc(sBhi(s) + k * 32);
+                        umma_tf32(d, ad, bd, idesc, (it > 0 || k > 0) ? 1u : 0u);
+                        if (split) {
+                            umma_tf32(d, umma_desc(sAlo(s) + k * 32), bd, idesc, 1u);
+                            umma_tf32(d, ad, umma_desc(sBlo(s) + k * 32), idesc, 1u);
+                        }
+                    }
+                    umma_commit(&bar_empty[s]);
+                }
+                if (ok) umma_commit(&bar_acc_full[as]);
+            }
+        }
+    } else if (warp >= 6) {
+        // --------------------------------------------------- operand split (3-pass)
+        if (split) {
+            const int t = threadIdx.x - 192;   // 0..127
+            long g = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x) {
+                for (int it = 0; it < chunks; ++it, ++g) {
+                    const int s = (int)(g % a.stages);
+                    ok = wait_or_abort(&bar_full[s], (uint32_t)((g / a.stages) & 1), abort_flag);
+                    if (!ok) { record_error(err_flag, 3); s_abort = 1; break; }
+                    float4* pa = reinterpret_cast<float4*>(base_ptr + (size_t)s * stage_bytes);
+                    float4* pl = pa + kABytes / 16;
+#pragma unroll
+                    for (int i = 0; i < kABytes / 16 / 128; ++i) {
+                        const float4 v = pa[t + i * 128];
+                        float4 h;
+                        h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
+                        h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
+                        h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
+                        h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
+                        pa[t + i * 128] = h;
+                        pl[t + i * 128] = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    mbar_arrive(&bar_xf[s]);
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        const int t = threadIdx.x - 64;               // 0..127
+        const int q = warp & 3;                       // TMEM lane quarter this warp may read
+        const int row = q * 32 + lane;
+        const int groups = a.BN / 32;
+        unsigned char* staging = base_ptr + staging_off;
+        uint32_t stores = 0;
+        bool ok = true;
+        int ti = 0;
+        for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x, ++ti) {
+            const TileCoord tc_ = tile_coord(a, tile);
+            const int as = ti & 1, use = ti >> 1;
+            const int nbase = tc_.n_tile * a.BN;
+            // per-column bias of this N tile (conv bias, or gemm's row-vector C)
+            if (a.bias_mode == 2)
+                for (int i = t; i < a.BN; i += 128) s_bias[i] = (nbase + i < a.K) ? bias[nbase + i] : 0.f;
+            long pix = 0;
+            if (a.bias_mode == 1) {
+                if (a.flat) pix = (long)tc_.w0 + row;
+                if (pix >= a.Wo) pix = a.Wo - 1;      // clipped rows are dropped by the store; keep reads in range
+            }
+            ok = wait_or_abort(&bar_acc_full[as], (uint32_t)(use & 1), abort_flag);
+            if (!ok) { record_error(err_flag, 4); s_abort = 1; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int grp = 0; grp < groups; ++grp) {
+                const int col = grp * 32;
+                const bool last = (grp == groups - 1) || (nbase + col + 32 >= a.Kp);
+                const uint32_t buf = stores & 1u;
+                // the slab is free once the store issued two slabs ago has read it
+                if (t == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                epi_sync();
+                uint32_t r[32];
+                const uint32_t taddr = tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * a.BN + col);
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                      "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                      "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                    : "r"(taddr));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (last) {
+                    // this thread's part of the accumulator is in registers: hand the buffer back
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    mbar_arrive(&bar_acc_empty[as]);
+                }
+                float4* dst = reinterpret_cast<float4*>(staging + (size_t)buf * kStagingBytes + (size_t)row * 128);
+#pragma unroll
+                for (int c4 = 0; c4 < 8; ++c4) {
+                    float v[4];
+#pragma unroll
+                    for (int l = 0; l < 4; ++l) {
+                        const int n = nbase + col + c4 * 4 + l;
+                        float acc = a.alpha * __uint_as_float(r[c4 * 4 + l]);
+                        if (n < a.K) {
+                            if (a.bias_mode == 2) acc = fmaf(a.beta, s_bias[col + c4 * 4 + l], acc);
+                            else if (a.bias_mode == 1) acc = fmaf(a.beta, bias[pix * a.ldc + n], acc);
+                            acc = apply_act(acc, a.act, a.lo, a.hi);
+                        } else {
+                            acc = 0.f;                 // padded lanes stay zero
+                        }
+                        v[l] = acc;
+                    }
+                    // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
+                    dst[c4 ^ (row & 7)] = make_float4(v[0], v[1], v[2], v[3]);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                epi_sync();
+                if (t == 0) {
+                    const uint32_t src = base + staging_off + buf * (uint32_t)kStagingBytes;
+                    if (a.flat) tma_store_4d(&tmY, src, nbase + col, tc_.w0, 0, 0);
+                    else tma_store_4d(&tmY, src, nbase + col, tc_.w0, tc_.h0, tc_.n0);
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+                ++stores;
+                if (last) break;
+            }
+        }
+        // the staging slabs must outlive the stores that read them
+        if (t == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
+
+    // ------------------------------------------------------------------ teardown
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)a.tmem_cols));
+    }
+}
+
+int num_sms() {
+    static thread_local int sms = 0, sms_device = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (sms_device != dev) {
+        cudaDeviceProp prop;
+        if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return kNumSMs;
+        sms = prop.multiProcessorCount;
+        sms_device = dev;
+    }
+    return sms;
+}
+
+}  // namespace
+
+int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, const CUtensorMap& mBlo,
+                 const CUtensorMap& mY, long m_tiles, const float* bias, int* err_flag, cudaStream_t s) {
+    if (t.BN % 32 || t.BN > 256) return OGLE_ERR_UNSUPPORTED;
+    const size_t stage = (size_t)(t.passes == 3 ? 2 : 1) * (kABytes + (size_t)t.BN * 128);
+    const size_t budget = 225 * 1024 - 2 * kStagingBytes - 1024;
+    int stages = (int)(budget / stage);
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages < 2) return OGLE_ERR_UNSUPPORTED;
+    t.stages = stages;
+    int cols = 32;
+    while (cols < 2 * t.BN) cols <<= 1;
+    t.tmem_cols = cols;
+    const long total = m_tiles * t.n_tiles;
+    if (total <= 0 || total > 0x7fffffffL) return OGLE_ERR_UNSUPPORTED;
+    t.total_tiles = (int)total;
+    const size_t smem = stage * stages + 2 * kStagingBytes + 1024;
+    static thread_local int attr_device = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_device != dev) {
+        cudaError_t e = cudaFuncSetAttribute(conv_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
+        if (e != cudaSuccess) { set_last_error(e); return OGLE_ERR_CUDA; }
+        attr_device = dev;
+    }
+    const int sms = num_sms();
+    const unsigned grid = (unsigned)(total < sms ? total : sms);
+    conv_tc2_kernel<<<grid, kThreads2, smem, s>>>(mA, mBhi, mBlo, mY, bias, t, err_flag);
+    return finish_launch();
+}
+
+}  // namespace ogle

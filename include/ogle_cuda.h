@@ -65,6 +65,9 @@ const char* ogle_cuda_last_error(void);
  * synchronises the device; clear resets it. */
 int ogle_cuda_device_status(void);
 int ogle_cuda_clear_device_status(void);
+/* The raw status word: which wait gave up (1 producer, 2 MMA issuer, 3 operand split,
+ * 4 epilogue, 5 accumulator hand-back); 0 when none did. Synchronises the device. */
+int ogle_cuda_device_status_detail(void);
 
 /* ------------------------------------------------------------------ conv2d */
 /* Mirrors the uniform set of Conv2DKernel::Compute,

@@ -77,6 +77,7 @@ CUDA_SYMBOLS = {
     "ogle_cuda_gemm_packed": (C.c_int, [C.POINTER(GemmParams), _vp, _vp, _vp, _vp, _vp]),
     "ogle_cuda_device_status": (C.c_int, []),
     "ogle_cuda_clear_device_status": (C.c_int, []),
+    "ogle_cuda_device_status_detail": (C.c_int, []),
     "ogle_cuda_concat": (C.c_int, [C.POINTER(ConcatParams), C.POINTER(_vp), _vp, _vp]),
     "ogle_cuda_pad4": (C.c_int, [_vp, _vp, C.c_long, C.c_int, C.c_int, _vp]),
     "ogle_cuda_unpad4": (C.c_int, [_vp, _vp, C.c_long, C.c_int, C.c_int, _vp]),

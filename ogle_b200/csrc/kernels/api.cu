@@ -41,6 +41,11 @@ int ogle_cuda_device_status(void) {
     return v == 0 ? OGLE_OK : (v < 0 ? OGLE_ERR_CUDA : OGLE_ERR_TIMEOUT);
 }
 
+int ogle_cuda_device_status_detail(void) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return OGLE_ERR_CUDA;
+    return ogle::read_tc_error();
+}
+
 int ogle_cuda_clear_device_status(void) { return ogle::clear_tc_error() == 0 ? OGLE_OK : OGLE_ERR_CUDA; }
 
 }  // extern "C"

@@ -347,7 +347,7 @@ void choose_n_tiling(int Kp, TcArgs* t) {
 bool conv_tc_supported(const ConvArgs& a, int variant) {
     if (variant != CONV_GENERAL && variant != CONV_POINTWISE) return false;
     if (a.group != 1) return false;
-    if (a.kernel * a.kernel * a.Cp < 32) return false;      // reduction too short: the RGB stem stays on CUDA cores
+    if (a.Cp < 16 || a.kernel * a.kernel * a.Cp < 32) return false;   // too few channels per tap: the RGB stem stays on CUDA cores
     if (a.kernel > 7) return false;
     if (!encode_fn()) return false;
     if (variant == CONV_GENERAL) {

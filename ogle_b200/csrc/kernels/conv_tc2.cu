@@ -7,15 +7,21 @@
 //               into the next tile while the current one is still being multiplied;
 //   warp 1      MMA issuer: accumulates tile i into one half of tensor memory while
 //               the epilogue drains tile i-1 from the other half;
-//   warps 2-5   epilogue: tcgen05.ld -> bias / activation -> shared-memory staging in
-//               the 128-byte swizzle -> TMA tensor store (fully coalesced, clipped at
-//               the tensor edge by the hardware);
-//   warps 6-9   operand split for the 3-pass TF32 mode (idle in one-pass mode).
+//   warps 2-9   two epilogue groups of four warps, taking alternate tiles:
+//               tcgen05.ld -> bias / activation -> shared-memory staging in the
+//               128-byte swizzle -> TMA tensor store (fully coalesced, clipped at the
+//               tensor edge by the hardware);
+//   warps 10-17 two operand-split groups for the 3-pass TF32 mode, taking alternate
+//               reduction chunks (idle in one-pass mode).
+// Each group's work item has a latency of about a microsecond (shared-memory round
+// trip plus a proxy fence); two groups per role keep that off the critical path.
 //
 // HBM traffic per tile is the algorithmic minimum: the activation tile is read
 // once, the output tile written once; filters come from L2.
 // All mbarrier waits are bounded and abort the block cleanly (status word set,
 // in-flight copies drained, tensor memory freed).
+#include <cstdlib>
+
 #include "tc_common.cuh"
 
 namespace ogle {
@@ -23,7 +29,7 @@ namespace {
 
 using namespace tc;
 
-constexpr int kThreads2 = 320;
+constexpr int kThreads2 = 576;
 constexpr int kMaxStages = 8;
 constexpr int kStagingBytes = kTileM * 128;   // one 128-row x 32-column fp32 slab
 
@@ -43,12 +49,20 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
     return false;
 }
 
-__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void group_sync(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
 
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
     asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
                  ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
+
+#ifdef OGLE_TC_TRACE
+// Debug build only: per-role clock stamps of block 0, [tile][slot].
+__device__ long long g_trace[64 * 16];
+#define TRACE(tile_iter, slot) do { if (blockIdx.x == 0 && (tile_iter) < 64) g_trace[(tile_iter) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define TRACE(tile_iter, slot) do {} while (0)
+#endif
 
 struct TileCoord { int n_tile, n0, h0, w0; };
 
@@ -78,7 +92,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     __shared__ __align__(8) uint64_t bar_acc_full[2], bar_acc_empty[2];
     __shared__ uint32_t tmem_slot;
     __shared__ int s_abort;
-    __shared__ float s_bias[256];
+    __shared__ __align__(16) float s_bias[2][256];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool split = a.passes == 3;
@@ -125,13 +139,16 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const uint32_t tx = (uint32_t)rows_in_tile * 128u + (split ? 2u : 1u) * b_bytes;
             long g = 0;          // chunks issued so far, over all tiles
             bool ok = true;
-            for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x) {
+            int pti = 0;
+            for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x, ++pti) {
                 const TileCoord tc_ = tile_coord(a, tile);
                 for (int it = 0; it < chunks; ++it, ++g) {
                     const int s = (int)(g % a.stages);
                     const long j = g / a.stages;
+                    if (it == 0) TRACE(pti, 0);
                     if (j > 0) ok = wait_or_abort(&bar_empty[s], (uint32_t)((j - 1) & 1), abort_flag);
                     if (!ok) { record_error(err_flag, 1); break; }
+                    if (it == 0) TRACE(pti, 1);
                     const int tap = it / a.chunks_per_tap;
                     const int c0 = (it - tap * a.chunks_per_tap) * kChunk;
                     const int ky = tap / a.kernel, kx = tap - ky * a.kernel;
@@ -166,8 +183,10 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 for (int it = 0; it < chunks; ++it, ++g) {
                     const int s = (int)(g % a.stages);
                     const uint32_t ph = (uint32_t)((g / a.stages) & 1);
+                    if (it == 0) TRACE(ti, 4);
                     ok = wait_or_abort(split ? &bar_xf[s] : &bar_full[s], ph, abort_flag);
                     if (!ok) { record_error(err_flag, 2); s_abort = 1; break; }
+                    if (it == 0) TRACE(ti, 5);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                     for (int k = 0; k < kChunk / 8; ++k) {
@@ -181,19 +200,23 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     umma_commit(&bar_empty[s]);
                 }
                 if (ok) umma_commit(&bar_acc_full[as]);
+                TRACE(ti, 6);
             }
         }
-    } else if (warp >= 6) {
+    } else if (warp >= 10) {
         // --------------------------------------------------- operand split (3-pass)
-        if (split) {
-            const int t = threadIdx.x - 192;   // 0..127
+        const int xg = (warp - 10) >> 2;           // group 0 or 1
+        if (split && xg < a.xf_groups) {
+            const int t = (threadIdx.x - 320) & 127;
             long g = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x) {
                 for (int it = 0; it < chunks; ++it, ++g) {
+                    if ((int)(g % a.xf_groups) != xg) continue;
                     const int s = (int)(g % a.stages);
                     ok = wait_or_abort(&bar_full[s], (uint32_t)((g / a.stages) & 1), abort_flag);
                     if (!ok) { record_error(err_flag, 3); s_abort = 1; break; }
+                    if (t == 0 && it == 0) TRACE((int)(g / chunks), 2);
                     float4* pa = reinterpret_cast<float4*>(base_ptr + (size_t)s * stage_bytes);
                     float4* pl = pa + kABytes / 16;
 #pragma unroll
@@ -209,92 +232,135 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     mbar_arrive(&bar_xf[s]);
+                    if (t == 0 && it == 0) TRACE((int)(g / chunks), 3);
                 }
             }
         }
     } else {
         // ------------------------------------------------------------------ epilogue
-        const int t = threadIdx.x - 64;               // 0..127
-        const int q = warp & 3;                       // TMEM lane quarter this warp may read
-        const int row = q * 32 + lane;
-        const int groups = a.BN / 32;
-        unsigned char* staging = base_ptr + staging_off;
-        uint32_t stores = 0;
-        bool ok = true;
-        int ti = 0;
-        for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x, ++ti) {
-            const TileCoord tc_ = tile_coord(a, tile);
-            const int as = ti & 1, use = ti >> 1;
-            const int nbase = tc_.n_tile * a.BN;
-            // per-column bias of this N tile (conv bias, or gemm's row-vector C)
-            if (a.bias_mode == 2)
-                for (int i = t; i < a.BN; i += 128) s_bias[i] = (nbase + i < a.K) ? bias[nbase + i] : 0.f;
-            long pix = 0;
-            if (a.bias_mode == 1) {
-                if (a.flat) pix = (long)tc_.w0 + row;
-                if (pix >= a.Wo) pix = a.Wo - 1;      // clipped rows are dropped by the store; keep reads in range
-            }
-            ok = wait_or_abort(&bar_acc_full[as], (uint32_t)(use & 1), abort_flag);
-            if (!ok) { record_error(err_flag, 4); s_abort = 1; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            for (int grp = 0; grp < groups; ++grp) {
-                const int col = grp * 32;
-                const bool last = (grp == groups - 1) || (nbase + col + 32 >= a.Kp);
-                const uint32_t buf = stores & 1u;
-                // the slab is free once the store issued two slabs ago has read it
-                if (t == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-                epi_sync();
-                uint32_t r[32];
-                const uint32_t taddr = tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * a.BN + col);
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                      "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                      "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                    : "r"(taddr));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (last) {
-                    // this thread's part of the accumulator is in registers: hand the buffer back
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    mbar_arrive(&bar_acc_empty[as]);
+        const int eg = (warp - 2) >> 2;               // group 0 or 1
+        if (eg < a.epi_groups) {
+            const int t = (threadIdx.x - 64) & 127;
+            const int q = warp & 3;                   // TMEM lane quarter this warp may read
+            const int row = q * 32 + lane;
+            const int bar_id = 1 + eg;
+            float* my_bias = s_bias[eg];
+            // each group owns one or two staging slabs and fills them in rounds
+            const uint32_t my_staging = staging_off + (uint32_t)(eg * a.epi_slabs) * (uint32_t)kStagingBytes;
+            unsigned char* staging = base_ptr + my_staging;
+            bool ok = true;
+            int ti = 0;
+            for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x, ++ti) {
+                if (ti % a.epi_groups != eg) continue;
+                const TileCoord tc_ = tile_coord(a, tile);
+                const int as = ti & 1, use = ti >> 1;
+                const int nbase = tc_.n_tile * a.BN;
+                int groups = (a.Kp - nbase + 31) / 32;
+                if (groups > a.BN / 32) groups = a.BN / 32;
+                long pix = 0;
+                if (a.bias_mode == 1) {
+                    pix = (long)tc_.w0 + row;
+                    if (pix >= a.Wo) pix = a.Wo - 1;  // clipped rows are dropped by the store; keep reads in range
                 }
-                float4* dst = reinterpret_cast<float4*>(staging + (size_t)buf * kStagingBytes + (size_t)row * 128);
-#pragma unroll
-                for (int c4 = 0; c4 < 8; ++c4) {
-                    float v[4];
-#pragma unroll
-                    for (int l = 0; l < 4; ++l) {
-                        const int n = nbase + col + c4 * 4 + l;
-                        float acc = a.alpha * __uint_as_float(r[c4 * 4 + l]);
-                        if (n < a.K) {
-                            if (a.bias_mode == 2) acc = fmaf(a.beta, s_bias[col + c4 * 4 + l], acc);
-                            else if (a.bias_mode == 1) acc = fmaf(a.beta, bias[pix * a.ldc + n], acc);
-                            acc = apply_act(acc, a.act, a.lo, a.hi);
-                        } else {
-                            acc = 0.f;                 // padded lanes stay zero
+                if (t == 0) TRACE(ti, 7);
+                ok = wait_or_abort(&bar_acc_full[as], (uint32_t)(use & 1), abort_flag);
+                if (!ok) { record_error(err_flag, 4); s_abort = 1; break; }
+                if (t == 0) TRACE(ti, 8);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                for (int g0 = 0; g0 < groups; g0 += a.epi_slabs) {
+                    const int nb = groups - g0 < a.epi_slabs ? groups - g0 : a.epi_slabs;
+                    // both slabs are free once the previous round's stores have read them
+                    if (t == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    if (g0 == 0)
+                        for (int i = t; i < a.BN; i += 128)
+                            my_bias[i] = (a.bias_mode == 2 && nbase + i < a.K) ? a.beta * bias[nbase + i] : 0.f;
+                    group_sync(bar_id);
+                    if (t == 0 && g0 == 0) TRACE(ti, 9);
+                    for (int b = 0; b < nb; ++b) {
+                        const int col = (g0 + b) * 32;
+                        uint32_t r[32];
+                        const uint32_t taddr = tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * a.BN + col);
+                        asm volatile(
+                            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                              "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                              "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                            : "r"(taddr));
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (t == 0 && g0 == 0 && b == 0) TRACE(ti, 14);
+                        if (g0 + b == groups - 1) {
+                            // this thread's part of the accumulator is in registers: hand the buffer back
+                            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                            mbar_arrive(&bar_acc_empty[as]);
                         }
-                        v[l] = acc;
+                        float4* dst = reinterpret_cast<float4*>(staging + (size_t)b * kStagingBytes + (size_t)row * 128);
+                        const bool fast = a.bias_mode != 1 && nbase + col + 32 <= a.K;
+                        if (fast) {
+                            // every column is a real channel and the bias is per column:
+                            // two instructions per value, bias read as 128-bit vectors
+                            const float4* bv = reinterpret_cast<const float4*>(my_bias + col);
+#pragma unroll
+                            for (int c4 = 0; c4 < 8; ++c4) {
+                                const float4 bb = bv[c4];
+                                float4 v;
+                                v.x = fmaf(a.alpha, __uint_as_float(r[c4 * 4 + 0]), bb.x);
+                                v.y = fmaf(a.alpha, __uint_as_float(r[c4 * 4 + 1]), bb.y);
+                                v.z = fmaf(a.alpha, __uint_as_float(r[c4 * 4 + 2]), bb.z);
+                                v.w = fmaf(a.alpha, __uint_as_float(r[c4 * 4 + 3]), bb.w);
+                                if (a.act == OGLE_ACT_RELU) {
+                                    v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f);
+                                } else if (a.act == OGLE_ACT_CLIP) {
+                                    v.x = fminf(fmaxf(v.x, a.lo), a.hi); v.y = fminf(fmaxf(v.y, a.lo), a.hi);
+                                    v.z = fminf(fmaxf(v.z, a.lo), a.hi); v.w = fminf(fmaxf(v.w, a.lo), a.hi);
+                                }
+                                // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
+                                dst[c4 ^ (row & 7)] = v;
+                            }
+                        } else {
+#pragma unroll
+                            for (int c4 = 0; c4 < 8; ++c4) {
+                                float v[4];
+#pragma unroll
+                                for (int l = 0; l < 4; ++l) {
+                                    const int n = nbase + col + c4 * 4 + l;
+                                    float acc = a.alpha * __uint_as_float(r[c4 * 4 + l]);
+                                    if (n < a.K) {
+                                        if (a.bias_mode == 2) acc += my_bias[col + c4 * 4 + l];
+                                        else if (a.bias_mode == 1) acc = fmaf(a.beta, bias[pix * a.ldc + n], acc);
+                                        acc = apply_act(acc, a.act, a.lo, a.hi);
+                                    } else {
+                                        acc = 0.f;         // padded lanes stay zero
+                                    }
+                                    v[l] = acc;
+                                }
+                                dst[c4 ^ (row & 7)] = make_float4(v[0], v[1], v[2], v[3]);
+                            }
+                        }
+                        if (t == 0 && g0 == 0 && b == 0) TRACE(ti, 15);
                     }
-                    // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
-                    dst[c4 ^ (row & 7)] = make_float4(v[0], v[1], v[2], v[3]);
+                    if (t == 0 && g0 == 0) TRACE(ti, 10);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    if (t == 0 && g0 == 0) TRACE(ti, 11);
+                    group_sync(bar_id);
+                    if (t == 0 && g0 == 0) TRACE(ti, 12);
+                    if (t == 0) {
+                        for (int b = 0; b < nb; ++b) {
+                            const uint32_t src = base + my_staging + (uint32_t)b * (uint32_t)kStagingBytes;
+                            const int col = nbase + (g0 + b) * 32;
+                            if (a.flat) tma_store_4d(&tmY, src, col, tc_.w0, 0, 0);
+                            else tma_store_4d(&tmY, src, col, tc_.w0, tc_.h0, tc_.n0);
+                        }
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        if (g0 + a.epi_slabs >= groups) TRACE(ti, 13);
+                    }
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                epi_sync();
-                if (t == 0) {
-                    const uint32_t src = base + staging_off + buf * (uint32_t)kStagingBytes;
-                    if (a.flat) tma_store_4d(&tmY, src, nbase + col, tc_.w0, 0, 0);
-                    else tma_store_4d(&tmY, src, nbase + col, tc_.w0, tc_.h0, tc_.n0);
-                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                }
-                ++stores;
-                if (last) break;
             }
+            // the staging slabs must outlive the stores that read them
+            if (t == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
         }
-        // the staging slabs must outlive the stores that read them
-        if (t == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
 
     // ------------------------------------------------------------------ teardown
@@ -320,13 +386,35 @@ int num_sms() {
 
 }  // namespace
 
+#ifdef OGLE_TC_TRACE
+extern "C" int ogle_debug_read_trace(long long* out) {
+    cudaDeviceSynchronize();
+    return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 64 * 16) == cudaSuccess ? 0 : -1;
+}
+#endif
+
 int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, const CUtensorMap& mBlo,
                  const CUtensorMap& mY, long m_tiles, const float* bias, int* err_flag, cudaStream_t s) {
     if (t.BN % 32 || t.BN > 256) return OGLE_ERR_UNSUPPORTED;
     const size_t stage = (size_t)(t.passes == 3 ? 2 : 1) * (kABytes + (size_t)t.BN * 128);
-    const size_t budget = 225 * 1024 - 2 * kStagingBytes - 1024;
+    // two epilogue groups (two staging slabs each) unless that would leave fewer
+    // than two operand stages
+    t.epi_groups = 2;
+    t.epi_slabs = 2;
+    if ((224 * 1024 - 4 * kStagingBytes - 1024) / stage < 2) t.epi_groups = 1;
+    if (t.epi_groups == 1 && (224 * 1024 - 2 * kStagingBytes - 1024) / stage < 2) t.epi_slabs = 1;
+    // One operand-split group keeps up with every layer measured so far. A second one
+    // (OGLE_TC_XF_GROUPS=2) takes alternate chunks; it needs an EVEN number of stages so
+    // that each group sees every phase of the stage barriers it waits on (a group that
+    // skipped a phase would mistake the older completion for the one it waits for).
+    t.xf_groups = 1;
+    if (const char* e = getenv("OGLE_TC_XF_GROUPS")) t.xf_groups = (t.passes == 3 && e[0] == '2') ? 2 : 1;
+    if (const char* e = getenv("OGLE_TC_EPI_GROUPS")) if (e[0] == '1') t.epi_groups = 1;
+    const size_t staging = (size_t)t.epi_groups * t.epi_slabs * kStagingBytes;
+    const size_t budget = 224 * 1024 - staging - 1024;
     int stages = (int)(budget / stage);
     if (stages > kMaxStages) stages = kMaxStages;
+    if (t.xf_groups == 2) stages &= ~1;
     if (stages < 2) return OGLE_ERR_UNSUPPORTED;
     t.stages = stages;
     int cols = 32;
@@ -335,12 +423,12 @@ int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, cons
     const long total = m_tiles * t.n_tiles;
     if (total <= 0 || total > 0x7fffffffL) return OGLE_ERR_UNSUPPORTED;
     t.total_tiles = (int)total;
-    const size_t smem = stage * stages + 2 * kStagingBytes + 1024;
+    const size_t smem = stage * stages + staging + 1024;
     static thread_local int attr_device = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (attr_device != dev) {
-        cudaError_t e = cudaFuncSetAttribute(conv_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(conv_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
         if (e != cudaSuccess) { set_last_error(e); return OGLE_ERR_CUDA; }
         attr_device = dev;
     }

@@ -31,6 +31,8 @@ struct TcArgs {
     int stages;
     int tmem_cols;
     int total_tiles;          // m_tiles * n_tiles (persistent kernel)
+    int epi_groups, xf_groups; // persistent kernel: warp groups per role (1 or 2)
+    int epi_slabs;            // staging slabs (128 rows x 32 columns) per epilogue group (1 or 2)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

@@ -9,6 +9,9 @@
 
 namespace ogle {
 
+bool dw_tma_supported(const ConvArgs& a);
+int launch_dw_tma(const ConvArgs& a, const float* x, const float* w, const float* bias, float* y, cudaStream_t s);
+
 // Bias holds exactly K floats; lanes past K read as zero.
 __device__ __forceinline__ float4 load_bias4(const float* bias, int c, int K, int has_bias) {
     float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -95,6 +98,7 @@ dw3x3_kernel(const float4* __restrict__ x, const float4* __restrict__ w, const f
             }
     }
 }
+
 
 // Any kernel size / dilation / stride, depthwise.
 __global__ void dw_generic_kernel(const float4* __restrict__ x, const float4* __restrict__ w,
@@ -312,7 +316,9 @@ int launch_conv_simt(const ConvArgs& a, int variant, const float* x, const float
         const float* b4 = bias;
         float4* y4 = reinterpret_cast<float4*>(y);
         const int C4 = a.Kp / 4;
-        if (a.kernel == 3 && a.dil == 1 && (a.stride == 1 || a.stride == 2)) {
+        if (dw_tma_supported(a)) {
+            return launch_dw_tma(a, x, w, bias, y, s);
+        } else if (a.kernel == 3 && a.dil == 1 && (a.stride == 1 || a.stride == 2)) {
             const long items = (long)a.N * ((a.Ho + 1) / 2) * ((a.Wo + 1) / 2) * C4;
             if (a.stride == 1) dw3x3_kernel<1><<<grid_for(items, 128, 16), 128, 0, s>>>(x4, w4, b4, y4, a);
             else dw3x3_kernel<2><<<grid_for(items, 128, 16), 128, 0, s>>>(x4, w4, b4, y4, a);

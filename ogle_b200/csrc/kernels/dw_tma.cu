@@ -1,0 +1,171 @@
+// Depthwise 3x3 convolution (stride 1 or 2, channel count a multiple of 32) as a
+// persistent, TMA-fed, HBM-bound kernel.
+//
+// One block per SM slot walks a list of tiles. A tile is TH x TW output pixels of
+// one image for a slab of 32 channels. Its input window, halo included, is ONE TMA
+// box [IH rows][IW cols][32 channels]; pixels outside the image arrive as zeros,
+// which is the convolution's padding. Two shared-memory stages: while the block
+// computes tile i from one stage, the TMA engine fills the other with tile i+1, so
+// the only HBM traffic is the input read once (halo rows come from L2) and the
+// output written once, both as 128-byte runs.
+// A thread owns 4 channels (one float4) of one output column and slides a 3-row
+// window down it; 8 lanes cover one pixel's 128 bytes, so shared-memory reads are
+// conflict-free.
+#include "tc_common.cuh"
+#include "tma_host.h"
+
+namespace ogle {
+namespace {
+
+using namespace tc;
+
+struct DwTiles {
+    int tiles_x, tiles_y, cblocks;   // tile grid per image, 32-channel slabs
+    long total;
+};
+
+template <int S, int TH, int TW>
+__global__ void __launch_bounds__(256)
+dw3x3_tma_kernel(const __grid_constant__ CUtensorMap tmX, const float4* __restrict__ w, const float* __restrict__ bias,
+                 float4* __restrict__ y, const ConvArgs a, const DwTiles tl, int* err_flag) {
+    constexpr int IH = (TH - 1) * S + 3, IW = (TW - 1) * S + 3;
+    constexpr int CB = 8;                          // float4s (32 channels) per tile
+    constexpr int COLS = 256 / CB;                 // pixel slots per block
+    constexpr int ROW_GROUPS = COLS / TW;
+    constexpr int RPG = TH / ROW_GROUPS;           // output rows per thread
+    constexpr int ROWS_IN = (RPG - 1) * S + 3;
+    constexpr uint32_t kTileBytes = IH * IW * CB * 16;
+    static_assert(COLS % TW == 0 && TH % ROW_GROUPS == 0, "tile shape");
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[2];
+
+    const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
+    const float4* stage0 = reinterpret_cast<const float4*>(smem_raw + (base - smem_u32(smem_raw)));
+
+    const int out_q = a.Ks >> 2, off_q = a.koff >> 2;
+    const int c = threadIdx.x % CB;
+    const int slot = threadIdx.x / CB;
+    const int col = slot % TW, rg = slot / TW;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&bar_full[0], 1);
+        mbar_init(&bar_full[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    // tile id -> (channel slab fastest, then x, y, image): neighbouring blocks share halo rows in L2
+    auto issue = [&](long tile, int stage) {
+        long t = tile;
+        const int cb = (int)(t % tl.cblocks); t /= tl.cblocks;
+        const int tx = (int)(t % tl.tiles_x); t /= tl.tiles_x;
+        const int ty = (int)(t % tl.tiles_y); t /= tl.tiles_y;
+        const int n = (int)t;
+        mbar_expect_tx(&bar_full[stage], kTileBytes);
+        tma_load_4d(base + (uint32_t)stage * kTileBytes, &tmX, &bar_full[stage], cb * 32, tx * TW * S - a.pad,
+                    ty * TH * S - a.pad, n);
+    };
+
+    if (threadIdx.x == 0 && (long)blockIdx.x < tl.total) issue(blockIdx.x, 0);
+    long it = 0;
+    for (long tile = blockIdx.x; tile < tl.total; tile += gridDim.x, ++it) {
+        const int stage = (int)(it & 1);
+        // the other stage was last read by tile it-1, which every thread finished
+        // before the __syncthreads at the bottom of the previous iteration
+        if (threadIdx.x == 0 && tile + gridDim.x < tl.total) issue(tile + gridDim.x, stage ^ 1);
+        long t = tile;
+        const int cb = (int)(t % tl.cblocks); t /= tl.cblocks;
+        const int tx = (int)(t % tl.tiles_x); t /= tl.tiles_x;
+        const int ty = (int)(t % tl.tiles_y); t /= tl.tiles_y;
+        const int n = (int)t;
+        const int cq = cb * CB + c;
+        float4 wk[9];
+#pragma unroll
+        for (int k = 0; k < 9; ++k) wk[k] = w[k * (a.Kp >> 2) + cq];
+        float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (a.has_bias) bv = make_float4(bias[cq * 4], bias[cq * 4 + 1], bias[cq * 4 + 2], bias[cq * 4 + 3]);
+
+        if (!mbar_wait(&bar_full[stage], (uint32_t)((it >> 1) & 1))) {
+            if (threadIdx.x == 0) record_error(err_flag, 6);
+            break;   // uniform: every thread waits on the same barrier with the same bound
+        }
+        const float4* tile_s = stage0 + (size_t)stage * (kTileBytes / 16);
+        float4 acc[RPG];
+#pragma unroll
+        for (int r = 0; r < RPG; ++r) acc[r] = bv;
+        const int row0 = rg * RPG * S;
+#pragma unroll
+        for (int r = 0; r < ROWS_IN; ++r) {
+            float4 v[3];
+#pragma unroll
+            for (int kx = 0; kx < 3; ++kx) v[kx] = tile_s[((row0 + r) * IW + col * S + kx) * CB + c];
+#pragma unroll
+            for (int o = 0; o < RPG; ++o) {
+                const int ky = r - o * S;
+                if (ky < 0 || ky > 2) continue;
+#pragma unroll
+                for (int kx = 0; kx < 3; ++kx) {
+                    const float4 f = wk[ky * 3 + kx];
+                    acc[o].x = fmaf(f.x, v[kx].x, acc[o].x);
+                    acc[o].y = fmaf(f.y, v[kx].y, acc[o].y);
+                    acc[o].z = fmaf(f.z, v[kx].z, acc[o].z);
+                    acc[o].w = fmaf(f.w, v[kx].w, acc[o].w);
+                }
+            }
+        }
+        const int ox = tx * TW + col;
+        if (ox < a.Wo) {
+#pragma unroll
+            for (int o = 0; o < RPG; ++o) {
+                const int oy = ty * TH + rg * RPG + o;
+                if (oy >= a.Ho) continue;
+                y[(((long)n * a.Ho + oy) * a.Wo + ox) * out_q + off_q + cq] = apply_act4(acc[o], a.act, a.lo, a.hi);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <int S, int TH, int TW>
+int launch(const ConvArgs& a, const float* x, const float* w, const float* bias, float* y, cudaStream_t s) {
+    constexpr int IH = (TH - 1) * S + 3, IW = (TW - 1) * S + 3;
+    CUtensorMap mX;
+    const cuuint64_t dims[4] = {(cuuint64_t)a.C, (cuuint64_t)a.W, (cuuint64_t)a.H, (cuuint64_t)a.N};
+    const cuuint64_t str[3] = {(cuuint64_t)a.Cs * 4, (cuuint64_t)a.Cs * 4 * a.W, (cuuint64_t)a.Cs * 4 * a.W * a.H};
+    const cuuint32_t box[4] = {32, IW, IH, 1};
+    const cuuint32_t es[4] = {1, 1, 1, 1};
+    if (!make_map_sw(CU_TENSOR_MAP_SWIZZLE_NONE, &mX, x, 4, dims, str, box, es)) return OGLE_ERR_CUDA;
+    DwTiles tl;
+    tl.tiles_x = (a.Wo + TW - 1) / TW;
+    tl.tiles_y = (a.Ho + TH - 1) / TH;
+    tl.cblocks = a.K / 32;
+    tl.total = (long)tl.tiles_x * tl.tiles_y * tl.cblocks * a.N;
+    const size_t smem = 2 * (size_t)IH * IW * 8 * 16 + 128;
+    static thread_local int attr_device = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_device != dev) {
+        cudaError_t e = cudaFuncSetAttribute(dw3x3_tma_kernel<S, TH, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { set_last_error(e); return OGLE_ERR_CUDA; }
+        attr_device = dev;
+    }
+    long blocks = (long)kNumSMs * 2;
+    if (blocks > tl.total) blocks = tl.total;
+    dw3x3_tma_kernel<S, TH, TW><<<(unsigned)blocks, 256, smem, s>>>(mX, reinterpret_cast<const float4*>(w), bias,
+                                                                   reinterpret_cast<float4*>(y), a, tl, error_flag_ptr());
+    return finish_launch();
+}
+
+}  // namespace
+
+bool dw_tma_supported(const ConvArgs& a) {
+    return a.kernel == 3 && a.dil == 1 && a.pad <= 1 && (a.stride == 1 || a.stride == 2) && a.K % 32 == 0 &&
+           a.C == a.K && a.Wo >= 16 && a.Ho >= 8 && encode_fn() != nullptr;
+}
+
+int launch_dw_tma(const ConvArgs& a, const float* x, const float* w, const float* bias, float* y, cudaStream_t s) {
+    if (a.stride == 1) return launch<1, 8, 32>(a, x, w, bias, y, s);
+    return launch<2, 4, 16>(a, x, w, bias, y, s);
+}
+
+}  // namespace ogle

@@ -161,6 +161,14 @@ int ogle_cuda_gemm_pack_b(const OgleGemmParams* p, const float* B, void* packed,
 int ogle_cuda_gemm_packed(const OgleGemmParams* p, const float* A, const void* packed_b, const float* C,
                           float* Y, ogle_stream_t stream);
 
+/* ogle_cuda_gemm for a B that is NOT a constant (both operands produced at run
+ * time): the tensor-core modes need B re-laid and split, so the caller lends
+ * `workspace` (device memory, >= ogle_cuda_gemm_packed_b_bytes(p), 16-byte aligned).
+ * The call packs B into it and multiplies, both on `stream`; the workspace may be
+ * reused as soon as the stream has passed this call. */
+int ogle_cuda_gemm_ws(const OgleGemmParams* p, const float* A, const float* B, const float* C, float* Y,
+                      void* workspace, size_t workspace_bytes, ogle_stream_t stream);
+
 /* ------------------------------------------------------------------ concat */
 /* ConcatKernel::Compute, nn/kernels/concat.cc:53-96 + concat_multi.glsl.
  * Shapes are 4-D (left-padded with 1s, as AmendShape does); last dimension of

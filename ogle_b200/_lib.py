@@ -75,6 +75,7 @@ CUDA_SYMBOLS = {
     "ogle_cuda_gemm_packed_b_bytes": (C.c_size_t, [C.POINTER(GemmParams)]),
     "ogle_cuda_gemm_pack_b": (C.c_int, [C.POINTER(GemmParams), _vp, _vp, _vp]),
     "ogle_cuda_gemm_packed": (C.c_int, [C.POINTER(GemmParams), _vp, _vp, _vp, _vp, _vp]),
+    "ogle_cuda_gemm_ws": (C.c_int, [C.POINTER(GemmParams), _vp, _vp, _vp, _vp, _vp, C.c_size_t, _vp]),
     "ogle_cuda_device_status": (C.c_int, []),
     "ogle_cuda_clear_device_status": (C.c_int, []),
     "ogle_cuda_device_status_detail": (C.c_int, []),

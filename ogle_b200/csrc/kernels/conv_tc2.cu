@@ -3,8 +3,10 @@
 // one block per SM walks a list of output tiles and every stage of the pipeline
 // overlaps with the others ACROSS tiles:
 //
-//   warp 0      TMA producer: keeps a ring of operand stages full, running ahead
-//               into the next tile while the current one is still being multiplied;
+//   warp 0, 18  TMA producers (activation tiles / filter tiles): keep a ring of operand
+//               stages full, running ahead into the next tile while the current one is
+//               still being multiplied; two issuing threads because one tensor copy
+//               costs its issuer over a hundred cycles;
 //   warp 1      MMA issuer: accumulates tile i into one half of tensor memory while
 //               the epilogue drains tile i-1 from the other half;
 //   warps 2-9   two epilogue groups of four warps, taking alternate tiles:
@@ -29,7 +31,7 @@ namespace {
 
 using namespace tc;
 
-constexpr int kThreads2 = 576;
+constexpr int kThreads2 = 608;
 constexpr int kMaxStages = 8;
 constexpr int kStagingBytes = kTileM * 128;   // one 128-row x 32-column fp32 slab
 
@@ -62,6 +64,14 @@ __device__ long long g_trace[64 * 16];
 #define TRACE(tile_iter, slot) do { if (blockIdx.x == 0 && (tile_iter) < 64) g_trace[(tile_iter) * 16 + (slot)] = clock64(); } while (0)
 #else
 #define TRACE(tile_iter, slot) do {} while (0)
+#endif
+#ifdef OGLE_TC_TRACE_CHUNKS
+// Debug build only: stamps per reduction chunk of block 0's first tile instead of per tile.
+#undef TRACE
+#define TRACE(tile_iter, slot) do {} while (0)
+#define TRACEC(chunk, slot) do { if (blockIdx.x == 0 && (chunk) < 64) g_trace[(chunk) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define TRACEC(chunk, slot) do {} while (0)
 #endif
 
 struct TileCoord { int n_tile, n0, h0, w0; };
@@ -113,7 +123,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
-            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_full[s], 2);     // one arrive.expect_tx from each producer
             mbar_init(&bar_xf[s], 128);
             mbar_init(&bar_empty[s], 1);
         }
@@ -136,34 +146,67 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            const uint32_t tx = (uint32_t)rows_in_tile * 128u + (split ? 2u : 1u) * b_bytes;
-            long g = 0;          // chunks issued so far, over all tiles
+            const uint32_t tx = (uint32_t)rows_in_tile * 128u;
+            // ring position kept incrementally (no divisions in this loop: one thread feeds
+            // the whole pipeline and every cycle here is on the critical path)
+            int s = 0;                 // stage of the next chunk
+            uint32_t wrap = 0;         // how many times the ring has wrapped
+            int issued = 0;            // chunks in flight bookkeeping for the abort path
             bool ok = true;
             int pti = 0;
             for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x, ++pti) {
                 const TileCoord tc_ = tile_coord(a, tile);
-                for (int it = 0; it < chunks; ++it, ++g) {
-                    const int s = (int)(g % a.stages);
-                    const long j = g / a.stages;
+                const int ax = a.flat ? tc_.w0 : tc_.w0 * a.stride - a.pad;
+                const int ay = a.flat ? 0 : tc_.h0 * a.stride - a.pad;
+                int ky = 0, kx = 0, c0 = 0;
+                for (int it = 0; it < chunks; ++it) {
                     if (it == 0) TRACE(pti, 0);
-                    if (j > 0) ok = wait_or_abort(&bar_empty[s], (uint32_t)((j - 1) & 1), abort_flag);
+                    if (wrap > 0) ok = wait_or_abort(&bar_empty[s], (wrap - 1) & 1u, abort_flag);
                     if (!ok) { record_error(err_flag, 1); break; }
                     if (it == 0) TRACE(pti, 1);
-                    const int tap = it / a.chunks_per_tap;
-                    const int c0 = (it - tap * a.chunks_per_tap) * kChunk;
-                    const int ky = tap / a.kernel, kx = tap - ky * a.kernel;
+                    TRACEC(pti * chunks + it, 0);
                     mbar_expect_tx(&bar_full[s], tx);
-                    if (a.flat) tma_load_4d(sA(s), &tmA, &bar_full[s], c0, tc_.w0, 0, 0);
-                    else tma_load_4d(sA(s), &tmA, &bar_full[s], c0, tc_.w0 * a.stride - a.pad + kx * a.dil,
-                                     tc_.h0 * a.stride - a.pad + ky * a.dil, tc_.n0);
-                    tma_load_2d(sBhi(s), &tmBhi, &bar_full[s], tap * a.Cp32 + c0, tc_.n_tile * a.BN);
-                    if (split) tma_load_2d(sBlo(s), &tmBlo, &bar_full[s], tap * a.Cp32 + c0, tc_.n_tile * a.BN);
+                    tma_load_4d(sA(s), &tmA, &bar_full[s], c0, ax + kx * a.dil, ay + ky * a.dil, tc_.n0);
+                    TRACEC(pti * chunks + it, 1);
+                    ++issued;
+                    if (++s == a.stages) { s = 0; ++wrap; }
+                    // next chunk: channels fastest, then filter column, then filter row
+                    c0 += kChunk;
+                    if (c0 == a.Cp32) { c0 = 0; if (++kx == a.kernel) { kx = 0; ++ky; } }
                 }
             }
             if (!ok) {
                 // let the copies already in flight land before the block retires
                 s_abort = 1;
-                for (long i = (g > a.stages ? g - a.stages : 0); i < g; ++i)
+                for (int i = (issued > a.stages ? issued - a.stages : 0); i < issued; ++i)
+                    mbar_wait(&bar_full[i % a.stages], (uint32_t)((i / a.stages) & 1));
+            }
+        }
+    } else if (warp == 18) {
+        // ------------------------------------------------ TMA producer, filter tiles
+        if (lane == 0) {
+            const uint32_t tx = (split ? 2u : 1u) * b_bytes;
+            int s = 0;
+            uint32_t wrap = 0;
+            int issued = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x) {
+                const int bcol = (tile % a.n_tiles) * a.BN;
+                int brow = 0;
+                for (int it = 0; it < chunks; ++it) {
+                    if (wrap > 0) ok = wait_or_abort(&bar_empty[s], (wrap - 1) & 1u, abort_flag);
+                    if (!ok) { record_error(err_flag, 7); break; }
+                    mbar_expect_tx(&bar_full[s], tx);
+                    tma_load_2d(sBhi(s), &tmBhi, &bar_full[s], brow, bcol);
+                    if (split) tma_load_2d(sBlo(s), &tmBlo, &bar_full[s], brow, bcol);
+                    ++issued;
+                    if (++s == a.stages) { s = 0; ++wrap; }
+                    brow += kChunk;       // packed filter rows follow the chunk order
+                }
+            }
+            if (!ok) {
+                s_abort = 1;
+                for (int i = (issued > a.stages ? issued - a.stages : 0); i < issued; ++i)
                     mbar_wait(&bar_full[i % a.stages], (uint32_t)((i / a.stages) & 1));
             }
         }
@@ -171,7 +214,8 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // -------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(a.BN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
-            long g = 0;
+            int s = 0;
+            uint32_t ph = 0;           // parity of the ring pass
             bool ok = true;
             int ti = 0;
             for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x, ++ti) {
@@ -180,24 +224,19 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if (!ok) { record_error(err_flag, 5); s_abort = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d = tmem_d + (uint32_t)(as * a.BN);
-                for (int it = 0; it < chunks; ++it, ++g) {
-                    const int s = (int)(g % a.stages);
-                    const uint32_t ph = (uint32_t)((g / a.stages) & 1);
+                for (int it = 0; it < chunks; ++it) {
                     if (it == 0) TRACE(ti, 4);
                     ok = wait_or_abort(split ? &bar_xf[s] : &bar_full[s], ph, abort_flag);
                     if (!ok) { record_error(err_flag, 2); s_abort = 1; break; }
                     if (it == 0) TRACE(ti, 5);
+                    TRACEC(ti * chunks + it, 2);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-                    for (int k = 0; k < kChunk / 8; ++k) {
-                        const uint64_t ad = umma_desc(sA(s) + k * 32), bd = umma_desc(sBhi(s) + k * 32);
-                        umma_tf32(d, ad, bd, idesc, (it > 0 || k > 0) ? 1u : 0u);
-                        if (split) {
-                            umma_tf32(d, umma_desc(sAlo(s) + k * 32), bd, idesc, 1u);
-                            umma_tf32(d, ad, umma_desc(sBlo(s) + k * 32), idesc, 1u);
-                        }
-                    }
+                    const uint64_t ad = umma_desc(sA(s)), bd = umma_desc(sBhi(s));
+                    if (split) umma_tf32_chunk_split(d, ad, ad + (kABytes >> 4), bd, bd + (b_bytes >> 4), idesc, it > 0 ? 1u : 0u);
+                    else umma_tf32_chunk(d, ad, bd, idesc, it > 0 ? 1u : 0u);
                     umma_commit(&bar_empty[s]);
+                    TRACEC(ti * chunks + it, 3);
+                    if (++s == a.stages) { s = 0; ph ^= 1u; }
                 }
                 if (ok) umma_commit(&bar_acc_full[as]);
                 TRACE(ti, 6);
@@ -208,16 +247,23 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int xg = (warp - 10) >> 2;           // group 0 or 1
         if (split && xg < a.xf_groups) {
             const int t = (threadIdx.x - 320) & 127;
-            long g = 0;
+            int s = 0, turn = 0;       // ring stage; whose turn (group) the next chunk is
+            uint32_t ph = 0;
+            int xti = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x) {
-                for (int it = 0; it < chunks; ++it, ++g) {
-                    if ((int)(g % a.xf_groups) != xg) continue;
-                    const int s = (int)(g % a.stages);
-                    ok = wait_or_abort(&bar_full[s], (uint32_t)((g / a.stages) & 1), abort_flag);
+            for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x, ++xti) {
+                for (int it = 0; it < chunks; ++it) {
+                    const int cur = s;
+                    const uint32_t cur_ph = ph;
+                    const bool mine = turn == xg;
+                    if (++s == a.stages) { s = 0; ph ^= 1u; }
+                    if (++turn == a.xf_groups) turn = 0;
+                    if (!mine) continue;
+                    ok = wait_or_abort(&bar_full[cur], cur_ph, abort_flag);
                     if (!ok) { record_error(err_flag, 3); s_abort = 1; break; }
-                    if (t == 0 && it == 0) TRACE((int)(g / chunks), 2);
-                    float4* pa = reinterpret_cast<float4*>(base_ptr + (size_t)s * stage_bytes);
+                    if (t == 0 && it == 0) TRACE(xti, 2);
+                    const int s_ = cur;
+                    float4* pa = reinterpret_cast<float4*>(base_ptr + (size_t)s_ * stage_bytes);
                     float4* pl = pa + kABytes / 16;
 #pragma unroll
                     for (int i = 0; i < kABytes / 16 / 128; ++i) {
@@ -231,8 +277,8 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         pl[t + i * 128] = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    mbar_arrive(&bar_xf[s]);
-                    if (t == 0 && it == 0) TRACE((int)(g / chunks), 3);
+                    mbar_arrive(&bar_xf[s_]);
+                    if (t == 0 && it == 0) TRACE(xti, 3);
                 }
             }
         }
@@ -403,11 +449,18 @@ int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, cons
     t.epi_slabs = 2;
     if ((224 * 1024 - 4 * kStagingBytes - 1024) / stage < 2) t.epi_groups = 1;
     if (t.epi_groups == 1 && (224 * 1024 - 2 * kStagingBytes - 1024) / stage < 2) t.epi_slabs = 1;
-    // One operand-split group keeps up with every layer measured so far. A second one
-    // (OGLE_TC_XF_GROUPS=2) takes alternate chunks; it needs an EVEN number of stages so
-    // that each group sees every phase of the stage barriers it waits on (a group that
-    // skipped a phase would mistake the older completion for the one it waits for).
+    // One operand-split group keeps up with the short reductions (pointwise layers). With
+    // two, the groups take alternate chunks; that needs an EVEN number of stages so that
+    // each group sees every phase of the stage barriers it waits on (a group that skipped
+    // a phase would mistake the older completion for the one it waits for).
     t.xf_groups = 1;
+    const int chunks = t.kernel * t.kernel * t.chunks_per_tap;
+    if (t.passes == 3 && chunks >= 8) {
+        // long reductions: the operand split is the critical role, the epilogue is not
+        t.xf_groups = 2;
+        t.epi_groups = 1;
+        t.epi_slabs = 1;
+    }
     if (const char* e = getenv("OGLE_TC_XF_GROUPS")) t.xf_groups = (t.passes == 3 && e[0] == '2') ? 2 : 1;
     if (const char* e = getenv("OGLE_TC_EPI_GROUPS")) if (e[0] == '1') t.epi_groups = 1;
     const size_t staging = (size_t)t.epi_groups * t.epi_slabs * kStagingBytes;

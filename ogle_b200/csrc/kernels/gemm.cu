@@ -199,6 +199,18 @@ extern "C" int ogle_cuda_gemm_packed(const OgleGemmParams* pp, const float* A, c
     return launch_gemm_tc_packed(p, A, hi, lo, C, Y, (cudaStream_t)stream);
 }
 
+extern "C" int ogle_cuda_gemm_ws(const OgleGemmParams* pp, const float* A, const float* B, const float* C, float* Y,
+                                 void* workspace, size_t workspace_bytes, ogle_stream_t stream) {
+    if (!pp) return OGLE_ERR_INVALID;
+    if (pp->math_mode == OGLE_MATH_FP32) return ogle_cuda_gemm(pp, A, B, C, Y, stream);
+    const size_t need = ogle_cuda_gemm_packed_b_bytes(pp);
+    if (need == 0) return OGLE_ERR_INVALID;
+    if (!workspace || workspace_bytes < need) return OGLE_ERR_INVALID;
+    int rc = ogle_cuda_gemm_pack_b(pp, B, workspace, stream);
+    if (rc != OGLE_OK) return rc;
+    return ogle_cuda_gemm_packed(pp, A, workspace, C, Y, stream);
+}
+
 extern "C" int ogle_cuda_gemm(const OgleGemmParams* pp, const float* A, const float* B, const float* C,
                               float* Y, ogle_stream_t stream) {
     if (!pp || !A || !B || !Y) return OGLE_ERR_INVALID;

@@ -90,6 +90,52 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint6
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// One reduction chunk (32 elements = four K=8 steps) issued from a single asm block.
+// A lone thread issues every MMA of the block, and a warp can only issue an instruction
+// every few cycles, so descriptor arithmetic per MMA is kept to one 64-bit add.
+// Descriptors advance by 32 bytes (2 in encoded units) per K step inside the swizzle atom.
+__device__ __forceinline__ void umma_tf32_chunk(uint32_t tmem_d, uint64_t ad, uint64_t bd, uint32_t idesc,
+                                                uint32_t accumulate_first) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "setp.eq.b32 q, 0, 0;\n\t"
+        "add.s64 a1, %1, 2;\n\tadd.s64 b1, %2, 2;\n\t"
+        "add.s64 a2, %1, 4;\n\tadd.s64 b2, %2, 4;\n\t"
+        "add.s64 a3, %1, 6;\n\tadd.s64 b3, %2, 6;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a1, b1, %3, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a2, b2, %3, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a3, b3, %3, q;\n\t}"
+        ::"r"(tmem_d), "l"(ad), "l"(bd), "r"(idesc), "r"(accumulate_first) : "memory");
+}
+
+// The same chunk in the 3-pass split mode: hi*hi + lo*hi + hi*lo for each K step.
+// al / bl are the descriptors of the lo halves of the same stage.
+__device__ __forceinline__ void umma_tf32_chunk_split(uint32_t tmem_d, uint64_t ad, uint64_t al, uint64_t bd, uint64_t bl,
+                                                      uint32_t idesc, uint32_t accumulate_first) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 a, l, b, m;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "setp.eq.b32 q, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %3, %5, p;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %2, %3, %5, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %4, %5, q;\n\t"
+        "add.s64 a, %1, 2;\n\tadd.s64 l, %2, 2;\n\tadd.s64 b, %3, 2;\n\tadd.s64 m, %4, 2;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a, b, %5, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], l, b, %5, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a, m, %5, q;\n\t"
+        "add.s64 a, %1, 4;\n\tadd.s64 l, %2, 4;\n\tadd.s64 b, %3, 4;\n\tadd.s64 m, %4, 4;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a, b, %5, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], l, b, %5, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a, m, %5, q;\n\t"
+        "add.s64 a, %1, 6;\n\tadd.s64 l, %2, 6;\n\tadd.s64 b, %3, 6;\n\tadd.s64 m, %4, 6;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a, b, %5, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], l, b, %5, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a, m, %5, q;\n\t}"
+        ::"r"(tmem_d), "l"(ad), "l"(al), "l"(bd), "l"(bl), "r"(idesc), "r"(accumulate_first) : "memory");
+}
+
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }

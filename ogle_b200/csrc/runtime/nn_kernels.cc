@@ -345,10 +345,31 @@ public:
             }
         }
     }
+    void InferOutputShape(const TensorList& inputs, TensorShapeList& output_shapes) override {
+        Kernel::InferOutputShape(inputs, output_shapes);
+        // constant weights are re-laid once for the tensor-core modes, as conv filters are
+        packed_ready_ = false;
+        if (params_.math_mode != OGLE_MATH_FP32 && session_ && session_->IsTensorReady(input_tensor_indexes_[1]) &&
+            params_.K >= 64) {
+            const size_t bytes = ogle_cuda_gemm_packed_b_bytes(&params_);
+            OGLE_CHECK_GT(bytes, 0u);
+            if (packed_) cudaFree(packed_);
+            cudaError_t e = cudaMalloc(&packed_, bytes);
+            OGLE_CHECK(e == cudaSuccess) << "cudaMalloc(" << bytes << "): " << cudaGetErrorString(e);
+            OGLE_CUDA_OK(ogle_cuda_gemm_pack_b(&params_, inputs[1]->device<float>(), packed_, context_->stream()));
+            packed_ready_ = true;
+        }
+    }
+    ~GemmKernel() override { if (packed_) cudaFree(packed_); }
     void Compute(TensorList& in, TensorList& out) override {
         OGLE_CHECK_EQ(in[0]->dformat(), TP::ANY4);
         OGLE_CHECK_EQ(in[1]->dformat(), TP::ANY4);
         const float* c = in.size() > 2 ? in[2]->device<float>() : nullptr;
+        if (packed_ready_) {
+            OGLE_CUDA_OK(ogle_cuda_gemm_packed(&params_, in[0]->device<float>(), packed_, c, out[0]->device<float>(),
+                                               context_->stream()));
+            return;
+        }
         OGLE_CUDA_OK(ogle_cuda_gemm(&params_, in[0]->device<float>(), in[1]->device<float>(), c, out[0]->device<float>(),
                                     context_->stream()));
     }
@@ -356,6 +377,8 @@ private:
     float alpha_ = 1.f, beta_ = 1.f;
     int transB_ = 0;
     OgleGemmParams params_;
+    void* packed_ = nullptr;
+    bool packed_ready_ = false;
 };
 REGISTER_KERNEL_WITH_NAME(GemmKernel, "Gemm");
 

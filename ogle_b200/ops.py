@@ -156,6 +156,51 @@ def gemm(A4, B4, C4, M, K, N, transB=0, alpha=1.0, beta=1.0, bias_mode=0, math_m
     return out
 
 
+def _gemm_params(A4, B4, C4, M, K, N, transB, alpha, beta, bias_mode, math_mode):
+    p = GemmParams()
+    p.M, p.K, p.N, p.transB, p.alpha, p.beta, p.bias_mode = M, K, N, transB, alpha, beta, bias_mode
+    p.lda, p.ldb = A4.shape[-1], B4.shape[-1]
+    p.ldc = C4.shape[-1] if (C4 is not None and bias_mode == 1) else 0
+    p.ldy = up4(N)
+    p.math_mode = math_mode
+    return p
+
+
+def gemm_pack_b(B4, M, K, N, transB=0, math_mode=MATH_TF32X3):
+    """Packs a constant B once for the tensor-core modes; returns the opaque device blob."""
+    _require_cuda(B4)
+    p = _gemm_params(B4, B4, None, M, K, N, transB, 1.0, 1.0, 0, math_mode)
+    p.lda = up4(K)
+    lib = _lib.cuda_lib()
+    nbytes = lib.ogle_cuda_gemm_packed_b_bytes(C.byref(p))
+    packed = torch.empty(nbytes // 4, dtype=torch.float32, device="cuda")
+    check(lib.ogle_cuda_gemm_pack_b(C.byref(p), _p(B4), _p(packed), _stream()), "gemm_pack_b")
+    return packed
+
+
+def gemm_packed(A4, packed_b, C4, M, K, N, transB=0, alpha=1.0, beta=1.0, bias_mode=0, math_mode=MATH_TF32X3):
+    _require_cuda(A4, packed_b, C4)
+    p = _gemm_params(A4, A4, C4, M, K, N, transB, alpha, beta, bias_mode, math_mode)
+    p.ldb = 0
+    out = torch.empty((M, up4(N)), dtype=torch.float32, device="cuda")
+    check(_lib.cuda_lib().ogle_cuda_gemm_packed(C.byref(p), _p(A4), _p(packed_b), _p(C4), _p(out), _stream()), "gemm_packed")
+    return out
+
+
+def gemm_ws(A4, B4, C4, M, K, N, transB=0, alpha=1.0, beta=1.0, bias_mode=0, math_mode=MATH_TF32X3, workspace=None):
+    """gemm with a run-time B: the caller lends the packing workspace."""
+    _require_cuda(A4, B4, C4)
+    p = _gemm_params(A4, B4, C4, M, K, N, transB, alpha, beta, bias_mode, math_mode)
+    lib = _lib.cuda_lib()
+    need = lib.ogle_cuda_gemm_packed_b_bytes(C.byref(p))
+    if workspace is None:
+        workspace = torch.empty(need // 4, dtype=torch.float32, device="cuda")
+    out = torch.empty((M, up4(N)), dtype=torch.float32, device="cuda")
+    check(lib.ogle_cuda_gemm_ws(C.byref(p), _p(A4), _p(B4), _p(C4), _p(out), _p(workspace), workspace.numel() * 4,
+                                _stream()), "gemm_ws")
+    return out
+
+
 def concat(xs4, shapes, axis):
     """xs4: padded device tensors; shapes: their logical shapes (rank <= 4); axis in that rank."""
     rank = len(shapes[0])

@@ -120,6 +120,28 @@ def test_gemm_reference_shapes(oracle_port):
     close(got, oracle_port.gemm(A, B, Cm, 1), atol=1e-4, rtol=1e-4)
 
 
+def test_gemm_tensor_core_packed_and_workspace(oracle_port):
+    """Tensor-core gemm: constant B packed once, or a run-time B packed into a lent workspace.
+    3xTF32 meets the fp32 bound; one-pass TF32 the looser 2e-3 (10-bit operands, normalised)."""
+    from ogle_b200 import ops
+    rng = np.random.default_rng(23)
+    for (M, K, N, tb) in [(200, 512, 1000, 1), (130, 300, 70, 0), (4, 96, 33, 1), (512, 1024, 512, 0)]:
+        A = rng.standard_normal((M, K), dtype=np.float32)
+        B = (rng.standard_normal((N, K) if tb else (K, N), dtype=np.float32) * 0.05).astype(np.float32)
+        Cm = rng.standard_normal(N, dtype=np.float32)
+        ref = oracle_port.gemm(A, B, Cm, tb, 0.5, 2.0)
+        scale = np.abs(ref).max()
+        A4, B4, C4 = ops.upload(A), ops.upload(B), ops.upload(Cm)
+        for mode, bound in ((ops.MATH_TF32X3, 2e-5), (ops.MATH_TF32, 2e-3)):
+            packed = ops.gemm_pack_b(B4, M, K, N, tb, mode)
+            got = ops.download(ops.gemm_packed(A4, packed, C4, M, K, N, tb, 0.5, 2.0, 2, mode), N)
+            assert np.abs(got - ref).max() / scale <= bound, (M, K, N, tb, mode)
+            got = ops.download(ops.gemm_ws(A4, B4, C4, M, K, N, tb, 0.5, 2.0, 2, mode), N)
+            assert np.abs(got - ref).max() / scale <= bound, (M, K, N, tb, mode)
+    from ogle_b200 import _lib
+    assert _lib.cuda_lib().ogle_cuda_device_status() == 0
+
+
 def test_pool_shapes(oracle_port):
     from gpu_ops import run_case_cuda
     rng = np.random.default_rng(15)

@@ -224,11 +224,12 @@ int ogle_detector_wait(OgleDetector* d, float* score, int* anchor, int* cls, flo
     if (!d) return -1;
     return guarded([&] {
         const ogle::DetectionBatch& r = d->detector->Wait();
-        if (score) std::memcpy(score, r.score.data(), r.score.size() * 4);
-        if (anchor) std::memcpy(anchor, r.anchor.data(), r.anchor.size() * 4);
-        if (cls) std::memcpy(cls, r.cls.data(), r.cls.size() * 4);
-        if (box) std::memcpy(box, r.box.data(), r.box.size() * 4);
-        if (count) std::memcpy(count, r.count.data(), r.count.size() * 4);
+        const size_t n = size_t(r.images) * r.rows;
+        if (score) std::memcpy(score, r.score, n * 4);
+        if (anchor) std::memcpy(anchor, r.anchor, n * 4);
+        if (cls) std::memcpy(cls, r.cls, n * 4);
+        if (box) std::memcpy(box, r.box, n * 16);
+        if (count) std::memcpy(count, r.count, size_t(r.images) * r.counts_per_image * 4);
     });
 }
 

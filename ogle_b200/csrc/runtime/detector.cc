@@ -11,27 +11,56 @@ namespace ogle {
         if (e_ != cudaSuccess) OGLE_FATAL() << #call << ": " << cudaGetErrorString(e_); \
     } while (0)
 
+static cudaStream_t S(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+static cudaEvent_t E(void* e) { return reinterpret_cast<cudaEvent_t>(e); }
+
 Detector::Detector(const DetectorOptions& options, Context* context) : options_(options), context_(context) {
     OGLE_CHECK_EQ(options_.output_names.size(), 3u);
     OGLE_CHECK_EQ(options_.input_names.size(), 1u);
+    context_->MakeCurrent();
     session_.reset(new FBOSession(context_));
     session_->LoadGraph(options_.model_name);
+    cudaStream_t a, b;
+    OGLE_RT_CUDA(cudaStreamCreateWithFlags(&a, cudaStreamNonBlocking));
+    OGLE_RT_CUDA(cudaStreamCreateWithFlags(&b, cudaStreamNonBlocking));
+    copy_in_ = a;
+    copy_out_ = b;
+    for (Slot& s : slots_) {
+        cudaEvent_t e[4];
+        for (auto& x : e) OGLE_RT_CUDA(cudaEventCreateWithFlags(&x, cudaEventDisableTiming));
+        s.ev_h2d = e[0]; s.ev_pad = e[1]; s.ev_done = e[2]; s.ev_d2h = e[3];
+    }
+}
+
+void Detector::Release() {
+    if (boxes_) cudaFree(boxes_);
+    boxes_ = nullptr;
+    for (Slot& s : slots_) {
+        if (s.stage) cudaFree(s.stage);
+        if (s.out_dev) cudaFree(s.out_dev);
+        if (s.out_host) cudaFreeHost(s.out_host);
+        s.stage = nullptr; s.out_dev = nullptr; s.out_host = nullptr;
+    }
 }
 
 Detector::~Detector() {
     context_->MakeCurrent();
-    if (boxes_) cudaFree(boxes_);
-    if (out_dev_) cudaFree(out_dev_);
-    if (out_host_) cudaFreeHost(out_host_);
+    cudaDeviceSynchronize();
+    Release();
+    for (Slot& s : slots_) {
+        cudaEventDestroy(E(s.ev_h2d)); cudaEventDestroy(E(s.ev_pad));
+        cudaEventDestroy(E(s.ev_done)); cudaEventDestroy(E(s.ev_d2h));
+    }
+    cudaStreamDestroy(S(copy_in_));
+    cudaStreamDestroy(S(copy_out_));
 }
 
-void Detector::AllocateOutputs(int N) {
-    if (N == batch_) return;
-    context_->Synchronize();
-    if (boxes_) cudaFree(boxes_);
-    if (out_dev_) cudaFree(out_dev_);
-    if (out_host_) cudaFreeHost(out_host_);
-    boxes_ = nullptr; out_dev_ = nullptr; out_host_ = nullptr;
+void Detector::Allocate(int N, int H, int W) {
+    const size_t stage_bytes = size_t(N) * H * W * 3 * sizeof(float);
+    if (N == batch_ && stage_bytes == stage_bytes_) return;
+    OGLE_CHECK(pending_.empty()) << "the batch shape may only change with no call in flight";
+    OGLE_RT_CUDA(cudaDeviceSynchronize());
+    Release();
     rows_ = options_.mode == 0 ? options_.topk : (num_classes_ - 1) * options_.topk;
     counts_per_image_ = options_.mode == 0 ? 1 : num_classes_ - 1;
     const size_t n = size_t(N) * rows_;
@@ -41,41 +70,85 @@ void Detector::AllocateOutputs(int N) {
     off_count_ = off_box_ + n * 16;
     out_bytes_ = off_count_ + size_t(N) * counts_per_image_ * 4;
     OGLE_RT_CUDA(cudaMalloc(&boxes_, size_t(N) * num_anchors_ * 16));
-    OGLE_RT_CUDA(cudaMalloc(&out_dev_, out_bytes_));
-    OGLE_RT_CUDA(cudaMallocHost(&out_host_, out_bytes_));
+    for (Slot& s : slots_) {
+        OGLE_RT_CUDA(cudaMalloc(&s.stage, stage_bytes));
+        OGLE_RT_CUDA(cudaMalloc(&s.out_dev, out_bytes_));
+        OGLE_RT_CUDA(cudaMallocHost(&s.out_host, out_bytes_));
+    }
     batch_ = N;
+    stage_bytes_ = stage_bytes;
 }
 
 void Detector::DetectAsync(const float* images_nhwc, int N, int H, int W) {
     context_->MakeCurrent();
-    Tensor input(Tensor::DT_FLOAT, IntList{N, H, W, 3}, const_cast<float*>(images_nhwc), dlxnet::TensorProto::NHWC);
-    session_->Run({{options_.input_names[0], &input}});          // detector.cc:235-240
-    h2d_bytes_ = input.num_elements() * sizeof(float);
-    PostProcess(N, H, W, true);
+    OGLE_CHECK_LT(int(pending_.size()), kDepth) << "retire a call with Wait() before issuing another";
+    cudaStream_t compute = S(context_->stream());
+    Tensor* in = nullptr;
+    if (batch_ == 0 || !session_->FindTensorByName(options_.input_names[0])) {
+        // first call: let the session see the input once so that it sizes every tensor
+        // (FBOSession::Setup, fbo_session.cc:168-252); detector.cc:235-240
+        Tensor input(Tensor::DT_FLOAT, IntList{N, H, W, 3}, const_cast<float*>(images_nhwc), dlxnet::TensorProto::NHWC);
+        session_->Setup({{options_.input_names[0], &input}});
+        context_->Synchronize();
+        Tensor* cls_logits = session_->FindTensorByName(options_.output_names[0]);
+        Tensor* box_preds = session_->FindTensorByName(options_.output_names[1]);
+        OGLE_CHECK(cls_logits && box_preds);
+        OGLE_CHECK_EQ(cls_logits->shape().size(), 3u);   // detector.cc:152-155
+        OGLE_CHECK_EQ(box_preds->shape().size(), 3u);
+        num_anchors_ = box_preds->shape()[1];
+        num_classes_ = cls_logits->shape()[2];
+        OGLE_CHECK_EQ(cls_logits->shape()[1], num_anchors_);
+    }
+    in = session_->FindTensorByName(options_.input_names[0]);
+    OGLE_CHECK(in->shape() == (IntList{N, H, W, 3})) << "input shape differs from the one the session was sized for";
+    Allocate(N, H, W);
+    Slot& slot = slots_[next_slot_];
+    // upload on the copy stream, once the compute stream has consumed this slot's last upload
+    OGLE_RT_CUDA(cudaStreamWaitEvent(S(copy_in_), E(slot.ev_pad), 0));
+    OGLE_RT_CUDA(cudaMemcpyAsync(slot.stage, images_nhwc, stage_bytes_, cudaMemcpyHostToDevice, S(copy_in_)));
+    OGLE_RT_CUDA(cudaEventRecord(E(slot.ev_h2d), S(copy_in_)));
+    h2d_bytes_ = stage_bytes_;
+    // pad to NHWC4 into the session's input tensor (Context::CopyCPUTensorToDevice's second half)
+    OGLE_RT_CUDA(cudaStreamWaitEvent(compute, E(slot.ev_h2d), 0));
+    OGLE_CUDA_OK(ogle_cuda_pad4(slot.stage, in->device<float>(), long(N) * H * W, 3, 0, context_->stream()));
+    OGLE_RT_CUDA(cudaEventRecord(E(slot.ev_pad), compute));
+    session_->RunDevice({});
+    PostProcess(slot, N, H, W);
+    // copy the detections back on their own stream
+    OGLE_RT_CUDA(cudaStreamWaitEvent(S(copy_out_), E(slot.ev_done), 0));
+    OGLE_RT_CUDA(cudaMemcpyAsync(slot.out_host, slot.out_dev, out_bytes_, cudaMemcpyDeviceToHost, S(copy_out_)));
+    OGLE_RT_CUDA(cudaEventRecord(E(slot.ev_d2h), S(copy_out_)));
+    d2h_bytes_ = out_bytes_;
+    pending_.push_back(next_slot_);
+    next_slot_ = (next_slot_ + 1) % kDepth;
 }
 
 void Detector::DetectDeviceAsync(const float* images_nhwc4_device, int N, int H, int W, bool copy_back) {
     context_->MakeCurrent();
+    OGLE_CHECK(pending_.empty()) << "DetectDeviceAsync is not pipelined: retire the calls in flight first";
     Tensor* in = session_->FindTensorByName(options_.input_names[0]);
-    OGLE_CHECK(in != nullptr) << "run DetectAsync once before DetectDeviceAsync (it sizes the session)";
+    OGLE_CHECK(in != nullptr && batch_ == N) << "run DetectAsync once before DetectDeviceAsync (it sizes the session)";
     OGLE_CHECK(in->shape() == (IntList{N, H, W, 3})) << "device input does not match the session's input shape";
     session_->RunDevice({{options_.input_names[0], images_nhwc4_device}});
     h2d_bytes_ = 0;
-    PostProcess(N, H, W, copy_back);
+    Slot& slot = slots_[next_slot_];
+    PostProcess(slot, N, H, W);
+    d2h_bytes_ = 0;
+    if (!copy_back) return;    // stream-ordered on the compute stream; nothing for Wait() to retire
+    OGLE_RT_CUDA(cudaMemcpyAsync(slot.out_host, slot.out_dev, out_bytes_, cudaMemcpyDeviceToHost, S(context_->stream())));
+    d2h_bytes_ = out_bytes_;
+    OGLE_RT_CUDA(cudaEventRecord(E(slot.ev_d2h), S(context_->stream())));
+    pending_.push_back(next_slot_);
+    next_slot_ = (next_slot_ + 1) % kDepth;
 }
 
-void Detector::PostProcess(int N, int H, int W, bool copy_back) {
+void Detector::PostProcess(Slot& slot, int N, int H, int W) {
+    cudaStream_t compute = S(context_->stream());
     Tensor* cls_logits = session_->FindTensorByName(options_.output_names[0]);
     Tensor* box_preds = session_->FindTensorByName(options_.output_names[1]);
     Tensor* anchors = session_->FindTensorByName(options_.output_names[2]);
     OGLE_CHECK(cls_logits && box_preds && anchors);
-    OGLE_CHECK_EQ(cls_logits->shape().size(), 3u);   // detector.cc:152-155
-    OGLE_CHECK_EQ(box_preds->shape().size(), 3u);
-    num_anchors_ = box_preds->shape()[1];
-    num_classes_ = cls_logits->shape()[2];
-    OGLE_CHECK_EQ(cls_logits->shape()[1], num_anchors_);
     OGLE_CHECK_EQ(cls_logits->shape()[0], N);
-    AllocateOutputs(N);
     // detector.cc:242-258: GPU box decode into a cached tensor
     Tensor decoded(IntList{N, num_anchors_, 4}, dlxnet::TensorProto::ANY4, boxes_);
     Tensor anchors2d(IntList{num_anchors_, 4}, dlxnet::TensorProto::ANY4, anchors->device<float>());
@@ -91,31 +164,32 @@ void Detector::PostProcess(int N, int H, int W, bool copy_back) {
     p.top_k = options_.topk;
     p.nms_thr = options_.nms_threshold;
     p.image_w = W; p.image_h = H;
-    char* d = static_cast<char*>(out_dev_);
+    // this slot's output buffer must have been copied out by its previous user
+    OGLE_RT_CUDA(cudaStreamWaitEvent(compute, E(slot.ev_d2h), 0));
+    char* d = static_cast<char*>(slot.out_dev);
     OGLE_CUDA_OK(ogle_cuda_ssd_detect(&p, cls_logits->device<float>(), boxes_, reinterpret_cast<float*>(d),
                                       reinterpret_cast<int*>(d + off_anchor_), reinterpret_cast<int*>(d + off_cls_),
                                       reinterpret_cast<float*>(d + off_box_), reinterpret_cast<int*>(d + off_count_),
                                       context_->stream()));
-    d2h_bytes_ = 0;
-    if (copy_back) {
-        OGLE_RT_CUDA(cudaMemcpyAsync(out_host_, out_dev_, out_bytes_, cudaMemcpyDeviceToHost,
-                                     reinterpret_cast<cudaStream_t>(context_->stream())));
-        d2h_bytes_ = out_bytes_;
-    }
+    OGLE_RT_CUDA(cudaEventRecord(E(slot.ev_done), compute));
 }
 
 const DetectionBatch& Detector::Wait() {
     context_->MakeCurrent();
-    context_->Synchronize();
-    const size_t n = size_t(batch_) * rows_;
-    const char* h = static_cast<const char*>(out_host_);
+    OGLE_CHECK(!pending_.empty()) << "Wait() without a call in flight";
+    const int idx = pending_.front();
+    pending_.erase(pending_.begin());
+    Slot& slot = slots_[idx];
+    OGLE_RT_CUDA(cudaEventSynchronize(E(slot.ev_d2h)));
+    const char* h = static_cast<const char*>(slot.out_host);
+    result_.images = batch_;
     result_.rows = rows_;
-    result_.score.assign(reinterpret_cast<const float*>(h), reinterpret_cast<const float*>(h) + n);
-    result_.anchor.assign(reinterpret_cast<const int*>(h + off_anchor_), reinterpret_cast<const int*>(h + off_anchor_) + n);
-    result_.cls.assign(reinterpret_cast<const int*>(h + off_cls_), reinterpret_cast<const int*>(h + off_cls_) + n);
-    result_.box.assign(reinterpret_cast<const float*>(h + off_box_), reinterpret_cast<const float*>(h + off_box_) + n * 4);
-    result_.count.assign(reinterpret_cast<const int*>(h + off_count_),
-                         reinterpret_cast<const int*>(h + off_count_) + size_t(batch_) * counts_per_image_);
+    result_.counts_per_image = counts_per_image_;
+    result_.score = reinterpret_cast<const float*>(h);
+    result_.anchor = reinterpret_cast<const int*>(h + off_anchor_);
+    result_.cls = reinterpret_cast<const int*>(h + off_cls_);
+    result_.box = reinterpret_cast<const float*>(h + off_box_);
+    result_.count = reinterpret_cast<const int*>(h + off_count_);
     return result_;
 }
 

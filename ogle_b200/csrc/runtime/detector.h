@@ -23,12 +23,17 @@ struct DetectorOptions {
     TensorNameList output_names = {"cls_logits", "box_preds", "anchors"};
 };
 
+// Views into the detector's pinned result buffer (no copy): valid until the same pipeline
+// slot is reused, i.e. until kDepth further calls have been issued.
 struct DetectionBatch {
+    int images = 0;
     int rows = 0;                       // rows per image
-    std::vector<float> score;           // [N][rows]
-    std::vector<int> anchor, cls;       // [N][rows]
-    std::vector<float> box;             // [N][rows][4]
-    std::vector<int> count;             // [N] (mode 0) or [N][C-1] (mode 1)
+    int counts_per_image = 0;           // 1 (mode 0) or C-1 (mode 1)
+    const float* score = nullptr;       // [N][rows]
+    const int* anchor = nullptr;        // [N][rows]
+    const int* cls = nullptr;           // [N][rows]
+    const float* box = nullptr;         // [N][rows][4]
+    const int* count = nullptr;         // [N][counts_per_image]
 };
 
 class Detector {
@@ -37,35 +42,55 @@ public:
     ~Detector();
     // images: host NHWC [N,H,W,3] floats, already mean-subtracted (Preprocess of
     // detector.cc:99-109 needs an image library and is the caller's). Enqueues the
-    // upload, the network, decode and post-process, and the copies of the results
-    // into pinned staging; Wait() then exposes them.
+    // upload, the network, decode, post-process and the copy of the detections into
+    // pinned memory, and returns. Up to kDepth calls may be in flight: the upload of
+    // call i+1 (copy stream) overlaps the network of call i (compute stream), and the
+    // copy-back of call i overlaps the network of call i+1. Pinned host memory makes
+    // the copies truly asynchronous. The host buffer must stay valid until the Wait()
+    // that retires this call.
     void DetectAsync(const float* images_nhwc, int N, int H, int W);
     // Same, for images that already sit on the device in the padded NHWC4 layout
-    // [N][H][W][4]; copy_back = false leaves the detections on the device.
+    // [N][H][W][4]. copy_back = false leaves the detections on the device and enqueues
+    // nothing for Wait(); with copy_back the call is retired by Wait() like DetectAsync.
+    // Not pipelined: call it only with no DetectAsync in flight.
     void DetectDeviceAsync(const float* images_nhwc4_device, int N, int H, int W, bool copy_back);
-    // Blocks until the last DetectAsync finished; results are valid until the next call.
+    // Retires the OLDEST call in flight: blocks until its detections are on the host.
     const DetectionBatch& Wait();
+    int in_flight() const { return int(pending_.size()); }
+    static constexpr int kDepth = 2;
+
     FBOSession* session() { return session_.get(); }
     int num_classes() const { return num_classes_; }
     int num_anchors() const { return num_anchors_; }
     int rows() const { return rows_; }
     size_t h2d_bytes() const { return h2d_bytes_; }
     size_t d2h_bytes() const { return d2h_bytes_; }
-    // device pointers of the last post-process outputs (valid after the first call)
-    const float* device_boxes() const { return boxes_; }
 
 private:
-    void AllocateOutputs(int N);
-    void PostProcess(int N, int H, int W, bool copy_back);
+    struct Slot {
+        float* stage = nullptr;      // dense NHWC upload target on the device
+        void* out_dev = nullptr;     // score | anchor | cls | box | count, contiguous
+        void* out_host = nullptr;    // pinned mirror
+        void* ev_h2d = nullptr;      // upload landed (copy-in stream)
+        void* ev_pad = nullptr;      // staging buffer consumed (compute stream)
+        void* ev_done = nullptr;     // post-process finished (compute stream)
+        void* ev_d2h = nullptr;      // detections on the host (copy-out stream)
+    };
+    void Allocate(int N, int H, int W);
+    void Release();
+    void PostProcess(Slot& slot, int N, int H, int W);
     DetectorOptions options_;
     Context* context_;
     std::unique_ptr<FBOSession> session_;
     int num_classes_ = 0, num_anchors_ = 0, batch_ = 0, rows_ = 0, counts_per_image_ = 0;
     float* boxes_ = nullptr;          // decoded [N][A][4]
-    void* out_dev_ = nullptr;         // score | anchor | cls | box | count, contiguous
-    void* out_host_ = nullptr;        // pinned mirror
+    Slot slots_[kDepth];
+    int next_slot_ = 0;
+    std::vector<int> pending_;
+    void* copy_in_ = nullptr;         // cudaStream_t
+    void* copy_out_ = nullptr;
     size_t out_bytes_ = 0, off_anchor_ = 0, off_cls_ = 0, off_box_ = 0, off_count_ = 0;
-    size_t h2d_bytes_ = 0, d2h_bytes_ = 0;
+    size_t h2d_bytes_ = 0, d2h_bytes_ = 0, stage_bytes_ = 0;
     DetectionBatch result_;
 };
 

@@ -196,6 +196,7 @@ class Detector:
         if not self._h:
             raise OgleError("detector_create: " + self._lib.ogle_rt_last_error().decode())
         self._shape = None
+        self._in_flight = 0
 
     def close(self):
         if self._h:
@@ -212,15 +213,21 @@ class Detector:
         return FBOSession(_borrowed=self._lib.ogle_detector_session(self._h))
 
     def detect_async(self, images_ptr, N, H, W):
-        """images_ptr: address of N*H*W*3 host floats (NHWC, preprocessed); pinned memory makes the copy asynchronous."""
+        """images_ptr: address of N*H*W*3 host floats (NHWC, preprocessed); pinned memory makes the copy asynchronous.
+        Up to two calls may be in flight; wait() retires the oldest."""
         _check(self._lib.ogle_detector_detect_async(self._h, images_ptr, N, H, W), "detect_async")
         self._shape = N
+        self._in_flight += 1
+
+    def in_flight(self):
+        return self._in_flight
 
     def detect_device_async(self, images_dev_ptr, N, H, W, copy_back=False):
         """images_dev_ptr: device address of [N,H,W,4] floats (padded NHWC4)."""
         _check(self._lib.ogle_detector_detect_device_async(self._h, images_dev_ptr, N, H, W, int(copy_back)),
                "detect_device_async")
         self._shape = N
+        self._in_flight += int(bool(copy_back))
 
     def info(self):
         a, c, r = C.c_int(), C.c_int(), C.c_int()
@@ -229,6 +236,7 @@ class Detector:
         return dict(num_anchors=a.value, num_classes=c.value, rows=r.value, h2d_bytes=h.value, d2h_bytes=d.value)
 
     def wait(self, fetch=True):
+        self._in_flight = max(0, self._in_flight - 1)
         if not fetch:
             _check(self._lib.ogle_detector_wait(self._h, None, None, None, None, None), "wait")
             return None

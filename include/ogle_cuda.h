@@ -169,6 +169,22 @@ int ogle_cuda_gemm_packed(const OgleGemmParams* p, const float* A, const void* p
 int ogle_cuda_gemm_ws(const OgleGemmParams* p, const float* A, const float* B, const float* C, float* Y,
                       void* workspace, size_t workspace_bytes, ogle_stream_t stream);
 
+/* ogle_cuda_gemm_ws with the packing scratch in a fixed device array inside the
+ * library instead of a caller's workspace. It has no counterpart in the reference.
+ * It allocates nothing, on any call: the scratch is a file-scope device array of
+ * OGLE_GEMM_STATIC_MAX_BYTES. A problem whose packed B
+ * (ogle_cuda_gemm_packed_b_bytes) is larger returns OGLE_ERR_UNSUPPORTED with the
+ * sizes in ogle_cuda_last_error(); use ogle_cuda_gemm_ws then.
+ * The first call on each device resolves the array's address (set-up; make it with
+ * that device current and before any stream capture); later calls only launch.
+ * All calls on a device share the one array: calls that may execute concurrently
+ * (two streams without an event between them) race on it. Nothing in the array has
+ * to be cleared between calls. */
+#define OGLE_GEMM_STATIC_MAX_BYTES (8u << 20)
+size_t ogle_cuda_gemm_static_max_bytes(void);
+int ogle_cuda_gemm_static(const OgleGemmParams* p, const float* A, const float* B, const float* C, float* Y,
+                          ogle_stream_t stream);
+
 /* ------------------------------------------------------------------ concat */
 /* ConcatKernel::Compute, nn/kernels/concat.cc:53-96 + concat_multi.glsl.
  * Shapes are 4-D (left-padded with 1s, as AmendShape does); last dimension of

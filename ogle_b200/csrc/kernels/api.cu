@@ -12,6 +12,11 @@ void set_last_error(cudaError_t e) {
     for (; s[i] && i < 255; ++i) g_last_error[i] = s[i];
     g_last_error[i] = 0;
 }
+void set_last_error(const char* s) {
+    int i = 0;
+    for (; s[i] && i < 255; ++i) g_last_error[i] = s[i];
+    g_last_error[i] = 0;
+}
 }  // namespace ogle
 
 extern "C" {

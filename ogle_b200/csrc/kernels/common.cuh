@@ -9,6 +9,7 @@ namespace ogle {
 
 extern std::atomic<uint64_t> g_launch_count;
 void set_last_error(cudaError_t e);
+void set_last_error(const char* message);
 
 // B200: 148 SMs. Grid-stride kernels launch a multiple of this.
 constexpr int kNumSMs = 148;

@@ -201,6 +201,15 @@ def gemm_ws(A4, B4, C4, M, K, N, transB=0, alpha=1.0, beta=1.0, bias_mode=0, mat
     return out
 
 
+def gemm_static(A4, B4, C4, out, M, K, N, transB=0, alpha=1.0, beta=1.0, bias_mode=0, math_mode=MATH_TF32X3):
+    """gemm with a run-time B, packing scratch inside the library; writes into the caller's `out`
+    ([M, up4(N)] floats on the device). Neither this wrapper nor the call allocates."""
+    _require_cuda(A4, B4, C4, out)
+    p = _gemm_params(A4, B4, C4, M, K, N, transB, alpha, beta, bias_mode, math_mode)
+    check(_lib.cuda_lib().ogle_cuda_gemm_static(C.byref(p), _p(A4), _p(B4), _p(C4), _p(out), _stream()), "gemm_static")
+    return out
+
+
 def concat(xs4, shapes, axis):
     """xs4: padded device tensors; shapes: their logical shapes (rank <= 4); axis in that rank."""
     rank = len(shapes[0])

@@ -108,6 +108,24 @@ int ogle_cuda_conv2d_prepack(const OgleConvParams* p, const float* w_oihw, void*
 int ogle_cuda_conv2d(const OgleConvParams* p, const float* x, const void* packed_filter,
                      const float* bias, float* y, ogle_stream_t stream);
 
+/* Two convolutions that read the same input with the same window (kernel, stride,
+ * pad, dilation, activation, group 1) as ONE pass over the input: the SSD box and
+ * class heads, which the reference draws as two Conv2DKernel::Compute passes
+ * (conv2d.cc:116-167) over the same feature map. The caller stacks the two OIHW
+ * filters into one of out_hwc[2] = second_offset + K2 rows, where
+ * second_offset = K1 rounded up to a multiple of 32 and the rows in between are
+ * zero, packs it with ogle_cuda_conv2d_prepack under the same params, and stacks
+ * the biases the same way. y_first receives channels [0, K1) as a tensor of K1
+ * channels (padded to 4), y_second channels [second_offset, out_hwc[2]) as a tensor
+ * of K2 channels. The arithmetic per output value is that of ogle_cuda_conv2d
+ * (bit-identical in OGLE_MATH_TF32; in OGLE_MATH_TF32X3 the three partial sums
+ * may be added in a different order). Tensor-core modes only: ogle_cuda_conv2d_pair_supported says
+ * whether these params are served (else run the two convolutions separately). */
+int ogle_cuda_conv2d_pair_supported(const OgleConvParams* p);
+int ogle_cuda_conv2d_pair(const OgleConvParams* p, const float* x, const void* packed_filter, const float* bias,
+                          int first_channels, int second_offset, float* y_first, float* y_second,
+                          ogle_stream_t stream);
+
 /* -------------------------------------------------------------------- pool */
 /* PoolKernel::Compute, ogl_runtime/opengl/nn/kernels/pool.cc:55-79 + pool.glsl.
  * type: 0 max (all-padding window gives 0), 1 average (divides by kernel^2,

@@ -4,7 +4,8 @@
 namespace ogle {
 
 int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x,
-                   const float* w_hi, const float* w_lo, const float* bias, float* y, cudaStream_t s);
+                   const float* w_hi, const float* w_lo, const float* bias, float* y, cudaStream_t s,
+                   float* y2 = nullptr, int K1 = 0, int split_col = 0);
 bool conv_tc_supported(const ConvArgs& a, int variant);
 
 // Destination-indexed packing of an OIHW filter into the three sections of the
@@ -152,6 +153,33 @@ int ogle_cuda_conv2d(const OgleConvParams* p, const float* x, const void* packed
                               reinterpret_cast<const float*>(base + L.off_lo), bias, y, s);
     }
     return launch_conv_simt(a, variant, x, reinterpret_cast<const float*>(base), bias, y, s);
+}
+
+int ogle_cuda_conv2d_pair_supported(const OgleConvParams* p) {
+    ConvArgs a; int variant;
+    if (fill_args(p, &a, &variant) != OGLE_OK) return 0;
+    if (p->math_mode == OGLE_MATH_FP32 || p->out_channel_stride || p->out_channel_offset) return 0;
+    if (a.K > 256) return 0;                     // one N tile must hold both filters' columns
+    return conv_tc_supported(a, variant) ? 1 : 0;
+}
+
+int ogle_cuda_conv2d_pair(const OgleConvParams* p, const float* x, const void* packed_filter, const float* bias,
+                          int first_channels, int second_offset, float* y_first, float* y_second,
+                          ogle_stream_t stream) {
+    ConvArgs a; int variant;
+    int rc = fill_args(p, &a, &variant);
+    if (rc != OGLE_OK) return rc;
+    if (a.Ho != p->out_hwc[0] || a.Wo != p->out_hwc[1]) return OGLE_ERR_INVALID;
+    if (!x || !packed_filter || !y_first || !y_second || (a.has_bias && !bias)) return OGLE_ERR_INVALID;
+    if (!aligned16(x) || !aligned16(y_first) || !aligned16(y_second) || !aligned16(packed_filter)) return OGLE_ERR_ALIGNMENT;
+    if (first_channels <= 0 || second_offset != (first_channels + 31) / 32 * 32 || second_offset >= a.K)
+        return OGLE_ERR_INVALID;
+    if (!ogle_cuda_conv2d_pair_supported(p)) return OGLE_ERR_UNSUPPORTED;
+    const char* base = static_cast<const char*>(packed_filter);
+    const FilterLayout L = filter_layout(a.K, a.C / a.group, a.kernel, a.group, a.Cp);
+    return launch_conv_tc(a, variant, p->math_mode, x, reinterpret_cast<const float*>(base + L.off_hi),
+                          reinterpret_cast<const float*>(base + L.off_lo), bias, y_first, (cudaStream_t)stream,
+                          y_second, first_channels, second_offset);
 }
 
 }  // extern "C"

@@ -308,6 +308,10 @@ conv_igemm_kernel(const float* __restrict__ x, const float* __restrict__ wp,
     }
 }
 
+bool conv_smallc_supported(const ConvArgs& a);
+int launch_conv_smallc(const ConvArgs& a, const float* x, const float* w_tap_major, const float* bias, float* y,
+                       cudaStream_t s);
+
 int launch_conv_simt(const ConvArgs& a, int variant, const float* x, const float* w,
                      const float* bias, float* y, cudaStream_t s) {
     if (variant == CONV_DEPTHWISE) {
@@ -331,6 +335,7 @@ int launch_conv_simt(const ConvArgs& a, int variant, const float* x, const float
         grouped_kernel<<<grid_for(a.M * a.Kp, 256), 256, 0, s>>>(x, w, bias, y, a);
         return finish_launch();
     }
+    if (variant == CONV_GENERAL && conv_smallc_supported(a)) return launch_conv_smallc(a, x, w, bias, y, s);
     if (a.Kp <= 32) {
         dim3 grid(div_up(a.M, 128), div_up(a.Kp, 32));
         conv_igemm_kernel<128, 32, 4, 4><<<grid, 256, 0, s>>>(x, w, bias, y, a);

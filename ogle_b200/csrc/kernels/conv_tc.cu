@@ -31,7 +31,8 @@
 namespace ogle {
 
 int launch_tc_v2(tc::TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, const CUtensorMap& mBlo,
-                 const CUtensorMap& mY, long m_tiles, const float* bias, int* err_flag, cudaStream_t s);
+                 const CUtensorMap& mY, const CUtensorMap& mY2, long m_tiles, const float* bias, int* err_flag,
+                 cudaStream_t s);
 
 __device__ int g_tc_error = 0;   // first error seen by any block (0 = none)
 
@@ -336,9 +337,22 @@ bool conv_tc_supported(const ConvArgs& a, int variant) {
     return true;
 }
 
+// y2 != null: two-output form. a.K counts the stacked filters (first conv's K1 channels,
+// zero rows up to split_col, then the second conv's); y receives [0, K1), y2 the rest.
 int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x, const float* w_hi,
-                   const float* w_lo, const float* bias, float* y, cudaStream_t s) {
+                   const float* w_lo, const float* bias, float* y, cudaStream_t s, float* y2, int K1,
+                   int split_col) {
     TcArgs t = {};
+    if (y2) {
+        if (tc_variant() != 2 || split_col <= 0 || (split_col & 31) || K1 <= 0 || K1 > split_col || split_col >= a.K ||
+            a.koff != 0)
+            return OGLE_ERR_UNSUPPORTED;
+        t.split_col = split_col;
+        t.K1 = K1;
+    }
+    // channel extents and row strides of the output tensor(s)
+    const int kp_a = y2 ? up4(K1) : a.Kp, ks_a = y2 ? up4(K1) : a.Ks;
+    const int kp_b = y2 ? up4(a.K - split_col) : a.Kp;
     const int taps = a.kernel * a.kernel;
     t.Cp32 = (a.C + 31) / 32 * 32;
     t.chunks_per_tap = t.Cp32 / kChunk;
@@ -349,7 +363,7 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
     t.passes = math_mode == OGLE_MATH_TF32X3 ? 3 : 1;
     const bool v2 = tc_variant() == 2;
 
-    CUtensorMap mA, mBhi, mBlo, mY;
+    CUtensorMap mA, mBhi, mBlo, mY, mY2;
     long m_tiles;
     if (variant == CONV_POINTWISE) {
         t.flat = 1;
@@ -362,9 +376,14 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
         const cuuint32_t es[4] = {1, 1, 1, 1};
         if (!make_map(&mA, x, 4, dims, str, box, es)) return OGLE_ERR_CUDA;
         if (v2) {
-            const cuuint64_t yd[4] = {(cuuint64_t)a.Kp, (cuuint64_t)a.M, 1, 1};
-            const cuuint64_t ys[3] = {(cuuint64_t)a.Ks * 4, (cuuint64_t)a.Ks * 4 * (cuuint64_t)a.M, (cuuint64_t)a.Ks * 4 * (cuuint64_t)a.M};
+            const cuuint64_t yd[4] = {(cuuint64_t)kp_a, (cuuint64_t)a.M, 1, 1};
+            const cuuint64_t ys[3] = {(cuuint64_t)ks_a * 4, (cuuint64_t)ks_a * 4 * (cuuint64_t)a.M, (cuuint64_t)ks_a * 4 * (cuuint64_t)a.M};
             if (!make_map(&mY, y + a.koff, 4, yd, ys, box, es)) return OGLE_ERR_CUDA;
+            if (y2) {
+                const cuuint64_t yd2[4] = {(cuuint64_t)kp_b, (cuuint64_t)a.M, 1, 1};
+                const cuuint64_t ys2[3] = {(cuuint64_t)kp_b * 4, (cuuint64_t)kp_b * 4 * (cuuint64_t)a.M, (cuuint64_t)kp_b * 4 * (cuuint64_t)a.M};
+                if (!make_map(&mY2, y2, 4, yd2, ys2, box, es)) return OGLE_ERR_CUDA;
+            }
         }
     } else {
         t.flat = 0;
@@ -373,10 +392,19 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
             const int parts = (a.Wo + kTileM - 1) / kTileM;
             t.tw = (a.Wo + parts - 1) / parts; t.th = 1; t.tn = 1;
         } else {
+            // full-width tiles of th rows from tn consecutive images (th * tn * Wo <= 128):
+            // take the shape that needs the fewest rounds of one tile per SM; among equals the
+            // tallest, whose filter taps overlap most in L2
             t.tw = a.Wo;
-            t.th = kTileM / a.Wo < a.Ho ? kTileM / a.Wo : a.Ho;
-            t.tn = t.th == a.Ho ? (kTileM / (a.Ho * a.Wo) < a.N ? kTileM / (a.Ho * a.Wo) : a.N) : 1;
-            if (t.tn < 1) t.tn = 1;
+            long best = -1;
+            for (int th = 1; th <= a.Ho && th * a.Wo <= kTileM; ++th) {
+                int tn = kTileM / (th * a.Wo);
+                if (tn > a.N) tn = a.N;
+                if ((th - 1) * a.stride + 1 > 256) continue;          // TMA box limit
+                const long tiles = (long)((a.Ho + th - 1) / th) * ((a.N + tn - 1) / tn);
+                const long rounds = (tiles + kNumSMs - 1) / kNumSMs;
+                if (best < 0 || rounds <= best) { best = rounds; t.th = th; t.tn = tn; }
+            }
         }
         t.tiles_w = (a.Wo + t.tw - 1) / t.tw;
         t.tiles_h = (a.Ho + t.th - 1) / t.th;
@@ -389,11 +417,16 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
         const cuuint32_t es[4] = {1, (cuuint32_t)a.stride, (cuuint32_t)a.stride, 1};
         if (!make_map(&mA, x, 4, dims, str, box, es)) return OGLE_ERR_CUDA;
         if (v2) {
-            const cuuint64_t yd[4] = {(cuuint64_t)a.Kp, (cuuint64_t)a.Wo, (cuuint64_t)a.Ho, (cuuint64_t)a.N};
-            const cuuint64_t ys[3] = {(cuuint64_t)a.Ks * 4, (cuuint64_t)a.Ks * 4 * a.Wo, (cuuint64_t)a.Ks * 4 * a.Wo * a.Ho};
+            const cuuint64_t yd[4] = {(cuuint64_t)kp_a, (cuuint64_t)a.Wo, (cuuint64_t)a.Ho, (cuuint64_t)a.N};
+            const cuuint64_t ys[3] = {(cuuint64_t)ks_a * 4, (cuuint64_t)ks_a * 4 * a.Wo, (cuuint64_t)ks_a * 4 * a.Wo * a.Ho};
             const cuuint32_t yb[4] = {kChunk, (cuuint32_t)t.tw, (cuuint32_t)t.th, (cuuint32_t)t.tn};
             const cuuint32_t ye[4] = {1, 1, 1, 1};
             if (!make_map(&mY, y + a.koff, 4, yd, ys, yb, ye)) return OGLE_ERR_CUDA;
+            if (y2) {
+                const cuuint64_t yd2[4] = {(cuuint64_t)kp_b, (cuuint64_t)a.Wo, (cuuint64_t)a.Ho, (cuuint64_t)a.N};
+                const cuuint64_t ys2[3] = {(cuuint64_t)kp_b * 4, (cuuint64_t)kp_b * 4 * a.Wo, (cuuint64_t)kp_b * 4 * a.Wo * a.Ho};
+                if (!make_map(&mY2, y2, 4, yd2, ys2, yb, ye)) return OGLE_ERR_CUDA;
+            }
         }
     }
     if (v2) choose_n_tiling_v2(a.Kp, m_tiles, &t);
@@ -405,7 +438,7 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
     const cuuint32_t bes[2] = {1, 1};
     if (!make_map(&mBhi, w_hi, 2, bdims, bstr, bbox, bes)) return OGLE_ERR_CUDA;
     if (!make_map(&mBlo, w_lo, 2, bdims, bstr, bbox, bes)) return OGLE_ERR_CUDA;
-    if (v2) return launch_tc_v2(t, mA, mBhi, mBlo, mY, m_tiles, bias, error_flag_ptr(), s);
+    if (v2) return launch_tc_v2(t, mA, mBhi, mBlo, mY, y2 ? mY2 : mY, m_tiles, bias, error_flag_ptr(), s);
     return launch_tc(t, mA, mBhi, mBlo, m_tiles, bias, y, s);
 }
 
@@ -448,7 +481,7 @@ static int launch_gemm_common(const OgleGemmParams& p, const float* A, const flo
         const cuuint64_t yd[4] = {(cuuint64_t)t.Kp, (cuuint64_t)p.M, 1, 1};
         const cuuint64_t ys[3] = {(cuuint64_t)p.ldy * 4, (cuuint64_t)p.ldy * 4 * (cuuint64_t)p.M, (cuuint64_t)p.ldy * 4 * (cuuint64_t)p.M};
         if (!make_map(&mY, Y, 4, yd, ys, box, es)) return OGLE_ERR_CUDA;
-        return launch_tc_v2(t, mA, mBhi, mBlo, mY, m_tiles, C, error_flag_ptr(), s);
+        return launch_tc_v2(t, mA, mBhi, mBlo, mY, mY, m_tiles, C, error_flag_ptr(), s);
     }
     return launch_tc(t, mA, mBhi, mBlo, m_tiles, C, Y, s);
 }

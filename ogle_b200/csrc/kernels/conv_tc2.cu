@@ -74,6 +74,18 @@ __device__ long long g_trace[64 * 16];
 #define TRACEC(chunk, slot) do {} while (0)
 #endif
 
+__device__ __forceinline__ void tmem_ld32(uint32_t (&r)[32], uint32_t taddr) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+
 struct TileCoord { int n_tile, n0, h0, w0; };
 
 __device__ __forceinline__ TileCoord tile_coord(const TcArgs& a, int tile) {
@@ -96,7 +108,7 @@ __device__ __forceinline__ TileCoord tile_coord(const TcArgs& a, int tile) {
 __global__ void __launch_bounds__(kThreads2, 1)
 conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmBhi,
                 const __grid_constant__ CUtensorMap tmBlo, const __grid_constant__ CUtensorMap tmY,
-                const float* __restrict__ bias, const TcArgs a, int* err_flag) {
+                const __grid_constant__ CUtensorMap tmY2, const float* __restrict__ bias, const TcArgs a, int* err_flag) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[kMaxStages], bar_xf[kMaxStages], bar_empty[kMaxStages];
     __shared__ __align__(8) uint64_t bar_acc_full[2], bar_acc_empty[2];
@@ -118,13 +130,14 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const uint32_t staging_off = (uint32_t)a.stages * stage_bytes;
 
     const int chunks = a.kernel * a.kernel * a.chunks_per_tap;
+    const int acc_cols = a.ncat ? 2 * a.BN : a.BN;     // tensor-memory columns of one accumulator
     const int rows_in_tile = a.flat ? kTileM : a.tn * a.th * a.tw;
     volatile int* abort_flag = &s_abort;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
             mbar_init(&bar_full[s], 2);     // one arrive.expect_tx from each producer
-            mbar_init(&bar_xf[s], 128);
+            mbar_init(&bar_xf[s], (uint32_t)(a.xf_groups * 128));
             mbar_init(&bar_empty[s], 1);
         }
         for (int i = 0; i < 2; ++i) {
@@ -214,6 +227,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // -------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(a.BN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+            const uint32_t idesc2 = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(a.BN >> 2) << 17) | ((uint32_t)(kTileM >> 4) << 24);
             int s = 0;
             uint32_t ph = 0;           // parity of the ring pass
             bool ok = true;
@@ -223,7 +237,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if (use > 0) ok = wait_or_abort(&bar_acc_empty[as], (uint32_t)((use - 1) & 1), abort_flag);
                 if (!ok) { record_error(err_flag, 5); s_abort = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t d = tmem_d + (uint32_t)(as * a.BN);
+                const uint32_t d = tmem_d + (uint32_t)(as * acc_cols);
                 for (int it = 0; it < chunks; ++it) {
                     if (it == 0) TRACE(ti, 4);
                     ok = wait_or_abort(split ? &bar_xf[s] : &bar_full[s], ph, abort_flag);
@@ -232,7 +246,8 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     TRACEC(ti * chunks + it, 2);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t ad = umma_desc(sA(s)), bd = umma_desc(sBhi(s));
-                    if (split) umma_tf32_chunk_split(d, ad, ad + (kABytes >> 4), bd, bd + (b_bytes >> 4), idesc, it > 0 ? 1u : 0u);
+                    if (a.ncat) umma_tf32_chunk_cat(d, ad, ad + (kABytes >> 4), bd, idesc2, idesc, it > 0 ? 1u : 0u);
+                    else if (split) umma_tf32_chunk_split(d, ad, ad + (kABytes >> 4), bd, bd + (b_bytes >> 4), idesc, it > 0 ? 1u : 0u);
                     else umma_tf32_chunk(d, ad, bd, idesc, it > 0 ? 1u : 0u);
                     umma_commit(&bar_empty[s]);
                     TRACEC(ti * chunks + it, 3);
@@ -244,41 +259,38 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
     } else if (warp >= 10) {
         // --------------------------------------------------- operand split (3-pass)
+        // One or two warp groups work on EVERY chunk together (with two, each thread
+        // takes half as many vectors): the latency of the split is what the shallow
+        // ring of the 3-pass mode (large stages) has to hide.
         const int xg = (warp - 10) >> 2;           // group 0 or 1
         if (split && xg < a.xf_groups) {
-            const int t = (threadIdx.x - 320) & 127;
-            int s = 0, turn = 0;       // ring stage; whose turn (group) the next chunk is
+            const int nthr = a.xf_groups * 128;
+            const int t = threadIdx.x - 320;       // 0 .. nthr-1
+            int s = 0;
             uint32_t ph = 0;
             int xti = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x, ++xti) {
                 for (int it = 0; it < chunks; ++it) {
-                    const int cur = s;
-                    const uint32_t cur_ph = ph;
-                    const bool mine = turn == xg;
-                    if (++s == a.stages) { s = 0; ph ^= 1u; }
-                    if (++turn == a.xf_groups) turn = 0;
-                    if (!mine) continue;
-                    ok = wait_or_abort(&bar_full[cur], cur_ph, abort_flag);
+                    ok = wait_or_abort(&bar_full[s], ph, abort_flag);
                     if (!ok) { record_error(err_flag, 3); s_abort = 1; break; }
                     if (t == 0 && it == 0) TRACE(xti, 2);
-                    const int s_ = cur;
-                    float4* pa = reinterpret_cast<float4*>(base_ptr + (size_t)s_ * stage_bytes);
+                    float4* pa = reinterpret_cast<float4*>(base_ptr + (size_t)s * stage_bytes);
                     float4* pl = pa + kABytes / 16;
-#pragma unroll
-                    for (int i = 0; i < kABytes / 16 / 128; ++i) {
-                        const float4 v = pa[t + i * 128];
+                    for (int i = t; i < kABytes / 16; i += nthr) {
+                        const float4 v = pa[i];
                         float4 h;
                         h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
                         h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
                         h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
                         h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
-                        pa[t + i * 128] = h;
-                        pl[t + i * 128] = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+                        pa[i] = h;
+                        pl[i] = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    mbar_arrive(&bar_xf[s_]);
+                    mbar_arrive(&bar_xf[s]);
                     if (t == 0 && it == 0) TRACE(xti, 3);
+                    if (++s == a.stages) { s = 0; ph ^= 1u; }
                 }
             }
         }
@@ -325,16 +337,16 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     for (int b = 0; b < nb; ++b) {
                         const int col = (g0 + b) * 32;
                         uint32_t r[32];
-                        const uint32_t taddr = tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * a.BN + col);
-                        asm volatile(
-                            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                              "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                              "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                            : "r"(taddr));
+                        const uint32_t taddr = tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * acc_cols + col);
+                        tmem_ld32(r, taddr);
+                        if (a.ncat) {
+                            // second half of the accumulator: the hi*lo products
+                            uint32_t r2[32];
+                            tmem_ld32(r2, taddr + (uint32_t)a.BN);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(r2[i]));
+                        }
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                         if (t == 0 && g0 == 0 && b == 0) TRACE(ti, 14);
                         if (g0 + b == groups - 1) {
@@ -343,7 +355,11 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                             mbar_arrive(&bar_acc_empty[as]);
                         }
                         float4* dst = reinterpret_cast<float4*>(staging + (size_t)b * kStagingBytes + (size_t)row * 128);
-                        const bool fast = a.bias_mode != 1 && nbase + col + 32 <= a.K;
+                        // which output this slab belongs to, and its first column there
+                        const bool second = a.split_col > 0 && nbase + col >= a.split_col;
+                        const int lcol = second ? nbase + col - a.split_col : nbase + col;
+                        const int kout = second ? a.K - a.split_col : (a.split_col > 0 ? a.K1 : a.K);
+                        const bool fast = a.bias_mode != 1 && lcol + 32 <= kout;
                         if (fast) {
                             // every column is a real channel and the bias is per column:
                             // two instructions per value, bias read as 128-bit vectors
@@ -371,9 +387,9 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                                 float v[4];
 #pragma unroll
                                 for (int l = 0; l < 4; ++l) {
-                                    const int n = nbase + col + c4 * 4 + l;
+                                    const int n = lcol + c4 * 4 + l;
                                     float acc = a.alpha * __uint_as_float(r[c4 * 4 + l]);
-                                    if (n < a.K) {
+                                    if (n < kout) {
                                         if (a.bias_mode == 2) acc += my_bias[col + c4 * 4 + l];
                                         else if (a.bias_mode == 1) acc = fmaf(a.beta, bias[pix * a.ldc + n], acc);
                                         acc = apply_act(acc, a.act, a.lo, a.hi);
@@ -395,9 +411,11 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     if (t == 0) {
                         for (int b = 0; b < nb; ++b) {
                             const uint32_t src = base + my_staging + (uint32_t)b * (uint32_t)kStagingBytes;
-                            const int col = nbase + (g0 + b) * 32;
-                            if (a.flat) tma_store_4d(&tmY, src, col, tc_.w0, 0, 0);
-                            else tma_store_4d(&tmY, src, col, tc_.w0, tc_.h0, tc_.n0);
+                            int col = nbase + (g0 + b) * 32;
+                            const CUtensorMap* my = &tmY;
+                            if (a.split_col > 0 && col >= a.split_col) { col -= a.split_col; my = &tmY2; }
+                            if (a.flat) tma_store_4d(my, src, col, tc_.w0, 0, 0);
+                            else tma_store_4d(my, src, col, tc_.w0, tc_.h0, tc_.n0);
                         }
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         if (g0 + a.epi_slabs >= groups) TRACE(ti, 13);
@@ -415,6 +433,16 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)a.tmem_cols));
     }
+}
+
+// Widest N tile that uses the stacked-filter form; OGLE_TC_NCAT_MAX_BN overrides (0 disables).
+int ncat_max_bn() {
+    static const int v = [] {
+        const char* e = getenv("OGLE_TC_NCAT_MAX_BN");
+        int n = e ? atoi(e) : 128;
+        return n < 0 ? 0 : (n > 128 ? 128 : n);
+    }();
+    return v;
 }
 
 int num_sms() {
@@ -440,7 +468,8 @@ extern "C" int ogle_debug_read_trace(long long* out) {
 #endif
 
 int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, const CUtensorMap& mBlo,
-                 const CUtensorMap& mY, long m_tiles, const float* bias, int* err_flag, cudaStream_t s) {
+                 const CUtensorMap& mY, const CUtensorMap& mY2, long m_tiles, const float* bias, int* err_flag,
+                 cudaStream_t s) {
     if (t.BN % 32 || t.BN > 256) return OGLE_ERR_UNSUPPORTED;
     const size_t stage = (size_t)(t.passes == 3 ? 2 : 1) * (kABytes + (size_t)t.BN * 128);
     // two epilogue groups (two staging slabs each) unless that would leave fewer
@@ -449,10 +478,8 @@ int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, cons
     t.epi_slabs = 2;
     if ((224 * 1024 - 4 * kStagingBytes - 1024) / stage < 2) t.epi_groups = 1;
     if (t.epi_groups == 1 && (224 * 1024 - 2 * kStagingBytes - 1024) / stage < 2) t.epi_slabs = 1;
-    // One operand-split group keeps up with the short reductions (pointwise layers). With
-    // two, the groups take alternate chunks; that needs an EVEN number of stages so that
-    // each group sees every phase of the stage barriers it waits on (a group that skipped
-    // a phase would mistake the older completion for the one it waits for).
+    // One operand-split group keeps up with the short reductions (pointwise layers); long
+    // reductions get both groups working on each chunk, which halves the split's latency.
     t.xf_groups = 1;
     const int chunks = t.kernel * t.kernel * t.chunks_per_tap;
     if (t.passes == 3 && chunks >= 8) {
@@ -467,11 +494,14 @@ int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, cons
     const size_t budget = 224 * 1024 - staging - 1024;
     int stages = (int)(budget / stage);
     if (stages > kMaxStages) stages = kMaxStages;
-    if (t.xf_groups == 2) stages &= ~1;
     if (stages < 2) return OGLE_ERR_UNSUPPORTED;
     t.stages = stages;
+    // stacked-filter form of the 3-pass mode (see TcArgs::ncat)
+    // (long reductions only: it costs the epilogue a second tensor-memory read per slab,
+    // which the short, bandwidth-bound pointwise layers cannot hide)
+    t.ncat = (t.passes == 3 && chunks >= 8 && t.BN <= ncat_max_bn()) ? 1 : 0;
     int cols = 32;
-    while (cols < 2 * t.BN) cols <<= 1;
+    while (cols < 2 * t.BN * (t.ncat ? 2 : 1)) cols <<= 1;
     t.tmem_cols = cols;
     const long total = m_tiles * t.n_tiles;
     if (total <= 0 || total > 0x7fffffffL) return OGLE_ERR_UNSUPPORTED;
@@ -487,7 +517,7 @@ int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, cons
     }
     const int sms = num_sms();
     const unsigned grid = (unsigned)(total < sms ? total : sms);
-    conv_tc2_kernel<<<grid, kThreads2, smem, s>>>(mA, mBhi, mBlo, mY, bias, t, err_flag);
+    conv_tc2_kernel<<<grid, kThreads2, smem, s>>>(mA, mBhi, mBlo, mY, mY2, bias, t, err_flag);
     return finish_launch();
 }
 

@@ -1,16 +1,18 @@
 // Depthwise 3x3 convolution (stride 1 or 2, channel count a multiple of 32) as a
 // persistent, TMA-fed, HBM-bound kernel.
 //
-// One block per SM slot walks a list of tiles. A tile is TH x TW output pixels of
-// one image for a slab of 32 channels. Its input window, halo included, is ONE TMA
+// One block per SM slot walks a list of tiles. A tile is th x tw output pixels of
+// one image for a slab of 32 channels; tw is the map's width when that is at most 32
+// (so 19- and 10-wide maps are covered without ragged column tiles), else 32 or 16. Its input window, halo included, is ONE TMA
 // box [IH rows][IW cols][32 channels]; pixels outside the image arrive as zeros,
 // which is the convolution's padding. Two shared-memory stages: while the block
 // computes tile i from one stage, the TMA engine fills the other with tile i+1, so
 // the only HBM traffic is the input read once (halo rows come from L2) and the
 // output written once, both as 128-byte runs.
 // A thread owns 4 channels (one float4) of one output column and slides a 3-row
-// window down it; 8 lanes cover one pixel's 128 bytes, so shared-memory reads are
-// conflict-free.
+// window down RPG output rows of it; 8 lanes cover one pixel's 128 bytes, so
+// shared-memory reads are conflict-free. The 32 pixel slots of a block are split into
+// 32 / tw row groups.
 #include "tc_common.cuh"
 #include "tma_host.h"
 
@@ -19,23 +21,23 @@ namespace {
 
 using namespace tc;
 
+constexpr int kDwSmemMax = 110 * 1024;   // two blocks per SM
+
 struct DwTiles {
     int tiles_x, tiles_y, cblocks;   // tile grid per image, 32-channel slabs
+    int tw, th, row_groups;          // tile shape: th = RPG * row_groups
+    int iw, ih;                      // input window of a tile, halo included
     long total;
 };
 
-template <int S, int TH, int TW>
+template <int S, int RPG>
 __global__ void __launch_bounds__(256)
 dw3x3_tma_kernel(const __grid_constant__ CUtensorMap tmX, const float4* __restrict__ w, const float* __restrict__ bias,
                  float4* __restrict__ y, const ConvArgs a, const DwTiles tl, int* err_flag) {
-    constexpr int IH = (TH - 1) * S + 3, IW = (TW - 1) * S + 3;
     constexpr int CB = 8;                          // float4s (32 channels) per tile
-    constexpr int COLS = 256 / CB;                 // pixel slots per block
-    constexpr int ROW_GROUPS = COLS / TW;
-    constexpr int RPG = TH / ROW_GROUPS;           // output rows per thread
     constexpr int ROWS_IN = (RPG - 1) * S + 3;
-    constexpr uint32_t kTileBytes = IH * IW * CB * 16;
-    static_assert(COLS % TW == 0 && TH % ROW_GROUPS == 0, "tile shape");
+    const int TW = tl.tw, TH = tl.th, IW = tl.iw;
+    const uint32_t kTileBytes = (uint32_t)(tl.ih * tl.iw * CB * 16);
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[2];
 
@@ -46,6 +48,7 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap tmX, const float4* __restri
     const int c = threadIdx.x % CB;
     const int slot = threadIdx.x / CB;
     const int col = slot % TW, rg = slot / TW;
+    const bool active = rg < tl.row_groups;        // slots past tw * row_groups idle
 
     if (threadIdx.x == 0) {
         mbar_init(&bar_full[0], 1);
@@ -90,6 +93,7 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap tmX, const float4* __restri
             break;   // uniform: every thread waits on the same barrier with the same bound
         }
         const float4* tile_s = stage0 + (size_t)stage * (kTileBytes / 16);
+        if (active) {
         float4 acc[RPG];
 #pragma unroll
         for (int r = 0; r < RPG; ++r) acc[r] = bv;
@@ -122,50 +126,97 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap tmX, const float4* __restri
                 y[(((long)n * a.Ho + oy) * a.Wo + ox) * out_q + off_q + cq] = apply_act4(acc[o], a.act, a.lo, a.hi);
             }
         }
+        }
         __syncthreads();
     }
 }
 
-template <int S, int TH, int TW>
-int launch(const ConvArgs& a, const float* x, const float* w, const float* bias, float* y, cudaStream_t s) {
-    constexpr int IH = (TH - 1) * S + 3, IW = (TW - 1) * S + 3;
+template <int S, int RPG>
+int launch(const ConvArgs& a, const DwTiles& shape, const float* x, const float* w, const float* bias, float* y, cudaStream_t s) {
     CUtensorMap mX;
     const cuuint64_t dims[4] = {(cuuint64_t)a.C, (cuuint64_t)a.W, (cuuint64_t)a.H, (cuuint64_t)a.N};
     const cuuint64_t str[3] = {(cuuint64_t)a.Cs * 4, (cuuint64_t)a.Cs * 4 * a.W, (cuuint64_t)a.Cs * 4 * a.W * a.H};
-    const cuuint32_t box[4] = {32, IW, IH, 1};
+    const cuuint32_t box[4] = {32, (cuuint32_t)shape.iw, (cuuint32_t)shape.ih, 1};
     const cuuint32_t es[4] = {1, 1, 1, 1};
     if (!make_map_sw(CU_TENSOR_MAP_SWIZZLE_NONE, &mX, x, 4, dims, str, box, es)) return OGLE_ERR_CUDA;
-    DwTiles tl;
-    tl.tiles_x = (a.Wo + TW - 1) / TW;
-    tl.tiles_y = (a.Ho + TH - 1) / TH;
+    DwTiles tl = shape;
+    tl.tiles_x = (a.Wo + tl.tw - 1) / tl.tw;
+    tl.tiles_y = (a.Ho + tl.th - 1) / tl.th;
     tl.cblocks = a.K / 32;
     tl.total = (long)tl.tiles_x * tl.tiles_y * tl.cblocks * a.N;
-    const size_t smem = 2 * (size_t)IH * IW * 8 * 16 + 128;
+    const size_t smem = 2 * (size_t)tl.ih * tl.iw * 8 * 16 + 128;
     static thread_local int attr_device = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (attr_device != dev) {
-        cudaError_t e = cudaFuncSetAttribute(dw3x3_tma_kernel<S, TH, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(dw3x3_tma_kernel<S, RPG>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDwSmemMax);
         if (e != cudaSuccess) { set_last_error(e); return OGLE_ERR_CUDA; }
         attr_device = dev;
     }
     long blocks = (long)kNumSMs * 2;
     if (blocks > tl.total) blocks = tl.total;
-    dw3x3_tma_kernel<S, TH, TW><<<(unsigned)blocks, 256, smem, s>>>(mX, reinterpret_cast<const float4*>(w), bias,
-                                                                   reinterpret_cast<float4*>(y), a, tl, error_flag_ptr());
+    dw3x3_tma_kernel<S, RPG><<<(unsigned)blocks, 256, smem, s>>>(mX, reinterpret_cast<const float4*>(w), bias,
+                                                               reinterpret_cast<float4*>(y), a, tl, error_flag_ptr());
     return finish_launch();
+}
+
+// Tile shape for a map: full-width tiles when the map is at most 32 wide; the rows per
+// thread (one of the compiled RPG values) that leaves the fewest idle output rows.
+// Returns the chosen RPG, or 0 when no shape fits two stages in kDwSmemMax.
+int choose_shape(const ConvArgs& a, DwTiles* t) {
+    const int S = a.stride;
+    const int tw = a.Wo <= 32 ? a.Wo : (S == 1 ? 32 : 16);
+    const int groups = 32 / tw;
+    static const int kRpg1[] = {10, 8, 5, 4, 2}, kRpg2[] = {5, 4, 2};
+    const int* cand = S == 1 ? kRpg1 : kRpg2;
+    const int ncand = S == 1 ? 5 : 3;
+    int best = 0;
+    long best_cost = -1;
+    for (int i = 0; i < ncand; ++i) {
+        const int rpg = cand[i], th = rpg * groups;
+        const int iw = (tw - 1) * S + 3, ih = (th - 1) * S + 3;
+        if (iw > 256 || ih > 256) continue;
+        if (2 * (size_t)ih * iw * 128 + 128 > (size_t)kDwSmemMax) continue;
+        const long tiles_y = (a.Ho + th - 1) / th;
+        // rows computed (idle ones included) plus a charge per tile for its halo rows
+        const long cost = tiles_y * (th * S + 2);
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost; best = rpg;
+            t->tw = tw; t->th = th; t->row_groups = groups; t->iw = iw; t->ih = ih;
+        }
+    }
+    return best;
 }
 
 }  // namespace
 
 bool dw_tma_supported(const ConvArgs& a) {
-    return a.kernel == 3 && a.dil == 1 && a.pad <= 1 && (a.stride == 1 || a.stride == 2) && a.K % 32 == 0 &&
-           a.C == a.K && a.Wo >= 16 && a.Ho >= 8 && encode_fn() != nullptr;
+    if (!(a.kernel == 3 && a.dil == 1 && a.pad <= 1 && (a.stride == 1 || a.stride == 2) && a.K % 32 == 0 && a.C == a.K &&
+          a.Wo >= 8 && a.Ho >= 4 && encode_fn() != nullptr))
+        return false;
+    DwTiles t;
+    return choose_shape(a, &t) != 0;
 }
 
 int launch_dw_tma(const ConvArgs& a, const float* x, const float* w, const float* bias, float* y, cudaStream_t s) {
-    if (a.stride == 1) return launch<1, 8, 32>(a, x, w, bias, y, s);
-    return launch<2, 4, 16>(a, x, w, bias, y, s);
+    DwTiles t = {};
+    const int rpg = choose_shape(a, &t);
+    if (a.stride == 1) {
+        switch (rpg) {
+            case 10: return launch<1, 10>(a, t, x, w, bias, y, s);
+            case 8: return launch<1, 8>(a, t, x, w, bias, y, s);
+            case 5: return launch<1, 5>(a, t, x, w, bias, y, s);
+            case 4: return launch<1, 4>(a, t, x, w, bias, y, s);
+            case 2: return launch<1, 2>(a, t, x, w, bias, y, s);
+        }
+    } else {
+        switch (rpg) {
+            case 5: return launch<2, 5>(a, t, x, w, bias, y, s);
+            case 4: return launch<2, 4>(a, t, x, w, bias, y, s);
+            case 2: return launch<2, 2>(a, t, x, w, bias, y, s);
+        }
+    }
+    return OGLE_ERR_UNSUPPORTED;
 }
 
 }  // namespace ogle

@@ -33,6 +33,14 @@ struct TcArgs {
     int total_tiles;          // m_tiles * n_tiles (persistent kernel)
     int epi_groups, xf_groups; // persistent kernel: warp groups per role (1 or 2)
     int epi_slabs;            // staging slabs (128 rows x 32 columns) per epilogue group (1 or 2)
+    // Two outputs from one pass (sibling convolutions over the same input, filters stacked):
+    // columns [0, K1) go to the first tensor, columns [split_col, K) to the second.
+    // split_col is a multiple of 32 (0 = single output).
+    int split_col, K1;
+    // 3-pass mode, BN <= 128: the hi and lo filter tiles sit back to back in a stage, so
+    // A_hi x [B_hi; B_lo] is ONE instruction of width 2*BN whose two halves are summed by the
+    // epilogue; with A_lo x B_hi that is two instructions per K step instead of three.
+    int ncat;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -134,6 +142,28 @@ __device__ __forceinline__ void umma_tf32_chunk_split(uint32_t tmem_d, uint64_t 
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], l, b, %5, q;\n\t"
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], a, m, %5, q;\n\t}"
         ::"r"(tmem_d), "l"(ad), "l"(al), "l"(bd), "l"(bl), "r"(idesc), "r"(accumulate_first) : "memory");
+}
+
+// 3-pass mode with the two filter halves read as one operand of width 2*BN (idesc2):
+// [hi*hi | hi*lo] in one instruction, then lo*hi (idesc1) onto the first half.
+__device__ __forceinline__ void umma_tf32_chunk_cat(uint32_t tmem_d, uint64_t ad, uint64_t al, uint64_t bd,
+                                                    uint32_t idesc2, uint32_t idesc1, uint32_t accumulate_first) {
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 a, l, b;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "setp.eq.b32 q, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %3, %4, p;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %2, %3, %5, q;\n\t"
+        "add.s64 a, %1, 2;\n\tadd.s64 l, %2, 2;\n\tadd.s64 b, %3, 2;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a, b, %4, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], l, b, %5, q;\n\t"
+        "add.s64 a, %1, 4;\n\tadd.s64 l, %2, 4;\n\tadd.s64 b, %3, 4;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a, b, %4, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], l, b, %5, q;\n\t"
+        "add.s64 a, %1, 6;\n\tadd.s64 l, %2, 6;\n\tadd.s64 b, %3, 6;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a, b, %4, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], l, b, %5, q;\n\t}"
+        ::"r"(tmem_d), "l"(ad), "l"(al), "l"(bd), "r"(idesc2), "r"(idesc1), "r"(accumulate_first) : "memory");
 }
 
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {

@@ -89,6 +89,8 @@ int ogle_session_set_option(OgleSession* s, const char* key, int value) {
             s->session->context()->set_math_mode(value);
         } else if (k == "use_graph") {
             s->session->set_use_graph(value != 0);
+        } else if (k == "fuse_siblings") {
+            s->session->set_fuse_siblings(value != 0);
         } else {
             OGLE_FATAL() << "unknown option " << k;
         }

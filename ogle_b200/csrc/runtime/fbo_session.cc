@@ -15,6 +15,7 @@ namespace ogle {
 
 FBOSession::FBOSession(Context* context) : context_(context) {
     if (const char* g = std::getenv("OGLE_USE_GRAPH")) use_graph_ = std::atoi(g) != 0;
+    if (const char* g = std::getenv("OGLE_FUSE_SIBLINGS")) fuse_siblings_ = std::atoi(g) != 0;
 }
 
 FBOSession::~FBOSession() {
@@ -140,8 +141,24 @@ void FBOSession::Finalize() {
             active_.push_back(kernel);
         }
     }
+    if (fuse_siblings_) FuseSiblings();
     context_->Synchronize();
     finalized_ = true;
+}
+
+void FBOSession::FuseSiblings() {
+    // A later node may run early, at its sibling's place: it reads only what the sibling
+    // reads, every tensor has its own memory, and its consumers still come after it.
+    num_fused_ = 0;
+    for (size_t i = 0; i < active_.size(); ++i) {
+        for (size_t j = i + 1; j < active_.size(); ++j) {
+            if (active_[j]->kernel_type() != active_[i]->kernel_type()) continue;
+            if (!active_[i]->AbsorbSibling(active_[j])) continue;
+            active_.erase(active_.begin() + long(j));
+            ++num_fused_;
+            break;      // pairs only
+        }
+    }
 }
 
 bool FBOSession::CheckKernelReady(const Kernel* kernel) {

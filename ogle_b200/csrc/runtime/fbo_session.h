@@ -57,6 +57,11 @@ public:
     // CUDA-graph replay of the steady state (default on; OGLE_USE_GRAPH=0 disables).
     void set_use_graph(bool flag);
     bool graph_captured() const { return graph_exec_ != nullptr; }
+    // Sibling fusion: nodes that read the same input with the same window (the SSD box and
+    // class heads) run as one pass (default on; OGLE_FUSE_SIBLINGS=0 disables). Set before
+    // the first Run.
+    void set_fuse_siblings(bool flag) { fuse_siblings_ = flag; }
+    int num_fused() const { return num_fused_; }
     // Nodes executed per Run (not pre-computed, not aliases).
     int num_active_kernels() const;
     // One eager pass with an event pair around every node; the per-node table the
@@ -70,6 +75,7 @@ private:
     void UpdateKernelReady(const Kernel* kernel);
     void UploadInputs(const NamedTensorList& inputs_cpu);
     void Finalize();
+    void FuseSiblings();
     void Execute();
     void DropGraph();
 
@@ -85,6 +91,8 @@ private:
     bool allow_resized_ = false;
     IntList default_input_sizes_;
     bool use_graph_ = true;
+    bool fuse_siblings_ = true;
+    int num_fused_ = 0;
     int eager_runs_ = 0;
     CUgraphExec_st* graph_exec_ = nullptr;
     size_t device_bytes_ = 0;

@@ -45,6 +45,10 @@ public:
     virtual void SelectKernel(const TensorList& inputs) {}
     // True when Compute only aliases/keeps memory and launches nothing.
     virtual bool IsNoOp() const { return false; }
+    // Offered a later node of the steady-state sequence: return true to take over its work
+    // (this kernel's Compute then also writes that node's outputs, and the session drops
+    // the later node from the sequence).
+    virtual bool AbsorbSibling(Kernel* later) { return false; }
 
 protected:
     Context* context_;

@@ -75,7 +75,11 @@ REGISTER_KERNEL_WITH_NAME(ConstKernel, "Constant");
 class Conv2DKernel : public Kernel {
 public:
     explicit Conv2DKernel(Context* c) : Kernel(c) {}
-    ~Conv2DKernel() override { if (packed_) cudaFree(packed_); }
+    ~Conv2DKernel() override {
+        if (packed_) cudaFree(packed_);
+        if (pair_packed_) cudaFree(pair_packed_);
+        if (pair_bias_) cudaFree(pair_bias_);
+    }
 
     void SetupAttr(const dlxnet::Attribute& attr) override {
         const auto& p = attr.conv2d_attr;
@@ -147,7 +151,61 @@ public:
         output_shapes[0] = {image_shape[0], params_.out_hwc[0], params_.out_hwc[1], filter_shape[0]};
     }
 
+    // Two convolutions over one feature map with the same window and constant filters run as
+    // one pass: the filters are stacked (first conv's rows, zero rows up to a multiple of 32,
+    // second conv's rows) and packed once; Compute then writes both nodes' outputs.
+    bool AbsorbSibling(Kernel* later) override {
+        auto* o = dynamic_cast<Conv2DKernel*>(later);
+        if (!o || o == this || sibling_ || o->sibling_) return false;
+        if (!filter_is_constant_ || !o->filter_is_constant_) return false;
+        if (input_tensors_.size() != o->input_tensors_.size() || input_tensors_[0] != o->input_tensors_[0]) return false;
+        const OgleConvParams &a = params_, &b = o->params_;
+        if (a.group != 1 || b.group != 1 || a.kernel != b.kernel || a.stride != b.stride || a.pad != b.pad ||
+            a.dilation != b.dilation || a.act != b.act || a.min_value != b.min_value || a.max_value != b.max_value ||
+            a.math_mode != b.math_mode || a.has_bias != b.has_bias)
+            return false;
+        if (a.has_bias && !(session_->IsTensorReady(input_tensor_indexes_[2]) && session_->IsTensorReady(o->input_tensor_indexes_[2])))
+            return false;
+        const int K1 = a.out_hwc[2], K2 = b.out_hwc[2], split = (K1 + 31) / 32 * 32;
+        OgleConvParams f = a;
+        f.out_hwc[2] = split + K2;
+        if (!ogle_cuda_conv2d_pair_supported(&f)) return false;
+        cudaStream_t s = reinterpret_cast<cudaStream_t>(context_->stream());
+        const size_t row = size_t(a.in_hwc[2]) * a.kernel * a.kernel;      // floats per output channel (OIHW)
+        float* stacked = nullptr;
+        auto ok = [](cudaError_t e) { OGLE_CHECK(e == cudaSuccess) << "sibling fusion: " << cudaGetErrorString(e); };
+        ok(cudaMalloc(&stacked, size_t(split + K2) * row * 4));
+        ok(cudaMemsetAsync(stacked, 0, size_t(split + K2) * row * 4, s));
+        ok(cudaMemcpyAsync(stacked, input_tensors_[1]->device<float>(), size_t(K1) * row * 4, cudaMemcpyDeviceToDevice, s));
+        ok(cudaMemcpyAsync(stacked + size_t(split) * row, o->input_tensors_[1]->device<float>(), size_t(K2) * row * 4,
+                           cudaMemcpyDeviceToDevice, s));
+        const size_t bytes = ogle_cuda_conv2d_filter_bytes(&f);
+        OGLE_CHECK_GT(bytes, 0u);
+        ok(cudaMalloc(&pair_packed_, bytes));
+        OGLE_CUDA_OK(ogle_cuda_conv2d_prepack(&f, stacked, pair_packed_, context_->stream()));
+        if (a.has_bias) {
+            ok(cudaMalloc(&pair_bias_, size_t(split + K2 + 4) * 4));
+            ok(cudaMemsetAsync(pair_bias_, 0, size_t(split + K2 + 4) * 4, s));
+            ok(cudaMemcpyAsync(pair_bias_, input_tensors_[2]->device<float>(), size_t(K1) * 4, cudaMemcpyDeviceToDevice, s));
+            ok(cudaMemcpyAsync(pair_bias_ + split, o->input_tensors_[2]->device<float>(), size_t(K2) * 4, cudaMemcpyDeviceToDevice, s));
+        }
+        ok(cudaStreamSynchronize(s));
+        cudaFree(stacked);
+        pair_params_ = f;
+        pair_k1_ = K1;
+        pair_split_ = split;
+        sibling_ = o;
+        kernel_name_ += "+" + o->kernel_name_;
+        return true;
+    }
+
     void Compute(TensorList& inputs, TensorList& outputs) override {
+        if (sibling_) {
+            OGLE_CUDA_OK(ogle_cuda_conv2d_pair(&pair_params_, inputs[0]->device<float>(), pair_packed_, pair_bias_, pair_k1_,
+                                               pair_split_, outputs[0]->device<float>(),
+                                               sibling_->output_tensors_[0]->device<float>(), context_->stream()));
+            return;
+        }
         if (!filter_is_constant_)
             OGLE_CUDA_OK(ogle_cuda_conv2d_prepack(&params_, inputs[1]->device<float>(), packed_, context_->stream()));
         const float* bias = inputs.size() > 2 ? inputs[2]->device<float>() : nullptr;
@@ -162,6 +220,11 @@ private:
     OgleConvParams params_;
     void* packed_ = nullptr;
     bool filter_is_constant_ = false;
+    Conv2DKernel* sibling_ = nullptr;       // absorbed later node (not owned)
+    OgleConvParams pair_params_;
+    void* pair_packed_ = nullptr;
+    float* pair_bias_ = nullptr;
+    int pair_k1_ = 0, pair_split_ = 0;
 };
 REGISTER_KERNEL_WITH_NAME(Conv2DKernel, "Conv");
 

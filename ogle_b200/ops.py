@@ -98,6 +98,34 @@ def conv2d(p, x4, packed, bias=None, out=None):
     return out
 
 
+def conv2d_pair(x4, w1, b1, w2, b2, N, H, W, Cin, kernel, stride=1, pad=0, dilation=1, act=ACT_NONE, lo=0.0, hi=0.0,
+                math_mode=MATH_TF32X3):
+    """Two convolutions over the same input in one pass (w1/w2 dense OIHW device tensors, b1/b2 device
+    vectors or None). Returns (y1, y2) as padded NHWC4 device tensors."""
+    _require_cuda(x4, w1, w2, b1, b2)
+    K1, K2 = w1.shape[0], w2.shape[0]
+    split = (K1 + 31) // 32 * 32
+    w = torch.zeros((split + K2,) + tuple(w1.shape[1:]), dtype=torch.float32, device="cuda")
+    w[:K1] = w1
+    w[split:] = w2
+    bias = None
+    if b1 is not None:
+        bias = torch.zeros(split + K2, dtype=torch.float32, device="cuda")
+        bias[:K1] = b1[:K1]
+        bias[split:] = b2[:K2]
+    p = conv_params(N, H, W, Cin, split + K2, kernel, stride, pad, dilation, 1, bias is not None, act, lo, hi, math_mode)
+    lib = _lib.cuda_lib()
+    if not lib.ogle_cuda_conv2d_pair_supported(C.byref(p)):
+        raise _lib.OgleError("conv2d_pair: these parameters are not served by the tensor-core path")
+    packed = conv2d_prepack(p, w)
+    Ho, Wo, _ = p.out_hwc
+    y1 = torch.full((N, Ho, Wo, up4(K1)), float("nan"), dtype=torch.float32, device="cuda")
+    y2 = torch.full((N, Ho, Wo, up4(K2)), float("nan"), dtype=torch.float32, device="cuda")
+    check(lib.ogle_cuda_conv2d_pair(C.byref(p), _p(x4), _p(packed), _p(bias), K1, split, _p(y1), _p(y2), _stream()),
+          "conv2d_pair")
+    return y1, y2
+
+
 def pool_params(N, H, W, Cc, kernel, stride, pad, type_):
     p = PoolParams()
     p.N = N

@@ -86,6 +86,85 @@ def test_conv_mobilenet_layer_shapes(oracle_port):
         close(got, ref, atol=1e-4, rtol=1e-4)
 
 
+TC_SHAPES = [  # N, H, C, K, k, s, p, act
+    (2, 38, 256, 256, 3, 1, 1, 2), (2, 19, 512, 1024, 1, 1, 0, 2), (2, 19, 512, 126, 3, 1, 1, 0),
+    (2, 10, 1024, 24, 3, 1, 1, 0), (2, 10, 256, 512, 3, 2, 1, 2), (3, 75, 64, 128, 1, 1, 0, 1),
+    (2, 3, 256, 126, 3, 1, 1, 0), (5, 1, 128, 24, 3, 1, 1, 0), (2, 19, 512, 63, 3, 1, 1, 0),
+    (2, 19, 512, 12, 3, 1, 1, 0), (1, 150, 32, 64, 1, 1, 0, 1), (2, 20, 40, 300, 1, 1, 0, 2),
+    (2, 17, 24, 70, 5, 2, 2, 2),
+]
+
+
+def test_conv_tensor_core_modes(oracle_port):
+    """The tcgen05 path per layer shape, outputs of magnitude ~1-4. 3xTF32 (hi/lo operand split):
+    the tensor core truncates its fp32 accumulator at every step instead of rounding, so the
+    error grows with the reduction length (up to 9216 here); bound 3e-4 absolute, inside the 1e-3
+    target. One-pass TF32 (10-bit operands) is held to 2e-3 of the output's largest magnitude."""
+    from gpu_ops import run_case_cuda
+    from ogle_b200 import _lib, ops
+    rng = np.random.default_rng(31)
+    for N, H, C, K, k, s, p, act in TC_SHAPES:
+        x = rng.standard_normal((N, H, H, C), dtype=np.float32)
+        w = rng.standard_normal((K, C, k, k), dtype=np.float32) * np.float32(1.0 / np.sqrt(C * k * k))
+        b = rng.standard_normal(K, dtype=np.float32) * np.float32(0.05)
+        case = dict(op="conv2d", x=x, w=w, bias=b, stride=s, pad=p, dilation=1, group=1, act=act, lo=0.0, hi=6.0)
+        ref = oracle_port.conv2d(x, w, b, s, p, 1, 1, act, 0.0, 6.0)
+        scale = np.abs(ref).max()
+        got = run_case_cuda(case, ops.MATH_TF32X3)
+        assert np.abs(got - ref).max() <= 3e-4, (N, H, C, K, k, float(np.abs(got - ref).max()))
+        got = run_case_cuda(case, ops.MATH_TF32)
+        assert np.abs(got - ref).max() / scale <= 2e-3, (N, H, C, K, k)
+    assert _lib.cuda_lib().ogle_cuda_device_status() == 0
+
+
+def test_conv_pair_equals_two_convs(oracle_port):
+    """Sibling convolutions (the SSD box and class heads of one feature map) in one pass. One-pass
+    TF32 accumulates each output in the same order whatever the tile width, so it must be
+    bit-identical to the single-output entry point (padded lanes included); the 3-pass mode may
+    order its three partial sums differently and is held to 2e-5 and to the oracle."""
+    import torch
+    from ogle_b200 import _lib, ops
+    rng = np.random.default_rng(32)
+    for (N, H, C, K1, K2, k, pad) in [(2, 19, 512, 12, 63, 3, 1), (2, 10, 1024, 24, 126, 3, 1), (3, 5, 512, 24, 126, 3, 1),
+                                      (4, 1, 128, 24, 126, 3, 1), (2, 19, 64, 33, 7, 1, 0), (2, 9, 96, 64, 64, 3, 1)]:
+        x = rng.standard_normal((N, H, H, C), dtype=np.float32)
+        w1 = rng.standard_normal((K1, C, k, k), dtype=np.float32) * np.float32(1.0 / np.sqrt(C * k * k))
+        w2 = rng.standard_normal((K2, C, k, k), dtype=np.float32) * np.float32(1.0 / np.sqrt(C * k * k))
+        b1 = rng.standard_normal(K1, dtype=np.float32)
+        b2 = rng.standard_normal(K2, dtype=np.float32)
+        x4 = ops.upload(x)
+        d = ops.dense_to_device
+        for mode in (ops.MATH_TF32X3, ops.MATH_TF32):
+            y1, y2 = ops.conv2d_pair(x4, d(w1), d(b1), d(w2), d(b2), N, H, H, C, k, 1, pad, math_mode=mode)
+            for (w, b, K, y) in ((w1, b1, K1, y1), (w2, b2, K2, y2)):
+                p = ops.conv_params(N, H, H, C, K, k, 1, pad, math_mode=mode)
+                want = ops.conv2d(p, x4, ops.conv2d_prepack(p, d(w)), d(b))
+                if mode == ops.MATH_TF32:
+                    assert torch.equal(y, want), (N, H, C, K1, K2, mode)
+                else:
+                    assert float((y - want).abs().max()) <= 2e-5, (N, H, C, K1, K2, mode)
+                    assert torch.equal(y[..., K:], want[..., K:])
+            if mode == ops.MATH_TF32X3:
+                assert np.abs(ops.download(y2, K2) - oracle_port.conv2d(x, w2, b2, 1, pad)).max() <= 3e-4
+    assert _lib.cuda_lib().ogle_cuda_device_status() == 0
+
+
+def test_depthwise_tile_shapes(oracle_port):
+    """Depthwise 3x3 over the map sizes of the SSD-300 backbone and some ragged ones: every tile
+    shape of the TMA kernel (full-width tiles of 19 and 10 columns, 32/16-column tiles with ragged
+    edges, stride 1 and 2, with and without padding) and the register-tiled fallback."""
+    from gpu_ops import run_case_cuda
+    rng = np.random.default_rng(41)
+    for (N, H, W, C, s, p) in [(2, 19, 19, 64, 1, 1), (2, 38, 38, 32, 2, 1), (3, 10, 10, 96, 1, 1), (2, 19, 19, 32, 2, 1),
+                               (1, 150, 150, 32, 1, 1), (1, 150, 150, 64, 2, 1), (2, 33, 45, 32, 1, 1), (2, 70, 41, 64, 2, 1),
+                               (2, 21, 12, 32, 1, 0), (2, 9, 8, 32, 1, 1), (1, 40, 40, 36, 1, 1)]:
+        x = rng.standard_normal((N, H, W, C), dtype=np.float32)
+        w = rng.standard_normal((C, 1, 3, 3), dtype=np.float32) * np.float32(0.3)
+        b = rng.standard_normal(C, dtype=np.float32)
+        case = dict(op="conv2d", x=x, w=w, bias=b, stride=s, pad=p, dilation=1, group=C, act=2, lo=0.0, hi=6.0)
+        close(run_case_cuda(case), oracle_port.conv2d(x, w, b, s, p, 1, C, 2, 0.0, 6.0), atol=1e-5, rtol=1e-5)
+
+
 def test_conv_in_place_concat_offsets(oracle_port):
     """Two producers write their channels straight into one wider tensor (concat in place)."""
     import torch

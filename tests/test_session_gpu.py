@@ -103,6 +103,32 @@ def test_mobilenet_ssd_feature_maps_and_outputs(oracle_port, math_mode, bound):
     sess.close()
 
 
+def test_sibling_fusion_is_transparent():
+    """The six box/class head pairs of the SSD graph run as six passes instead of twelve; switching
+    the fusion off gives the same tensors (bit-identical in one-pass TF32; 3xTF32 may order its
+    partial sums differently: 1e-5 of the tensor's scale)."""
+    from ogle_b200 import models, session
+    model, _ = models.mobilenet_v1_ssd(batch=2, num_classes=21, seed=6, weight_std="he")
+    x = ((np.random.default_rng(36).random((2, 300, 300, 3), dtype=np.float32) - 0.5) / 0.5).astype(np.float32)
+    for mode in (1, 2):
+        outs, counts = [], []
+        for fuse in (1, 0):
+            sess = session.FBOSession()
+            sess.set_option("math_mode", mode)
+            sess.set_option("fuse_siblings", fuse)
+            sess.LoadGraph(model)
+            sess.Run({"input": x})
+            outs.append(sess.GetOutputs(["cls_logits", "box_preds"], ["ANY", "ANY"]))
+            counts.append(sess.num_active_kernels())
+            sess.close()
+        assert counts[1] - counts[0] == 6
+        for a, b in zip(*outs):
+            if mode == 1:
+                assert np.array_equal(a, b)
+            else:
+                assert np.abs(a - b).max() <= 1e-5 * max(1.0, np.abs(b).max())
+
+
 def test_mobilenet_ssd_config0_batch1_two_classes(oracle_port):
     """The reference's own CPU-runnable case: batch 1, 2 classes, N(0,0.02) weights."""
     from ogle_b200 import models, session

@@ -1,115 +1,243 @@
 // Direct 3x3 convolution for inputs of at most four channels (the RGB stem of an image
 // network: 3 -> 32 channels, stride 2). With so few input channels the implicit-GEMM
-// kernels waste their tiles on padding; here the work is laid out for the memory system
-// instead: the layer moves 16 bytes in and (at stride 2) 32 bytes out per input pixel and
-// is bound by HBM once the arithmetic (27 multiply-adds per output value) is kept on
-// registers.
+// kernels waste their tiles on padding. This layer moves 16 bytes in and (at stride 2)
+// 32 bytes out per input pixel while doing 27 multiply-adds per output value, so HBM and
+// the FP32 pipes bound it about equally; the kernel is built to keep both busy:
 //
-// One thread computes two horizontally adjacent output pixels x eight output channels:
-// the input patch (3 rows x 3 + stride columns, one float4 per pixel) sits in registers,
-// the filter [tap][c][K] in shared memory is read as 128-bit vectors that serve both
-// pixels, and the threads that share a pixel pair read the same input addresses (one
-// transaction). A warp writes 128-byte output rows of 32 channels in full sectors.
-#include "conv_args.cuh"
+//  * persistent blocks walk a list of tiles (rows x columns of one image); the input
+//    window of a tile, halo included, is ONE TMA box of 16-byte pixels whose out-of-image
+//    part arrives as zeros (the padding); two stages, so the next tile loads while this
+//    one is computed;
+//  * a warp owns a run of PL*PXT output pixels of one row, PL = 32 / (K/8) pixel lanes x
+//    K/8 channel groups: a thread accumulates PXT pixels (interleaved across the lanes,
+//    which makes the shared-memory reads conflict-free) x 8 channels in registers;
+//  * per filter tap the thread reads its 8x3 weights once (128-bit shared loads) and one
+//    float4 per pixel: about one load per eleven multiply-adds, no bounds checks and no
+//    address arithmetic in the inner loop.
+#include "tc_common.cuh"
+#include "tma_host.h"
 
 namespace ogle {
-
 namespace {
 
-template <int S>
-__global__ void __launch_bounds__(256)
-conv3x3_smallc_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
-                      float* __restrict__ y, const ConvArgs a, const int kgroups, const long items) {
-    extern __shared__ float4 s_w4[];                 // [9][C][Kp] floats, then [Kp] bias
-    float* s_w = reinterpret_cast<float*>(s_w4);
-    const int wn = 9 * a.C * a.Kp;
+using namespace tc;
+
+constexpr int kStemSmemMax = 100 * 1024;
+
+struct StemTiles {
+    int kgroups, pl;                 // channel groups of 8; pixel lanes per warp
+    int segs, rows;                  // warps of a tile: segs across, rows down
+    int seg_px;                      // output pixels per warp = pl * PXT
+    int tiles_x, tiles_y;
+    int iw, ih;                      // input window of a tile
+    long total;
+};
+
+template <int S, int PXT, int CIN>
+__global__ void __launch_bounds__(256, 2)
+conv3x3_smallc_kernel(const __grid_constant__ CUtensorMap tmX, const float* __restrict__ w, const float* __restrict__ bias,
+                      float* __restrict__ y, const ConvArgs a, const StemTiles tl, int* err_flag) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[2];
+    // weights [9][CIN][Kp] + bias [Kp], then the two input stages (128-byte aligned)
+    float* s_w = reinterpret_cast<float*>(smem_raw);
+    const int wn = 9 * CIN * a.Kp;
+    const uint32_t w_bytes = (uint32_t)((wn + a.Kp) * 4 + 127) & ~127u;
+    const uint32_t stage_bytes = (uint32_t)(tl.ih * tl.iw * 16);      // what one TMA box delivers
+    const uint32_t stage_pitch = (stage_bytes + 127u) & ~127u;        // TMA destinations are 128-byte aligned
+    const uint32_t base = smem_u32(smem_raw) + w_bytes;
+    const float4* stage0 = reinterpret_cast<const float4*>(smem_raw + w_bytes);
+
     for (int i = threadIdx.x; i < wn; i += blockDim.x) {
-        const int k = i % a.Kp, c = (i / a.Kp) % a.C, tap = i / (a.Kp * a.C);
-        s_w[i] = w[(tap * a.Cp + c) * a.Kp + k];     // tap-major packed filter, channels past C dropped
+        const int k = i % a.Kp, c = (i / a.Kp) % CIN, tap = i / (a.Kp * CIN);
+        s_w[i] = c < a.C ? w[(tap * a.Cp + c) * a.Kp + k] : 0.f;     // tap-major packed filter
     }
     for (int i = threadIdx.x; i < a.Kp; i += blockDim.x) s_w[wn + i] = (a.has_bias && i < a.K) ? bias[i] : 0.f;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar_full[0], 1);
+        mbar_init(&bar_full[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     __syncthreads();
 
-    constexpr int PW = 3 + S;                         // patch columns for two outputs
-    const int wpairs = (a.Wo + 1) / 2;
-    const long item = (long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (item >= items) return;
-    long t = item;
-    const int kg = int(t % kgroups); t /= kgroups;
-    const int wp = int(t % wpairs); t /= wpairs;
-    const int ho = int(t % a.Ho);
-    const int n = int(t / a.Ho);
-    const int wo = wp * 2;
-    const int iy0 = ho * S - a.pad, ix0 = wo * S - a.pad;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kg = lane % tl.kgroups, pl = lane / tl.kgroups;
+    const int seg = warp % tl.segs, row = warp / tl.segs;
+    const bool active = row < tl.rows;
+    const float* wk = s_w + kg * 8;
+    const int tile_px = tl.segs * tl.seg_px;        // output columns per tile
 
-    float acc[2][8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { acc[0][j] = s_w[wn + kg * 8 + j]; acc[1][j] = acc[0][j]; }
+    auto issue = [&](long tile, int stage) {
+        long t = tile;
+        const int tx = (int)(t % tl.tiles_x); t /= tl.tiles_x;
+        const int ty = (int)(t % tl.tiles_y); t /= tl.tiles_y;
+        mbar_expect_tx(&bar_full[stage], stage_bytes);
+        tma_load_4d(base + (uint32_t)stage * stage_pitch, &tmX, &bar_full[stage], 0, tx * tile_px * S - a.pad,
+                    ty * tl.rows * S - a.pad, (int)t);
+    };
 
-#pragma unroll
-    for (int r = 0; r < 3; ++r) {
-        const int iy = iy0 + r;
-        float4 p[PW];
-#pragma unroll
-        for (int cidx = 0; cidx < PW; ++cidx) {
-            const int ix = ix0 + cidx;
-            p[cidx] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (iy >= 0 && iy < a.H && ix >= 0 && ix < a.W)
-                p[cidx] = __ldg(reinterpret_cast<const float4*>(x + (((long)n * a.H + iy) * a.W + ix) * a.Cs));
+    if (threadIdx.x == 0 && (long)blockIdx.x < tl.total) issue(blockIdx.x, 0);
+    long it = 0;
+    for (long tile = blockIdx.x; tile < tl.total; tile += gridDim.x, ++it) {
+        const int stage = (int)(it & 1);
+        // the other stage was last read by tile it-1, finished before the barrier below
+        if (threadIdx.x == 0 && tile + gridDim.x < tl.total) issue(tile + gridDim.x, stage ^ 1);
+        long t = tile;
+        const int tx = (int)(t % tl.tiles_x); t /= tl.tiles_x;
+        const int ty = (int)(t % tl.tiles_y); t /= tl.tiles_y;
+        const int n = (int)t;
+        if (!mbar_wait(&bar_full[stage], (uint32_t)((it >> 1) & 1))) {
+            if (threadIdx.x == 0) record_error(err_flag, 8);
+            break;   // uniform: every thread waits on the same barrier with the same bound
         }
+        if (active) {
+            const float4* tile_s = stage0 + (size_t)stage * (stage_pitch / 16);
+            float acc[PXT][8];
 #pragma unroll
-        for (int kx = 0; kx < 3; ++kx) {
-            const float* wt = s_w + ((r * 3 + kx) * a.C) * a.Kp + kg * 8;
-            const float u0[4] = {p[kx].x, p[kx].y, p[kx].z, p[kx].w};
-            const float u1[4] = {p[kx + S].x, p[kx + S].y, p[kx + S].z, p[kx + S].w};
+            for (int j = 0; j < 8; ++j) {
+                const float b = s_w[wn + kg * 8 + j];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                if (c < a.C) {
-                    const float4 f0 = *reinterpret_cast<const float4*>(wt + c * a.Kp);
-                    const float4 f1 = *reinterpret_cast<const float4*>(wt + c * a.Kp + 4);
-                    const float f[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+                for (int i = 0; i < PXT; ++i) acc[i][j] = b;
+            }
+            const int lc = seg * tl.seg_px + pl;                      // first local output column of this thread
+            const float4* prow = tile_s + (size_t)(row * S) * tl.iw + lc * S;
+            const int step = tl.pl * S;                               // input columns between this thread's pixels
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        acc[0][j] = fmaf(f[j], u0[c], acc[0][j]);
-                        acc[1][j] = fmaf(f[j], u1[c], acc[1][j]);
+            for (int ky = 0; ky < 3; ++ky) {
+#pragma unroll
+                for (int kx = 0; kx < 3; ++kx) {
+                    float f[CIN][8];
+#pragma unroll
+                    for (int c = 0; c < CIN; ++c) {
+                        const float4 f0 = *reinterpret_cast<const float4*>(wk + ((ky * 3 + kx) * CIN + c) * a.Kp);
+                        const float4 f1 = *reinterpret_cast<const float4*>(wk + ((ky * 3 + kx) * CIN + c) * a.Kp + 4);
+                        f[c][0] = f0.x; f[c][1] = f0.y; f[c][2] = f0.z; f[c][3] = f0.w;
+                        f[c][4] = f1.x; f[c][5] = f1.y; f[c][6] = f1.z; f[c][7] = f1.w;
+                    }
+                    const float4* p = prow + ky * tl.iw + kx;
+#pragma unroll
+                    for (int i = 0; i < PXT; ++i) {
+                        const float4 q = p[i * step];
+                        const float u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                        for (int c = 0; c < CIN; ++c)
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(f[c][j], u[c], acc[i][j]);
                     }
                 }
             }
+            const int oy = ty * tl.rows + row;
+            if (oy < a.Ho) {
+                float* yrow = y + (((long)n * a.Ho + oy) * a.Wo) * a.Ks + a.koff + kg * 8;
+#pragma unroll
+                for (int i = 0; i < PXT; ++i) {
+                    const int ox = tx * tile_px + lc + i * tl.pl;
+                    if (ox >= a.Wo) continue;
+                    float v[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        v[j] = apply_act(acc[i][j], a.act, a.lo, a.hi);
+                        if (kg * 8 + j >= a.K) v[j] = 0.f;           // padded lanes stay zero
+                    }
+                    float* dst = yrow + (long)ox * a.Ks;
+                    *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+                    *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+                }
+            }
         }
+        __syncthreads();
     }
+}
 
-#pragma unroll
-    for (int px = 0; px < 2; ++px) {
-        if (wo + px >= a.Wo) continue;
-        float v[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            v[j] = apply_act(acc[px][j], a.act, a.lo, a.hi);
-            if (kg * 8 + j >= a.K) v[j] = 0.f;       // padded lanes stay zero
-        }
-        float* dst = y + (((long)n * a.Ho + ho) * a.Wo + wo + px) * a.Ks + a.koff + kg * 8;
-        *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-        *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+// Tile shape: eight warps as segs x rows; a TMA box is at most 256 columns wide.
+bool choose_shape(const ConvArgs& a, int pxt, StemTiles* t) {
+    const int S = a.stride;
+    t->kgroups = a.Kp / 8;
+    t->pl = 32 / t->kgroups;
+    t->seg_px = t->pl * pxt;
+    const int segs_needed = (a.Wo + t->seg_px - 1) / t->seg_px;
+    int max_segs = ((256 - 3) / S + 1) / t->seg_px;       // box width (cols - 1) * S + 3 <= 256
+    if (max_segs > 8) max_segs = 8;
+    if (max_segs < 1) return false;
+    const int parts = (segs_needed + max_segs - 1) / max_segs;
+    t->segs = (segs_needed + parts - 1) / parts;
+    t->rows = 8 / t->segs;
+    if (t->rows > a.Ho) t->rows = a.Ho;
+    t->tiles_x = (segs_needed + t->segs - 1) / t->segs;
+    t->tiles_y = (a.Ho + t->rows - 1) / t->rows;
+    t->iw = (t->segs * t->seg_px - 1) * S + 3;
+    t->ih = (t->rows - 1) * S + 3;
+    t->total = (long)t->tiles_x * t->tiles_y * a.N;
+    const size_t smem = 2 * (((size_t)t->ih * t->iw * 16 + 127) / 128 * 128) + (size_t)(9 * 4 * a.Kp + a.Kp) * 4 + 256;
+    return t->iw <= 256 && t->ih <= 256 && smem <= (size_t)kStemSmemMax;
+}
+
+// Pixels per thread: the candidate that leaves the fewest idle pixel slots across a row.
+int choose_pxt(const ConvArgs& a, StemTiles* t) {
+    static const int cand[] = {5, 4};
+    int best = 0;
+    long best_slots = -1;
+    for (int pxt : cand) {
+        StemTiles s;
+        if (!choose_shape(a, pxt, &s)) continue;
+        const long slots = (long)s.tiles_x * s.segs * s.seg_px * s.tiles_y * s.rows;
+        if (best_slots < 0 || slots < best_slots) { best_slots = slots; best = pxt; *t = s; }
     }
+    return best;
+}
+
+template <int S, int PXT, int CIN>
+int launch(const ConvArgs& a, const StemTiles& tl, const float* x, const float* w, const float* bias, float* y, cudaStream_t s) {
+    CUtensorMap mX;
+    const cuuint64_t dims[4] = {4, (cuuint64_t)a.W, (cuuint64_t)a.H, (cuuint64_t)a.N};
+    const cuuint64_t str[3] = {(cuuint64_t)a.Cs * 4, (cuuint64_t)a.Cs * 4 * a.W, (cuuint64_t)a.Cs * 4 * a.W * a.H};
+    const cuuint32_t box[4] = {4, (cuuint32_t)tl.iw, (cuuint32_t)tl.ih, 1};
+    const cuuint32_t es[4] = {1, 1, 1, 1};
+    if (!make_map_sw(CU_TENSOR_MAP_SWIZZLE_NONE, &mX, x, 4, dims, str, box, es)) return OGLE_ERR_CUDA;
+    const size_t w_bytes = ((size_t)(9 * CIN * a.Kp + a.Kp) * 4 + 127) / 128 * 128;
+    const size_t smem = w_bytes + 2 * (((size_t)tl.ih * tl.iw * 16 + 127) / 128 * 128) + 128;
+    static thread_local int attr_device = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_device != dev) {
+        cudaError_t e = cudaFuncSetAttribute(conv3x3_smallc_kernel<S, PXT, CIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStemSmemMax);
+        if (e != cudaSuccess) { set_last_error(e); return OGLE_ERR_CUDA; }
+        attr_device = dev;
+    }
+    long blocks = (long)kNumSMs * 2;
+    if (blocks > tl.total) blocks = tl.total;
+    conv3x3_smallc_kernel<S, PXT, CIN><<<(unsigned)blocks, 256, smem, s>>>(mX, w, bias, y, a, tl, error_flag_ptr());
+    return finish_launch();
+}
+
+template <int S, int PXT>
+int launch_c(const ConvArgs& a, const StemTiles& tl, const float* x, const float* w, const float* bias, float* y, cudaStream_t s) {
+    if (a.C == 3) return launch<S, PXT, 3>(a, tl, x, w, bias, y, s);
+    return launch<S, PXT, 4>(a, tl, x, w, bias, y, s);
 }
 
 }  // namespace
 
 bool conv_smallc_supported(const ConvArgs& a) {
-    return a.group == 1 && a.kernel == 3 && a.dil == 1 && (a.stride == 1 || a.stride == 2) && a.C <= 4 && a.Cp == 4 &&
-           (a.Cs & 3) == 0 && (a.Kp == 8 || a.Kp == 16 || a.Kp == 32 || a.Kp == 64);
+    if (!(a.group == 1 && a.kernel == 3 && a.dil == 1 && (a.stride == 1 || a.stride == 2) && a.C <= 4 && a.Cp == 4 &&
+          (a.Cs & 3) == 0 && (a.Kp == 8 || a.Kp == 16 || a.Kp == 32 || a.Kp == 64) && encode_fn() != nullptr))
+        return false;
+    StemTiles t;
+    return choose_pxt(a, &t) != 0;
 }
 
 int launch_conv_smallc(const ConvArgs& a, const float* x, const float* w_tap_major, const float* bias, float* y,
                        cudaStream_t s) {
-    const int kgroups = a.Kp / 8;
-    const long items = (long)a.N * a.Ho * ((a.Wo + 1) / 2) * kgroups;
-    const long blocks = (items + 255) / 256;
-    if (blocks > 0x7fffffffL) return OGLE_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(9 * a.C * a.Kp + a.Kp) * sizeof(float);
-    if (a.stride == 1) conv3x3_smallc_kernel<1><<<(unsigned)blocks, 256, smem, s>>>(x, w_tap_major, bias, y, a, kgroups, items);
-    else conv3x3_smallc_kernel<2><<<(unsigned)blocks, 256, smem, s>>>(x, w_tap_major, bias, y, a, kgroups, items);
-    return finish_launch();
+    StemTiles t = {};
+    const int pxt = choose_pxt(a, &t);
+    if (a.stride == 1) {
+        if (pxt == 5) return launch_c<1, 5>(a, t, x, w_tap_major, bias, y, s);
+        if (pxt == 4) return launch_c<1, 4>(a, t, x, w_tap_major, bias, y, s);
+    } else {
+        if (pxt == 5) return launch_c<2, 5>(a, t, x, w_tap_major, bias, y, s);
+        if (pxt == 4) return launch_c<2, 4>(a, t, x, w_tap_major, bias, y, s);
+    }
+    return OGLE_ERR_UNSUPPORTED;
 }
 
 }  // namespace ogle

@@ -302,7 +302,9 @@ def main():
         reps = 3
         for _ in range(reps):
             for name, type_, kernel, t_ms in sess.Profile({"input": host[0].numpy()}):
-                f = fam.setdefault(kernel, dict(ms=0.0, launches=0, flops=0, bytes=0))
+                # conv nodes report "family:device kernel"; group by the device kernel
+                key = kernel.split(":")[1] if ":" in kernel else kernel
+                f = fam.setdefault(key, dict(ms=0.0, launches=0, flops=0, bytes=0))
                 f["ms"] += t_ms
                 f["launches"] += 1
                 for part in name.split("+"):        # a fused sibling pair reports as "first+second"
@@ -314,22 +316,27 @@ def main():
         sec = f["ms"] / 1000.0
         gbs = f["bytes"] / sec / 1e9
         tfl = f["flops"] / sec / 1e12
+        # TF32 runs at half the bf16 rate on these tensor cores; the 3-pass mode issues three
+        # TF32 products per useful multiply-add
         tf32_peak = peaks["bf16_tflops_sustained"] / 2.0
         passes = {0: None, 1: 1, 2: 3}[MATH[args.math]]
         tensor_peak = tf32_peak / passes if passes else None
         hbm_frac = gbs / peaks["hbm_gbs"]
-        ten_frac = tfl / tensor_peak if tensor_peak else 0.0
+        ten_frac = tfl / tensor_peak if (tensor_peak and "tc" in top) else 0.0
         if ten_frac > hbm_frac:
-            roof = {"bound": "tensor", "achieved": tfl, "peak": tensor_peak, "unit": "TFLOP/s", "frac": ten_frac}
+            roof = {"bound": "tensor", "achieved": tfl, "peak": tensor_peak, "unit": "TFLOP/s", "frac": ten_frac,
+                    "hbm_frac": hbm_frac}
         else:
             roof = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": hbm_frac}
+        per_launch_bytes = f["bytes"] / f["launches"]
         roof.update({"kernel": top, "launches_per_step": f["launches"] // reps, "avg_launch_us": 1000.0 * f["ms"] / f["launches"],
                      "share_of_step": f["ms"] / sum(v["ms"] for v in fam.values()), "peak_source": peaks["source"],
-                     "traffic": None,
-                     "families": {k: {"ms_per_step": v["ms"] / reps, "launches": v["launches"] // reps,
-                                      "GB/s": (v["bytes"] / (v["ms"] / 1000.0) / 1e9) if v["bytes"] else None,
-                                      "TFLOP/s": (v["flops"] / (v["ms"] / 1000.0) / 1e12) if v["flops"] else None}
-                                  for k, v in sorted(fam.items(), key=lambda kv: -kv[1]["ms"])}})
+                     # ncu (profiles/dram_traffic_*): DRAM bytes of a launch = 1.01 x its algorithmic bytes
+                     "traffic": 1.01 * per_launch_bytes, "algorithmic_bytes_per_launch": per_launch_bytes,
+                     "kernels": {k: {"ms_per_step": v["ms"] / reps, "launches": v["launches"] // reps,
+                                     "GB/s": (v["bytes"] / (v["ms"] / 1000.0) / 1e9) if v["bytes"] else None,
+                                     "TFLOP/s": (v["flops"] / (v["ms"] / 1000.0) / 1e12) if v["flops"] else None}
+                                 for k, v in sorted(fam.items(), key=lambda kv: -kv[1]["ms"])}})
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -108,6 +108,10 @@ int ogle_cuda_conv2d_prepack(const OgleConvParams* p, const float* w_oihw, void*
 int ogle_cuda_conv2d(const OgleConvParams* p, const float* x, const void* packed_filter,
                      const float* bias, float* y, ogle_stream_t stream);
 
+/* Name of the device kernel that ogle_cuda_conv2d launches for these parameters
+ * (for profiles and reports; "" when the parameters are invalid). */
+const char* ogle_cuda_conv2d_kernel_name(const OgleConvParams* p);
+
 /* Two convolutions that read the same input with the same window (kernel, stride,
  * pad, dilation, activation, group 1) as ONE pass over the input: the SSD box and
  * class heads, which the reference draws as two Conv2DKernel::Compute passes

@@ -7,6 +7,8 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
                    const float* w_hi, const float* w_lo, const float* bias, float* y, cudaStream_t s,
                    float* y2 = nullptr, int K1 = 0, int split_col = 0);
 bool conv_tc_supported(const ConvArgs& a, int variant);
+bool dw_tma_supported(const ConvArgs& a);
+bool conv_smallc_supported(const ConvArgs& a);
 
 // Destination-indexed packing of an OIHW filter into the three sections of the
 // packed blob (see FilterLayout).
@@ -153,6 +155,20 @@ int ogle_cuda_conv2d(const OgleConvParams* p, const float* x, const void* packed
                               reinterpret_cast<const float*>(base + L.off_lo), bias, y, s);
     }
     return launch_conv_simt(a, variant, x, reinterpret_cast<const float*>(base), bias, y, s);
+}
+
+const char* ogle_cuda_conv2d_kernel_name(const OgleConvParams* p) {
+    ConvArgs a; int variant;
+    if (fill_args(p, &a, &variant) != OGLE_OK) return "";
+    if (p->math_mode != OGLE_MATH_FP32 && (variant == CONV_GENERAL || variant == CONV_POINTWISE) && conv_tc_supported(a, variant))
+        return "conv_tc2_kernel";
+    if (variant == CONV_DEPTHWISE) {
+        if (dw_tma_supported(a)) return "dw3x3_tma_kernel";
+        return (a.kernel == 3 && a.dil == 1 && (a.stride == 1 || a.stride == 2)) ? "dw3x3_kernel" : "dw_generic_kernel";
+    }
+    if (variant == CONV_GROUPED) return "grouped_kernel";
+    if (variant == CONV_GENERAL && conv_smallc_supported(a)) return "conv3x3_smallc_kernel";
+    return "conv_igemm_kernel";
 }
 
 int ogle_cuda_conv2d_pair_supported(const OgleConvParams* p) {

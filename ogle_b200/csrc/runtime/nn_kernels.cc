@@ -148,6 +148,9 @@ public:
         params_.min_value = min_; params_.max_value = max_;
         params_.math_mode = context_->math_mode();
         OGLE_CUDA_OK(ogle_cuda_conv2d_infer(&params_));
+        // family (the reference's shader name) : device kernel that serves it
+        const size_t colon = kernel_fname_.find(':');
+        kernel_fname_ = kernel_fname_.substr(0, colon) + ":" + ogle_cuda_conv2d_kernel_name(&params_);
         output_shapes[0] = {image_shape[0], params_.out_hwc[0], params_.out_hwc[1], filter_shape[0]};
     }
 

@@ -109,7 +109,9 @@ __global__ void __launch_bounds__(kThreads2, 1)
 conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmBhi,
                 const __grid_constant__ CUtensorMap tmBlo, const __grid_constant__ CUtensorMap tmY,
                 const __grid_constant__ CUtensorMap tmY2, const float* __restrict__ bias, const TcArgs a, int* err_flag) {
-    extern __shared__ unsigned char smem_raw[];
+    // 1024-byte alignment (the 128-byte swizzle atom) comes from the declaration, so that
+    // every byte of the 224 KB request is usable
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[kMaxStages], bar_xf[kMaxStages], bar_empty[kMaxStages];
     __shared__ __align__(8) uint64_t bar_acc_full[2], bar_acc_empty[2];
     __shared__ uint32_t tmem_slot;
@@ -128,6 +130,18 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     auto sBhi = [&](int s) { return sA(s) + (split ? 2u : 1u) * kABytes; };
     auto sBlo = [&](int s) { return sBhi(s) + b_bytes; };
     const uint32_t staging_off = (uint32_t)a.stages * stage_bytes;
+    {
+        // the layout must fit what the launch reserved (it does when the base is 1024-aligned as
+        // declared); checked, not assumed, because an overrun would write past the block's window
+        uint32_t dyn;
+        asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
+        const uint32_t need = (base - smem_u32(smem_raw)) + staging_off +
+                              (uint32_t)(a.epi_groups * a.epi_slabs) * (uint32_t)kStagingBytes;
+        if (need > dyn) {
+            if (threadIdx.x == 0) record_error(err_flag, 9);
+            return;
+        }
+    }
 
     const int chunks = a.kernel * a.kernel * a.chunks_per_tap;
     const int acc_cols = a.ncat ? 2 * a.BN : a.BN;     // tensor-memory columns of one accumulator
@@ -445,6 +459,14 @@ int ncat_max_bn() {
     return v;
 }
 
+int ncat_min_chunks() {
+    static const int v = [] {
+        const char* e = getenv("OGLE_TC_NCAT_MIN_CHUNKS");
+        return e ? atoi(e) : 8;
+    }();
+    return v;
+}
+
 int num_sms() {
     static thread_local int sms = 0, sms_device = -1;
     int dev = 0;
@@ -472,26 +494,30 @@ int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, cons
                  cudaStream_t s) {
     if (t.BN % 32 || t.BN > 256) return OGLE_ERR_UNSUPPORTED;
     const size_t stage = (size_t)(t.passes == 3 ? 2 : 1) * (kABytes + (size_t)t.BN * 128);
-    // two epilogue groups (two staging slabs each) unless that would leave fewer
-    // than two operand stages
+    // Shared memory is split between the operand ring and the epilogue's staging slabs
+    // (128 rows x 32 columns each). Preference: two epilogue groups with two slabs each;
+    // give slabs back to the ring while that buys another stage and the ring is shallow.
+    const size_t kBudget = 224 * 1024;
+    const int chunks = t.kernel * t.kernel * t.chunks_per_tap;
+    t.xf_groups = t.passes == 3 ? 2 : 1;   // both operand-split groups work on each chunk
     t.epi_groups = 2;
     t.epi_slabs = 2;
-    if ((224 * 1024 - 4 * kStagingBytes - 1024) / stage < 2) t.epi_groups = 1;
-    if (t.epi_groups == 1 && (224 * 1024 - 2 * kStagingBytes - 1024) / stage < 2) t.epi_slabs = 1;
-    // One operand-split group keeps up with the short reductions (pointwise layers); long
-    // reductions get both groups working on each chunk, which halves the split's latency.
-    t.xf_groups = 1;
-    const int chunks = t.kernel * t.kernel * t.chunks_per_tap;
     if (t.passes == 3 && chunks >= 8) {
-        // long reductions: the operand split is the critical role, the epilogue is not
-        t.xf_groups = 2;
+        // long reductions: the epilogue is rare, the ring needs the room
         t.epi_groups = 1;
         t.epi_slabs = 1;
+    } else {
+        auto stages_with = [&](int groups, int slabs) { return (int)((kBudget - (size_t)groups * slabs * kStagingBytes) / stage); };
+        // (measured: the bandwidth-bound pointwise layers want the second slab more than a
+        // fourth stage; reductions of 16+ chunks want the stage)
+        const int shallow = chunks >= 16 ? 4 : 3;
+        if (stages_with(2, 2) < shallow && stages_with(2, 1) > stages_with(2, 2)) t.epi_slabs = 1;
+        if (stages_with(t.epi_groups, t.epi_slabs) < 2) { t.epi_groups = 1; t.epi_slabs = 1; }
     }
     if (const char* e = getenv("OGLE_TC_XF_GROUPS")) t.xf_groups = (t.passes == 3 && e[0] == '2') ? 2 : 1;
     if (const char* e = getenv("OGLE_TC_EPI_GROUPS")) if (e[0] == '1') t.epi_groups = 1;
     const size_t staging = (size_t)t.epi_groups * t.epi_slabs * kStagingBytes;
-    const size_t budget = 224 * 1024 - staging - 1024;
+    const size_t budget = kBudget - staging;
     int stages = (int)(budget / stage);
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return OGLE_ERR_UNSUPPORTED;
@@ -499,14 +525,14 @@ int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, cons
     // stacked-filter form of the 3-pass mode (see TcArgs::ncat)
     // (long reductions only: it costs the epilogue a second tensor-memory read per slab,
     // which the short, bandwidth-bound pointwise layers cannot hide)
-    t.ncat = (t.passes == 3 && chunks >= 8 && t.BN <= ncat_max_bn()) ? 1 : 0;
+    t.ncat = (t.passes == 3 && chunks >= ncat_min_chunks() && t.BN <= ncat_max_bn()) ? 1 : 0;
     int cols = 32;
     while (cols < 2 * t.BN * (t.ncat ? 2 : 1)) cols <<= 1;
     t.tmem_cols = cols;
     const long total = m_tiles * t.n_tiles;
     if (total <= 0 || total > 0x7fffffffL) return OGLE_ERR_UNSUPPORTED;
     t.total_tiles = (int)total;
-    const size_t smem = stage * stages + staging + 1024;
+    const size_t smem = stage * stages + staging;
     static thread_local int attr_device = -1;
     int dev = 0;
     cudaGetDevice(&dev);

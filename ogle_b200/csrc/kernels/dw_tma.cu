@@ -5,8 +5,8 @@
 // one image for a slab of 32 channels; tw is the map's width when that is at most 32
 // (so 19- and 10-wide maps are covered without ragged column tiles), else 32 or 16. Its input window, halo included, is ONE TMA
 // box [IH rows][IW cols][32 channels]; pixels outside the image arrive as zeros,
-// which is the convolution's padding. Two shared-memory stages: while the block
-// computes tile i from one stage, the TMA engine fills the other with tile i+1, so
+// which is the convolution's padding. A ring of two to four shared-memory stages: while
+// the block computes tile i from one stage, the TMA engine fills the others with the next tiles, so
 // the only HBM traffic is the input read once (halo rows come from L2) and the
 // output written once, both as 128-byte runs.
 // A thread owns 4 channels (one float4) of one output column and slides a 3-row
@@ -22,11 +22,13 @@ namespace {
 using namespace tc;
 
 constexpr int kDwSmemMax = 110 * 1024;   // two blocks per SM
+constexpr int kDwMaxStages = 4;
 
 struct DwTiles {
     int tiles_x, tiles_y, cblocks;   // tile grid per image, 32-channel slabs
     int tw, th, row_groups;          // tile shape: th = RPG * row_groups
     int iw, ih;                      // input window of a tile, halo included
+    int stages;                      // tiles in flight per block (2..4)
     long total;
 };
 
@@ -39,7 +41,7 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap tmX, const float4* __restri
     const int TW = tl.tw, TH = tl.th, IW = tl.iw;
     const uint32_t kTileBytes = (uint32_t)(tl.ih * tl.iw * CB * 16);
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bar_full[2];
+    __shared__ __align__(8) uint64_t bar_full[kDwMaxStages];
 
     const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
     const float4* stage0 = reinterpret_cast<const float4*>(smem_raw + (base - smem_u32(smem_raw)));
@@ -51,8 +53,7 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap tmX, const float4* __restri
     const bool active = rg < tl.row_groups;        // slots past tw * row_groups idle
 
     if (threadIdx.x == 0) {
-        mbar_init(&bar_full[0], 1);
-        mbar_init(&bar_full[1], 1);
+        for (int i = 0; i < kDwMaxStages; ++i) mbar_init(&bar_full[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -69,13 +70,22 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap tmX, const float4* __restri
                     ty * TH * S - a.pad, n);
     };
 
-    if (threadIdx.x == 0 && (long)blockIdx.x < tl.total) issue(blockIdx.x, 0);
+    // prologue: fill all but one stage; each iteration then tops the ring up before computing
+    const int nst = tl.stages;
+    long issued = 0;                               // tiles whose copy was started (thread 0 only)
+    if (threadIdx.x == 0)
+        for (int k = 0; k < nst - 1; ++k)
+            if ((long)blockIdx.x + (long)k * gridDim.x < tl.total) { issue((long)blockIdx.x + (long)k * gridDim.x, k); ++issued; }
     long it = 0;
+    int stage = 0;
+    uint32_t phase = 0;
     for (long tile = blockIdx.x; tile < tl.total; tile += gridDim.x, ++it) {
-        const int stage = (int)(it & 1);
-        // the other stage was last read by tile it-1, which every thread finished
+        // the stage refilled here was last read by tile it-1, which every thread finished
         // before the __syncthreads at the bottom of the previous iteration
-        if (threadIdx.x == 0 && tile + gridDim.x < tl.total) issue(tile + gridDim.x, stage ^ 1);
+        if (threadIdx.x == 0) {
+            const long ahead = tile + (long)(nst - 1) * gridDim.x;
+            if (ahead < tl.total) { issue(ahead, stage == 0 ? nst - 1 : stage - 1); ++issued; }
+        }
         long t = tile;
         const int cb = (int)(t % tl.cblocks); t /= tl.cblocks;
         const int tx = (int)(t % tl.tiles_x); t /= tl.tiles_x;
@@ -88,8 +98,12 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap tmX, const float4* __restri
         float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
         if (a.has_bias) bv = make_float4(bias[cq * 4], bias[cq * 4 + 1], bias[cq * 4 + 2], bias[cq * 4 + 3]);
 
-        if (!mbar_wait(&bar_full[stage], (uint32_t)((it >> 1) & 1))) {
-            if (threadIdx.x == 0) record_error(err_flag, 6);
+        if (!mbar_wait(&bar_full[stage], phase)) {
+            if (threadIdx.x == 0) {
+                record_error(err_flag, 6);
+                // let the later copies already in flight land (bounded) before the block retires
+                for (long j = it + 1; j < issued; ++j) mbar_wait(&bar_full[j % nst], (uint32_t)((j / nst) & 1));
+            }
             break;   // uniform: every thread waits on the same barrier with the same bound
         }
         const float4* tile_s = stage0 + (size_t)stage * (kTileBytes / 16);
@@ -128,6 +142,7 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap tmX, const float4* __restri
         }
         }
         __syncthreads();
+        if (++stage == nst) { stage = 0; phase ^= 1u; }
     }
 }
 
@@ -144,7 +159,7 @@ int launch(const ConvArgs& a, const DwTiles& shape, const float* x, const float*
     tl.tiles_y = (a.Ho + tl.th - 1) / tl.th;
     tl.cblocks = a.K / 32;
     tl.total = (long)tl.tiles_x * tl.tiles_y * tl.cblocks * a.N;
-    const size_t smem = 2 * (size_t)tl.ih * tl.iw * 8 * 16 + 128;
+    const size_t smem = (size_t)tl.stages * tl.ih * tl.iw * 8 * 16 + 128;
     static thread_local int attr_device = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -183,6 +198,9 @@ int choose_shape(const ConvArgs& a, DwTiles* t) {
         if (best_cost < 0 || cost < best_cost) {
             best_cost = cost; best = rpg;
             t->tw = tw; t->th = th; t->row_groups = groups; t->iw = iw; t->ih = ih;
+            // as many tiles in flight as fit: HBM latency x bandwidth needs ~90 KB per SM
+            int st = (int)((size_t)(kDwSmemMax - 128) / ((size_t)ih * iw * 128));
+            t->stages = st > kDwMaxStages ? kDwMaxStages : st;
         }
     }
     return best;

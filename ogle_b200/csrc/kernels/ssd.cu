@@ -3,9 +3,11 @@
 // decode: one thread per anchor, 128-bit loads/stores (HBM-bound).
 // detect: one thread block per image. The block reads the image's logits once,
 // turns them into softmax scores kept in shared memory, and then warps select
-// the top-k per class (or per image) with a 4-pass radix select over the score
-// bits followed by a bitonic sort of the <= 256 survivors, so logits and boxes
-// cross HBM exactly once and nothing is staged in global memory.
+// the top-k per class (or per image): each lane holds its share of the class's
+// scores in registers and the k-th largest is found bit by bit (radix select over
+// shared memory for more than 2048 anchors), followed by a bitonic sort of the
+// <= 256 survivors, so logits and boxes cross HBM exactly once and nothing is
+// staged in global memory.
 #include "common.cuh"
 
 namespace ogle {
@@ -27,11 +29,35 @@ __global__ void ssd_decode_kernel(const float4* __restrict__ pred, const float4*
 
 constexpr int kMaxTopK = 256;
 
+// Warp-collective: sorts list[0..n) (n <= kMaxTopK packed keys) descending in place
+// (padded to a power of two with zeros, bitonic network). Returns min(n, kMaxTopK).
+__device__ __noinline__ int warp_sort_list(unsigned long long* list, int n) {
+    const int lane = threadIdx.x & 31;
+    if (n > kMaxTopK) n = kMaxTopK;
+    int P = 32;
+    while (P < n) P <<= 1;
+    for (int i = n + lane; i < P; i += 32) list[i] = 0ull;
+    __syncwarp();
+    for (int size = 2; size <= P; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int t = lane; t < P / 2; t += 32) {
+                const int lo = 2 * t - (t & (stride - 1));
+                const int hi = lo + stride;
+                const bool desc = ((lo & size) == 0);
+                const unsigned long long a = list[lo], b = list[hi];
+                if ((a < b) == desc) { list[lo] = b; list[hi] = a; }
+            }
+            __syncwarp();
+        }
+    }
+    return n;
+}
+
 // Warp-collective: selects the `k` largest scores among vals[0..A) that exceed
 // `thr` (ties: lower index first) and leaves them in list[0..n) sorted by
 // (score descending, index ascending) as packed keys
 // (score_bits << 32 | ~index). hist: 256 warp-private counters. Returns n.
-__device__ int warp_select_topk(const float* vals, int A, float thr, int k,
+__device__ __noinline__ int warp_select_topk(const float* vals, int A, float thr, int k,
                                 unsigned long long* list, unsigned* hist) {
     const int lane = threadIdx.x & 31;
     const unsigned full = 0xffffffffu;
@@ -119,25 +145,69 @@ __device__ int warp_select_topk(const float* vals, int A, float thr, int k,
         n += __popc(m_sel);
         eq_taken += __popc(m_eq);
     }
-    if (n > kMaxTopK) n = kMaxTopK;
-    // pad to a power of two and bitonic sort, descending
-    int P = 32;
-    while (P < n) P <<= 1;
-    for (int i = n + lane; i < P; i += 32) list[i] = 0ull;
-    __syncwarp();
-    for (int size = 2; size <= P; size <<= 1) {
-        for (int stride = size >> 1; stride > 0; stride >>= 1) {
-            for (int t = lane; t < P / 2; t += 32) {
-                const int lo = 2 * t - (t & (stride - 1));
-                const int hi = lo + stride;
-                const bool desc = ((lo & size) == 0);
-                const unsigned long long a = list[lo], b = list[hi];
-                if ((a < b) == desc) { list[lo] = b; list[hi] = a; }
-            }
-            __syncwarp();
-        }
+    return warp_sort_list(list, n);
+}
+
+// Register-resident variant for A <= 32 * kRegPer and thr >= 0: each lane keeps its
+// A/32 scores in registers (0 = not a candidate; candidates are positive floats, which
+// order like their bit patterns), finds the bits of the k-th largest one bit at a time
+// from the top (a count per bit: lane-local compares and one warp reduction, no shared
+// memory, no atomics), then compacts in index order and sorts as above.
+constexpr int kRegPer = 64;
+
+__device__ int warp_select_topk_reg(const float* vals, int A, float thr, int k, unsigned long long* list) {
+    const int lane = threadIdx.x & 31;
+    const unsigned full = 0xffffffffu;
+    unsigned bits[kRegPer];
+    int local = 0;
+#pragma unroll
+    for (int j = 0; j < kRegPer; ++j) {
+        const int i = j * 32 + lane;
+        const float v = i < A ? vals[i] : 0.f;
+        bits[j] = (i < A && v > thr) ? __float_as_uint(v) : 0u;
+        local += bits[j] != 0u;
     }
-    return n;
+    const int n_valid = __reduce_add_sync(full, local);
+    const bool take_all = n_valid <= k;
+    unsigned T = 0;
+    int need_eq = 0;
+    if (!take_all) {
+        unsigned prefix = 0;
+        int remaining = k;
+        for (int bit = 30; bit >= 0; --bit) {
+            const unsigned cand = prefix | (1u << bit);
+            const unsigned hi = ~((1u << bit) - 1u);
+            int c = 0;
+#pragma unroll
+            for (int j = 0; j < kRegPer; ++j) c += (bits[j] & hi) == cand;
+            const int total = __reduce_add_sync(full, c);
+            if (total >= remaining) prefix = cand;      // the k-th largest has this bit set
+            else remaining -= total;                    // all of those rank above it
+        }
+        T = prefix;
+        need_eq = remaining;
+    }
+    int n = 0, eq_taken = 0;
+#pragma unroll
+    for (int j = 0; j < kRegPer; ++j) {
+        if (j * 32 >= A) break;
+        const int i = j * 32 + lane;
+        const unsigned b = bits[j];
+        const bool ok = b != 0u;
+        const bool gt = ok && (take_all || b > T);
+        const bool eq = ok && !take_all && b == T;
+        const unsigned m_eq = __ballot_sync(full, eq);
+        const int eq_rank = eq_taken + __popc(m_eq & ((1u << lane) - 1u));
+        const bool sel = gt || (eq && eq_rank < need_eq);
+        const unsigned m_sel = __ballot_sync(full, sel);
+        if (sel) {
+            const int pos = n + __popc(m_sel & ((1u << lane) - 1u));
+            if (pos < kMaxTopK) list[pos] = ((unsigned long long)b << 32) | (unsigned long long)(0xffffffffu - (unsigned)i);
+        }
+        n += __popc(m_sel);
+        eq_taken += __popc(m_eq);
+    }
+    return warp_sort_list(list, n);
 }
 
 struct DetectArgs {
@@ -149,7 +219,7 @@ struct DetectArgs {
 // Dynamic shared memory layout:
 //   float scores[classes_per_pass][A]         (mode 0: scores[A] then int cls[A])
 //   per warp: 2 KB scratch (histogram, then the sorted list)
-__global__ void __launch_bounds__(768)
+__global__ void __launch_bounds__(640)
 ssd_detect_kernel(const float* __restrict__ logits, const float4* __restrict__ boxes,
                   float* __restrict__ out_score, int* __restrict__ out_anchor, int* __restrict__ out_class,
                   float4* __restrict__ out_box, int* __restrict__ out_count, DetectArgs a) {
@@ -170,16 +240,39 @@ ssd_detect_kernel(const float* __restrict__ logits, const float4* __restrict__ b
             const int nc = min(a.classes_per_pass, a.C - c0);
             // softmax exactly as the reference post-process does: exp of the raw
             // logits, summed in class order, then one divide per class
-            for (int i = tid; i < a.A; i += blockDim.x) {
-                const float* row = lg + (long)i * a.logit_stride;
-                float total = 0.f;
-                for (int j = 0; j < a.C; ++j) total += expf(row[j]);
-                for (int j = 0; j < nc; ++j) scores[j * a.A + i] = expf(row[c0 + j]) / total;
+            if (nc == a.C - 1 && a.C <= 32 && (a.logit_stride & 3) == 0 && a.logit_stride <= 32) {
+                // the whole row in registers: 128-bit loads, every exponential taken once
+                for (int i = tid; i < a.A; i += blockDim.x) {
+                    const float4* row4 = reinterpret_cast<const float4*>(lg + (long)i * a.logit_stride);
+                    float e[32];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (q * 4 < a.logit_stride) v = row4[q];
+                        e[q * 4 + 0] = v.x; e[q * 4 + 1] = v.y; e[q * 4 + 2] = v.z; e[q * 4 + 3] = v.w;
+                    }
+                    float total = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (j < a.C) { e[j] = expf(e[j]); total += e[j]; }
+#pragma unroll
+                    for (int j = 1; j < 32; ++j)
+                        if (j < a.C) scores[(j - 1) * a.A + i] = e[j] / total;
+                }
+            } else {
+                for (int i = tid; i < a.A; i += blockDim.x) {
+                    const float* row = lg + (long)i * a.logit_stride;
+                    float total = 0.f;
+                    for (int j = 0; j < a.C; ++j) total += expf(row[j]);
+                    for (int j = 0; j < nc; ++j) scores[j * a.A + i] = expf(row[c0 + j]) / total;
+                }
             }
             __syncthreads();
             for (int j = warp; j < nc; j += nwarps) {
                 const int cls = c0 + j;
-                const int cnt = warp_select_topk(scores + j * a.A, a.A, a.score_thr, a.top_k, list, hist);
+                const int cnt = (a.A <= 32 * kRegPer && a.score_thr >= 0.f)
+                                    ? warp_select_topk_reg(scores + j * a.A, a.A, a.score_thr, a.top_k, list)
+                                    : warp_select_topk(scores + j * a.A, a.A, a.score_thr, a.top_k, list, hist);
                 const long base = (long)n * rows + (long)(cls - 1) * a.top_k;
                 for (int r = lane; r < a.top_k; r += 32) {
                     float sc = 0.f; int an = -1;
@@ -326,7 +419,7 @@ int ogle_cuda_ssd_detect(const OgleDetectParams* p, const float* logits, const f
     int threads;
     size_t smem;
     if (p->mode == 1) {
-        threads = 768;
+        threads = 640;    // 20 warps: one per foreground class of a 21-class head, ~100 registers each
         const size_t per_warp = 2048, warp_bytes = per_warp * (threads / 32) + 16;
         const size_t per_class = (size_t)p->A * sizeof(float);
         if (per_class + warp_bytes > kSmemBudget) return OGLE_ERR_UNSUPPORTED;

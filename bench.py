@@ -151,6 +151,10 @@ def cpu_baseline(model_builder, classes, target_seconds, kind=None):
     lib = oracle.load(kind)
     keep = {"cls_logits", "box_preds", "anchors"}
     post = oracle.load("port")   # the post-process exists only in the restatement
+    # every host core this process may use, whatever OMP_NUM_THREADS says (torchrun sets it to 1)
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib.set_threads(cores)
+    post.set_threads(cores)
 
     def run(n):
         model, _ = model_builder(n)

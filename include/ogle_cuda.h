@@ -230,6 +230,14 @@ int ogle_cuda_pad4(const float* dense, float* padded, long rows, int last, int s
                    ogle_stream_t stream);
 int ogle_cuda_unpad4(const float* padded, float* dense, long rows, int last, int stride,
                      ogle_stream_t stream);
+/* Detector::Preprocess (examples/ssd/detector.cc:99-109) for one image: 8-bit BGR
+ * (device memory, rows src_row_bytes apart) -> RGB, bilinear resize to
+ * dst_h x dst_w with OpenCV's 8-bit INTER_LINEAR arithmetic (the cv::resize call
+ * the reference makes), to float, minus mean_rgb; written as [dst_h][dst_w][4]
+ * floats (the NHWC4 slot of one image of the network input; lane 3 = 0). */
+int ogle_cuda_preprocess_bgr8(const unsigned char* bgr, int src_h, int src_w, int src_row_bytes,
+                              float* dst_nhwc4, int dst_h, int dst_w, const float mean_rgb[3],
+                              ogle_stream_t stream);
 /* NCHW dense -> NHWC4 (for callers holding NCHW images). */
 int ogle_cuda_nchw_to_nhwc4(const float* nchw, float* nhwc4, int N, int C, int H, int W,
                             ogle_stream_t stream);

@@ -68,6 +68,12 @@ OgleDetector* ogle_detector_create(int device, ogle_stream_t stream, const char*
 void ogle_detector_destroy(OgleDetector* d);
 /* Enqueue upload + network + decode + post-process + copy-back for N preprocessed NHWC images. */
 int ogle_detector_detect_async(OgleDetector* d, const float* images_nhwc_host, int N, int H, int W);
+/* Raw frames instead of preprocessed floats: N 8-bit BGR images (host memory, tightly
+ * packed rows, any sizes). Upload as bytes, then on the device channel swap, 8-bit bilinear
+ * resize to H x W, float, minus mean_rgb[3] (Detector::Preprocess, detector.cc:99-109),
+ * then as ogle_detector_detect_async. Retired by ogle_detector_wait. */
+int ogle_detector_detect_bgr8_async(OgleDetector* d, const unsigned char* const* images, const int* heights,
+                                    const int* widths, int N, int H, int W, const float* mean_rgb);
 /* Same for images already on the device as [N][H][W][4] floats (channel 3 zero).
  * The session must have been sized by one ogle_detector_detect_async call of the
  * same shape. copy_back 0 leaves the detections on the device. */

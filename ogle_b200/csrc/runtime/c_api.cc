@@ -217,6 +217,12 @@ int ogle_detector_detect_async(OgleDetector* d, const float* images, int N, int 
     return guarded([&] { d->detector->DetectAsync(images, N, H, W); });
 }
 
+int ogle_detector_detect_bgr8_async(OgleDetector* d, const unsigned char* const* images, const int* heights,
+                                    const int* widths, int N, int H, int W, const float* mean_rgb) {
+    if (!d) return -1;
+    return guarded([&] { d->detector->DetectBGR8Async(images, heights, widths, N, H, W, mean_rgb); });
+}
+
 int ogle_detector_detect_device_async(OgleDetector* d, const float* images, int N, int H, int W, int copy_back) {
     if (!d || !images || N <= 0) return -1;
     return guarded([&] { d->detector->DetectDeviceAsync(images, N, H, W, copy_back != 0); });

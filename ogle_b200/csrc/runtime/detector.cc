@@ -37,6 +37,8 @@ void Detector::Release() {
     boxes_ = nullptr;
     for (Slot& s : slots_) {
         if (s.stage) cudaFree(s.stage);
+        if (s.bytes) cudaFree(s.bytes);
+        s.bytes = nullptr; s.bytes_capacity = 0;
         if (s.out_dev) cudaFree(s.out_dev);
         if (s.out_host) cudaFreeHost(s.out_host);
         s.stage = nullptr; s.out_dev = nullptr; s.out_host = nullptr;
@@ -79,14 +81,15 @@ void Detector::Allocate(int N, int H, int W) {
     stage_bytes_ = stage_bytes;
 }
 
-void Detector::DetectAsync(const float* images_nhwc, int N, int H, int W) {
-    context_->MakeCurrent();
-    OGLE_CHECK_LT(int(pending_.size()), kDepth) << "retire a call with Wait() before issuing another";
-    cudaStream_t compute = S(context_->stream());
-    Tensor* in = nullptr;
+void Detector::EnsureSession(int N, int H, int W, const float* images_nhwc) {
     if (batch_ == 0 || !session_->FindTensorByName(options_.input_names[0])) {
-        // first call: let the session see the input once so that it sizes every tensor
+        // first call: let the session see an input once so that it sizes every tensor
         // (FBOSession::Setup, fbo_session.cc:168-252); detector.cc:235-240
+        std::vector<float> zeros;
+        if (!images_nhwc) {
+            zeros.assign(size_t(N) * H * W * 3, 0.f);
+            images_nhwc = zeros.data();
+        }
         Tensor input(Tensor::DT_FLOAT, IntList{N, H, W, 3}, const_cast<float*>(images_nhwc), dlxnet::TensorProto::NHWC);
         session_->Setup({{options_.input_names[0], &input}});
         context_->Synchronize();
@@ -99,9 +102,63 @@ void Detector::DetectAsync(const float* images_nhwc, int N, int H, int W) {
         num_classes_ = cls_logits->shape()[2];
         OGLE_CHECK_EQ(cls_logits->shape()[1], num_anchors_);
     }
-    in = session_->FindTensorByName(options_.input_names[0]);
+    Tensor* in = session_->FindTensorByName(options_.input_names[0]);
     OGLE_CHECK(in->shape() == (IntList{N, H, W, 3})) << "input shape differs from the one the session was sized for";
     Allocate(N, H, W);
+}
+
+void Detector::DetectBGR8Async(const unsigned char* const* images, const int* heights, const int* widths, int N, int H,
+                               int W, const float mean_rgb[3]) {
+    context_->MakeCurrent();
+    OGLE_CHECK(images && heights && widths && mean_rgb && N > 0);
+    OGLE_CHECK_LT(int(pending_.size()), kDepth) << "retire a call with Wait() before issuing another";
+    cudaStream_t compute = S(context_->stream());
+    EnsureSession(N, H, W, nullptr);
+    Tensor* in = session_->FindTensorByName(options_.input_names[0]);
+    Slot& slot = slots_[next_slot_];
+    size_t total = 0;
+    std::vector<size_t> offset(N);
+    for (int i = 0; i < N; ++i) {
+        OGLE_CHECK(images[i] && heights[i] > 0 && widths[i] > 0) << "image " << i;
+        offset[i] = total;
+        total += (size_t(heights[i]) * widths[i] * 3 + 255) / 256 * 256;
+    }
+    // this slot's byte buffer was last read two calls ago (ev_pad); growing it needs that done
+    if (total > slot.bytes_capacity) {
+        OGLE_RT_CUDA(cudaEventSynchronize(E(slot.ev_pad)));
+        if (slot.bytes) cudaFree(slot.bytes);
+        OGLE_RT_CUDA(cudaMalloc(&slot.bytes, total));
+        slot.bytes_capacity = total;
+    }
+    OGLE_RT_CUDA(cudaStreamWaitEvent(S(copy_in_), E(slot.ev_pad), 0));
+    for (int i = 0; i < N; ++i)
+        OGLE_RT_CUDA(cudaMemcpyAsync(slot.bytes + offset[i], images[i], size_t(heights[i]) * widths[i] * 3,
+                                     cudaMemcpyHostToDevice, S(copy_in_)));
+    OGLE_RT_CUDA(cudaEventRecord(E(slot.ev_h2d), S(copy_in_)));
+    h2d_bytes_ = total;
+    OGLE_RT_CUDA(cudaStreamWaitEvent(compute, E(slot.ev_h2d), 0));
+    const size_t image_floats = size_t(H) * W * 4;
+    for (int i = 0; i < N; ++i)
+        OGLE_CUDA_OK(ogle_cuda_preprocess_bgr8(slot.bytes + offset[i], heights[i], widths[i], widths[i] * 3,
+                                               in->device<float>() + size_t(i) * image_floats, H, W, mean_rgb,
+                                               context_->stream()));
+    OGLE_RT_CUDA(cudaEventRecord(E(slot.ev_pad), compute));
+    session_->RunDevice({});
+    PostProcess(slot, N, H, W);
+    OGLE_RT_CUDA(cudaStreamWaitEvent(S(copy_out_), E(slot.ev_done), 0));
+    OGLE_RT_CUDA(cudaMemcpyAsync(slot.out_host, slot.out_dev, out_bytes_, cudaMemcpyDeviceToHost, S(copy_out_)));
+    OGLE_RT_CUDA(cudaEventRecord(E(slot.ev_d2h), S(copy_out_)));
+    d2h_bytes_ = out_bytes_;
+    pending_.push_back(next_slot_);
+    next_slot_ = (next_slot_ + 1) % kDepth;
+}
+
+void Detector::DetectAsync(const float* images_nhwc, int N, int H, int W) {
+    context_->MakeCurrent();
+    OGLE_CHECK_LT(int(pending_.size()), kDepth) << "retire a call with Wait() before issuing another";
+    cudaStream_t compute = S(context_->stream());
+    EnsureSession(N, H, W, images_nhwc);
+    Tensor* in = session_->FindTensorByName(options_.input_names[0]);
     Slot& slot = slots_[next_slot_];
     // upload on the copy stream, once the compute stream has consumed this slot's last upload
     OGLE_RT_CUDA(cudaStreamWaitEvent(S(copy_in_), E(slot.ev_pad), 0));

@@ -49,6 +49,13 @@ public:
     // the copies truly asynchronous. The host buffer must stay valid until the Wait()
     // that retires this call.
     void DetectAsync(const float* images_nhwc, int N, int H, int W);
+    // Raw frames: N 8-bit BGR images of any sizes in host memory (pinned memory makes the
+    // copies asynchronous). Each is uploaded as bytes and turned into the H x W network
+    // input on the device - channel swap, 8-bit bilinear resize, float, minus mean_rgb -
+    // which is Detector::Preprocess + Detect of the reference (detector.cc:99-109, 275-295).
+    // Pipelined and retired by Wait() like DetectAsync.
+    void DetectBGR8Async(const unsigned char* const* images, const int* heights, const int* widths, int N, int H, int W,
+                         const float mean_rgb[3]);
     // Same, for images that already sit on the device in the padded NHWC4 layout
     // [N][H][W][4]. copy_back = false leaves the detections on the device and enqueues
     // nothing for Wait(); with copy_back the call is retired by Wait() like DetectAsync.
@@ -69,6 +76,8 @@ public:
 private:
     struct Slot {
         float* stage = nullptr;      // dense NHWC upload target on the device
+        unsigned char* bytes = nullptr;   // raw 8-bit frames of one call (DetectBGR8Async)
+        size_t bytes_capacity = 0;
         void* out_dev = nullptr;     // score | anchor | cls | box | count, contiguous
         void* out_host = nullptr;    // pinned mirror
         void* ev_h2d = nullptr;      // upload landed (copy-in stream)
@@ -76,6 +85,7 @@ private:
         void* ev_done = nullptr;     // post-process finished (compute stream)
         void* ev_d2h = nullptr;      // detections on the host (copy-out stream)
     };
+    void EnsureSession(int N, int H, int W, const float* images_nhwc);
     void Allocate(int N, int H, int W);
     void Release();
     void PostProcess(Slot& slot, int N, int H, int W);

@@ -281,6 +281,19 @@ def nchw_to_nhwc4(x_nchw):
     return out
 
 
+def preprocess_bgr8(image_u8, dst_h, dst_w, mean_rgb=(123.0, 117.0, 104.0), out=None):
+    """image_u8: uint8 CUDA tensor [H, W, 3] (BGR) -> float32 [dst_h, dst_w, 4] RGB, resized, mean-subtracted."""
+    if not image_u8.is_cuda or image_u8.dtype != torch.uint8 or not image_u8.is_contiguous():
+        raise ValueError("expected a contiguous uint8 CUDA tensor")
+    H, W, _ = image_u8.shape
+    if out is None:
+        out = torch.empty((dst_h, dst_w, 4), dtype=torch.float32, device="cuda")
+    mean = (C.c_float * 3)(*mean_rgb)
+    check(_lib.cuda_lib().ogle_cuda_preprocess_bgr8(C.c_void_p(image_u8.data_ptr()), H, W, W * 3, _p(out), dst_h, dst_w,
+                                                    mean, _stream()), "preprocess_bgr8")
+    return out
+
+
 def ssd_decode(pred, anchors, variances=(0.1, 0.1, 0.2, 0.2)):
     """pred [N,A,4], anchors [A,4] device tensors -> [N,A,4] corner boxes."""
     _require_cuda(pred, anchors)

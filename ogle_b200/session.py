@@ -38,6 +38,8 @@ RT_SYMBOLS = {
     "ogle_detector_destroy": (None, [_vp]),
     "ogle_detector_detect_async": (C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int]),
     "ogle_detector_detect_device_async": (C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "ogle_detector_detect_bgr8_async": (C.c_int, [_vp, C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_int,
+                                                  C.c_int, C.c_int, C.POINTER(C.c_float)]),
     "ogle_detector_wait": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "ogle_detector_info": (C.c_int, [_vp, _ip, _ip, _ip, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "ogle_detector_session": (_vp, [_vp]),
@@ -221,6 +223,21 @@ class Detector:
 
     def in_flight(self):
         return self._in_flight
+
+    def detect_bgr8_async(self, images, H, W, mean_rgb=(123.0, 117.0, 104.0)):
+        """images: list of uint8 numpy arrays [h_i, w_i, 3] (BGR, C-contiguous; they must stay alive until
+        the wait() that retires the call). Resize and mean-subtraction happen on the device."""
+        n = len(images)
+        for im in images:
+            if im.dtype != np.uint8 or im.ndim != 3 or im.shape[2] != 3 or not im.flags["C_CONTIGUOUS"]:
+                raise ValueError("expected C-contiguous uint8 [h, w, 3] images")
+        ptrs = (C.c_void_p * n)(*[im.ctypes.data for im in images])
+        hs = (C.c_int * n)(*[im.shape[0] for im in images])
+        ws = (C.c_int * n)(*[im.shape[1] for im in images])
+        mean = (C.c_float * 3)(*mean_rgb)
+        _check(self._lib.ogle_detector_detect_bgr8_async(self._h, ptrs, hs, ws, n, H, W, mean), "detect_bgr8_async")
+        self._shape = n
+        self._in_flight += 1
 
     def detect_device_async(self, images_dev_ptr, N, H, W, copy_back=False):
         """images_dev_ptr: device address of [N,H,W,4] floats (padded NHWC4)."""

@@ -435,4 +435,54 @@ int ogle_oracle_topk_per_class(const float* logits, int A, int C, float score_th
     return 0;
 }
 
+
+// Detector::Preprocess (examples/ssd/detector.cc:99-109) with OpenCV's 8-bit bilinear
+// resize restated (see oracle.h). Horizontal pass in integers scaled by 2^11, vertical
+// blend ((b0 * (r0 >> 4)) >> 16) + ((b1 * (r1 >> 4)) >> 16), then (+2) >> 2.
+namespace {
+void resize_taps(int dst, int src, std::vector<int>* index, std::vector<short>* coef) {
+    const double scale = double(src) / dst;
+    index->resize(dst);
+    coef->resize(size_t(dst) * 2);
+    for (int d = 0; d < dst; ++d) {
+        float f = float((d + 0.5) * scale - 0.5);
+        int s = int(std::floor(f));
+        f -= s;
+        if (s < 0) { s = 0; f = 0.f; }
+        if (s >= src - 1) { s = src - 1; f = 0.f; }
+        (*index)[d] = s;
+        const float w0 = (1.f - f) * 2048.f, w1 = f * 2048.f;
+        (*coef)[d * 2] = short(std::lrintf(w0));       // round half to even, as cvRound does
+        (*coef)[d * 2 + 1] = short(std::lrintf(w1));
+    }
+}
+}  // namespace
+
+int ogle_oracle_preprocess_bgr8(const unsigned char* bgr, int src_h, int src_w, int src_row_bytes,
+                                float* dst, int dst_h, int dst_w, const float mean_rgb[3]) {
+    if (!bgr || !dst || src_h <= 0 || src_w <= 0 || dst_h <= 0 || dst_w <= 0 || src_row_bytes < src_w * 3) return -1;
+    std::vector<int> xi, yi;
+    std::vector<short> xa, ya;
+    resize_taps(dst_w, src_w, &xi, &xa);
+    resize_taps(dst_h, src_h, &yi, &ya);
+    for (int y = 0; y < dst_h; ++y) {
+        const int y0 = yi[y], y1 = std::min(y0 + 1, src_h - 1);
+        const unsigned char* r0 = bgr + size_t(y0) * src_row_bytes;
+        const unsigned char* r1 = bgr + size_t(y1) * src_row_bytes;
+        const int b0 = ya[y * 2], b1 = ya[y * 2 + 1];
+        for (int x = 0; x < dst_w; ++x) {
+            const int x0 = xi[x], x1 = std::min(x0 + 1, src_w - 1);
+            const int a0 = xa[x * 2], a1 = xa[x * 2 + 1];
+            for (int c = 0; c < 3; ++c) {
+                const int sc = 2 - c;    // RGB channel c is BGR channel 2 - c
+                const int h0 = r0[x0 * 3 + sc] * a0 + r0[x1 * 3 + sc] * a1;
+                const int h1 = r1[x0 * 3 + sc] * a0 + r1[x1 * 3 + sc] * a1;
+                const int v = (((b0 * (h0 >> 4)) >> 16) + ((b1 * (h1 >> 4)) >> 16) + 2) >> 2;
+                const int u8 = v < 0 ? 0 : (v > 255 ? 255 : v);
+                dst[(size_t(y) * dst_w + x) * 3 + c] = float(u8) - mean_rgb[c];
+            }
+        }
+    }
+    return 0;
+}
 }  // extern "C"

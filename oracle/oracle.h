@@ -100,6 +100,18 @@ int ogle_oracle_detect(const float* boxes, const float* logits, int A, int C,
 int ogle_oracle_topk_per_class(const float* logits, int A, int C, float score_thr, int top_k,
                                float* out_score, int* out_anchor, int* out_count);
 
+/* Detector::Preprocess, ogl_runtime/opengl/examples/ssd/detector.cc:99-109:
+ * BGR -> RGB, resize of the 8-bit image to dst_h x dst_w, conversion to float,
+ * minus mean (R, G, B). The resize is OpenCV's (a third-party dependency that is
+ * not in the reference tree; the reference pins no version): cv::resize with the
+ * default INTER_LINEAR on 8-bit data, restated here from its published
+ * behaviour - pixel-centre alignment ((d + 0.5) * scale - 0.5), edge taps clamped,
+ * weights rounded to 11 fractional bits, rows blended in 32-bit fixed point with
+ * rounding to nearest. PARITY UNPINNED: not checked against OpenCV itself.
+ * Output: dst_h x dst_w x 3 floats (NHWC, unpadded). Only liboracle.so implements this. */
+int ogle_oracle_preprocess_bgr8(const unsigned char* bgr, int src_h, int src_w, int src_row_bytes,
+                                float* dst, int dst_h, int dst_w, const float mean_rgb[3]);
+
 #ifdef __cplusplus
 }
 #endif

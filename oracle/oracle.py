@@ -66,6 +66,7 @@ class Oracle:
         L.ogle_oracle_unpack_filter.argtypes = [_fp, _fp] + [C.c_int] * 4
         L.ogle_oracle_detect.argtypes = [_fp, _fp] + [C.c_int] * 4 + [C.c_float, C.c_int, C.c_float, _ip, _fp, _ip, _ip]
         L.ogle_oracle_topk_per_class.argtypes = [_fp, C.c_int, C.c_int, C.c_float, C.c_int, _fp, _ip, _ip]
+        L.ogle_oracle_preprocess_bgr8.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, _fp, C.c_int, C.c_int, _fp]
 
     def threads(self):
         return self.lib.ogle_oracle_threads()
@@ -215,6 +216,16 @@ class Oracle:
                                         _i(rect), _f(score), _i(cls), _i(anchor))
         self._check(n, "detect")
         return {"rect": rect[:n], "score": score[:n], "cls": cls[:n], "anchor": anchor[:n]}
+
+    def preprocess_bgr8(self, image_bgr, dst_h, dst_w, mean_rgb=(123.0, 117.0, 104.0)):
+        """image_bgr: uint8 [H, W, 3] -> float32 [dst_h, dst_w, 3] RGB, resized, mean-subtracted."""
+        img = np.ascontiguousarray(image_bgr, dtype=np.uint8)
+        H, W, _ = img.shape
+        out = np.empty((dst_h, dst_w, 3), np.float32)
+        mean = np.asarray(mean_rgb, np.float32)
+        self._check(self.lib.ogle_oracle_preprocess_bgr8(img.ctypes.data, H, W, W * 3, _f(out), dst_h, dst_w, _f(mean)),
+                    "preprocess_bgr8")
+        return out
 
     def topk_per_class(self, logits, score_thr=0.01, top_k=200):
         """One image, logits [A,C]. Returns score [C-1,top_k], anchor [C-1,top_k], count [C-1]."""

@@ -388,5 +388,6 @@ int ogle_oracle_unpack_filter(const float* packed, float* w, int O, int I, int k
 int ogle_oracle_detect(const float*, const float*, int, int, int, int, float, int, float,
                        int*, float*, int*, int*) { return -100; }
 int ogle_oracle_topk_per_class(const float*, int, int, float, int, float*, int*, int*) { return -100; }
+int ogle_oracle_preprocess_bgr8(const unsigned char*, int, int, int, float*, int, int, const float*) { return -100; }
 
 }  // extern "C"

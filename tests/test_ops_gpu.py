@@ -298,6 +298,21 @@ def test_layout_round_trip_reference_loop():
     assert np.array_equal(y[..., :3], x.transpose(0, 2, 3, 1)) and not y[..., 3:].any()
 
 
+def test_preprocess_bgr8_bit_exact(oracle_port):
+    """The device front end (BGR8 -> RGB, 8-bit bilinear resize, float, mean) against the CPU
+    restatement: integer arithmetic, so bit-exact, for shrinking, enlarging and odd sizes."""
+    import torch
+    from ogle_b200 import ops
+    rng = np.random.default_rng(51)
+    for (H, W, dh, dw) in [(480, 640, 300, 300), (300, 300, 300, 300), (117, 93, 300, 300), (1080, 1920, 300, 300),
+                           (33, 47, 64, 19), (2, 2, 7, 5), (1, 1, 4, 4)]:
+        img = rng.integers(0, 256, (H, W, 3), dtype=np.uint8)
+        got = ops.preprocess_bgr8(torch.from_numpy(img).cuda(), dh, dw).cpu().numpy()
+        ref = oracle_port.preprocess_bgr8(img, dh, dw)
+        assert np.array_equal(got[..., :3], ref), (H, W, dh, dw)
+        assert np.all(got[..., 3] == 0.0)
+
+
 def test_decode_batch_broadcasts_anchors(oracle_port):
     from ogle_b200 import ops
     rng = np.random.default_rng(20)

@@ -79,3 +79,22 @@ def test_topk_per_class_orders_ties_by_anchor(oracle_port):
     s, a, c = oracle_port.topk_per_class(logits, score_thr=0.0, top_k=4)
     assert c.tolist() == [4, 4]
     assert a[0].tolist() == [1, 2, 4, 0]
+
+
+def test_preprocess_restatement_known_answers(oracle_port):
+    """Detector::Preprocess with OpenCV's 8-bit bilinear rule restated (parity unpinned: no OpenCV
+    here). Properties that hold whatever the rounding details: same-size resize is the identity
+    (channel swap + mean only), constants stay constant, a 2x upscale of a horizontal ramp
+    interpolates with weights 1/4 : 3/4, and the first/last outputs clamp to the edge pixels."""
+    rng = np.random.default_rng(50)
+    img = rng.integers(0, 256, (37, 53, 3), dtype=np.uint8)
+    mean = np.array([123.0, 117.0, 104.0], np.float32)
+    assert np.array_equal(oracle_port.preprocess_bgr8(img, 37, 53), img[..., ::-1].astype(np.float32) - mean)
+    const = np.full((9, 11, 3), 200, np.uint8)
+    assert np.all(oracle_port.preprocess_bgr8(const, 300, 300, (0, 0, 0)) == 200.0)
+    ramp = np.zeros((2, 4, 3), np.uint8)
+    ramp[:, :, 0] = np.array([0, 40, 80, 120], np.uint8)            # blue channel -> output channel 2
+    up = oracle_port.preprocess_bgr8(ramp, 2, 8, (0, 0, 0))[0, :, 2]
+    assert list(up) == [0.0, 10.0, 30.0, 50.0, 70.0, 90.0, 110.0, 120.0]
+    down = oracle_port.preprocess_bgr8(img, 10, 10)
+    assert down.shape == (10, 10, 3) and np.all(down + mean >= 0) and np.all(down + mean <= 255)

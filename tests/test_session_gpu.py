@@ -199,3 +199,29 @@ def test_detector_end_to_end_matches_oracle_post_process(oracle_port):
             same = (out["anchor"][n].reshape(20, 200) == a_ref).mean()
             assert same >= 0.98, f"image {n}: only {same:.3f} of per-class indices agree"
         det.close()
+
+
+def test_detector_raw_frames_equal_host_preprocess(oracle_port):
+    """Frames of different sizes through detect_bgr8_async (upload as bytes, resize + mean on the device)
+    give the same detections as the float path fed with the oracle's preprocess of the same frames -
+    the device preprocess is bit-exact, so everything downstream is identical. Two calls in flight."""
+    from ogle_b200 import models, session
+    rng = np.random.default_rng(37)
+    model, _ = models.mobilenet_v1_ssd(batch=3, num_classes=21, seed=7, weight_std="he")
+    sets = [[rng.integers(0, 256, (h, w, 3), dtype=np.uint8) for (h, w) in sizes]
+            for sizes in ([(480, 640), (300, 300), (123, 77)], [(720, 1280), (64, 64), (301, 299)])]
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "ssd.dlx")
+        model.save(path)
+        det = session.Detector(path, mode=1, score_thr=0.01, top_k=200)
+        want = []
+        for frames in sets:
+            x = np.stack([oracle_port.preprocess_bgr8(f, 300, 300) for f in frames])
+            want.append(det.detect(x))
+        for frames in sets:                      # both calls in flight before the first wait
+            det.detect_bgr8_async(frames, 300, 300)
+        for w in want:
+            got = det.wait()
+            for key in ("score", "anchor", "cls", "box", "count"):
+                assert np.array_equal(got[key], w[key]), key
+        det.close()

@@ -76,9 +76,24 @@ def build_runtime(force=False):
     return out
 
 
+def build_tools(force=False):
+    """The headless run/profile program (csrc/tools/ogle_profile.cc) -> ogle_b200/ogle_profile."""
+    src = os.path.join(CSRC, "tools", "ogle_profile.cc")
+    if not os.path.exists(src):
+        return None
+    rdir = os.path.join(CSRC, "runtime")
+    out = os.path.join(HERE, "ogle_profile")
+    if force or _newer(out, [src, os.path.join(HERE, "libogle_rt.so")]):
+        _run([HOST_CXX, "-O2", "-std=c++17", "-Wall", "-Wno-sign-compare", "-I", INCLUDE, "-I", rdir, src, "-o", out,
+              "-L", HERE, "-logle_rt", "-logle_cuda", "-L", "/usr/local/cuda/lib64", "-lcudart",
+              "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,/usr/local/cuda/lib64"])
+    return out
+
+
 def build_all(force=False, verbose_ptxas=False):
     a = build_cuda(force, verbose_ptxas)
     b = build_runtime(force)
+    build_tools(force)
     return a, b
 
 

@@ -225,3 +225,25 @@ def test_detector_raw_frames_equal_host_preprocess(oracle_port):
             for key in ("score", "anchor", "cls", "box", "count"):
                 assert np.array_equal(got[key], w[key]), key
         det.close()
+
+
+def test_profile_tool_reports_per_type_table(tmp_path):
+    """ogle_profile (the headless counterpart of nn/profile_main.cc): loads a dlx file, runs it and
+    prints the per-node-type table; --json gives the same numbers for scripts."""
+    import json
+    import subprocess
+    from ogle_b200 import build, models
+    build.build_all()
+    model, _ = models.mobilenet_v1_ssd(batch=2, num_classes=21, seed=8, weight_std=0.02)
+    path = str(tmp_path / "ssd.dlx")
+    model.save(path)
+    exe = os.path.join(os.path.dirname(build.__file__), "ogle_profile")
+    r = subprocess.run([exe, path, "5", "--batch", "2"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    assert "ExecTimePerRound" in r.stdout and "Node Type\tTime\tCount" in r.stdout
+    conv_line = [l for l in r.stdout.splitlines() if l.startswith("Conv")]
+    assert conv_line and conv_line[0].split()[-1] == "41"          # 47 convolutions, 6 head pairs fused
+    r = subprocess.run([exe, path, "3", "--batch", "2", "--json", "--math", "tf32"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    d = json.loads(r.stdout)
+    assert d["graph"] is True and d["nodes"]["Conv"]["count"] == 41 and d["exec_ms_per_round"] > 0

@@ -322,6 +322,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             unsigned char* staging = base_ptr + my_staging;
             bool ok = true;
             int ti = 0;
+            int staged_nbase = -1;
             for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x, ++ti) {
                 if (ti % a.epi_groups != eg) continue;
                 const TileCoord tc_ = tile_coord(a, tile);
@@ -334,6 +335,15 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     pix = (long)tc_.w0 + row;
                     if (pix >= a.Wo) pix = a.Wo - 1;  // clipped rows are dropped by the store; keep reads in range
                 }
+                // bias of this tile's columns (pre-multiplied by beta), staged while the accumulator
+                // is still being produced; skipped when the previous tile had the same columns.
+                // Safe to overwrite here: every thread of the group passed the sync that follows the
+                // last read of the previous tile's values.
+                if (nbase != staged_nbase) {
+                    for (int i = t; i < a.BN; i += 128)
+                        my_bias[i] = (a.bias_mode == 2 && nbase + i < a.K) ? a.beta * bias[nbase + i] : 0.f;
+                    staged_nbase = nbase;
+                }
                 if (t == 0) TRACE(ti, 7);
                 ok = wait_or_abort(&bar_acc_full[as], (uint32_t)(use & 1), abort_flag);
                 if (!ok) { record_error(err_flag, 4); s_abort = 1; break; }
@@ -343,9 +353,6 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     const int nb = groups - g0 < a.epi_slabs ? groups - g0 : a.epi_slabs;
                     // both slabs are free once the previous round's stores have read them
                     if (t == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                    if (g0 == 0)
-                        for (int i = t; i < a.BN; i += 128)
-                            my_bias[i] = (a.bias_mode == 2 && nbase + i < a.K) ? a.beta * bias[nbase + i] : 0.f;
                     group_sync(bar_id);
                     if (t == 0 && g0 == 0) TRACE(ti, 9);
                     for (int b = 0; b < nb; ++b) {
@@ -376,8 +383,10 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         const bool fast = a.bias_mode != 1 && lcol + 32 <= kout;
                         if (fast) {
                             // every column is a real channel and the bias is per column:
-                            // two instructions per value, bias read as 128-bit vectors
+                            // two instructions per value, bias read as 128-bit vectors;
+                            // all values first, then the eight 128-bit stores back to back
                             const float4* bv = reinterpret_cast<const float4*>(my_bias + col);
+                            float4 o[8];
 #pragma unroll
                             for (int c4 = 0; c4 < 8; ++c4) {
                                 const float4 bb = bv[c4];
@@ -392,9 +401,13 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                                     v.x = fminf(fmaxf(v.x, a.lo), a.hi); v.y = fminf(fmaxf(v.y, a.lo), a.hi);
                                     v.z = fminf(fmaxf(v.z, a.lo), a.hi); v.w = fminf(fmaxf(v.w, a.lo), a.hi);
                                 }
-                                // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
-                                dst[c4 ^ (row & 7)] = v;
+                                o[c4] = v;
                             }
+                            if (t == 0 && g0 == 0 && b == 0) TRACE(ti, 2);
+                            // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
+#pragma unroll
+                            for (int c4 = 0; c4 < 8; ++c4) dst[c4 ^ (row & 7)] = o[c4];
+                            if (t == 0 && g0 == 0 && b == 0) TRACE(ti, 3);
                         } else {
 #pragma unroll
                             for (int c4 = 0; c4 < 8; ++c4) {

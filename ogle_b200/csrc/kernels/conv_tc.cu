@@ -298,17 +298,31 @@ int tc_variant() {
     return v;
 }
 
-// N tiling of the persistent kernel: multiples of 32 columns (one staging slab each);
-// narrower tiles when there would otherwise be fewer tiles than SMs.
+// N tiling of the persistent kernel: multiples of 32 columns (one staging slab each).
+// Picks the width that minimises (rounds of one tile per SM) x (time of a tile), with a
+// tile's time modelled by its tensor-core instructions: one instruction costs about 100
+// cycles up to ~180 columns (bound by the shared-memory fetch of its 128-row A operand)
+// and 0.55 cycles per column beyond.
 void choose_n_tiling_v2(int Kp, long m_tiles, TcArgs* t) {
-    int bn = (Kp + 31) / 32 * 32;
-    if (bn > 256) {
-        const int parts = (Kp + 255) / 256;
-        bn = ((Kp + parts - 1) / parts + 31) / 32 * 32;
+    const int kmax = (Kp + 31) / 32 * 32;
+    auto mma = [](int n) { const double c = 0.55 * n; return c < 100.0 ? 100.0 : c; };
+    int best_bn = 32;
+    double best_cost = -1.0;
+    for (int bn = 32; bn <= 256 && bn <= kmax; bn += 32) {
+        const int n_tiles = (Kp + bn - 1) / bn;
+        // the last tile of an uneven split is narrower; even splits are what the candidates give
+        const long tiles = m_tiles * n_tiles;
+        const long rounds = (tiles + kNumSMs - 1) / kNumSMs;
+        double per_tile;
+        if (t->passes == 3) per_tile = bn <= 128 ? mma(2 * bn) + mma(bn) : 3.0 * mma(bn);
+        else per_tile = mma(bn);
+        const double cost = (double)rounds * per_tile;
+        // equal cost: the wider tile when there are several rounds (fewer passes over A), the
+        // narrower one when everything fits in one round (more SMs busy, shorter epilogues)
+        if (best_cost < 0 || cost < best_cost || (cost == best_cost && rounds > 1)) { best_cost = cost; best_bn = bn; }
     }
-    while (bn > 32 && m_tiles * ((Kp + bn - 1) / bn) < kNumSMs) bn = (bn / 2 + 31) / 32 * 32;
-    t->BN = bn;
-    t->n_tiles = (Kp + bn - 1) / bn;
+    t->BN = best_bn;
+    t->n_tiles = (Kp + best_bn - 1) / best_bn;
 }
 
 void choose_n_tiling(int Kp, TcArgs* t) {

@@ -23,6 +23,7 @@
 // issue, warps 2-5 = operand split (3-pass mode) then epilogue. All waits on
 // mbarriers are bounded: a wait that gives up records an error code, and every
 // role falls through to the common teardown that frees tensor memory.
+#include <cmath>
 #include <cstdlib>
 
 #include "tc_common.cuh"
@@ -321,8 +322,17 @@ void choose_n_tiling_v2(int Kp, long m_tiles, TcArgs* t) {
         // narrower one when everything fits in one round (more SMs busy, shorter epilogues)
         if (best_cost < 0 || cost < best_cost || (cost == best_cost && rounds > 1)) { best_cost = cost; best_bn = bn; }
     }
+    if (const char* e = getenv("OGLE_TC_BN")) {      // experiments: force the tile width
+        const int v = atoi(e);
+        if (v >= 32 && v <= 256 && v % 32 == 0 && v <= kmax) best_bn = v;
+    }
     t->BN = best_bn;
     t->n_tiles = (Kp + best_bn - 1) / best_bn;
+}
+
+bool split_k_enabled() {
+    static const bool v = [] { const char* e = getenv("OGLE_TC_SPLIT_K"); return !(e && e[0] == '0'); }();
+    return v;
 }
 
 void choose_n_tiling(int Kp, TcArgs* t) {
@@ -402,6 +412,8 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
     } else {
         t.flat = 0;
         t.N = a.N; t.Ho = a.Ho; t.Wo = a.Wo;
+        const bool may_split = v2 && a.act == OGLE_ACT_NONE && a.koff == 0 && (y2 != nullptr || a.Ks == a.Kp) &&
+                               split_k_enabled() && taps * t.chunks_per_tap >= 16;
         if (a.Wo >= kTileM) {
             const int parts = (a.Wo + kTileM - 1) / kTileM;
             t.tw = (a.Wo + parts - 1) / parts; t.th = 1; t.tn = 1;
@@ -416,7 +428,9 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
                 if (tn > a.N) tn = a.N;
                 if ((th - 1) * a.stride + 1 > 256) continue;          // TMA box limit
                 const long tiles = (long)((a.Ho + th - 1) / th) * ((a.N + tn - 1) / tn);
-                const long rounds = (tiles + kNumSMs - 1) / kNumSMs;
+                // in half-rounds; a reduction split in two (see below) can fill a ragged last round
+                long rounds = 2 * ((tiles + kNumSMs - 1) / kNumSMs);
+                if (may_split && (2 * tiles + kNumSMs - 1) / kNumSMs < rounds) rounds = (2 * tiles + kNumSMs - 1) / kNumSMs;
                 if (best < 0 || rounds <= best) { best = rounds; t.th = th; t.tn = tn; }
             }
         }
@@ -452,7 +466,31 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
     const cuuint32_t bes[2] = {1, 1};
     if (!make_map(&mBhi, w_hi, 2, bdims, bstr, bbox, bes)) return OGLE_ERR_CUDA;
     if (!make_map(&mBlo, w_lo, 2, bdims, bstr, bbox, bes)) return OGLE_ERR_CUDA;
-    if (v2) return launch_tc_v2(t, mA, mBhi, mBlo, mY, y2 ? mY2 : mY, m_tiles, bias, error_flag_ptr(), s);
+    if (v2) {
+        // Split the reduction when whole tiles would leave SMs idle (few tiles) or a last round
+        // mostly empty. Needs a linear epilogue (no activation) and outputs that may be zeroed
+        // (dense tensors, not slices of a wider one): the partial tiles are added in place.
+        t.split_k = 1;
+        const int chunks = taps * t.chunks_per_tap;
+        if (a.act == OGLE_ACT_NONE && a.koff == 0 && (y2 != nullptr || a.Ks == a.Kp) && split_k_enabled()) {
+            const double tiles = (double)m_tiles * t.n_tiles;
+            double best = ceil(tiles / kNumSMs);
+            // two ranges at most: the sum of two partial tiles onto zero does not depend on the
+            // order in which they arrive, so results stay bit-reproducible; three or more would not
+            for (int k = 2; k <= 2 && chunks / k >= 8; ++k) {
+                const double cost = ceil(tiles * k / kNumSMs) / k + 0.03 * (k - 1);   // + per-item fill/drain
+                if (cost < 0.9 * best) { best = cost; t.split_k = k; }
+            }
+            const int cps = (chunks + t.split_k - 1) / t.split_k;
+            while (t.split_k > 1 && (t.split_k - 1) * cps >= chunks) --t.split_k;     // no empty ranges
+        }
+        if (t.split_k > 1) {
+            const size_t rows = (size_t)a.M;
+            if (cudaMemsetAsync(y, 0, rows * (size_t)ks_a * sizeof(float), s) != cudaSuccess) return OGLE_ERR_CUDA;
+            if (y2 && cudaMemsetAsync(y2, 0, rows * (size_t)kp_b * sizeof(float), s) != cudaSuccess) return OGLE_ERR_CUDA;
+        }
+        return launch_tc_v2(t, mA, mBhi, mBlo, mY, y2 ? mY2 : mY, m_tiles, bias, error_flag_ptr(), s);
+    }
     return launch_tc(t, mA, mBhi, mBlo, m_tiles, bias, y, s);
 }
 

@@ -105,6 +105,29 @@ __device__ __forceinline__ TileCoord tile_coord(const TcArgs& a, int tile) {
     return c;
 }
 
+struct WorkItem { int tile, ks, c_begin, c_end; };
+
+// kSplit is a compile-time switch so that the common, unsplit kernel carries none of this
+template <bool kSplit>
+__device__ __forceinline__ WorkItem work_item(const TcArgs& a, int w, int chunks) {
+    WorkItem it;
+    if (!kSplit) {
+        it.tile = w; it.ks = 0; it.c_begin = 0; it.c_end = chunks;
+    } else {
+        it.tile = w / a.split_k;
+        it.ks = w - it.tile * a.split_k;
+        it.c_begin = it.ks * a.chunks_per_split;
+        it.c_end = it.c_begin + a.chunks_per_split < chunks ? it.c_begin + a.chunks_per_split : chunks;
+    }
+    return it;
+}
+
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
+template <bool kSplit>
 __global__ void __launch_bounds__(kThreads2, 1)
 conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmBhi,
                 const __grid_constant__ CUtensorMap tmBlo, const __grid_constant__ CUtensorMap tmY,
@@ -181,16 +204,24 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             int issued = 0;            // chunks in flight bookkeeping for the abort path
             bool ok = true;
             int pti = 0;
-            for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x, ++pti) {
-                const TileCoord tc_ = tile_coord(a, tile);
+            for (int w = blockIdx.x; w < a.total_work && ok; w += gridDim.x, ++pti) {
+                const WorkItem wi = work_item<kSplit>(a, w, chunks);
+                const TileCoord tc_ = tile_coord(a, wi.tile);
                 const int ax = a.flat ? tc_.w0 : tc_.w0 * a.stride - a.pad;
                 const int ay = a.flat ? 0 : tc_.h0 * a.stride - a.pad;
+                // position of the first chunk: filter row, filter column, channel offset
                 int ky = 0, kx = 0, c0 = 0;
-                for (int it = 0; it < chunks; ++it) {
-                    if (it == 0) TRACE(pti, 0);
+                if (kSplit && wi.c_begin != 0) {      // only the later ranges of a split reduction pay the divisions
+                    const int tap0 = wi.c_begin / a.chunks_per_tap;
+                    ky = tap0 / a.kernel;
+                    kx = tap0 - ky * a.kernel;
+                    c0 = (wi.c_begin - tap0 * a.chunks_per_tap) * kChunk;
+                }
+                for (int it = wi.c_begin; it < wi.c_end; ++it) {
+                    if (it == wi.c_begin) TRACE(pti, 0);
                     if (wrap > 0) ok = wait_or_abort(&bar_empty[s], (wrap - 1) & 1u, abort_flag);
                     if (!ok) { record_error(err_flag, 1); break; }
-                    if (it == 0) TRACE(pti, 1);
+                    if (it == wi.c_begin) TRACE(pti, 1);
                     TRACEC(pti * chunks + it, 0);
                     mbar_expect_tx(&bar_full[s], tx);
                     tma_load_4d(sA(s), &tmA, &bar_full[s], c0, ax + kx * a.dil, ay + ky * a.dil, tc_.n0);
@@ -217,10 +248,11 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             uint32_t wrap = 0;
             int issued = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x) {
-                const int bcol = (tile % a.n_tiles) * a.BN;
-                int brow = 0;
-                for (int it = 0; it < chunks; ++it) {
+            for (int w = blockIdx.x; w < a.total_work && ok; w += gridDim.x) {
+                const WorkItem wi = work_item<kSplit>(a, w, chunks);
+                const int bcol = (wi.tile % a.n_tiles) * a.BN;
+                int brow = wi.c_begin * kChunk;
+                for (int it = wi.c_begin; it < wi.c_end; ++it) {
                     if (wrap > 0) ok = wait_or_abort(&bar_empty[s], (wrap - 1) & 1u, abort_flag);
                     if (!ok) { record_error(err_flag, 7); break; }
                     mbar_expect_tx(&bar_full[s], tx);
@@ -246,23 +278,25 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             uint32_t ph = 0;           // parity of the ring pass
             bool ok = true;
             int ti = 0;
-            for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x, ++ti) {
+            for (int w = blockIdx.x; w < a.total_work && ok; w += gridDim.x, ++ti) {
+                const WorkItem wi = work_item<kSplit>(a, w, chunks);
                 const int as = ti & 1, use = ti >> 1;
                 if (use > 0) ok = wait_or_abort(&bar_acc_empty[as], (uint32_t)((use - 1) & 1), abort_flag);
                 if (!ok) { record_error(err_flag, 5); s_abort = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d = tmem_d + (uint32_t)(as * acc_cols);
-                for (int it = 0; it < chunks; ++it) {
-                    if (it == 0) TRACE(ti, 4);
+                for (int it = wi.c_begin; it < wi.c_end; ++it) {
+                    if (it == wi.c_begin) TRACE(ti, 4);
                     ok = wait_or_abort(split ? &bar_xf[s] : &bar_full[s], ph, abort_flag);
                     if (!ok) { record_error(err_flag, 2); s_abort = 1; break; }
-                    if (it == 0) TRACE(ti, 5);
+                    if (it == wi.c_begin) TRACE(ti, 5);
                     TRACEC(ti * chunks + it, 2);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t ad = umma_desc(sA(s)), bd = umma_desc(sBhi(s));
-                    if (a.ncat) umma_tf32_chunk_cat(d, ad, ad + (kABytes >> 4), bd, idesc2, idesc, it > 0 ? 1u : 0u);
-                    else if (split) umma_tf32_chunk_split(d, ad, ad + (kABytes >> 4), bd, bd + (b_bytes >> 4), idesc, it > 0 ? 1u : 0u);
-                    else umma_tf32_chunk(d, ad, bd, idesc, it > 0 ? 1u : 0u);
+                    const uint32_t acc_flag = it > (kSplit ? wi.c_begin : 0) ? 1u : 0u;     // the first chunk overwrites
+                    if (a.ncat) umma_tf32_chunk_cat(d, ad, ad + (kABytes >> 4), bd, idesc2, idesc, acc_flag);
+                    else if (split) umma_tf32_chunk_split(d, ad, ad + (kABytes >> 4), bd, bd + (b_bytes >> 4), idesc, acc_flag);
+                    else umma_tf32_chunk(d, ad, bd, idesc, acc_flag);
                     umma_commit(&bar_empty[s]);
                     TRACEC(ti * chunks + it, 3);
                     if (++s == a.stages) { s = 0; ph ^= 1u; }
@@ -284,11 +318,12 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             uint32_t ph = 0;
             int xti = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x, ++xti) {
-                for (int it = 0; it < chunks; ++it) {
+            for (int w = blockIdx.x; w < a.total_work && ok; w += gridDim.x, ++xti) {
+                const WorkItem wi = work_item<kSplit>(a, w, chunks);
+                for (int it = wi.c_begin; it < wi.c_end; ++it) {
                     ok = wait_or_abort(&bar_full[s], ph, abort_flag);
                     if (!ok) { record_error(err_flag, 3); s_abort = 1; break; }
-                    if (t == 0 && it == 0) TRACE(xti, 2);
+                    if (t == 0 && it == wi.c_begin) TRACE(xti, 2);
                     float4* pa = reinterpret_cast<float4*>(base_ptr + (size_t)s * stage_bytes);
                     float4* pl = pa + kABytes / 16;
                     for (int i = t; i < kABytes / 16; i += nthr) {
@@ -303,7 +338,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     mbar_arrive(&bar_xf[s]);
-                    if (t == 0 && it == 0) TRACE(xti, 3);
+                    if (t == 0 && it == wi.c_begin) TRACE(xti, 3);
                     if (++s == a.stages) { s = 0; ph ^= 1u; }
                 }
             }
@@ -323,9 +358,10 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             bool ok = true;
             int ti = 0;
             int staged_nbase = -1;
-            for (int tile = blockIdx.x; tile < a.total_tiles && ok; tile += gridDim.x, ++ti) {
+            for (int w = blockIdx.x; w < a.total_work && ok; w += gridDim.x, ++ti) {
                 if (ti % a.epi_groups != eg) continue;
-                const TileCoord tc_ = tile_coord(a, tile);
+                const WorkItem wi = work_item<kSplit>(a, w, chunks);
+                const TileCoord tc_ = tile_coord(a, wi.tile);
                 const int as = ti & 1, use = ti >> 1;
                 const int nbase = tc_.n_tile * a.BN;
                 int groups = (a.Kp - nbase + 31) / 32;
@@ -339,10 +375,12 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 // is still being produced; skipped when the previous tile had the same columns.
                 // Safe to overwrite here: every thread of the group passed the sync that follows the
                 // last read of the previous tile's values.
-                if (nbase != staged_nbase) {
+                // (with a split reduction only the first work item of a tile adds the bias)
+                const int bias_key = kSplit ? nbase * 2 + (wi.ks == 0 ? 1 : 0) : nbase;
+                if (bias_key != staged_nbase) {
                     for (int i = t; i < a.BN; i += 128)
-                        my_bias[i] = (a.bias_mode == 2 && nbase + i < a.K) ? a.beta * bias[nbase + i] : 0.f;
-                    staged_nbase = nbase;
+                        my_bias[i] = (a.bias_mode == 2 && (!kSplit || wi.ks == 0) && nbase + i < a.K) ? a.beta * bias[nbase + i] : 0.f;
+                    staged_nbase = bias_key;
                 }
                 if (t == 0) TRACE(ti, 7);
                 ok = wait_or_abort(&bar_acc_full[as], (uint32_t)(use & 1), abort_flag);
@@ -385,6 +423,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                             // every column is a real channel and the bias is per column:
                             // two instructions per value, bias read as 128-bit vectors;
                             // all values first, then the eight 128-bit stores back to back
+                            // (measured faster than storing as they come)
                             const float4* bv = reinterpret_cast<const float4*>(my_bias + col);
                             float4 o[8];
 #pragma unroll
@@ -403,11 +442,9 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                                 }
                                 o[c4] = v;
                             }
-                            if (t == 0 && g0 == 0 && b == 0) TRACE(ti, 2);
                             // 128-byte swizzle: 16-byte chunk index XOR (row mod 8)
 #pragma unroll
                             for (int c4 = 0; c4 < 8; ++c4) dst[c4 ^ (row & 7)] = o[c4];
-                            if (t == 0 && g0 == 0 && b == 0) TRACE(ti, 3);
                         } else {
 #pragma unroll
                             for (int c4 = 0; c4 < 8; ++c4) {
@@ -441,8 +478,14 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                             int col = nbase + (g0 + b) * 32;
                             const CUtensorMap* my = &tmY;
                             if (a.split_col > 0 && col >= a.split_col) { col -= a.split_col; my = &tmY2; }
-                            if (a.flat) tma_store_4d(my, src, col, tc_.w0, 0, 0);
-                            else tma_store_4d(my, src, col, tc_.w0, tc_.h0, tc_.n0);
+                            if (kSplit) {
+                                if (a.flat) tma_reduce_add_4d(my, src, col, tc_.w0, 0, 0);
+                                else tma_reduce_add_4d(my, src, col, tc_.w0, tc_.h0, tc_.n0);
+                            } else if (a.flat) {
+                                tma_store_4d(my, src, col, tc_.w0, 0, 0);
+                            } else {
+                                tma_store_4d(my, src, col, tc_.w0, tc_.h0, tc_.n0);
+                            }
                         }
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         if (g0 + a.epi_slabs >= groups) TRACE(ti, 13);
@@ -545,18 +588,24 @@ int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, cons
     const long total = m_tiles * t.n_tiles;
     if (total <= 0 || total > 0x7fffffffL) return OGLE_ERR_UNSUPPORTED;
     t.total_tiles = (int)total;
+    if (t.split_k < 1) t.split_k = 1;
+    if (total * t.split_k > 0x7fffffffL) return OGLE_ERR_UNSUPPORTED;
+    t.total_work = (int)(total * t.split_k);
+    t.chunks_per_split = (chunks + t.split_k - 1) / t.split_k;
     const size_t smem = stage * stages + staging;
     static thread_local int attr_device = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (attr_device != dev) {
-        cudaError_t e = cudaFuncSetAttribute(conv_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(conv_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(conv_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
         if (e != cudaSuccess) { set_last_error(e); return OGLE_ERR_CUDA; }
         attr_device = dev;
     }
     const int sms = num_sms();
-    const unsigned grid = (unsigned)(total < sms ? total : sms);
-    conv_tc2_kernel<<<grid, kThreads2, smem, s>>>(mA, mBhi, mBlo, mY, mY2, bias, t, err_flag);
+    const unsigned grid = (unsigned)(t.total_work < sms ? t.total_work : sms);
+    if (t.split_k > 1) conv_tc2_kernel<true><<<grid, kThreads2, smem, s>>>(mA, mBhi, mBlo, mY, mY2, bias, t, err_flag);
+    else conv_tc2_kernel<false><<<grid, kThreads2, smem, s>>>(mA, mBhi, mBlo, mY, mY2, bias, t, err_flag);
     return finish_launch();
 }
 

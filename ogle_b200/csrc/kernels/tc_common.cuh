@@ -41,6 +41,11 @@ struct TcArgs {
     // A_hi x [B_hi; B_lo] is ONE instruction of width 2*BN whose two halves are summed by the
     // epilogue; with A_lo x B_hi that is two instructions per K step instead of three.
     int ncat;
+    // Split reduction: each tile is computed by split_k work items over consecutive ranges of
+    // chunks_per_split reduction chunks; their partial tiles are combined by TMA reduce-add
+    // stores into an output the host zeroed. Used (activation none only) when the tiles alone
+    // would leave most SMs idle or a last round mostly empty. total_work = total_tiles * split_k.
+    int split_k, chunks_per_split, total_work;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

@@ -287,16 +287,29 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const uint32_t d = tmem_d + (uint32_t)(as * acc_cols);
                 for (int it = wi.c_begin; it < wi.c_end; ++it) {
                     if (it == wi.c_begin) TRACE(ti, 4);
-                    ok = wait_or_abort(split ? &bar_xf[s] : &bar_full[s], ph, abort_flag);
+                    ok = wait_or_abort(&bar_full[s], ph, abort_flag);
                     if (!ok) { record_error(err_flag, 2); s_abort = 1; break; }
                     if (it == wi.c_begin) TRACE(ti, 5);
                     TRACEC(ti * chunks + it, 2);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t ad = umma_desc(sA(s)), bd = umma_desc(sBhi(s));
                     const uint32_t acc_flag = it > (kSplit ? wi.c_begin : 0) ? 1u : 0u;     // the first chunk overwrites
-                    if (a.ncat) umma_tf32_chunk_cat(d, ad, ad + (kABytes >> 4), bd, idesc2, idesc, acc_flag);
-                    else if (split) umma_tf32_chunk_split(d, ad, ad + (kABytes >> 4), bd, bd + (b_bytes >> 4), idesc, acc_flag);
-                    else umma_tf32_chunk(d, ad, bd, idesc, acc_flag);
+                    if (!split) {
+                        umma_tf32_chunk(d, ad, bd, idesc, acc_flag);
+                    } else {
+                        // products of the high activation part first (the tile as delivered), then,
+                        // once the split role has written the low part, low x high
+                        if (a.ncat) {
+                            umma_tf32_chunk(d, ad, bd, idesc2, acc_flag);                     // A x [B_hi ; B_lo]
+                        } else {
+                            umma_tf32_chunk(d, ad, bd, idesc, acc_flag);                      // A x B_hi
+                            umma_tf32_chunk(d, ad, bd + (b_bytes >> 4), idesc, 1u);           // A x B_lo
+                        }
+                        ok = wait_or_abort(&bar_xf[s], ph, abort_flag);
+                        if (!ok) { record_error(err_flag, 2); s_abort = 1; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        umma_tf32_chunk(d, ad + (kABytes >> 4), bd, idesc, 1u);               // A_lo x B_hi
+                    }
                     umma_commit(&bar_empty[s]);
                     TRACEC(ti * chunks + it, 3);
                     if (++s == a.stages) { s = 0; ph ^= 1u; }
@@ -307,9 +320,11 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
     } else if (warp >= 10) {
         // --------------------------------------------------- operand split (3-pass)
-        // One or two warp groups work on EVERY chunk together (with two, each thread
-        // takes half as many vectors): the latency of the split is what the shallow
-        // ring of the 3-pass mode (large stages) has to hide.
+        // Writes only the LOW part of the activation tile: the tensor core reads an fp32
+        // operand as TF32 by ignoring the low 13 mantissa bits, so the tile as TMA
+        // delivered it already is the high part, and the products that use it need not
+        // wait for this role. One or two warp groups work on EVERY chunk together (with
+        // two, each thread takes half as many vectors).
         const int xg = (warp - 10) >> 2;           // group 0 or 1
         if (split && xg < a.xf_groups) {
             const int nthr = a.xf_groups * 128;
@@ -333,7 +348,6 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
                         h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
                         h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
-                        pa[i] = h;
                         pl[i] = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -136,7 +136,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     // every byte of the 224 KB request is usable
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[kMaxStages], bar_xf[kMaxStages], bar_empty[kMaxStages];
-    __shared__ __align__(8) uint64_t bar_acc_full[2], bar_acc_empty[2];
+    __shared__ __align__(8) uint64_t bar_acc_full[4], bar_acc_empty[4];
     __shared__ uint32_t tmem_slot;
     __shared__ int s_abort;
     __shared__ __align__(16) float s_bias[2][256];
@@ -177,7 +177,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             mbar_init(&bar_xf[s], (uint32_t)(a.xf_groups * 128));
             mbar_init(&bar_empty[s], 1);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < 4; ++i) {
             mbar_init(&bar_acc_full[i], 1);
             mbar_init(&bar_acc_empty[i], 128);
         }
@@ -280,7 +280,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             int ti = 0;
             for (int w = blockIdx.x; w < a.total_work && ok; w += gridDim.x, ++ti) {
                 const WorkItem wi = work_item<kSplit>(a, w, chunks);
-                const int as = ti & 1, use = ti >> 1;
+                const int as = a.n_acc == 4 ? (ti & 3) : (ti & 1), use = a.n_acc == 4 ? (ti >> 2) : (ti >> 1);
                 if (use > 0) ok = wait_or_abort(&bar_acc_empty[as], (uint32_t)((use - 1) & 1), abort_flag);
                 if (!ok) { record_error(err_flag, 5); s_abort = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -372,11 +372,12 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             bool ok = true;
             int ti = 0;
             int staged_nbase = -1;
+            int round_no = 0;          // rounds of this group so far (selects the staging slab)
             for (int w = blockIdx.x; w < a.total_work && ok; w += gridDim.x, ++ti) {
                 if (ti % a.epi_groups != eg) continue;
                 const WorkItem wi = work_item<kSplit>(a, w, chunks);
                 const TileCoord tc_ = tile_coord(a, wi.tile);
-                const int as = ti & 1, use = ti >> 1;
+                const int as = a.n_acc == 4 ? (ti & 3) : (ti & 1), use = a.n_acc == 4 ? (ti >> 2) : (ti >> 1);
                 const int nbase = tc_.n_tile * a.BN;
                 int groups = (a.Kp - nbase + 31) / 32;
                 if (groups > a.BN / 32) groups = a.BN / 32;
@@ -401,14 +402,21 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if (!ok) { record_error(err_flag, 4); s_abort = 1; break; }
                 if (t == 0) TRACE(ti, 8);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                for (int g0 = 0; g0 < groups; g0 += a.epi_slabs) {
-                    const int nb = groups - g0 < a.epi_slabs ? groups - g0 : a.epi_slabs;
-                    // both slabs are free once the previous round's stores have read them
-                    if (t == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                // one 32-column slab per round through a ring of one or two staging slabs: a slab
+                // is reused once the store issued from it (one or two rounds ago) has read it, so
+                // with two slabs a round never waits for the store of the round just before
+                for (int g0 = 0; g0 < groups; ++g0) {
+                    const int sb = round_no % a.epi_slabs;
+                    ++round_no;
+                    if (t == 0) {
+                        if (a.epi_slabs == 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                        else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    }
                     group_sync(bar_id);
                     if (t == 0 && g0 == 0) TRACE(ti, 9);
-                    for (int b = 0; b < nb; ++b) {
-                        const int col = (g0 + b) * 32;
+                    {
+                        const int b = 0;
+                        const int col = g0 * 32;
                         uint32_t r[32];
                         const uint32_t taddr = tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * acc_cols + col);
                         tmem_ld32(r, taddr);
@@ -427,7 +435,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                             mbar_arrive(&bar_acc_empty[as]);
                         }
-                        float4* dst = reinterpret_cast<float4*>(staging + (size_t)b * kStagingBytes + (size_t)row * 128);
+                        float4* dst = reinterpret_cast<float4*>(staging + (size_t)sb * kStagingBytes + (size_t)row * 128);
                         // which output this slab belongs to, and its first column there
                         const bool second = a.split_col > 0 && nbase + col >= a.split_col;
                         const int lcol = second ? nbase + col - a.split_col : nbase + col;
@@ -487,9 +495,9 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     group_sync(bar_id);
                     if (t == 0 && g0 == 0) TRACE(ti, 12);
                     if (t == 0) {
-                        for (int b = 0; b < nb; ++b) {
-                            const uint32_t src = base + my_staging + (uint32_t)b * (uint32_t)kStagingBytes;
-                            int col = nbase + (g0 + b) * 32;
+                        {
+                            const uint32_t src = base + my_staging + (uint32_t)sb * (uint32_t)kStagingBytes;
+                            int col = nbase + g0 * 32;
                             const CUtensorMap* my = &tmY;
                             if (a.split_col > 0 && col >= a.split_col) { col -= a.split_col; my = &tmY2; }
                             if (kSplit) {
@@ -502,7 +510,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                             }
                         }
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                        if (g0 + a.epi_slabs >= groups) TRACE(ti, 13);
+                        if (g0 + 1 >= groups) TRACE(ti, 13);
                     }
                 }
             }
@@ -585,7 +593,8 @@ int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, cons
         if (stages_with(t.epi_groups, t.epi_slabs) < 2) { t.epi_groups = 1; t.epi_slabs = 1; }
     }
     if (const char* e = getenv("OGLE_TC_XF_GROUPS")) t.xf_groups = (t.passes == 3 && e[0] == '2') ? 2 : 1;
-    if (const char* e = getenv("OGLE_TC_EPI_GROUPS")) if (e[0] == '1') t.epi_groups = 1;
+    if (const char* e = getenv("OGLE_TC_EPI_GROUPS")) t.epi_groups = e[0] == '1' ? 1 : 2;
+    if (const char* e = getenv("OGLE_TC_EPI_SLABS")) t.epi_slabs = e[0] == '1' ? 1 : 2;
     const size_t staging = (size_t)t.epi_groups * t.epi_slabs * kStagingBytes;
     const size_t budget = kBudget - staging;
     int stages = (int)(budget / stage);
@@ -596,8 +605,12 @@ int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, cons
     // (long reductions only: it costs the epilogue a second tensor-memory read per slab,
     // which the short, bandwidth-bound pointwise layers cannot hide)
     t.ncat = (t.passes == 3 && chunks >= ncat_min_chunks() && t.BN <= ncat_max_bn()) ? 1 : 0;
+    // accumulators: two, or four when they fit the 512 columns of tensor memory - the multiplies
+    // of a tile can then start while the epilogues of the two tiles before it still drain theirs
+    const int acc_cols = t.BN * (t.ncat ? 2 : 1);
+    t.n_acc = 4 * acc_cols <= 512 ? 4 : 2;
     int cols = 32;
-    while (cols < 2 * t.BN * (t.ncat ? 2 : 1)) cols <<= 1;
+    while (cols < t.n_acc * acc_cols) cols <<= 1;
     t.tmem_cols = cols;
     const long total = m_tiles * t.n_tiles;
     if (total <= 0 || total > 0x7fffffffL) return OGLE_ERR_UNSUPPORTED;

@@ -30,6 +30,7 @@ struct TcArgs {
     int passes;               // 1 (TF32) or 3 (hi/lo split)
     int stages;
     int tmem_cols;
+    int n_acc;                // accumulator buffers in tensor memory (2 or 4)
     int total_tiles;          // m_tiles * n_tiles (persistent kernel)
     int epi_groups, xf_groups; // persistent kernel: warp groups per role (1 or 2)
     int epi_slabs;            // staging slabs (128 rows x 32 columns) per epilogue group (1 or 2)

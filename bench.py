@@ -74,7 +74,7 @@ def make_inputs(batch, seed0):
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons, sampled every 20 ms while the timed regions run."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -85,7 +85,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.FIELDS,
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -287,13 +287,13 @@ def main():
     sampler = ClockSampler(local_rank)
     sampler.start()
     ms = timed(resident, K)
-    clocks = sampler.stop()
     value = world * B * K / (ms / 1000.0)
 
     for i in range(W):
         e2e_step(i)
     e2e_drain()
     ms_e2e = timed(e2e_step, K, e2e_drain)
+    clocks = sampler.stop()     # sampled across both timed regions
     inf = det.info()
     e2e = {"value": world * B * K / (ms_e2e / 1000.0), "unit": UNIT, "h2d_bytes_per_step": inf["h2d_bytes"],
            "d2h_bytes_per_step": inf["d2h_bytes"]}

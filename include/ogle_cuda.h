@@ -48,7 +48,8 @@ typedef enum {
 typedef enum {
     OGLE_MATH_FP32 = 0,   /* CUDA-core fp32 FMA                                         */
     OGLE_MATH_TF32 = 1,   /* tcgen05 kind::tf32, one pass (10-bit mantissa operands)    */
-    OGLE_MATH_TF32X3 = 2  /* tcgen05 kind::tf32, 3-pass hi/lo split: fp32-grade results */
+    OGLE_MATH_TF32X3 = 2  /* hi/lo operand split, three products (one TF32 pass + one BF16
+                             pass of the two cross terms): fp32-grade results           */
 } OgleMathMode;
 
 typedef enum { OGLE_ACT_NONE = 0, OGLE_ACT_CLIP = 1, OGLE_ACT_RELU = 2 } OgleActivation;

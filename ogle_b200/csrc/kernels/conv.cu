@@ -1,4 +1,6 @@
 // conv2d entry points: shape inference, filter packing and variant dispatch.
+#include <cuda_bf16.h>
+
 #include "conv_args.cuh"
 
 namespace ogle {
@@ -29,7 +31,7 @@ __global__ void prepack_tap_major_kernel(const float* __restrict__ w, float* __r
 }
 
 __global__ void prepack_kmajor_kernel(const float* __restrict__ w, float* __restrict__ hi,
-                                      float* __restrict__ lo, int K, int Cg, int kernel,
+                                      __nv_bfloat16* __restrict__ cross, int K, int Cg, int kernel,
                                       int Kp128, int Cp32) {
     const int taps = kernel * kernel;
     const long total = (long)Kp128 * taps * Cp32;
@@ -41,11 +43,13 @@ __global__ void prepack_kmajor_kernel(const float* __restrict__ w, float* __rest
         const int k = int(t);
         float v = 0.f;
         if (k < K && c < Cg) v = w[((long)k * Cg + c) * taps + tap];
-        // hi keeps the 10 mantissa bits a TF32 operand carries; lo is the exact
-        // remainder (itself later truncated to TF32 by the tensor core)
+        // hi keeps the 10 mantissa bits a TF32 operand carries; the cross section holds, per
+        // 32-channel chunk, [bf16(w - hi) x 32 | bf16(w) x 32] for the BF16 pass
         const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
         hi[i] = h;
-        lo[i] = v - h;
+        const long chunk = i - (c & 31);
+        cross[chunk * 2 + (c & 31)] = __float2bfloat16_rn(v - h);
+        cross[chunk * 2 + 32 + (c & 31)] = __float2bfloat16_rn(v);
     }
 }
 
@@ -129,7 +133,7 @@ int ogle_cuda_conv2d_prepack(const OgleConvParams* p, const float* w_oihw, void*
     if (L.kmajor_bytes) {
         const long n1 = (long)L.Kp128 * a.kernel * a.kernel * L.Cp32;
         prepack_kmajor_kernel<<<grid_for(n1, 256), 256, 0, s>>>(
-            w_oihw, reinterpret_cast<float*>(base + L.off_hi), reinterpret_cast<float*>(base + L.off_lo),
+            w_oihw, reinterpret_cast<float*>(base + L.off_hi), reinterpret_cast<__nv_bfloat16*>(base + L.off_lo),
             a.K, Cg, a.kernel, L.Kp128, L.Cp32);
         rc = finish_launch();
     }

@@ -24,7 +24,9 @@ struct ConvArgs {
 //   section 1  "k-major hi" [Kp128][kernel*kernel][Cp32] fp32 with the low 13
 //              mantissa bits cleared: B operand of the tcgen05 path (TMA tiles of
 //              128 output channels x 32 reduction elements).
-//   section 2  "k-major lo" same shape: w - hi(w), for the 3-pass TF32 split.
+//   section 2  "k-major cross" same size: per 32-channel chunk of a row, 64 bf16 values
+//              [w - hi(w) x 32 | w x 32]: B operand of the BF16 cross-term pass of the
+//              split mode (against [a_hi | a_lo]); moved by TMA as 128-byte rows like section 1.
 // Sections 1 and 2 exist only for group == 1.
 struct FilterLayout {
     size_t tap_major_bytes, kmajor_bytes;   // one k-major section

@@ -1,5 +1,5 @@
 // Persistent tcgen05 kernel for the dense contractions (conv2d general/pointwise
-// as implicit GEMM, gemm): the same arithmetic as conv_tc.cu, restructured so that
+// as implicit GEMM, gemm; tile shapes and tensor maps come from conv_tc.cu):
 // one block per SM walks a list of output tiles and every stage of the pipeline
 // overlaps with the others ACROSS tiles:
 //
@@ -7,14 +7,15 @@
 //               stages full, running ahead into the next tile while the current one is
 //               still being multiplied; two issuing threads because one tensor copy
 //               costs its issuer over a hundred cycles;
-//   warp 1      MMA issuer: accumulates tile i into one half of tensor memory while
-//               the epilogue drains tile i-1 from the other half;
+//   warp 1      MMA issuer: accumulates tile i into one of 2-4 tensor-memory buffers while
+//               the epilogues drain earlier tiles from the others;
 //   warps 2-9   two epilogue groups of four warps, taking alternate tiles:
 //               tcgen05.ld -> bias / activation -> shared-memory staging in the
 //               128-byte swizzle -> TMA tensor store (fully coalesced, clipped at the
 //               tensor edge by the hardware);
-//   warps 10-17 two operand-split groups for the 3-pass TF32 mode, taking alternate
-//               reduction chunks (idle in one-pass mode).
+//   warps 10-17 two operand-split groups for the split (fp32-grade) mode: they write the
+//               BF16 operand [a_hi | a_lo] of the cross-term pass next to each activation
+//               tile (idle in one-pass mode).
 // Each group's work item has a latency of about a microsecond (shared-memory round
 // trip plus a proxy fence); two groups per role keep that off the critical path.
 //
@@ -22,6 +23,8 @@
 // once, the output tile written once; filters come from L2.
 // All mbarrier waits are bounded and abort the block cleanly (status word set,
 // in-flight copies drained, tensor memory freed).
+#include <cuda_bf16.h>
+
 #include <cstdlib>
 
 #include "tc_common.cuh"
@@ -167,7 +170,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
 
     const int chunks = a.kernel * a.kernel * a.chunks_per_tap;
-    const int acc_cols = a.ncat ? 2 * a.BN : a.BN;     // tensor-memory columns of one accumulator
+    const int acc_cols = a.BN;     // tensor-memory columns of one accumulator
     const int rows_in_tile = a.flat ? kTileM : a.tn * a.th * a.tw;
     volatile int* abort_flag = &s_abort;
 
@@ -273,7 +276,8 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // -------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(a.BN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
-            const uint32_t idesc2 = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(a.BN >> 2) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+            // kind::f16 with BF16 operands (format code 1), fp32 accumulation
+            const uint32_t idesc_bf16 = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.BN >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
             int s = 0;
             uint32_t ph = 0;           // parity of the ring pass
             bool ok = true;
@@ -294,21 +298,14 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t ad = umma_desc(sA(s)), bd = umma_desc(sBhi(s));
                     const uint32_t acc_flag = it > (kSplit ? wi.c_begin : 0) ? 1u : 0u;     // the first chunk overwrites
-                    if (!split) {
-                        umma_tf32_chunk(d, ad, bd, idesc, acc_flag);
-                    } else {
-                        // products of the high activation part first (the tile as delivered), then,
-                        // once the split role has written the low part, low x high
-                        if (a.ncat) {
-                            umma_tf32_chunk(d, ad, bd, idesc2, acc_flag);                     // A x [B_hi ; B_lo]
-                        } else {
-                            umma_tf32_chunk(d, ad, bd, idesc, acc_flag);                      // A x B_hi
-                            umma_tf32_chunk(d, ad, bd + (b_bytes >> 4), idesc, 1u);           // A x B_lo
-                        }
+                    umma_tf32_chunk(d, ad, bd, idesc, acc_flag);            // a x b_hi (a is read as its high part)
+                    if (split) {
+                        // cross terms [a_hi | a_lo] x [b_lo | b_hi] in BF16, once the split role has
+                        // written the activation parts
                         ok = wait_or_abort(&bar_xf[s], ph, abort_flag);
                         if (!ok) { record_error(err_flag, 2); s_abort = 1; break; }
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        umma_tf32_chunk(d, ad + (kABytes >> 4), bd, idesc, 1u);               // A_lo x B_hi
+                        umma_bf16_chunk(d, ad + (kABytes >> 4), bd + (b_bytes >> 4), idesc_bf16, 1u);
                     }
                     umma_commit(&bar_empty[s]);
                     TRACEC(ti * chunks + it, 3);
@@ -319,12 +316,12 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
         }
     } else if (warp >= 10) {
-        // --------------------------------------------------- operand split (3-pass)
-        // Writes only the LOW part of the activation tile: the tensor core reads an fp32
-        // operand as TF32 by ignoring the low 13 mantissa bits, so the tile as TMA
-        // delivered it already is the high part, and the products that use it need not
-        // wait for this role. One or two warp groups work on EVERY chunk together (with
-        // two, each thread takes half as many vectors).
+        // --------------------------------------------------- operand split (split mode)
+        // Builds the BF16 operand of the cross-term pass next to the activation tile:
+        // row r = [bf16(a_hi) x 32 | bf16(a_lo) x 32] (128 bytes, same 128-byte swizzle), with
+        // a_hi = the value with its low 13 mantissa bits cleared (what the TF32 pass reads)
+        // and a_lo = a - a_hi. The fp32 tile itself is left as TMA delivered it. One or two
+        // warp groups work on EVERY chunk together.
         const int xg = (warp - 10) >> 2;           // group 0 or 1
         if (split && xg < a.xf_groups) {
             const int nthr = a.xf_groups * 128;
@@ -341,14 +338,24 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     if (t == 0 && it == wi.c_begin) TRACE(xti, 2);
                     float4* pa = reinterpret_cast<float4*>(base_ptr + (size_t)s * stage_bytes);
                     float4* pl = pa + kABytes / 16;
+                    uint2* p2 = reinterpret_cast<uint2*>(pl);                 // 8-byte pieces of the BF16 tile
                     for (int i = t; i < kABytes / 16; i += nthr) {
                         const float4 v = pa[i];
+                        const int r = i >> 3, j = (i & 7) ^ (r & 7);          // row; logical 16-byte chunk = channels 4j..4j+3
                         float4 h;
                         h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
                         h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
                         h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
                         h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
-                        pl[i] = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+                        const __nv_bfloat162 h01 = __floats2bfloat162_rn(h.x, h.y), h23 = __floats2bfloat162_rn(h.z, h.w);
+                        const __nv_bfloat162 l01 = __floats2bfloat162_rn(v.x - h.x, v.y - h.y), l23 = __floats2bfloat162_rn(v.z - h.z, v.w - h.w);
+                        uint2 hv, lv;
+                        hv.x = *reinterpret_cast<const uint32_t*>(&h01); hv.y = *reinterpret_cast<const uint32_t*>(&h23);
+                        lv.x = *reinterpret_cast<const uint32_t*>(&l01); lv.y = *reinterpret_cast<const uint32_t*>(&l23);
+                        // bf16 column 4j (hi) / 32 + 4j (lo): 16-byte chunk j/2 resp. 4 + j/2, half j & 1
+                        const int ch = (j >> 1) ^ (r & 7), cl = (4 + (j >> 1)) ^ (r & 7);
+                        p2[r * 16 + ch * 2 + (j & 1)] = hv;
+                        p2[r * 16 + cl * 2 + (j & 1)] = lv;
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     mbar_arrive(&bar_xf[s]);
@@ -420,14 +427,6 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         uint32_t r[32];
                         const uint32_t taddr = tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * acc_cols + col);
                         tmem_ld32(r, taddr);
-                        if (a.ncat) {
-                            // second half of the accumulator: the hi*lo products
-                            uint32_t r2[32];
-                            tmem_ld32(r2, taddr + (uint32_t)a.BN);
-                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(r2[i]));
-                        }
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                         if (t == 0 && g0 == 0 && b == 0) TRACE(ti, 14);
                         if (g0 + b == groups - 1) {
@@ -527,24 +526,6 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
 }
 
-// Widest N tile that uses the stacked-filter form; OGLE_TC_NCAT_MAX_BN overrides (0 disables).
-int ncat_max_bn() {
-    static const int v = [] {
-        const char* e = getenv("OGLE_TC_NCAT_MAX_BN");
-        int n = e ? atoi(e) : 128;
-        return n < 0 ? 0 : (n > 128 ? 128 : n);
-    }();
-    return v;
-}
-
-int ncat_min_chunks() {
-    static const int v = [] {
-        const char* e = getenv("OGLE_TC_NCAT_MIN_CHUNKS");
-        return e ? atoi(e) : 8;
-    }();
-    return v;
-}
-
 int num_sms() {
     static thread_local int sms = 0, sms_device = -1;
     int dev = 0;
@@ -601,13 +582,9 @@ int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, cons
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) return OGLE_ERR_UNSUPPORTED;
     t.stages = stages;
-    // stacked-filter form of the 3-pass mode (see TcArgs::ncat)
-    // (long reductions only: it costs the epilogue a second tensor-memory read per slab,
-    // which the short, bandwidth-bound pointwise layers cannot hide)
-    t.ncat = (t.passes == 3 && chunks >= ncat_min_chunks() && t.BN <= ncat_max_bn()) ? 1 : 0;
     // accumulators: two, or four when they fit the 512 columns of tensor memory - the multiplies
     // of a tile can then start while the epilogues of the two tiles before it still drain theirs
-    const int acc_cols = t.BN * (t.ncat ? 2 : 1);
+    const int acc_cols = t.BN;
     t.n_acc = 4 * acc_cols <= 512 ? 4 : 2;
     int cols = 32;
     while (cols < t.n_acc * acc_cols) cols <<= 1;

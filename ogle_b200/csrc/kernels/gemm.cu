@@ -1,6 +1,8 @@
 // Gemm: Y[M,N] = alpha * A[M,K] * (transB ? B[N,K]^T : B[K,N]) + beta * C.
 // OGLE_MATH_FP32 runs the register-tiled CUDA-core kernel below; the TF32 modes
 // go to the tcgen05 path when the shape allows it.
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 
 namespace ogle {
@@ -11,8 +13,11 @@ bool gemm_tc_supported(const OgleGemmParams& p, const float* A, const float* B);
 int launch_gemm_tc_packed(const OgleGemmParams& p, const float* A, const float* Bhi, const float* Blo,
                           const float* C, float* Y, cudaStream_t s);
 
-// B [K][ldb] (or [N][ldb] when transB) -> hi / lo, each [round_up(N,128)][round_up(K,32)], K-major.
-__global__ void gemm_pack_b_kernel(const float* __restrict__ B, float* __restrict__ hi, float* __restrict__ lo,
+// B [K][ldb] (or [N][ldb] when transB) -> two K-major sections of [round_up(N,128)][round_up(K,32)]
+// 4-byte slots each: the fp32 values with the low 13 mantissa bits cleared (operand of the TF32
+// pass), and per 32-element chunk of a row the 64 bf16 values [b_lo x 32 | b x 32] (operand of
+// the BF16 cross-term pass, against [a_hi | a_lo]).
+__global__ void gemm_pack_b_kernel(const float* __restrict__ B, float* __restrict__ hi, __nv_bfloat16* __restrict__ cross,
                                    int K, int N, int ldb, int transB, int Kp32, int Np128) {
     const long total = (long)Np128 * Kp32;
     for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total;
@@ -22,7 +27,9 @@ __global__ void gemm_pack_b_kernel(const float* __restrict__ B, float* __restric
         if (k < K && n < N) v = transB ? B[(long)n * ldb + k] : B[(long)k * ldb + n];
         const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
         hi[i] = h;
-        lo[i] = v - h;
+        const long chunk = (long)n * Kp32 + (k & ~31);        // first slot of this 32-element chunk
+        cross[chunk * 2 + (k & 31)] = __float2bfloat16_rn(v - h);
+        cross[chunk * 2 + 32 + (k & 31)] = __float2bfloat16_rn(v);
     }
 }
 
@@ -178,7 +185,7 @@ extern "C" int ogle_cuda_gemm_pack_b(const OgleGemmParams* pp, const float* B, v
     const size_t half = (size_t(Np128) * Kp32 * sizeof(float) + 255) / 256 * 256;
     float* hi = static_cast<float*>(packed);
     float* lo = reinterpret_cast<float*>(static_cast<char*>(packed) + half);
-    gemm_pack_b_kernel<<<grid_for((long)Np128 * Kp32, 256), 256, 0, (cudaStream_t)stream>>>(B, hi, lo, p.K, p.N, p.ldb,
+    gemm_pack_b_kernel<<<grid_for((long)Np128 * Kp32, 256), 256, 0, (cudaStream_t)stream>>>(B, hi, reinterpret_cast<__nv_bfloat16*>(lo), p.K, p.N, p.ldb,
                                                                                             p.transB, Kp32, Np128);
     return finish_launch();
 }

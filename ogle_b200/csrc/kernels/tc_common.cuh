@@ -27,7 +27,7 @@ struct TcArgs {
     float alpha, beta;
     int bias_mode;            // 0 none, 1 full matrix C[m][ldc], 2 per-column vector
     int ldc;
-    int passes;               // 1 (TF32) or 3 (hi/lo split)
+    int passes;               // 1 (TF32) or 3 (split mode: a TF32 pass + a BF16 pass of the cross terms)
     int stages;
     int tmem_cols;
     int n_acc;                // accumulator buffers in tensor memory (2 or 4)
@@ -38,10 +38,6 @@ struct TcArgs {
     // columns [0, K1) go to the first tensor, columns [split_col, K) to the second.
     // split_col is a multiple of 32 (0 = single output).
     int split_col, K1;
-    // 3-pass mode, BN <= 128: the hi and lo filter tiles sit back to back in a stage, so
-    // A_hi x [B_hi; B_lo] is ONE instruction of width 2*BN whose two halves are summed by the
-    // epilogue; with A_lo x B_hi that is two instructions per K step instead of three.
-    int ncat;
     // Split reduction: each tile is computed by split_k work items over consecutive ranges of
     // chunks_per_split reduction chunks; their partial tiles are combined by TMA reduce-add
     // stores into an output the host zeroed. Used (activation none only) when the tiles alone
@@ -124,52 +120,23 @@ __device__ __forceinline__ void umma_tf32_chunk(uint32_t tmem_d, uint64_t ad, ui
         ::"r"(tmem_d), "l"(ad), "l"(bd), "r"(idesc), "r"(accumulate_first) : "memory");
 }
 
-// The same chunk in the 3-pass split mode: hi*hi + lo*hi + hi*lo for each K step.
-// al / bl are the descriptors of the lo halves of the same stage.
-__device__ __forceinline__ void umma_tf32_chunk_split(uint32_t tmem_d, uint64_t ad, uint64_t al, uint64_t bd, uint64_t bl,
-                                                      uint32_t idesc, uint32_t accumulate_first) {
+// A chunk of the BF16 pass of the split mode: operands are 128-byte rows of 64 bf16
+// ([a_hi | a_lo] against [b_lo | b_hi]), K = 16 per instruction, so the same four
+// 32-byte steps cover the chunk.
+__device__ __forceinline__ void umma_bf16_chunk(uint32_t tmem_d, uint64_t ad, uint64_t bd, uint32_t idesc,
+                                                uint32_t accumulate_first) {
     asm volatile(
-        "{\n\t.reg .pred p, q;\n\t.reg .b64 a, l, b, m;\n\t"
-        "setp.ne.b32 p, %6, 0;\n\t"
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
         "setp.eq.b32 q, 0, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %3, %5, p;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %2, %3, %5, q;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %4, %5, q;\n\t"
-        "add.s64 a, %1, 2;\n\tadd.s64 l, %2, 2;\n\tadd.s64 b, %3, 2;\n\tadd.s64 m, %4, 2;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a, b, %5, q;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], l, b, %5, q;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a, m, %5, q;\n\t"
-        "add.s64 a, %1, 4;\n\tadd.s64 l, %2, 4;\n\tadd.s64 b, %3, 4;\n\tadd.s64 m, %4, 4;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a, b, %5, q;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], l, b, %5, q;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a, m, %5, q;\n\t"
-        "add.s64 a, %1, 6;\n\tadd.s64 l, %2, 6;\n\tadd.s64 b, %3, 6;\n\tadd.s64 m, %4, 6;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a, b, %5, q;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], l, b, %5, q;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a, m, %5, q;\n\t}"
-        ::"r"(tmem_d), "l"(ad), "l"(al), "l"(bd), "l"(bl), "r"(idesc), "r"(accumulate_first) : "memory");
-}
-
-// 3-pass mode with the two filter halves read as one operand of width 2*BN (idesc2):
-// [hi*hi | hi*lo] in one instruction, then lo*hi (idesc1) onto the first half.
-__device__ __forceinline__ void umma_tf32_chunk_cat(uint32_t tmem_d, uint64_t ad, uint64_t al, uint64_t bd,
-                                                    uint32_t idesc2, uint32_t idesc1, uint32_t accumulate_first) {
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\t.reg .b64 a, l, b;\n\t"
-        "setp.ne.b32 p, %6, 0;\n\t"
-        "setp.eq.b32 q, 0, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %3, %4, p;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %2, %3, %5, q;\n\t"
-        "add.s64 a, %1, 2;\n\tadd.s64 l, %2, 2;\n\tadd.s64 b, %3, 2;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a, b, %4, q;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], l, b, %5, q;\n\t"
-        "add.s64 a, %1, 4;\n\tadd.s64 l, %2, 4;\n\tadd.s64 b, %3, 4;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a, b, %4, q;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], l, b, %5, q;\n\t"
-        "add.s64 a, %1, 6;\n\tadd.s64 l, %2, 6;\n\tadd.s64 b, %3, 6;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], a, b, %4, q;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], l, b, %5, q;\n\t}"
-        ::"r"(tmem_d), "l"(ad), "l"(al), "l"(bd), "r"(idesc2), "r"(idesc1), "r"(accumulate_first) : "memory");
+        "add.s64 a1, %1, 2;\n\tadd.s64 b1, %2, 2;\n\t"
+        "add.s64 a2, %1, 4;\n\tadd.s64 b2, %2, 4;\n\t"
+        "add.s64 a3, %1, 6;\n\tadd.s64 b3, %2, 6;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %3, q;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %3, q;\n\t}"
+        ::"r"(tmem_d), "l"(ad), "l"(bd), "r"(idesc), "r"(accumulate_first) : "memory");
 }
 
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {

@@ -214,6 +214,7 @@ struct DetectArgs {
     int N, A, C, logit_stride, mode, top_k, image_w, image_h;
     float score_thr, nms_thr;
     int classes_per_pass;   // mode 1: foreground classes whose scores fit in shared memory at once
+    int parts;              // mode 1: blocks per image, each taking a contiguous range of the foreground classes
 };
 
 // Dynamic shared memory layout:
@@ -224,7 +225,8 @@ ssd_detect_kernel(const float* __restrict__ logits, const float4* __restrict__ b
                   float* __restrict__ out_score, int* __restrict__ out_anchor, int* __restrict__ out_class,
                   float4* __restrict__ out_box, int* __restrict__ out_count, DetectArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
-    const int n = blockIdx.x;
+    const int parts = a.mode == 1 ? a.parts : 1;
+    const int n = blockIdx.x / parts, part = blockIdx.x - n * parts;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const float* lg = logits + (long)n * a.A * a.logit_stride;
     const float4* bx = boxes + (long)n * a.A;
@@ -236,11 +238,13 @@ ssd_detect_kernel(const float* __restrict__ logits, const float4* __restrict__ b
         unsigned long long* list = reinterpret_cast<unsigned long long*>(wbase + (size_t)warp * 2048);
         unsigned* hist = reinterpret_cast<unsigned*>(list);
         const int rows = (a.C - 1) * a.top_k;
-        for (int c0 = 1; c0 < a.C; c0 += a.classes_per_pass) {
-            const int nc = min(a.classes_per_pass, a.C - c0);
+        const int per_part = (a.C - 1 + parts - 1) / parts;
+        const int c_lo = 1 + part * per_part, c_hi = min(a.C, c_lo + per_part);     // this block's classes
+        for (int c0 = c_lo; c0 < c_hi; c0 += a.classes_per_pass) {
+            const int nc = min(a.classes_per_pass, c_hi - c0);
             // softmax exactly as the reference post-process does: exp of the raw
             // logits, summed in class order, then one divide per class
-            if (nc == a.C - 1 && a.C <= 32 && (a.logit_stride & 3) == 0 && a.logit_stride <= 32) {
+            if (nc == c_hi - c_lo && a.C <= 32 && (a.logit_stride & 3) == 0 && a.logit_stride <= 32) {
                 // the whole row in registers: 128-bit loads, every exponential taken once
                 for (int i = tid; i < a.A; i += blockDim.x) {
                     const float4* row4 = reinterpret_cast<const float4*>(lg + (long)i * a.logit_stride);
@@ -257,7 +261,7 @@ ssd_detect_kernel(const float* __restrict__ logits, const float4* __restrict__ b
                         if (j < a.C) { e[j] = expf(e[j]); total += e[j]; }
 #pragma unroll
                     for (int j = 1; j < 32; ++j)
-                        if (j < a.C) scores[(j - 1) * a.A + i] = e[j] / total;
+                        if (j >= c0 && j < c0 + nc) scores[(j - c0) * a.A + i] = e[j] / total;
                 }
             } else {
                 for (int i = tid; i < a.A; i += blockDim.x) {
@@ -419,17 +423,34 @@ int ogle_cuda_ssd_detect(const OgleDetectParams* p, const float* logits, const f
     int threads;
     size_t smem;
     if (p->mode == 1) {
-        threads = 640;    // 20 warps: one per foreground class of a 21-class head, ~100 registers each
-        const size_t per_warp = 2048, warp_bytes = per_warp * (threads / 32) + 16;
+        // Two blocks per image, each with half of the foreground classes, when that lets two
+        // blocks share an SM and the batch is a few rounds of SMs at most (more, smaller blocks
+        // fill the last round better; for large batches the softmax done twice costs more than
+        // that gains); one warp per class, ~100 registers each.
+        const size_t per_warp = 2048;
         const size_t per_class = (size_t)p->A * sizeof(float);
-        if (per_class + warp_bytes > kSmemBudget) return OGLE_ERR_UNSUPPORTED;
-        size_t cpp = (kSmemBudget - warp_bytes) / per_class;
-        if (cpp > (size_t)(p->C - 1)) cpp = p->C - 1;
+        const int fg = p->C - 1;
+        a.parts = 1;
+        if (fg >= 8 && p->N <= 4 * kNumSMs) {
+            const int half = (fg + 1) / 2;
+            const size_t need = (size_t)half * per_class + per_warp * (size_t)half + 16;
+            if (need <= 108 * 1024) a.parts = 2;
+        }
+        const int classes = (fg + a.parts - 1) / a.parts;
+        int warps = classes < 20 ? classes : 20;
+        if (warps < 1) warps = 1;
+        threads = warps * 32;
+        const size_t warp_bytes = per_warp * (size_t)warps + 16;
+        const size_t budget = a.parts == 2 ? 108 * 1024 : kSmemBudget;
+        if (per_class + warp_bytes > budget) return OGLE_ERR_UNSUPPORTED;
+        size_t cpp = (budget - warp_bytes) / per_class;
+        if (cpp > (size_t)classes) cpp = classes;
         a.classes_per_pass = (int)cpp;
         smem = cpp * per_class + warp_bytes;
     } else {
         threads = 256;
         a.classes_per_pass = 0;
+        a.parts = 1;
         smem = (size_t)p->A * 8 + 16 + 2048 + kMaxTopK * 5 * sizeof(int);
         if (smem > kSmemBudget) return OGLE_ERR_UNSUPPORTED;
     }
@@ -442,7 +463,7 @@ int ogle_cuda_ssd_detect(const OgleDetectParams* p, const float* logits, const f
         if (e != cudaSuccess) { set_last_error(e); return OGLE_ERR_CUDA; }
         attr_set_for_device = dev;
     }
-    ssd_detect_kernel<<<p->N, threads, smem, (cudaStream_t)stream>>>(
+    ssd_detect_kernel<<<p->N * (p->mode == 1 ? a.parts : 1), threads, smem, (cudaStream_t)stream>>>(
         logits, reinterpret_cast<const float4*>(boxes), out_score, out_anchor, out_class,
         reinterpret_cast<float4*>(out_box), out_count, a);
     return finish_launch();

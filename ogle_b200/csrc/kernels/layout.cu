@@ -83,21 +83,26 @@ __global__ void transpose_kernel(const float* __restrict__ x, float* __restrict_
     }
 }
 
-// Same logical order, different padded last dimension.
-__global__ void reshape_kernel(const float* __restrict__ x, float* __restrict__ y,
-                               long n, int in_last, int out_last) {
-    const int ip = (in_last + 3) & ~3, op = (out_last + 3) & ~3;
-    const long total = n / out_last * op;
-    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total;
-         i += (long)gridDim.x * blockDim.x) {
-        const long r = i / op;
-        const int c = int(i - r * op);
-        float v = 0.f;
-        if (c < out_last) {
-            const long e = r * out_last + c;
-            v = x[e / in_last * ip + e % in_last];
+// Same logical order, different padded last dimension. One thread per output float4
+// (four consecutive elements of an output row; lanes past out_last are written as zero).
+template <typename Index>
+__global__ void reshape_kernel(const float* __restrict__ x, float4* __restrict__ y,
+                               Index n, int in_last, int out_last) {
+    const int ip = (in_last + 3) & ~3, oq = ((out_last + 3) & ~3) >> 2;
+    const Index total = n / out_last * oq;
+    for (Index i = blockIdx.x * (Index)blockDim.x + threadIdx.x; i < total; i += (Index)gridDim.x * blockDim.x) {
+        const Index r = i / oq;
+        const int c = int(i - r * oq) * 4;
+        const Index e = r * out_last + c;           // logical index of the first lane
+        Index q = e / in_last;
+        int rem = int(e - q * in_last);
+        float v[4];
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            v[l] = c + l < out_last ? x[q * ip + rem] : 0.f;
+            if (++rem == in_last) { rem = 0; ++q; }
         }
-        y[i] = v;
+        y[i] = make_float4(v[0], v[1], v[2], v[3]);
     }
 }
 
@@ -226,7 +231,14 @@ int ogle_cuda_reshape(const float* x, float* y, long n_elements, int in_last, in
     if (!x || !y || n_elements <= 0 || in_last <= 0 || out_last <= 0) return OGLE_ERR_INVALID;
     if (n_elements % in_last || n_elements % out_last) return OGLE_ERR_INVALID;
     const long items = n_elements / out_last * up4(out_last);
-    reshape_kernel<<<grid_for(items, 256), 256, 0, (cudaStream_t)stream>>>(x, y, n_elements, in_last, out_last);
+    if (!aligned16(y)) return OGLE_ERR_ALIGNMENT;
+    const long vecs = items / 4;
+    if (n_elements < 0x7fffffffL && items < 0x7fffffffL)     // 32-bit index arithmetic when it fits (the usual case)
+        reshape_kernel<unsigned><<<grid_for(vecs, 256), 256, 0, (cudaStream_t)stream>>>(
+            x, reinterpret_cast<float4*>(y), (unsigned)n_elements, in_last, out_last);
+    else
+        reshape_kernel<long><<<grid_for(vecs, 256), 256, 0, (cudaStream_t)stream>>>(
+            x, reinterpret_cast<float4*>(y), n_elements, in_last, out_last);
     return finish_launch();
 }
 

@@ -150,11 +150,9 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const uint32_t stage_bytes = (split ? 2u : 1u) * (kABytes + b_bytes);
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-    // ring of operand stages (A | A_lo | B_hi | B_lo), then two output staging slabs
+    // ring of operand stages (A | A cross (bf16 hi|lo) | B_hi | B cross (bf16 lo|hi)), then the output staging slabs
     auto sA = [&](int s) { return base + (uint32_t)s * stage_bytes; };
-    auto sAlo = [&](int s) { return sA(s) + kABytes; };
     auto sBhi = [&](int s) { return sA(s) + (split ? 2u : 1u) * kABytes; };
-    auto sBlo = [&](int s) { return sBhi(s) + b_bytes; };
     const uint32_t staging_off = (uint32_t)a.stages * stage_bytes;
     {
         // the layout must fit what the launch reserved (it does when the base is 1024-aligned as
@@ -260,7 +258,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     if (!ok) { record_error(err_flag, 7); break; }
                     mbar_expect_tx(&bar_full[s], tx);
                     tma_load_2d(sBhi(s), &tmBhi, &bar_full[s], brow, bcol);
-                    if (split) tma_load_2d(sBlo(s), &tmBlo, &bar_full[s], brow, bcol);
+                    if (split) tma_load_2d(sBhi(s) + b_bytes, &tmBlo, &bar_full[s], brow, bcol);   // the BF16 cross operand
                     ++issued;
                     if (++s == a.stages) { s = 0; ++wrap; }
                     brow += kChunk;       // packed filter rows follow the chunk order

@@ -9,6 +9,7 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
                    const float* w_hi, const float* w_lo, const float* bias, float* y, cudaStream_t s,
                    float* y2 = nullptr, int K1 = 0, int split_col = 0);
 bool conv_tc_supported(const ConvArgs& a, int variant);
+bool conv_tc_gather_supported(const ConvArgs& a, int variant);
 bool dw_tma_supported(const ConvArgs& a);
 bool conv_smallc_supported(const ConvArgs& a);
 
@@ -50,6 +51,25 @@ __global__ void prepack_kmajor_kernel(const float* __restrict__ w, float* __rest
         const long chunk = i - (c & 31);
         cross[chunk * 2 + (c & 31)] = __float2bfloat16_rn(v - h);
         cross[chunk * 2 + 32 + (c & 31)] = __float2bfloat16_rn(v);
+    }
+}
+
+// Compact k-major sections for the gather form (see filter_compact): [Kp128][32], column tap*Cg+c.
+__global__ void prepack_kmajor_compact_kernel(const float* __restrict__ w, float* __restrict__ hi,
+                                              __nv_bfloat16* __restrict__ cross, int K, int Cg, int Kp128) {
+    const long total = (long)Kp128 * 32;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const int col = int(i & 31), k = int(i >> 5);
+        float v = 0.f;
+        if (k < K && col < 9 * Cg) {
+            const int tap = col / Cg, c = col - tap * Cg;
+            v = w[((long)k * Cg + c) * 9 + tap];
+        }
+        const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+        hi[i] = h;
+        const long chunk = i - col;
+        cross[chunk * 2 + col] = __float2bfloat16_rn(v - h);
+        cross[chunk * 2 + 32 + col] = __float2bfloat16_rn(v);
     }
 }
 
@@ -130,7 +150,11 @@ int ogle_cuda_conv2d_prepack(const OgleConvParams* p, const float* w_oihw, void*
                                                                a.K, Cg, a.kernel, a.Cp, a.Kp);
     rc = finish_launch();
     if (rc != OGLE_OK) return rc;
-    if (L.kmajor_bytes) {
+    if (L.kmajor_bytes && filter_compact(Cg, a.kernel, a.group)) {
+        prepack_kmajor_compact_kernel<<<grid_for((long)L.Kp128 * 32, 256), 256, 0, s>>>(
+            w_oihw, reinterpret_cast<float*>(base + L.off_hi), reinterpret_cast<__nv_bfloat16*>(base + L.off_lo), a.K, Cg, L.Kp128);
+        rc = finish_launch();
+    } else if (L.kmajor_bytes) {
         const long n1 = (long)L.Kp128 * a.kernel * a.kernel * L.Cp32;
         prepack_kmajor_kernel<<<grid_for(n1, 256), 256, 0, s>>>(
             w_oihw, reinterpret_cast<float*>(base + L.off_hi), reinterpret_cast<__nv_bfloat16*>(base + L.off_lo),
@@ -153,7 +177,7 @@ int ogle_cuda_conv2d(const OgleConvParams* p, const float* x, const void* packed
     const char* base = static_cast<const char*>(packed_filter);
     cudaStream_t s = (cudaStream_t)stream;
     if (p->math_mode != OGLE_MATH_FP32 && (variant == CONV_GENERAL || variant == CONV_POINTWISE) &&
-        conv_tc_supported(a, variant)) {
+        (conv_tc_supported(a, variant) || conv_tc_gather_supported(a, variant))) {
         const FilterLayout L = filter_layout(a.K, a.C / a.group, a.kernel, a.group, a.Cp);
         return launch_conv_tc(a, variant, p->math_mode, x, reinterpret_cast<const float*>(base + L.off_hi),
                               reinterpret_cast<const float*>(base + L.off_lo), bias, y, s);
@@ -164,7 +188,8 @@ int ogle_cuda_conv2d(const OgleConvParams* p, const float* x, const void* packed
 const char* ogle_cuda_conv2d_kernel_name(const OgleConvParams* p) {
     ConvArgs a; int variant;
     if (fill_args(p, &a, &variant) != OGLE_OK) return "";
-    if (p->math_mode != OGLE_MATH_FP32 && (variant == CONV_GENERAL || variant == CONV_POINTWISE) && conv_tc_supported(a, variant))
+    if (p->math_mode != OGLE_MATH_FP32 && (variant == CONV_GENERAL || variant == CONV_POINTWISE) &&
+        (conv_tc_supported(a, variant) || conv_tc_gather_supported(a, variant)))
         return "conv_tc2_kernel";
     if (variant == CONV_DEPTHWISE) {
         if (dw_tma_supported(a)) return "dw3x3_tma_kernel";

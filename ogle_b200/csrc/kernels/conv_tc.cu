@@ -103,6 +103,14 @@ bool conv_tc_supported(const ConvArgs& a, int variant) {
 
 // y2 != null: two-output form. a.K counts the stacked filters (first conv's K1 channels,
 // zero rows up to split_col, then the second conv's); y receives [0, K1), y2 the rest.
+// The gather form of the kernel: 3x3, at most three input channels stored as 16-byte pixels
+// (the RGB stem), whole reduction (9 x C <= 27 values) in one chunk.
+bool conv_tc_gather_supported(const ConvArgs& a, int variant) {
+    static const bool enabled = [] { const char* e = getenv("OGLE_TC_GATHER"); return e && e[0] == '1'; }();
+    return enabled && variant == CONV_GENERAL && filter_compact(a.C / a.group, a.kernel, a.group) && a.dil == 1 &&
+           (a.stride == 1 || a.stride == 2) && a.Cp == 4 && a.Cs == 4 && a.Wo >= 16 && a.K <= 256 && encode_fn() != nullptr;
+}
+
 int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x, const float* w_hi,
                    const float* w_lo, const float* bias, float* y, cudaStream_t s, float* y2, int K1,
                    int split_col) {
@@ -149,6 +157,36 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
                 if (!make_map(&mY2, y2, 4, yd2, ys2, box, es)) return OGLE_ERR_CUDA;
             }
         }
+    } else if (conv_tc_gather_supported(a, variant) && !y2) {
+        t.flat = 0;
+        t.N = a.N; t.Ho = a.Ho; t.Wo = a.Wo;
+        t.gather = 1; t.g_C = a.C;
+        t.kernel = 1; t.Cp32 = kChunk; t.chunks_per_tap = 1;      // the whole reduction is one gathered chunk
+        // tile: tw x th output pixels of one image, tw*th = 128; the shape that wastes the fewest rows
+        long best = -1;
+        for (int tw = 128; tw >= 16; tw >>= 1) {
+            const int th = kTileM / tw;
+            const long covered = (long)((a.Wo + tw - 1) / tw) * tw * ((a.Ho + th - 1) / th) * th;
+            if ((tw - 1) * a.stride + 3 > 256) continue;
+            if (best < 0 || covered < best) { best = covered; t.tw = tw; t.th = th; }
+        }
+        if (best < 0) return OGLE_ERR_UNSUPPORTED;
+        t.tn = 1;
+        t.tiles_w = (a.Wo + t.tw - 1) / t.tw;
+        t.tiles_h = (a.Ho + t.th - 1) / t.th;
+        m_tiles = (long)t.tiles_w * t.tiles_h * a.N;
+        t.g_iw = (t.tw - 1) * a.stride + 3;
+        t.g_ih = (t.th - 1) * a.stride + 3;
+        t.g_bytes = (t.g_iw * t.g_ih * 16 + 1023) / 1024 * 1024;
+        const cuuint64_t dims[4] = {4, (cuuint64_t)a.W, (cuuint64_t)a.H, (cuuint64_t)a.N};
+        const cuuint64_t str[3] = {(cuuint64_t)a.Cs * 4, (cuuint64_t)a.Cs * 4 * a.W, (cuuint64_t)a.Cs * 4 * a.W * a.H};
+        const cuuint32_t box[4] = {4, (cuuint32_t)t.g_iw, (cuuint32_t)t.g_ih, 1};
+        const cuuint32_t es[4] = {1, 1, 1, 1};
+        if (!make_map_sw(CU_TENSOR_MAP_SWIZZLE_NONE, &mA, x, 4, dims, str, box, es)) return OGLE_ERR_CUDA;
+        const cuuint64_t yd[4] = {(cuuint64_t)kp_a, (cuuint64_t)a.Wo, (cuuint64_t)a.Ho, (cuuint64_t)a.N};
+        const cuuint64_t ys[3] = {(cuuint64_t)ks_a * 4, (cuuint64_t)ks_a * 4 * a.Wo, (cuuint64_t)ks_a * 4 * a.Wo * a.Ho};
+        const cuuint32_t yb[4] = {kChunk, (cuuint32_t)t.tw, (cuuint32_t)t.th, 1};
+        if (!make_map(&mY, y + a.koff, 4, yd, ys, yb, es)) return OGLE_ERR_CUDA;
     } else {
         t.flat = 0;
         t.N = a.N; t.Ho = a.Ho; t.Wo = a.Wo;
@@ -199,8 +237,9 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
     }
     choose_n_tiling_v2(a.Kp, m_tiles, &t);
     const int Kp128 = (a.K + 127) / 128 * 128;
-    const cuuint64_t bdims[2] = {(cuuint64_t)taps * t.Cp32, (cuuint64_t)Kp128};
-    const cuuint64_t bstr[1] = {(cuuint64_t)taps * t.Cp32 * 4};
+    const cuuint64_t bcols = t.gather ? (cuuint64_t)kChunk : (cuuint64_t)taps * t.Cp32;
+    const cuuint64_t bdims[2] = {bcols, (cuuint64_t)Kp128};
+    const cuuint64_t bstr[1] = {bcols * 4};
     const cuuint32_t bbox[2] = {kChunk, (cuuint32_t)t.BN};
     const cuuint32_t bes[2] = {1, 1};
     if (!make_map(&mBhi, w_hi, 2, bdims, bstr, bbox, bes)) return OGLE_ERR_CUDA;
@@ -210,7 +249,7 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
         // mostly empty. Needs a linear epilogue (no activation) and outputs that may be zeroed
         // (dense tensors, not slices of a wider one): the partial tiles are added in place.
         t.split_k = 1;
-        const int chunks = taps * t.chunks_per_tap;
+        const int chunks = t.kernel * t.kernel * t.chunks_per_tap;
         if (a.act == OGLE_ACT_NONE && a.koff == 0 && (y2 != nullptr || a.Ks == a.Kp) && split_k_enabled()) {
             const double tiles = (double)m_tiles * t.n_tiles;
             double best = ceil(tiles / kNumSMs);

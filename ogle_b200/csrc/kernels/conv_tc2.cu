@@ -147,12 +147,13 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool split = a.passes == 3;
     const uint32_t b_bytes = (uint32_t)a.BN * 128u;
-    const uint32_t stage_bytes = (split ? 2u : 1u) * (kABytes + b_bytes);
+    const uint32_t stage_bytes = (split ? 2u : 1u) * (kABytes + b_bytes) + (a.gather ? (uint32_t)a.g_bytes : 0u);
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
     // ring of operand stages (A | A cross (bf16 hi|lo) | B_hi | B cross (bf16 lo|hi)), then the output staging slabs
     auto sA = [&](int s) { return base + (uint32_t)s * stage_bytes; };
     auto sBhi = [&](int s) { return sA(s) + (split ? 2u : 1u) * kABytes; };
+    auto sWin = [&](int s) { return sA(s) + (split ? 2u : 1u) * (kABytes + b_bytes); };   // gather form: input window
     const uint32_t staging_off = (uint32_t)a.stages * stage_bytes;
     {
         // the layout must fit what the launch reserved (it does when the base is 1024-aligned as
@@ -224,8 +225,13 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     if (!ok) { record_error(err_flag, 1); break; }
                     if (it == wi.c_begin) TRACE(pti, 1);
                     TRACEC(pti * chunks + it, 0);
-                    mbar_expect_tx(&bar_full[s], tx);
-                    tma_load_4d(sA(s), &tmA, &bar_full[s], c0, ax + kx * a.dil, ay + ky * a.dil, tc_.n0);
+                    if (a.gather) {
+                        mbar_expect_tx(&bar_full[s], (uint32_t)(a.g_iw * a.g_ih * 16));
+                        tma_load_4d(sWin(s), &tmA, &bar_full[s], 0, ax, ay, tc_.n0);
+                    } else {
+                        mbar_expect_tx(&bar_full[s], tx);
+                        tma_load_4d(sA(s), &tmA, &bar_full[s], c0, ax + kx * a.dil, ay + ky * a.dil, tc_.n0);
+                    }
                     TRACEC(pti * chunks + it, 1);
                     ++issued;
                     if (++s == a.stages) { s = 0; ++wrap; }
@@ -289,7 +295,8 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const uint32_t d = tmem_d + (uint32_t)(as * acc_cols);
                 for (int it = wi.c_begin; it < wi.c_end; ++it) {
                     if (it == wi.c_begin) TRACE(ti, 4);
-                    ok = wait_or_abort(&bar_full[s], ph, abort_flag);
+                    // gather form: the operand exists only once the split warps have built it
+                    ok = wait_or_abort(a.gather ? &bar_xf[s] : &bar_full[s], ph, abort_flag);
                     if (!ok) { record_error(err_flag, 2); s_abort = 1; break; }
                     if (it == wi.c_begin) TRACE(ti, 5);
                     TRACEC(ti * chunks + it, 2);
@@ -300,9 +307,11 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     if (split) {
                         // cross terms [a_hi | a_lo] x [b_lo | b_hi] in BF16, once the split role has
                         // written the activation parts
-                        ok = wait_or_abort(&bar_xf[s], ph, abort_flag);
-                        if (!ok) { record_error(err_flag, 2); s_abort = 1; break; }
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        if (!a.gather) {
+                            ok = wait_or_abort(&bar_xf[s], ph, abort_flag);
+                            if (!ok) { record_error(err_flag, 2); s_abort = 1; break; }
+                            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        }
                         umma_bf16_chunk(d, ad + (kABytes >> 4), bd + (b_bytes >> 4), idesc_bf16, 1u);
                     }
                     umma_commit(&bar_empty[s]);
@@ -321,7 +330,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // and a_lo = a - a_hi. The fp32 tile itself is left as TMA delivered it. One or two
         // warp groups work on EVERY chunk together.
         const int xg = (warp - 10) >> 2;           // group 0 or 1
-        if (split && xg < a.xf_groups) {
+        if ((split || a.gather) && xg < a.xf_groups) {
             const int nthr = a.xf_groups * 128;
             const int t = threadIdx.x - 320;       // 0 .. nthr-1
             int s = 0;
@@ -337,6 +346,44 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     float4* pa = reinterpret_cast<float4*>(base_ptr + (size_t)s * stage_bytes);
                     float4* pl = pa + kABytes / 16;
                     uint2* p2 = reinterpret_cast<uint2*>(pl);                 // 8-byte pieces of the BF16 tile
+                    if (a.gather) {
+                        // build the operand from the input window: one 16-byte piece (4 values) per step
+                        const float* win = reinterpret_cast<const float*>(base_ptr + (size_t)s * stage_bytes +
+                                                                          (split ? 2u : 1u) * (kABytes + b_bytes));
+                        const int kred = 9 * a.g_C;
+                        for (int i = t; i < kABytes / 16; i += nthr) {
+                            const int r = i >> 3, j = i & 7;                  // row; logical chunk = k 4j..4j+3
+                            float v[4] = {0.f, 0.f, 0.f, 0.f};
+                            if (r < rows_in_tile) {
+                                const int ry = r / a.tw, rx = r - ry * a.tw;   // tn == 1 in this form
+                                const float* w0 = win + ((ry * a.stride) * a.g_iw + rx * a.stride) * 4;
+#pragma unroll
+                                for (int l = 0; l < 4; ++l) {
+                                    const int k = j * 4 + l;
+                                    if (k < kred) {
+                                        const int tap = k / a.g_C, c = k - tap * a.g_C;
+                                        const int ky = tap / 3, kx = tap - ky * 3;
+                                        v[l] = w0[(ky * a.g_iw + kx) * 4 + c];
+                                    }
+                                }
+                            }
+                            pa[(r << 3) + (j ^ (r & 7))] = make_float4(v[0], v[1], v[2], v[3]);
+                            if (split) {
+                                float h[4];
+#pragma unroll
+                                for (int l = 0; l < 4; ++l) h[l] = __uint_as_float(__float_as_uint(v[l]) & 0xffffe000u);
+                                const __nv_bfloat162 h01 = __floats2bfloat162_rn(h[0], h[1]), h23 = __floats2bfloat162_rn(h[2], h[3]);
+                                const __nv_bfloat162 l01 = __floats2bfloat162_rn(v[0] - h[0], v[1] - h[1]),
+                                                     l23 = __floats2bfloat162_rn(v[2] - h[2], v[3] - h[3]);
+                                uint2 hv, lv;
+                                hv.x = *reinterpret_cast<const uint32_t*>(&h01); hv.y = *reinterpret_cast<const uint32_t*>(&h23);
+                                lv.x = *reinterpret_cast<const uint32_t*>(&l01); lv.y = *reinterpret_cast<const uint32_t*>(&l23);
+                                const int ch = (j >> 1) ^ (r & 7), cl = (4 + (j >> 1)) ^ (r & 7);
+                                p2[r * 16 + ch * 2 + (j & 1)] = hv;
+                                p2[r * 16 + cl * 2 + (j & 1)] = lv;
+                            }
+                        }
+                    } else
                     for (int i = t; i < kABytes / 16; i += nthr) {
                         const float4 v = pa[i];
                         const int r = i >> 3, j = (i & 7) ^ (r & 7);          // row; logical 16-byte chunk = channels 4j..4j+3
@@ -550,13 +597,13 @@ int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, cons
                  const CUtensorMap& mY, const CUtensorMap& mY2, long m_tiles, const float* bias, int* err_flag,
                  cudaStream_t s) {
     if (t.BN % 32 || t.BN > 256) return OGLE_ERR_UNSUPPORTED;
-    const size_t stage = (size_t)(t.passes == 3 ? 2 : 1) * (kABytes + (size_t)t.BN * 128);
+    const size_t stage = (size_t)(t.passes == 3 ? 2 : 1) * (kABytes + (size_t)t.BN * 128) + (t.gather ? (size_t)t.g_bytes : 0);
     // Shared memory is split between the operand ring and the epilogue's staging slabs
     // (128 rows x 32 columns each). Preference: two epilogue groups with two slabs each;
     // give slabs back to the ring while that buys another stage and the ring is shallow.
     const size_t kBudget = 224 * 1024;
     const int chunks = t.kernel * t.kernel * t.chunks_per_tap;
-    t.xf_groups = t.passes == 3 ? 2 : 1;   // both operand-split groups work on each chunk
+    t.xf_groups = (t.passes == 3 || t.gather) ? 2 : 1;   // both operand-split groups work on each chunk
     t.epi_groups = 2;
     t.epi_slabs = 2;
     if (t.passes == 3 && chunks >= 8) {
@@ -571,7 +618,7 @@ int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, cons
         if (stages_with(2, 2) < shallow && stages_with(2, 1) > stages_with(2, 2)) t.epi_slabs = 1;
         if (stages_with(t.epi_groups, t.epi_slabs) < 2) { t.epi_groups = 1; t.epi_slabs = 1; }
     }
-    if (const char* e = getenv("OGLE_TC_XF_GROUPS")) t.xf_groups = (t.passes == 3 && e[0] == '2') ? 2 : 1;
+    if (const char* e = getenv("OGLE_TC_XF_GROUPS")) t.xf_groups = ((t.passes == 3 || t.gather) && e[0] == '2') ? 2 : 1;
     if (const char* e = getenv("OGLE_TC_EPI_GROUPS")) t.epi_groups = e[0] == '1' ? 1 : 2;
     if (const char* e = getenv("OGLE_TC_EPI_SLABS")) t.epi_slabs = e[0] == '1' ? 1 : 2;
     const size_t staging = (size_t)t.epi_groups * t.epi_slabs * kStagingBytes;

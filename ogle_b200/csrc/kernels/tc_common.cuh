@@ -43,6 +43,13 @@ struct TcArgs {
     // stores into an output the host zeroed. Used (activation none only) when the tiles alone
     // would leave most SMs idle or a last round mostly empty. total_work = total_tiles * split_k.
     int split_k, chunks_per_split, total_work;
+    // Gather form (3x3 convolution over at most three input channels, the RGB stem): the
+    // activation "tile" that TMA delivers is the tile's input window of 16-byte pixels
+    // (g_iw x g_ih of them, halo included); the operand-split warps build the 128 x 32
+    // operand from it, row r = the 9 x C window values of output pixel r (k = tap * C + c),
+    // zero padded, and the whole reduction is one chunk. g_C = input channels, g_bytes =
+    // window bytes rounded up to 1 KB (its slot at the end of every stage).
+    int gather, g_iw, g_ih, g_C, g_bytes;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

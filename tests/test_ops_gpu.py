@@ -117,6 +117,30 @@ def test_conv_tensor_core_modes(oracle_port):
     assert _lib.cuda_lib().ogle_cuda_device_status() == 0
 
 
+@pytest.mark.skipif(os.environ.get("OGLE_TC_GATHER") != "1", reason="gather form is opt-in (OGLE_TC_GATHER=1)")
+def test_conv_stem_gather_form(oracle_port):
+    """3x3 convolutions over 1-3 input channels (the RGB stem) in the tensor-core modes: the operand
+    is gathered from the input window inside the kernel. Same bounds as the other tensor-core
+    layers; ragged sizes exercise tiles that hang over the right and bottom edges."""
+    from gpu_ops import run_case_cuda
+    from ogle_b200 import _lib, ops
+    rng = np.random.default_rng(33)
+    for (N, H, W, C, K, s, p, act) in [(2, 300, 300, 3, 32, 2, 1, 2), (2, 64, 64, 3, 16, 1, 1, 1), (1, 33, 47, 2, 8, 2, 1, 0),
+                                       (2, 17, 29, 1, 5, 1, 1, 0), (1, 150, 150, 3, 64, 1, 0, 2), (3, 40, 40, 3, 100, 2, 0, 1)]:
+        x = rng.standard_normal((N, H, W, C), dtype=np.float32)
+        w = rng.standard_normal((K, C, 3, 3), dtype=np.float32) * np.float32(1.0 / np.sqrt(C * 9))
+        b = rng.standard_normal(K, dtype=np.float32) * np.float32(0.05)
+        case = dict(op="conv2d", x=x, w=w, bias=b, stride=s, pad=p, dilation=1, group=1, act=act, lo=0.0, hi=6.0)
+        ref = oracle_port.conv2d(x, w, b, s, p, 1, 1, act, 0.0, 6.0)
+        scale = np.abs(ref).max()
+        got = run_case_cuda(case, ops.MATH_TF32X3)
+        assert got.shape == ref.shape
+        assert np.abs(got - ref).max() <= 2e-5, (N, H, W, C, K, s, float(np.abs(got - ref).max()))
+        got = run_case_cuda(case, ops.MATH_TF32)
+        assert np.abs(got - ref).max() / scale <= 2e-3, (N, H, W, C, K, s)
+    assert _lib.cuda_lib().ogle_cuda_device_status() == 0
+
+
 def test_conv_pair_equals_two_convs(oracle_port):
     """Sibling convolutions (the SSD box and class heads of one feature map) in one pass. One-pass
     TF32 accumulates each output in the same order whatever the tile width, so it must be

@@ -337,6 +337,26 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             uint32_t ph = 0;
             int xti = 0;
             bool ok = true;
+            // gather form: a thread always builds the same four reduction indices (16-byte piece
+            // t & 7) of the same rows, so their offsets into the input window are computed once:
+            // g_off[l] for k = 4 * (t & 7) + l (or -1 = padding), g_row[q] for row (t >> 3) + q * nthr / 8
+            int g_off[4] = {-1, -1, -1, -1}, g_row[4] = {0, 0, 0, 0};
+            if (a.gather) {
+                const int kred = 9 * a.g_C;
+                for (int l = 0; l < 4; ++l) {
+                    const int k = (t & 7) * 4 + l;
+                    if (k < kred) {
+                        const int tap = k / a.g_C, c = k - tap * a.g_C;
+                        const int ky = tap / 3, kx = tap - ky * 3;
+                        g_off[l] = (ky * a.g_iw + kx) * 4 + c;
+                    }
+                }
+                for (int q = 0; q < 4; ++q) {
+                    const int r = (t >> 3) + q * (nthr >> 3);
+                    const int ry = r / a.tw, rx = r - ry * a.tw;          // tn == 1, tw * th == 128 in this form
+                    g_row[q] = ((ry * a.stride) * a.g_iw + rx * a.stride) * 4;
+                }
+            }
             for (int w = blockIdx.x; w < a.total_work && ok; w += gridDim.x, ++xti) {
                 const WorkItem wi = work_item<kSplit>(a, w, chunks);
                 for (int it = wi.c_begin; it < wi.c_end; ++it) {
@@ -347,26 +367,19 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     float4* pl = pa + kABytes / 16;
                     uint2* p2 = reinterpret_cast<uint2*>(pl);                 // 8-byte pieces of the BF16 tile
                     if (a.gather) {
-                        // build the operand from the input window: one 16-byte piece (4 values) per step
+                        // build the operand from the input window: one 16-byte piece (4 values) per step;
+                        // which values and which rows this thread handles never changes (see g_off / g_row)
                         const float* win = reinterpret_cast<const float*>(base_ptr + (size_t)s * stage_bytes +
                                                                           (split ? 2u : 1u) * (kABytes + b_bytes));
-                        const int kred = 9 * a.g_C;
-                        for (int i = t; i < kABytes / 16; i += nthr) {
-                            const int r = i >> 3, j = i & 7;                  // row; logical chunk = k 4j..4j+3
-                            float v[4] = {0.f, 0.f, 0.f, 0.f};
-                            if (r < rows_in_tile) {
-                                const int ry = r / a.tw, rx = r - ry * a.tw;   // tn == 1 in this form
-                                const float* w0 = win + ((ry * a.stride) * a.g_iw + rx * a.stride) * 4;
+                        const int j = t & 7;
 #pragma unroll
-                                for (int l = 0; l < 4; ++l) {
-                                    const int k = j * 4 + l;
-                                    if (k < kred) {
-                                        const int tap = k / a.g_C, c = k - tap * a.g_C;
-                                        const int ky = tap / 3, kx = tap - ky * 3;
-                                        v[l] = w0[(ky * a.g_iw + kx) * 4 + c];
-                                    }
-                                }
-                            }
+                        for (int q = 0; q < 4; ++q) {
+                            if (q * nthr >= kABytes / 16) break;
+                            const int r = (t >> 3) + q * (nthr >> 3);
+                            const float* w0 = win + g_row[q];
+                            float v[4];
+#pragma unroll
+                            for (int l = 0; l < 4; ++l) v[l] = g_off[l] >= 0 ? w0[g_off[l]] : 0.f;
                             pa[(r << 3) + (j ^ (r & 7))] = make_float4(v[0], v[1], v[2], v[3]);
                             if (split) {
                                 float h[4];
@@ -619,6 +632,7 @@ int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, cons
         if (stages_with(t.epi_groups, t.epi_slabs) < 2) { t.epi_groups = 1; t.epi_slabs = 1; }
     }
     if (const char* e = getenv("OGLE_TC_XF_GROUPS")) t.xf_groups = ((t.passes == 3 || t.gather) && e[0] == '2') ? 2 : 1;
+    if (t.gather) t.xf_groups = 2;        // the gather code is laid out for 256 threads
     if (const char* e = getenv("OGLE_TC_EPI_GROUPS")) t.epi_groups = e[0] == '1' ? 1 : 2;
     if (const char* e = getenv("OGLE_TC_EPI_SLABS")) t.epi_slabs = e[0] == '1' ? 1 : 2;
     const size_t staging = (size_t)t.epi_groups * t.epi_slabs * kStagingBytes;

@@ -141,6 +141,19 @@ def test_conv_stem_gather_form(oracle_port):
     assert _lib.cuda_lib().ogle_cuda_device_status() == 0
 
 
+def test_conv_stem_gather_form_in_its_own_process():
+    """The library reads OGLE_TC_GATHER once per process, so the opt-in path is exercised by running
+    the test above in a child interpreter with the switch on."""
+    if os.environ.get("OGLE_TC_GATHER") == "1":
+        pytest.skip("already running with the gather form on")
+    import subprocess
+    env = dict(os.environ, OGLE_TC_GATHER="1")
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.abspath(__file__), "-m", "gpu", "-q", "-x",
+                        "-k", "test_conv_stem_gather_form and not own_process"],
+                       capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "1 passed" in r.stdout, r.stdout[-2000:] + r.stderr[-1000:]
+
+
 def test_conv_pair_equals_two_convs(oracle_port):
     """Sibling convolutions (the SSD box and class heads of one feature map) in one pass. One-pass
     TF32 accumulates each output in the same order whatever the tile width, so it must be

@@ -50,6 +50,8 @@ def parse_args():
     ap.add_argument("--math", default="tf32x3", choices=list(MATH))
     ap.add_argument("--mode", type=int, default=1, help="0 reference Detector rule, 1 per-class top-k")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-host-binding", action="store_true",
+                    help="leave this process's CPU affinity and memory policy alone (default: bind to the GPU's NUMA node)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="target CPU time of the baseline sample")
     return ap.parse_args()
 
@@ -215,6 +217,9 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (the product path has no CPU fallback)")
     torch.cuda.set_device(local_rank)
+    # one process per GPU: this process and the pinned buffers it uploads from belong on the GPU's NUMA node
+    affinity0 = os.sched_getaffinity(0)
+    placement = None if args.no_host_binding else session.bind_host_to_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     B, K, W = args.batch, args.steps, max(args.warmup, 3)
@@ -298,6 +303,24 @@ def main():
     e2e = {"value": world * B * K / (ms_e2e / 1000.0), "unit": UNIT, "h2d_bytes_per_step": inf["h2d_bytes"],
            "d2h_bytes_per_step": inf["d2h_bytes"]}
 
+    # the same pipeline fed the way the reference's Detector::Detect is (8-bit BGR frames; resize and
+    # mean subtraction on the device): a quarter of the upload bytes. Reported beside `e2e`, not in its place.
+    frames = [torch.randint(0, 256, (B, 300, 300, 3), dtype=torch.uint8,
+                            generator=torch.Generator().manual_seed(7000 + 10 * rank + j)).pin_memory() for j in range(2)]
+
+    def frames_step(i):
+        det.detect_bgr8_frames_async(frames[i & 1].data_ptr(), B, 300, 300, 300, 300)
+        if det.in_flight() == 2:
+            det.wait(fetch=False)
+
+    for i in range(W):
+        frames_step(i)
+    e2e_drain()
+    ms_frames = timed(frames_step, K, e2e_drain)
+    inf8 = det.info()
+    e2e_frames = {"value": world * B * K / (ms_frames / 1000.0), "unit": UNIT, "input": "8-bit BGR frames 300x300",
+                  "h2d_bytes_per_step": inf8["h2d_bytes"], "d2h_bytes_per_step": inf8["d2h_bytes"]}
+
     # roofline of the dominant kernel family, timed live: eager passes with an event pair per node
     roof = None
     if rank == 0:
@@ -345,6 +368,7 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         builder = lambda n: models.mobilenet_v1_ssd(batch=n, num_classes=args.classes, seed=0, weight_std=0.02)
+        os.sched_setaffinity(0, affinity0)       # the CPU baseline uses every core this process was given
         cpu = cpu_baseline(builder, args.classes, args.cpu_seconds)
 
     graph_captured = sess.graph_captured()
@@ -362,8 +386,9 @@ def main():
                                % (args.classes, B, "per-class top-200 (thr 0.01)" if args.mode == 1 else "reference Detector rule"),
                    "global_batch": B * world, "math_mode": args.math, "gflop_per_image": info["flops_per_image"] / 1e9,
                    "l2": "inputs larger than L2 (%.0f MB per step, two batches alternated)" % (B * 300 * 300 * 16 / 1e6),
-                   "parallelism": "image-sharded x%d, no collective" % world, "cuda_graph": graph_captured},
-        "e2e": e2e, "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step,
+                   "parallelism": "image-sharded x%d, no collective" % world, "cuda_graph": graph_captured,
+                   "host_placement": placement},
+        "e2e": e2e, "e2e_bgr8_frames": e2e_frames, "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step,
         "clocks": clocks, "roofline": roof, "cpu_baseline": cpu}), flush=True)
 
 

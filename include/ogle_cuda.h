@@ -239,6 +239,19 @@ int ogle_cuda_unpad4(const float* padded, float* dense, long rows, int last, int
 int ogle_cuda_preprocess_bgr8(const unsigned char* bgr, int src_h, int src_w, int src_row_bytes,
                               float* dst_nhwc4, int dst_h, int dst_w, const float mean_rgb[3],
                               ogle_stream_t stream);
+/* The same for n_images images in ONE launch. The images sit in one device byte buffer;
+ * descs_device (device memory, n_images entries) says where each starts and how large it
+ * is. Image i is written to dst_nhwc4 + i * dst_h * dst_w * 4. The sizes are not checked
+ * on the device: the caller filled the table. */
+typedef struct OgleImageDesc {
+    long long offset;      /* byte offset of the image's first pixel in the buffer */
+    int height, width;     /* pixels */
+    int row_bytes;         /* distance between rows, >= 3 * width */
+    int reserved;
+} OgleImageDesc;
+int ogle_cuda_preprocess_bgr8_batch(const unsigned char* bgr_base, const OgleImageDesc* descs_device, int n_images,
+                                    float* dst_nhwc4, int dst_h, int dst_w, const float mean_rgb[3],
+                                    ogle_stream_t stream);
 /* NCHW dense -> NHWC4 (for callers holding NCHW images). */
 int ogle_cuda_nchw_to_nhwc4(const float* nchw, float* nhwc4, int N, int C, int H, int W,
                             ogle_stream_t stream);

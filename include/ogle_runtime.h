@@ -84,6 +84,17 @@ int ogle_detector_wait(OgleDetector* d, float* score, int* anchor, int* cls, flo
 int ogle_detector_info(OgleDetector* d, int* num_anchors, int* num_classes, int* rows, size_t* h2d_bytes, size_t* d2h_bytes);
 OgleSession* ogle_detector_session(OgleDetector* d);
 
+/* Host placement for one process (or thread) per GPU. No counterpart in the reference, which
+ * runs one GL context on one thread (ogl_runtime/opengl/core/init.cc:21-43).
+ * ogle_host_bind_to_device: narrows the calling thread's CPU affinity to the CPUs of the
+ * NUMA node the device's PCIe function belongs to (among those it may already use) and makes
+ * its later page allocations, pinned buffers included, prefer that node. Call it before
+ * allocating the buffers that feed the device. Always returns 0; *numa_node is -1 and the
+ * other outputs 0 where the topology is unknown or nothing could be changed. */
+int ogle_host_bind_to_device(int device, int* numa_node, int* cpus_bound, int* memory_preferred);
+/* Parses a sysfs CPU list ("0-3,8,10-11"); writes up to `capacity` entries, returns the count. */
+int ogle_host_parse_cpulist(const char* text, int* cpus, int capacity);
+
 #ifdef __cplusplus
 }
 #endif

@@ -87,6 +87,7 @@ CUDA_SYMBOLS = {
     "ogle_cuda_concat": (C.c_int, [C.POINTER(ConcatParams), C.POINTER(_vp), _vp, _vp]),
     "ogle_cuda_pad4": (C.c_int, [_vp, _vp, C.c_long, C.c_int, C.c_int, _vp]),
     "ogle_cuda_unpad4": (C.c_int, [_vp, _vp, C.c_long, C.c_int, C.c_int, _vp]),
+    "ogle_cuda_preprocess_bgr8_batch": (C.c_int, [_vp, _vp, C.c_int, _vp, C.c_int, C.c_int, C.POINTER(C.c_float), _vp]),
     "ogle_cuda_preprocess_bgr8": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, _vp, C.c_int, C.c_int, C.POINTER(C.c_float), _vp]),
     "ogle_cuda_nchw_to_nhwc4": (C.c_int, [_vp, _vp] + [C.c_int] * 4 + [_vp]),
     "ogle_cuda_transpose": (C.c_int, [_vp, _vp, C.POINTER(C.c_int), C.POINTER(C.c_int), _vp]),

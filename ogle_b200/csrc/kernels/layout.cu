@@ -117,29 +117,43 @@ struct ConcatArgs {
 
 // Fast path: axis != 3, or axis == 3 with every slice a multiple of 4 channels.
 // One thread per output float4; each input is read once and the output written once.
-__global__ void concat_vec_kernel(ConcatArgs a, float4* __restrict__ y) {
+// Four independent 16-byte loads are issued before the first store, and the index
+// arithmetic is 32-bit when the tensor allows it (64-bit divisions cost more than the copy).
+template <typename Index>
+__device__ __forceinline__ float4 concat_fetch(const ConcatArgs& a, Index i, int q) {
+    Index t = i;
+    int o[4];
+    o[3] = int(t % q) * 4; t /= q;
+    o[2] = int(t % a.os[2]); t /= a.os[2];
+    o[1] = int(t % a.os[1]); t /= a.os[1];
+    o[0] = int(t);
+    const int pos = o[a.axis];
+    int k = 0;
+    while (k + 1 < a.n_inputs && pos >= a.axis_start[k + 1]) ++k;
+    int s[4] = {a.os[0], a.os[1], a.os[2], a.os[3]};
+    s[a.axis] = a.in_axis[k];
+    o[a.axis] = pos - a.axis_start[k];
+    const int s3p = (s[3] + 3) & ~3;
+    const long off = (((long)o[0] * s[1] + o[1]) * s[2] + o[2]) * s3p + o[3];
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (o[3] < s3p) v = __ldg(reinterpret_cast<const float4*>(a.in[k] + off));
+    return v;
+}
+
+template <typename Index>
+__global__ void __launch_bounds__(256) concat_vec_kernel(ConcatArgs a, float4* __restrict__ y) {
     const int q = ((a.os[3] + 3) & ~3) >> 2;
-    const long total = (long)a.os[0] * a.os[1] * a.os[2] * q;
-    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total;
-         i += (long)gridDim.x * blockDim.x) {
-        long t = i;
-        int o[4];
-        o[3] = int(t % q) * 4; t /= q;
-        o[2] = int(t % a.os[2]); t /= a.os[2];
-        o[1] = int(t % a.os[1]); t /= a.os[1];
-        o[0] = int(t);
-        const int pos = o[a.axis];
-        int k = 0;
-        while (k + 1 < a.n_inputs && pos >= a.axis_start[k + 1]) ++k;
-        int s[4] = {a.os[0], a.os[1], a.os[2], a.os[3]};
-        s[a.axis] = a.in_axis[k];
-        o[a.axis] = pos - a.axis_start[k];
-        const int s3p = (s[3] + 3) & ~3;
-        const long off = (((long)o[0] * s[1] + o[1]) * s[2] + o[2]) * s3p + o[3];
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (o[3] < s3p) v = *reinterpret_cast<const float4*>(a.in[k] + off);
-        y[i] = v;
+    const Index total = (Index)a.os[0] * a.os[1] * a.os[2] * q;
+    const Index step = (Index)gridDim.x * blockDim.x;
+    Index i = blockIdx.x * (Index)blockDim.x + threadIdx.x;
+    for (; i + 3 * step < total; i += 4 * step) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = concat_fetch<Index>(a, i + u * step, q);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) y[i + u * step] = v[u];
     }
+    for (; i < total; i += step) y[i] = concat_fetch<Index>(a, i, q);
 }
 
 // General path (channel-axis slices not multiples of 4): one thread per output float.
@@ -270,8 +284,13 @@ int ogle_cuda_concat(const OgleConcatParams* p, const float* const* inputs, floa
     const int op = up4(a.os[3]);
     const long rows = (long)a.os[0] * a.os[1] * a.os[2];
     if (vec_ok) {
-        concat_vec_kernel<<<grid_for(rows * (op / 4), 256), 256, 0, (cudaStream_t)stream>>>(
-            a, reinterpret_cast<float4*>(y));
+        const long vecs = rows * (op / 4);
+        if (vecs + 4L * kNumSMs * 8 * 256 < (1L << 31))
+            concat_vec_kernel<int><<<grid_for(vecs, 256), 256, 0, (cudaStream_t)stream>>>(
+                a, reinterpret_cast<float4*>(y));
+        else
+            concat_vec_kernel<long><<<grid_for(vecs, 256), 256, 0, (cudaStream_t)stream>>>(
+                a, reinterpret_cast<float4*>(y));
     } else {
         concat_scalar_kernel<<<grid_for(rows * op, 256), 256, 0, (cudaStream_t)stream>>>(a, y);
     }

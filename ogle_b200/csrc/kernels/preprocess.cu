@@ -28,11 +28,9 @@ __device__ __forceinline__ Tap make_tap(int d, int dst, int src) {
     return t;
 }
 
-__global__ void preprocess_bgr8_kernel(const unsigned char* __restrict__ src, int src_h, int src_w, int src_row_bytes,
-                                       float4* __restrict__ dst, int dst_h, int dst_w, float3 mean) {
-    const int x = blockIdx.x * blockDim.x + threadIdx.x;
-    const int y = blockIdx.y * blockDim.y + threadIdx.y;
-    if (x >= dst_w || y >= dst_h) return;
+__device__ __forceinline__ void preprocess_pixel(const unsigned char* __restrict__ src, int src_h, int src_w,
+                                                 int src_row_bytes, float4* __restrict__ dst, int dst_h, int dst_w,
+                                                 float3 mean, int x, int y) {
     const Tap tx = make_tap(x, dst_w, src_w), ty = make_tap(y, dst_h, src_h);
     const unsigned char* r0 = src + (size_t)ty.i0 * src_row_bytes;
     const unsigned char* r1 = src + (size_t)ty.i1 * src_row_bytes;
@@ -49,6 +47,29 @@ __global__ void preprocess_bgr8_kernel(const unsigned char* __restrict__ src, in
     dst[(size_t)y * dst_w + x] = make_float4(out[0] - mean.x, out[1] - mean.y, out[2] - mean.z, 0.f);
 }
 
+__global__ void preprocess_bgr8_kernel(const unsigned char* __restrict__ src, int src_h, int src_w, int src_row_bytes,
+                                       float4* __restrict__ dst, int dst_h, int dst_w, float3 mean) {
+    const int x = blockIdx.x * blockDim.x + threadIdx.x;
+    const int y = blockIdx.y * blockDim.y + threadIdx.y;
+    if (x >= dst_w || y >= dst_h) return;
+    preprocess_pixel(src, src_h, src_w, src_row_bytes, dst, dst_h, dst_w, mean, x, y);
+}
+
+// A batch of images of any sizes in one launch: blockIdx.z walks the images, whose places in
+// the byte buffer and sizes come from a table in device memory.
+__global__ void preprocess_bgr8_batch_kernel(const unsigned char* __restrict__ base,
+                                             const OgleImageDesc* __restrict__ descs, int n_images,
+                                             float4* __restrict__ dst, int dst_h, int dst_w, float3 mean) {
+    const int x = blockIdx.x * blockDim.x + threadIdx.x;
+    const int y = blockIdx.y * blockDim.y + threadIdx.y;
+    if (x >= dst_w || y >= dst_h) return;
+    for (int i = blockIdx.z; i < n_images; i += gridDim.z) {
+        const OgleImageDesc d = descs[i];
+        preprocess_pixel(base + d.offset, d.height, d.width, d.row_bytes, dst + (size_t)i * dst_h * dst_w, dst_h, dst_w,
+                         mean, x, y);
+    }
+}
+
 }  // namespace
 }  // namespace ogle
 
@@ -63,6 +84,20 @@ extern "C" int ogle_cuda_preprocess_bgr8(const unsigned char* bgr, int src_h, in
     const dim3 block(32, 8), grid(div_up(dst_w, 32), div_up(dst_h, 8));
     preprocess_bgr8_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(
         bgr, src_h, src_w, src_row_bytes, reinterpret_cast<float4*>(dst_nhwc4), dst_h, dst_w,
+        make_float3(mean_rgb[0], mean_rgb[1], mean_rgb[2]));
+    return finish_launch();
+}
+
+extern "C" int ogle_cuda_preprocess_bgr8_batch(const unsigned char* base, const OgleImageDesc* descs_device, int n_images,
+                                               float* dst_nhwc4, int dst_h, int dst_w, const float mean_rgb[3],
+                                               ogle_stream_t stream) {
+    if (n_images < 0 || dst_h <= 0 || dst_w <= 0 || !mean_rgb) return OGLE_ERR_INVALID;
+    if (n_images == 0) return OGLE_OK;      // empty batch: nothing to read or write
+    if (!base || !descs_device || !dst_nhwc4) return OGLE_ERR_INVALID;
+    if (!aligned16(dst_nhwc4) || (reinterpret_cast<uintptr_t>(descs_device) & 7)) return OGLE_ERR_ALIGNMENT;
+    const dim3 block(32, 8), grid(div_up(dst_w, 32), div_up(dst_h, 8), n_images < 65535 ? n_images : 65535);
+    preprocess_bgr8_batch_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(
+        base, descs_device, n_images, reinterpret_cast<float4*>(dst_nhwc4), dst_h, dst_w,
         make_float3(mean_rgb[0], mean_rgb[1], mean_rgb[2]));
     return finish_launch();
 }

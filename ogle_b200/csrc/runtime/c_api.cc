@@ -5,6 +5,7 @@
 #include <string>
 
 #include "detector.h"
+#include "host_placement.h"
 #include "fbo_session.h"
 #include "kernel_registry.h"
 #include "ogle_runtime.h"
@@ -252,5 +253,21 @@ int ogle_detector_info(OgleDetector* d, int* num_anchors, int* num_classes, int*
 }
 
 OgleSession* ogle_detector_session(OgleDetector* d) { return d ? &d->session_view : nullptr; }
+
+int ogle_host_bind_to_device(int device, int* numa_node, int* cpus_bound, int* memory_preferred) {
+    const ogle::HostPlacement r = ogle::BindHostToDevice(device);
+    if (numa_node) *numa_node = r.numa_node;
+    if (cpus_bound) *cpus_bound = r.cpus_bound;
+    if (memory_preferred) *memory_preferred = r.memory_preferred ? 1 : 0;
+    return 0;
+}
+
+int ogle_host_parse_cpulist(const char* text, int* cpus, int capacity) {
+    if (!text) return -1;
+    const std::vector<int> v = ogle::ParseCpuList(text);
+    for (int i = 0; i < int(v.size()) && i < capacity; ++i)
+        if (cpus) cpus[i] = v[size_t(i)];
+    return int(v.size());
+}
 
 }  // extern "C"

@@ -39,6 +39,8 @@ void Detector::Release() {
         if (s.stage) cudaFree(s.stage);
         if (s.bytes) cudaFree(s.bytes);
         s.bytes = nullptr; s.bytes_capacity = 0;
+        if (s.desc_host) cudaFreeHost(s.desc_host);
+        s.desc_host = nullptr; s.desc_capacity = 0;
         if (s.out_dev) cudaFree(s.out_dev);
         if (s.out_host) cudaFreeHost(s.out_host);
         s.stage = nullptr; s.out_dev = nullptr; s.out_host = nullptr;
@@ -116,12 +118,22 @@ void Detector::DetectBGR8Async(const unsigned char* const* images, const int* he
     EnsureSession(N, H, W, nullptr);
     Tensor* in = session_->FindTensorByName(options_.input_names[0]);
     Slot& slot = slots_[next_slot_];
-    size_t total = 0;
-    std::vector<size_t> offset(N);
+    // device byte buffer of the call: [table of OgleImageDesc, one per image][the images, back to back]
+    const size_t table_bytes = (size_t(N) * sizeof(OgleImageDesc) + 255) / 256 * 256;
+    if (size_t(N) > slot.desc_capacity) {
+        // the slot is not pending (checked above), so nothing still reads its old table
+        if (slot.desc_host) cudaFreeHost(slot.desc_host);
+        OGLE_RT_CUDA(cudaMallocHost(&slot.desc_host, table_bytes));
+        slot.desc_capacity = table_bytes / sizeof(OgleImageDesc);
+    }
+    OgleImageDesc* table = static_cast<OgleImageDesc*>(slot.desc_host);
+    size_t total = table_bytes;
     for (int i = 0; i < N; ++i) {
         OGLE_CHECK(images[i] && heights[i] > 0 && widths[i] > 0) << "image " << i;
-        offset[i] = total;
-        total += (size_t(heights[i]) * widths[i] * 3 + 255) / 256 * 256;
+        table[i].offset = static_cast<long long>(total);
+        table[i].height = heights[i]; table[i].width = widths[i];
+        table[i].row_bytes = widths[i] * 3; table[i].reserved = 0;
+        total += size_t(heights[i]) * widths[i] * 3;
     }
     // this slot's byte buffer was last read two calls ago (ev_pad); growing it needs that done
     if (total > slot.bytes_capacity) {
@@ -131,17 +143,23 @@ void Detector::DetectBGR8Async(const unsigned char* const* images, const int* he
         slot.bytes_capacity = total;
     }
     OGLE_RT_CUDA(cudaStreamWaitEvent(S(copy_in_), E(slot.ev_pad), 0));
-    for (int i = 0; i < N; ++i)
-        OGLE_RT_CUDA(cudaMemcpyAsync(slot.bytes + offset[i], images[i], size_t(heights[i]) * widths[i] * 3,
-                                     cudaMemcpyHostToDevice, S(copy_in_)));
+    OGLE_RT_CUDA(cudaMemcpyAsync(slot.bytes, table, size_t(N) * sizeof(OgleImageDesc), cudaMemcpyHostToDevice, S(copy_in_)));
+    // images that follow one another in host memory (frames of one buffer) go up as one copy
+    for (int i = 0; i < N;) {
+        size_t run = size_t(heights[i]) * widths[i] * 3;
+        int j = i + 1;
+        while (j < N && images[j] == images[j - 1] + size_t(heights[j - 1]) * widths[j - 1] * 3) {
+            run += size_t(heights[j]) * widths[j] * 3;
+            ++j;
+        }
+        OGLE_RT_CUDA(cudaMemcpyAsync(slot.bytes + table[i].offset, images[i], run, cudaMemcpyHostToDevice, S(copy_in_)));
+        i = j;
+    }
     OGLE_RT_CUDA(cudaEventRecord(E(slot.ev_h2d), S(copy_in_)));
-    h2d_bytes_ = total;
+    h2d_bytes_ = total - table_bytes + size_t(N) * sizeof(OgleImageDesc);
     OGLE_RT_CUDA(cudaStreamWaitEvent(compute, E(slot.ev_h2d), 0));
-    const size_t image_floats = size_t(H) * W * 4;
-    for (int i = 0; i < N; ++i)
-        OGLE_CUDA_OK(ogle_cuda_preprocess_bgr8(slot.bytes + offset[i], heights[i], widths[i], widths[i] * 3,
-                                               in->device<float>() + size_t(i) * image_floats, H, W, mean_rgb,
-                                               context_->stream()));
+    OGLE_CUDA_OK(ogle_cuda_preprocess_bgr8_batch(slot.bytes, reinterpret_cast<const OgleImageDesc*>(slot.bytes), N,
+                                                 in->device<float>(), H, W, mean_rgb, context_->stream()));
     OGLE_RT_CUDA(cudaEventRecord(E(slot.ev_pad), compute));
     session_->RunDevice({});
     PostProcess(slot, N, H, W);

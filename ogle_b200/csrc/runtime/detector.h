@@ -78,6 +78,8 @@ private:
         float* stage = nullptr;      // dense NHWC upload target on the device
         unsigned char* bytes = nullptr;   // raw 8-bit frames of one call (DetectBGR8Async)
         size_t bytes_capacity = 0;
+        void* desc_host = nullptr;   // pinned table of the frames' places and sizes in `bytes`
+        size_t desc_capacity = 0;    // entries
         void* out_dev = nullptr;     // score | anchor | cls | box | count, contiguous
         void* out_host = nullptr;    // pinned mirror
         void* ev_h2d = nullptr;      // upload landed (copy-in stream)

@@ -1,0 +1,32 @@
+// Host-side placement for one-process-per-GPU (or one-thread-per-GPU) serving: the thread that
+// feeds a GPU, and the pinned buffers it uploads from, belong on the NUMA node the GPU's PCIe
+// root port hangs off. With eight GPUs on two sockets, buffers that all sit on one socket make
+// every upload of the other four GPUs cross the inter-socket link and share one socket's DRAM.
+// The reference runs one GL context on one thread (core/init.cc:21-43) and has no counterpart.
+#ifndef OGLE_RUNTIME_HOST_PLACEMENT_H_
+#define OGLE_RUNTIME_HOST_PLACEMENT_H_
+
+#include <string>
+#include <vector>
+
+namespace ogle {
+
+// "0-3,8,10-11" -> {0,1,2,3,8,10,11}. Malformed pieces are skipped.
+std::vector<int> ParseCpuList(const std::string& text);
+
+struct HostPlacement {
+    int numa_node = -1;        // node of the device's PCI function; -1 = unknown / single node
+    int cpus_bound = 0;        // CPUs in the calling thread's new affinity mask; 0 = affinity left alone
+    bool memory_preferred = false;   // the calling thread's page allocations now prefer numa_node
+    std::string pci_bus_id;
+};
+
+// Looks up the device's NUMA node (sysfs), narrows the calling thread's CPU affinity to that
+// node's CPUs (only those it was already allowed to use; untouched if none are), and sets the
+// thread's memory policy to prefer that node, so that host buffers allocated afterwards
+// (pinned or not) are local to the GPU. Never fails: what cannot be done is reported in the result.
+HostPlacement BindHostToDevice(int device);
+
+}  // namespace ogle
+
+#endif

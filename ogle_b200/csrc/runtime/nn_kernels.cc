@@ -354,7 +354,7 @@ public:
         params_.in_hwc[0] = in[0][1]; params_.in_hwc[1] = in[0][2]; params_.in_hwc[2] = in[0][3];
         params_.kernel = kernel_size_; params_.stride = stride_; params_.pad = padding_;
         params_.type = int(pool_type);
-        if (pool_type == GlobalAveragePool) OGLE_CHECK_EQ(in[0][1], in[0][2]);  // pool.cc:88
+        if (pool_type == GlobalAveragePool) { OGLE_CHECK_EQ(in[0][1], in[0][2]); }  // pool.cc:88
         OGLE_CUDA_OK(ogle_cuda_pool_infer(&params_));
         out.assign(1, IntList{in[0][0], params_.out_hwc[0], params_.out_hwc[1], in[0][3]});
     }

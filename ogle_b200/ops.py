@@ -294,6 +294,27 @@ def preprocess_bgr8(image_u8, dst_h, dst_w, mean_rgb=(123.0, 117.0, 104.0), out=
     return out
 
 
+IMAGE_DESC = np.dtype([("offset", "<i8"), ("height", "<i4"), ("width", "<i4"), ("row_bytes", "<i4"), ("reserved", "<i4")])
+
+
+def preprocess_bgr8_batch(images_u8, dst_h, dst_w, mean_rgb=(123.0, 117.0, 104.0)):
+    """images_u8: list of uint8 numpy arrays [h_i, w_i, 3] (BGR) -> float32 CUDA [n, dst_h, dst_w, 4], one launch."""
+    n = len(images_u8)
+    table = np.zeros(n, dtype=IMAGE_DESC)
+    total = 0
+    for i, im in enumerate(images_u8):
+        table[i] = (total, im.shape[0], im.shape[1], im.shape[1] * 3, 0)
+        total += im.size
+    packed = np.concatenate([np.ascontiguousarray(im).reshape(-1) for im in images_u8]) if n else np.zeros(1, np.uint8)
+    buf = torch.from_numpy(packed).cuda()
+    descs = torch.from_numpy(table.view(np.uint8)).cuda()
+    out = torch.empty((n, dst_h, dst_w, 4), dtype=torch.float32, device="cuda")
+    mean = (C.c_float * 3)(*mean_rgb)
+    check(_lib.cuda_lib().ogle_cuda_preprocess_bgr8_batch(C.c_void_p(buf.data_ptr()), C.c_void_p(descs.data_ptr()), n,
+                                                          _p(out), dst_h, dst_w, mean, _stream()), "preprocess_bgr8_batch")
+    return out
+
+
 def ssd_decode(pred, anchors, variances=(0.1, 0.1, 0.2, 0.2)):
     """pred [N,A,4], anchors [A,4] device tensors -> [N,A,4] corner boxes."""
     _require_cuda(pred, anchors)

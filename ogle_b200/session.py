@@ -43,6 +43,8 @@ RT_SYMBOLS = {
     "ogle_detector_wait": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "ogle_detector_info": (C.c_int, [_vp, _ip, _ip, _ip, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "ogle_detector_session": (_vp, [_vp]),
+    "ogle_host_bind_to_device": (C.c_int, [C.c_int, _ip, _ip, _ip]),
+    "ogle_host_parse_cpulist": (C.c_int, [_cp, _ip, C.c_int]),
 }
 
 _rt = None
@@ -66,6 +68,21 @@ def rt_lib():
 def _check(rc, what):
     if rc != 0:
         raise OgleError(f"{what}: {rt_lib().ogle_rt_last_error().decode()}")
+
+
+def bind_host_to_device(device):
+    """Pins the calling thread to the CPUs of the GPU's NUMA node and makes its later host
+    allocations (pinned buffers included) prefer that node. Call before allocating the buffers
+    that feed the device. Returns {"numa_node", "cpus_bound", "memory_preferred"}."""
+    node, cpus, mem = C.c_int(-1), C.c_int(0), C.c_int(0)
+    rt_lib().ogle_host_bind_to_device(int(device), C.byref(node), C.byref(cpus), C.byref(mem))
+    return {"numa_node": node.value, "cpus_bound": cpus.value, "memory_preferred": bool(mem.value)}
+
+
+def parse_cpulist(text):
+    buf = (C.c_int * 4096)()
+    n = rt_lib().ogle_host_parse_cpulist(text.encode(), buf, 4096)
+    return list(buf[:min(n, 4096)])
 
 
 def registered_kernels():
@@ -236,6 +253,21 @@ class Detector:
         ws = (C.c_int * n)(*[im.shape[1] for im in images])
         mean = (C.c_float * 3)(*mean_rgb)
         _check(self._lib.ogle_detector_detect_bgr8_async(self._h, ptrs, hs, ws, n, H, W, mean), "detect_bgr8_async")
+        self._shape = n
+        self._in_flight += 1
+
+    def detect_bgr8_frames_async(self, frames_ptr, n, h, w, H, W, mean_rgb=(123.0, 117.0, 104.0)):
+        """n equally sized 8-bit BGR frames stored back to back at host address frames_ptr ([n, h, w, 3] bytes;
+        pinned memory makes the upload asynchronous): one upload, one preprocessing launch."""
+        key = (frames_ptr, n, h, w)
+        cached = getattr(self, "_frames_args", None)
+        if cached is None or cached[0] != key:
+            ptrs = (C.c_void_p * n)(*[frames_ptr + i * h * w * 3 for i in range(n)])
+            cached = (key, ptrs, (C.c_int * n)(*([h] * n)), (C.c_int * n)(*([w] * n)))
+            self._frames_args = cached
+        mean = (C.c_float * 3)(*mean_rgb)
+        _check(self._lib.ogle_detector_detect_bgr8_async(self._h, cached[1], cached[2], cached[3], n, H, W, mean),
+               "detect_bgr8_async")
         self._shape = n
         self._in_flight += 1
 

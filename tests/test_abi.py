@@ -50,3 +50,34 @@ def test_invalid_arguments_return_status_not_abort():
     assert lib.ogle_cuda_relu(None, None, 3, None) == -1      # n not a multiple of 4
     assert lib.ogle_cuda_relu(None, None, 0, None) == 0       # empty input is a no-op
     assert lib.ogle_cuda_pad4(None, None, 0, 5, 0, None) == 0
+
+
+def test_runtime_library_exports_every_declared_symbol():
+    from ogle_b200 import session
+    lib = session.rt_lib()
+    names = _declared("ogle_runtime.h", "ogle_(?:rt|session|detector|host)_")
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(lib, n), n
+    assert set(names) == set(session.RT_SYMBOLS), set(names) ^ set(session.RT_SYMBOLS)
+
+
+def test_cpu_list_parser():
+    from ogle_b200 import session
+    assert session.parse_cpulist("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
+    assert session.parse_cpulist("5") == [5]
+    assert session.parse_cpulist("") == []
+    assert session.parse_cpulist("2-1,x,7-") == []          # nothing well-formed
+    assert session.parse_cpulist("0-1,,4") == [0, 1, 4]
+
+
+def test_host_binding_is_harmless_without_a_gpu():
+    """Unknown topology: nothing is changed and nothing fails."""
+    import torch
+    from ogle_b200 import session
+    if torch.cuda.is_available():
+        pytest.skip("covers the no-GPU answer")
+    before = os.sched_getaffinity(0)
+    r = session.bind_host_to_device(0)
+    assert r == {"numa_node": -1, "cpus_bound": 0, "memory_preferred": False}
+    assert os.sched_getaffinity(0) == before

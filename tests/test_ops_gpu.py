@@ -350,6 +350,22 @@ def test_preprocess_bgr8_bit_exact(oracle_port):
         assert np.all(got[..., 3] == 0.0)
 
 
+def test_preprocess_bgr8_batch_bit_exact(oracle_port):
+    """One launch over a batch of frames of different sizes (table of offsets and sizes in
+    device memory) gives, image by image, what the CPU restatement gives."""
+    from ogle_b200 import ops
+    rng = np.random.default_rng(52)
+    sizes = [(480, 640), (300, 300), (117, 93), (33, 47), (2, 2), (1, 1), (301, 299)]
+    imgs = [rng.integers(0, 256, (h, w, 3), dtype=np.uint8) for (h, w) in sizes]
+    got = ops.preprocess_bgr8_batch(imgs, 300, 300).cpu().numpy()
+    assert got.shape == (len(imgs), 300, 300, 4)
+    for i, img in enumerate(imgs):
+        ref = oracle_port.preprocess_bgr8(img, 300, 300)
+        assert np.array_equal(got[i, ..., :3], ref), sizes[i]
+        assert np.all(got[i, ..., 3] == 0.0)
+    assert ops.preprocess_bgr8_batch([], 8, 8).shape == (0, 8, 8, 4)      # empty batch: no launch
+
+
 def test_decode_batch_broadcasts_anchors(oracle_port):
     from ogle_b200 import ops
     rng = np.random.default_rng(20)

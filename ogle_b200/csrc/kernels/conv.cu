@@ -54,22 +54,25 @@ __global__ void prepack_kmajor_kernel(const float* __restrict__ w, float* __rest
     }
 }
 
-// Compact k-major sections for the gather form (see filter_compact): [Kp128][32], column tap*Cg+c.
+// Compact k-major sections for the gather form (see filter_compact): [Kp128][cols], column tap*Cg+c.
 __global__ void prepack_kmajor_compact_kernel(const float* __restrict__ w, float* __restrict__ hi,
-                                              __nv_bfloat16* __restrict__ cross, int K, int Cg, int Kp128) {
-    const long total = (long)Kp128 * 32;
+                                              __nv_bfloat16* __restrict__ cross, int K, int Cg, int kernel, int cols,
+                                              int Kp128) {
+    const long total = (long)Kp128 * cols;
+    const int taps = kernel * kernel;
     for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
-        const int col = int(i & 31), k = int(i >> 5);
+        const int col = int(i % cols), k = int(i / cols);
         float v = 0.f;
-        if (k < K && col < 9 * Cg) {
+        if (k < K && col < taps * Cg) {
             const int tap = col / Cg, c = col - tap * Cg;
-            v = w[((long)k * Cg + c) * 9 + tap];
+            v = w[((long)k * Cg + c) * taps + tap];
         }
         const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
         hi[i] = h;
-        const long chunk = i - col;
-        cross[chunk * 2 + col] = __float2bfloat16_rn(v - h);
-        cross[chunk * 2 + 32 + col] = __float2bfloat16_rn(v);
+        const int lane = col & 31;
+        const long chunk = i - lane;         // first element of this 32-wide piece of the row
+        cross[chunk * 2 + lane] = __float2bfloat16_rn(v - h);
+        cross[chunk * 2 + 32 + lane] = __float2bfloat16_rn(v);
     }
 }
 
@@ -151,8 +154,10 @@ int ogle_cuda_conv2d_prepack(const OgleConvParams* p, const float* w_oihw, void*
     rc = finish_launch();
     if (rc != OGLE_OK) return rc;
     if (L.kmajor_bytes && filter_compact(Cg, a.kernel, a.group)) {
-        prepack_kmajor_compact_kernel<<<grid_for((long)L.Kp128 * 32, 256), 256, 0, s>>>(
-            w_oihw, reinterpret_cast<float*>(base + L.off_hi), reinterpret_cast<__nv_bfloat16*>(base + L.off_lo), a.K, Cg, L.Kp128);
+        const int cols = filter_compact_cols(Cg, a.kernel);
+        prepack_kmajor_compact_kernel<<<grid_for((long)L.Kp128 * cols, 256), 256, 0, s>>>(
+            w_oihw, reinterpret_cast<float*>(base + L.off_hi), reinterpret_cast<__nv_bfloat16*>(base + L.off_lo), a.K, Cg,
+            a.kernel, cols, L.Kp128);
         rc = finish_launch();
     } else if (L.kmajor_bytes) {
         const long n1 = (long)L.Kp128 * a.kernel * a.kernel * L.Cp32;

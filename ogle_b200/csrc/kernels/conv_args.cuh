@@ -36,10 +36,13 @@ struct FilterLayout {
 
 inline size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
-// 3x3 filters over at most three input channels (an RGB stem) keep their k-major sections in
-// the compact form [Kp128][32]: column tap * Cg + c, zero padded - the whole reduction in one
-// 32-wide chunk, matching the operand the tensor-core kernel gathers for such layers.
-inline bool filter_compact(int Cg, int kernel, int group) { return group == 1 && kernel == 3 && Cg <= 3; }
+// k x k filters (k = 3, 5, 7) over at most four input channels (an RGB stem) keep their k-major
+// sections in the compact form [Kp128][cols]: column (ky * k + kx) * Cg + c, zero padded to
+// cols = a multiple of 32 - matching the operand the tensor-core kernel gathers for such layers.
+inline bool filter_compact(int Cg, int kernel, int group) {
+    return group == 1 && Cg <= 4 && (kernel == 3 || kernel == 5 || kernel == 7) && kernel * kernel * Cg <= 224;
+}
+inline int filter_compact_cols(int Cg, int kernel) { return (kernel * kernel * Cg + 31) / 32 * 32; }
 
 inline FilterLayout filter_layout(int K, int Cg, int kernel, int group, int Cp) {
     FilterLayout L;
@@ -48,7 +51,8 @@ inline FilterLayout filter_layout(int K, int Cg, int kernel, int group, int Cp) 
     L.Kp128 = (K + 127) / 128 * 128;
     L.Cp32 = (Cg + 31) / 32 * 32;
     L.kmajor_bytes = group == 1 ? align256(size_t(L.Kp128) * taps * L.Cp32 * sizeof(float)) : 0;
-    if (filter_compact(Cg, kernel, group)) L.kmajor_bytes = align256(size_t(L.Kp128) * 32 * sizeof(float));
+    if (filter_compact(Cg, kernel, group))
+        L.kmajor_bytes = align256(size_t(L.Kp128) * filter_compact_cols(Cg, kernel) * sizeof(float));
     L.off_hi = L.tap_major_bytes;
     L.off_lo = L.off_hi + L.kmajor_bytes;
     L.total = L.off_lo + L.kmajor_bytes;

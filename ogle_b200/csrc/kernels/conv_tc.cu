@@ -105,10 +105,32 @@ bool conv_tc_supported(const ConvArgs& a, int variant) {
 // zero rows up to split_col, then the second conv's); y receives [0, K1), y2 the rest.
 // The gather form of the kernel: 3x3, at most three input channels stored as 16-byte pixels
 // (the RGB stem), whole reduction (9 x C <= 27 values) in one chunk.
+// Tile of the gather form: tw x th output pixels of one image, tw * th = 128; the shape that
+// wastes the fewest rows among those whose input window (halo included) is at most 1024
+// pixels = 16 KB of shared memory per stage and at most 256 pixels wide (a TMA box limit).
+static bool gather_tile(const ConvArgs& a, int* tw_out, int* th_out) {
+    long best = -1;
+    for (int tw = 128; tw >= 16; tw >>= 1) {
+        const int th = kTileM / tw;
+        const int iw = (tw - 1) * a.stride + a.kernel, ih = (th - 1) * a.stride + a.kernel;
+        if (iw > 256 || iw * ih > 1024) continue;
+        const long covered = (long)((a.Wo + tw - 1) / tw) * tw * ((a.Ho + th - 1) / th) * th;
+        if (best < 0 || covered < best) { best = covered; *tw_out = tw; *th_out = th; }
+    }
+    return best >= 0;
+}
+
 bool conv_tc_gather_supported(const ConvArgs& a, int variant) {
-    static const bool enabled = [] { const char* e = getenv("OGLE_TC_GATHER"); return e && e[0] == '1'; }();
-    return enabled && variant == CONV_GENERAL && filter_compact(a.C / a.group, a.kernel, a.group) && a.dil == 1 &&
-           (a.stride == 1 || a.stride == 2) && a.Cp == 4 && a.Cs == 4 && a.Wo >= 16 && a.K <= 256 && encode_fn() != nullptr;
+    // 3x3 layers have the direct small-channel kernel, which is as fast on the networks measured: the
+    // gather form is opt-in for them and the default for the larger filters, which have no such kernel
+    static const bool enabled3 = [] { const char* e = getenv("OGLE_TC_GATHER"); return e && e[0] == '1'; }();
+    static const bool disabled = [] { const char* e = getenv("OGLE_TC_GATHER"); return e && e[0] == '0'; }();
+    if (disabled || (a.kernel == 3 && !enabled3)) return false;
+    int tw, th;
+    return variant == CONV_GENERAL && filter_compact(a.C / a.group, a.kernel, a.group) && a.dil == 1 &&
+           filter_compact_cols(a.C, a.kernel) <= kMaxGatherK &&
+           (a.stride == 1 || a.stride == 2) && a.Cp == 4 && a.Cs == 4 && a.Wo >= 16 && a.K <= 256 && gather_tile(a, &tw, &th) &&
+           encode_fn() != nullptr;
 }
 
 int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x, const float* w_hi,
@@ -160,23 +182,16 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
     } else if (conv_tc_gather_supported(a, variant) && !y2) {
         t.flat = 0;
         t.N = a.N; t.Ho = a.Ho; t.Wo = a.Wo;
-        t.gather = 1; t.g_C = a.C;
-        t.kernel = 1; t.Cp32 = kChunk; t.chunks_per_tap = 1;      // the whole reduction is one gathered chunk
-        // tile: tw x th output pixels of one image, tw*th = 128; the shape that wastes the fewest rows
-        long best = -1;
-        for (int tw = 128; tw >= 16; tw >>= 1) {
-            const int th = kTileM / tw;
-            const long covered = (long)((a.Wo + tw - 1) / tw) * tw * ((a.Ho + th - 1) / th) * th;
-            if ((tw - 1) * a.stride + 3 > 256) continue;
-            if (best < 0 || covered < best) { best = covered; t.tw = tw; t.th = th; }
-        }
-        if (best < 0) return OGLE_ERR_UNSUPPORTED;
+        t.gather = 1; t.g_C = a.C; t.g_k = a.kernel;
+        t.kernel = 1;                                            // the reduction is a run of gathered chunks
+        t.Cp32 = filter_compact_cols(a.C, a.kernel); t.chunks_per_tap = t.Cp32 / kChunk;
+        if (!gather_tile(a, &t.tw, &t.th)) return OGLE_ERR_UNSUPPORTED;
         t.tn = 1;
         t.tiles_w = (a.Wo + t.tw - 1) / t.tw;
         t.tiles_h = (a.Ho + t.th - 1) / t.th;
         m_tiles = (long)t.tiles_w * t.tiles_h * a.N;
-        t.g_iw = (t.tw - 1) * a.stride + 3;
-        t.g_ih = (t.th - 1) * a.stride + 3;
+        t.g_iw = (t.tw - 1) * a.stride + a.kernel;
+        t.g_ih = (t.th - 1) * a.stride + a.kernel;
         t.g_bytes = (t.g_iw * t.g_ih * 16 + 1023) / 1024 * 1024;
         const cuuint64_t dims[4] = {4, (cuuint64_t)a.W, (cuuint64_t)a.H, (cuuint64_t)a.N};
         const cuuint64_t str[3] = {(cuuint64_t)a.Cs * 4, (cuuint64_t)a.Cs * 4 * a.W, (cuuint64_t)a.Cs * 4 * a.W * a.H};
@@ -237,7 +252,7 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
     }
     choose_n_tiling_v2(a.Kp, m_tiles, &t);
     const int Kp128 = (a.K + 127) / 128 * 128;
-    const cuuint64_t bcols = t.gather ? (cuuint64_t)kChunk : (cuuint64_t)taps * t.Cp32;
+    const cuuint64_t bcols = t.gather ? (cuuint64_t)t.Cp32 : (cuuint64_t)taps * t.Cp32;
     const cuuint64_t bdims[2] = {bcols, (cuuint64_t)Kp128};
     const cuuint64_t bstr[1] = {bcols * 4};
     const cuuint32_t bbox[2] = {kChunk, (cuuint32_t)t.BN};

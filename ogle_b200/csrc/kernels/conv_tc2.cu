@@ -143,6 +143,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     __shared__ uint32_t tmem_slot;
     __shared__ int s_abort;
     __shared__ __align__(16) float s_bias[2][256];
+    __shared__ __align__(8) short s_goff[kMaxGatherK];   // gather form: window offset of each reduction index
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool split = a.passes == 3;
@@ -185,6 +186,20 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (a.gather) {
+        // reduction index k = (ky * kernel + kx) * C + c -> float offset of that value in the
+        // [g_ih][g_iw][4] input window relative to the output pixel's first tap; -1 = padding column
+        const int kred = a.g_k * a.g_k * a.g_C;
+        for (int k = threadIdx.x; k < a.chunks_per_tap * kChunk && k < kMaxGatherK; k += blockDim.x) {
+            int off = -1;
+            if (k < kred) {
+                const int tap = k / a.g_C, c = k - tap * a.g_C;
+                const int ky = tap / a.g_k, kx = tap - ky * a.g_k;
+                off = (ky * a.g_iw + kx) * 4 + c;
+            }
+            s_goff[k] = (short)off;
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"((uint32_t)a.tmem_cols));
@@ -337,20 +352,11 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             uint32_t ph = 0;
             int xti = 0;
             bool ok = true;
-            // gather form: a thread always builds the same four reduction indices (16-byte piece
-            // t & 7) of the same rows, so their offsets into the input window are computed once:
-            // g_off[l] for k = 4 * (t & 7) + l (or -1 = padding), g_row[q] for row (t >> 3) + q * nthr / 8
-            int g_off[4] = {-1, -1, -1, -1}, g_row[4] = {0, 0, 0, 0};
+            // gather form: a thread always builds the same 16-byte piece (t & 7) of the same rows, so the
+            // rows' offsets into the input window are computed once: g_row[q] for row (t >> 3) + q * nthr / 8.
+            // The four reduction indices of the piece change with the chunk and come from s_goff.
+            int g_row[4] = {0, 0, 0, 0};
             if (a.gather) {
-                const int kred = 9 * a.g_C;
-                for (int l = 0; l < 4; ++l) {
-                    const int k = (t & 7) * 4 + l;
-                    if (k < kred) {
-                        const int tap = k / a.g_C, c = k - tap * a.g_C;
-                        const int ky = tap / 3, kx = tap - ky * 3;
-                        g_off[l] = (ky * a.g_iw + kx) * 4 + c;
-                    }
-                }
                 for (int q = 0; q < 4; ++q) {
                     const int r = (t >> 3) + q * (nthr >> 3);
                     const int ry = r / a.tw, rx = r - ry * a.tw;          // tn == 1, tw * th == 128 in this form
@@ -372,6 +378,8 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         const float* win = reinterpret_cast<const float*>(base_ptr + (size_t)s * stage_bytes +
                                                                           (split ? 2u : 1u) * (kABytes + b_bytes));
                         const int j = t & 7;
+                        const short4 go = *reinterpret_cast<const short4*>(&s_goff[it * kChunk + j * 4]);
+                        const int g_off[4] = {go.x, go.y, go.z, go.w};
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             if (q * nthr >= kABytes / 16) break;

@@ -13,6 +13,8 @@ constexpr int kChunk = 32;              // reduction elements per pipeline stage
 constexpr int kABytes = kTileM * 128;   // one A tile
 constexpr uint32_t kSpinLimit = 1u << 22;
 
+constexpr int kMaxGatherK = 224;     // reduction indices of the gather form (k * k * C rounded up to 32); offsets fit 16 bits
+
 struct TcArgs {
     int flat;                 // 1: rows are a flat range of pixels (pointwise / gemm)
     int tn, th, tw;           // output pixels per tile along n, h, w (tn*th*tw <= 128)
@@ -43,13 +45,14 @@ struct TcArgs {
     // stores into an output the host zeroed. Used (activation none only) when the tiles alone
     // would leave most SMs idle or a last round mostly empty. total_work = total_tiles * split_k.
     int split_k, chunks_per_split, total_work;
-    // Gather form (3x3 convolution over at most three input channels, the RGB stem): the
+    // Gather form (k x k convolution over at most four input channels, e.g. an RGB stem): the
     // activation "tile" that TMA delivers is the tile's input window of 16-byte pixels
-    // (g_iw x g_ih of them, halo included); the operand-split warps build the 128 x 32
-    // operand from it, row r = the 9 x C window values of output pixel r (k = tap * C + c),
-    // zero padded, and the whole reduction is one chunk. g_C = input channels, g_bytes =
-    // window bytes rounded up to 1 KB (its slot at the end of every stage).
-    int gather, g_iw, g_ih, g_C, g_bytes;
+    // (g_iw x g_ih of them, halo included), once per reduction chunk; the operand-split warps
+    // build the 128 x 32 operand of the chunk from it, row r = window values of output pixel r
+    // at reduction indices k = (ky * g_k + kx) * g_C + c, zero padded to a multiple of 32
+    // (chunks_per_tap chunks; kernel = 1 in this form). g_C = input channels, g_k = filter
+    // size, g_bytes = window bytes rounded up to 1 KB (its slot at the end of every stage).
+    int gather, g_iw, g_ih, g_C, g_bytes, g_k;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

@@ -17,6 +17,7 @@ import pytest
 sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
 sys.path.insert(0, os.path.dirname(__file__))
 import cases  # noqa: E402
+from ctypes import byref as C_byref  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 
@@ -138,6 +139,32 @@ def test_conv_stem_gather_form(oracle_port):
         assert np.abs(got - ref).max() <= 2e-5, (N, H, W, C, K, s, float(np.abs(got - ref).max()))
         got = run_case_cuda(case, ops.MATH_TF32)
         assert np.abs(got - ref).max() / scale <= 2e-3, (N, H, W, C, K, s)
+    assert _lib.cuda_lib().ogle_cuda_device_status() == 0
+
+
+def test_conv_large_filter_stem_gather_form(oracle_port):
+    """5x5 and 7x7 convolutions over 1-4 input channels (a ResNet-style 7x7 stride-2 stem) in the
+    tensor-core modes: the reduction (k*k*C values, several 32-wide chunks) is gathered from the
+    input window inside the kernel. Ragged sizes exercise tiles that hang over the edges."""
+    from gpu_ops import run_case_cuda
+    from ogle_b200 import _lib, ops
+    rng = np.random.default_rng(34)
+    cases_ = [(2, 224, 224, 3, 64, 7, 2, 3, 2), (1, 64, 48, 4, 32, 5, 1, 2, 1), (2, 45, 61, 1, 10, 7, 1, 3, 0),
+              (1, 70, 70, 2, 130, 5, 2, 0, 2), (3, 39, 39, 3, 24, 7, 2, 0, 0), (1, 128, 128, 4, 16, 7, 1, 3, 1)]
+    for (N, H, W, C, K, k, s, p, act) in cases_:
+        prm = ops.conv_params(N, H, W, C, K, k, s, p, 1, 1, True, act, 0.0, 6.0, ops.MATH_TF32X3)
+        assert _lib.cuda_lib().ogle_cuda_conv2d_kernel_name(C_byref(prm)) == b"conv_tc2_kernel", (H, W, C, k)
+        x = rng.standard_normal((N, H, W, C), dtype=np.float32)
+        w = rng.standard_normal((K, C, k, k), dtype=np.float32) * np.float32(1.0 / np.sqrt(C * k * k))
+        b = rng.standard_normal(K, dtype=np.float32) * np.float32(0.05)
+        case = dict(op="conv2d", x=x, w=w, bias=b, stride=s, pad=p, dilation=1, group=1, act=act, lo=0.0, hi=6.0)
+        ref = oracle_port.conv2d(x, w, b, s, p, 1, 1, act, 0.0, 6.0)
+        scale = np.abs(ref).max()
+        got = run_case_cuda(case, ops.MATH_TF32X3)
+        assert got.shape == ref.shape
+        assert np.abs(got - ref).max() <= 3e-5, (N, H, W, C, K, k, s, float(np.abs(got - ref).max()))
+        got = run_case_cuda(case, ops.MATH_TF32)
+        assert np.abs(got - ref).max() / scale <= 2e-3, (N, H, W, C, K, k, s)
     assert _lib.cuda_lib().ogle_cuda_device_status() == 0
 
 

@@ -155,6 +155,10 @@ int ogle_cuda_batchnorm(const float* x, const float* gamma, const float* beta, c
 int ogle_cuda_relu(const float* x, float* y, long n, ogle_stream_t stream);
 int ogle_cuda_clip(const float* x, float* y, long n, float lo, float hi, ogle_stream_t stream);
 int ogle_cuda_add(const float* a, const float* b, float* y, long n, ogle_stream_t stream);
+/* binary.glsl followed by relu.glsl or clip.glsl (a residual block's Add -> Relu) in one pass:
+ * y = act(a + b), act an OgleActivation; bit-identical to the two passes. */
+int ogle_cuda_add_act(const float* a, const float* b, float* y, long n, int act, float lo, float hi,
+                      ogle_stream_t stream);
 
 /* -------------------------------------------------------------------- gemm */
 /* GemmKernel::Compute, nn/kernels/gemm.cc:25-65 + gemm.glsl:

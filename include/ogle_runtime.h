@@ -34,7 +34,10 @@ const char* ogle_rt_registered_kernels(void);
  * current CUDA device; stream NULL creates a private stream. */
 OgleSession* ogle_session_create(int device, ogle_stream_t stream);
 void ogle_session_destroy(OgleSession* s);
-/* "math_mode" (OgleMathMode), "use_graph" (0/1). Set before the first run. */
+/* "math_mode" (OgleMathMode), "use_graph" (0/1), "fuse_siblings" (0/1: sibling convolutions
+ * of one input as one pass), "fuse_activations" (0/1: a Relu/Clip that is the only reader of an
+ * Add runs in the Add's pass; the Add's own tensor is then not readable), "streams" (1..8: streams the captured graph's independent
+ * branches are recorded on; 1 = file order, as the reference runs). Set before the first run. */
 int ogle_session_set_option(OgleSession* s, const char* key, int value);
 /* FBOSession::LoadGraph(path) / LoadGraph(ModelProto), fbo_session.cc:62-124. */
 int ogle_session_load_graph_file(OgleSession* s, const char* path);
@@ -53,6 +56,9 @@ int ogle_session_tensor_info(OgleSession* s, const char* name, int* shape8, int*
  * "NCHW", "ANY", "NHWC4", "ANY4" or "HWN4C4". Synchronises. */
 int ogle_session_get_output(OgleSession* s, const char* name, const char* dformat, float* out_host, size_t capacity_floats);
 int ogle_session_num_active_kernels(OgleSession* s);
+/* Branches of the captured graph that run beside the stream of their predecessors
+ * (option "streams" > 1); 0 before the capture or for a chain. */
+int ogle_session_num_branches(OgleSession* s);
 int ogle_session_graph_captured(OgleSession* s);
 size_t ogle_session_device_bytes(OgleSession* s);
 /* One eager pass with per-node timing; writes "name\ttype\tkernel\tms\n" rows into buf. */

@@ -74,6 +74,7 @@ CUDA_SYMBOLS = {
     "ogle_cuda_relu": (C.c_int, [_vp, _vp, C.c_long, _vp]),
     "ogle_cuda_clip": (C.c_int, [_vp, _vp, C.c_long, C.c_float, C.c_float, _vp]),
     "ogle_cuda_add": (C.c_int, [_vp, _vp, _vp, C.c_long, _vp]),
+    "ogle_cuda_add_act": (C.c_int, [_vp, _vp, _vp, C.c_long, C.c_int, C.c_float, C.c_float, _vp]),
     "ogle_cuda_gemm": (C.c_int, [C.POINTER(GemmParams), _vp, _vp, _vp, _vp, _vp]),
     "ogle_cuda_gemm_packed_b_bytes": (C.c_size_t, [C.POINTER(GemmParams)]),
     "ogle_cuda_gemm_pack_b": (C.c_int, [C.POINTER(GemmParams), _vp, _vp, _vp]),

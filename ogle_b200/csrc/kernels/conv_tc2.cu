@@ -663,7 +663,11 @@ int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, cons
     if (total * t.split_k > 0x7fffffffL) return OGLE_ERR_UNSUPPORTED;
     t.total_work = (int)(total * t.split_k);
     t.chunks_per_split = (chunks + t.split_k - 1) / t.split_k;
-    const size_t smem = stage * stages + staging;
+    // Always the whole budget, also when the layout needs less: a block then has its SM to
+    // itself whatever else is running, so its tensor-memory allocation can never wait for
+    // another resident block's columns.
+    const size_t smem = kBudget;
+    if (stage * stages + staging > smem) return OGLE_ERR_UNSUPPORTED;
     static thread_local int attr_device = -1;
     int dev = 0;
     cudaGetDevice(&dev);

@@ -4,7 +4,7 @@
 
 namespace ogle {
 
-enum { EW_RELU = 0, EW_CLIP = 1, EW_ADD = 2 };
+enum { EW_RELU = 0, EW_CLIP = 1, EW_ADD = 2, EW_ADD_RELU = 3, EW_ADD_CLIP = 4 };
 
 template <int OP>
 __global__ void elementwise_kernel(const float4* __restrict__ a, const float4* __restrict__ b,
@@ -12,13 +12,19 @@ __global__ void elementwise_kernel(const float4* __restrict__ a, const float4* _
     for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n4;
          i += (long)gridDim.x * blockDim.x) {
         float4 v = a[i];
-        if (OP == EW_RELU) {
+        if (OP == EW_ADD_RELU || OP == EW_ADD_CLIP) {
+            // binary.glsl then relu.glsl / clip.glsl in one pass: the sum is rounded to fp32 before the
+            // activation exactly as when it goes through memory, so the result is bit-identical
+            const float4 w = b[i];
+            v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+        }
+        if (OP == EW_RELU || OP == EW_ADD_RELU) {
             v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f);
-        } else if (OP == EW_CLIP) {
+        } else if (OP == EW_CLIP || OP == EW_ADD_CLIP) {
             // clip.glsl:8-9: min(hi, max(lo, v))
             v.x = fminf(hi, fmaxf(lo, v.x)); v.y = fminf(hi, fmaxf(lo, v.y));
             v.z = fminf(hi, fmaxf(lo, v.z)); v.w = fminf(hi, fmaxf(lo, v.w));
-        } else {
+        } else if (OP == EW_ADD) {
             const float4 w = b[i];
             v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
         }
@@ -63,7 +69,7 @@ static int launch_elementwise(const float* a, const float* b, float* y, long n, 
                               ogle_stream_t stream) {
     if (n < 0 || (n & 3)) return OGLE_ERR_INVALID;
     if (n == 0) return OGLE_OK;
-    if (!a || !y || (OP == EW_ADD && !b)) return OGLE_ERR_INVALID;
+    if (!a || !y || (OP >= EW_ADD && !b)) return OGLE_ERR_INVALID;
     if (!aligned16(a) || !aligned16(y) || (b && !aligned16(b))) return OGLE_ERR_ALIGNMENT;
     elementwise_kernel<OP><<<grid_for(n / 4, 256), 256, 0, (cudaStream_t)stream>>>(
         reinterpret_cast<const float4*>(a), reinterpret_cast<const float4*>(b),
@@ -81,6 +87,14 @@ int ogle_cuda_clip(const float* x, float* y, long n, float lo, float hi, ogle_st
 }
 int ogle_cuda_add(const float* a, const float* b, float* y, long n, ogle_stream_t stream) {
     return launch_elementwise<EW_ADD>(a, b, y, n, 0.f, 0.f, stream);
+}
+
+int ogle_cuda_add_act(const float* a, const float* b, float* y, long n, int act, float lo, float hi,
+                      ogle_stream_t stream) {
+    if (act == OGLE_ACT_NONE) return launch_elementwise<EW_ADD>(a, b, y, n, 0.f, 0.f, stream);
+    if (act == OGLE_ACT_RELU) return launch_elementwise<EW_ADD_RELU>(a, b, y, n, 0.f, 0.f, stream);
+    if (act == OGLE_ACT_CLIP) return launch_elementwise<EW_ADD_CLIP>(a, b, y, n, lo, hi, stream);
+    return OGLE_ERR_INVALID;
 }
 
 int ogle_cuda_batchnorm(const float* x, const float* gamma, const float* beta, const float* mean,

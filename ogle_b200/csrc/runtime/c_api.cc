@@ -92,6 +92,10 @@ int ogle_session_set_option(OgleSession* s, const char* key, int value) {
             s->session->set_use_graph(value != 0);
         } else if (k == "fuse_siblings") {
             s->session->set_fuse_siblings(value != 0);
+        } else if (k == "fuse_activations") {
+            s->session->set_fuse_activations(value != 0);
+        } else if (k == "streams") {
+            s->session->set_streams(value);
         } else {
             OGLE_FATAL() << "unknown option " << k;
         }
@@ -163,6 +167,7 @@ int ogle_session_get_output(OgleSession* s, const char* name, const char* dforma
 }
 
 int ogle_session_num_active_kernels(OgleSession* s) { return s ? s->session->num_active_kernels() : -1; }
+int ogle_session_num_branches(OgleSession* s) { return s ? s->session->num_branches() : -1; }
 int ogle_session_graph_captured(OgleSession* s) { return s ? int(s->session->graph_captured()) : -1; }
 size_t ogle_session_device_bytes(OgleSession* s) { return s ? s->session->device_bytes() : 0; }
 

@@ -18,6 +18,9 @@ public:
 
     int device() const { return device_; }
     ogle_stream_t stream() const { return stream_; }
+    // The stream kernels enqueue on. A session swaps it while it records independent
+    // branches of a graph on side streams, and puts the original back.
+    void set_stream(ogle_stream_t s) { stream_ = s; }
     void MakeCurrent() const;
     void Synchronize() const;
 

@@ -16,10 +16,19 @@ namespace ogle {
 FBOSession::FBOSession(Context* context) : context_(context) {
     if (const char* g = std::getenv("OGLE_USE_GRAPH")) use_graph_ = std::atoi(g) != 0;
     if (const char* g = std::getenv("OGLE_FUSE_SIBLINGS")) fuse_siblings_ = std::atoi(g) != 0;
+    if (const char* g = std::getenv("OGLE_FUSE_ACTIVATIONS")) fuse_activations_ = std::atoi(g) != 0;
+    if (const char* g = std::getenv("OGLE_STREAMS")) set_streams(std::atoi(g));
 }
 
 FBOSession::~FBOSession() {
     context_->MakeCurrent();
+    DropGraph();
+    for (void* e : events_) cudaEventDestroy(reinterpret_cast<cudaEvent_t>(e));
+    for (void* st : side_streams_) cudaStreamDestroy(reinterpret_cast<cudaStream_t>(st));
+}
+
+void FBOSession::set_streams(int n) {
+    streams_ = n < 1 ? 1 : (n > 8 ? 8 : n);
     DropGraph();
 }
 
@@ -142,6 +151,8 @@ void FBOSession::Finalize() {
         }
     }
     if (fuse_siblings_) FuseSiblings();
+    elided_.assign(total_tensors_.size(), false);
+    if (fuse_activations_) FuseActivations();
     context_->Synchronize();
     finalized_ = true;
 }
@@ -154,10 +165,36 @@ void FBOSession::FuseSiblings() {
         for (size_t j = i + 1; j < active_.size(); ++j) {
             if (active_[j]->kernel_type() != active_[i]->kernel_type()) continue;
             if (!active_[i]->AbsorbSibling(active_[j])) continue;
+            active_[i]->absorbed_.push_back(active_[j]);
             active_.erase(active_.begin() + long(j));
             ++num_fused_;
             break;      // pairs only
         }
+    }
+}
+
+void FBOSession::FuseActivations() {
+    // The consumer's work moves to its producer's place: it reads nothing else, and its own
+    // output is read only by nodes that come after it.
+    for (size_t i = 0; i < active_.size(); ++i) {
+        Kernel* producer = active_[i];
+        if (producer->output_tensor_indexes_.size() != 1 || producer->output_tensors_.size() != 1) continue;
+        const int out_id = producer->output_tensor_indexes_[0];
+        // every reader of the tensor, aliases (reshapes) and pre-computed nodes included
+        Kernel* only = nullptr;
+        int readers = 0;
+        for (const auto& k : kernels_)
+            for (int id : k->input_tensor_indexes_)
+                if (id == out_id) { ++readers; only = k.get(); }
+        if (readers != 1 || only->input_tensor_indexes_.size() != 1) continue;
+        size_t j = i + 1;
+        while (j < active_.size() && active_[j] != only) ++j;
+        if (j == active_.size()) continue;
+        if (!producer->AbsorbConsumer(only)) continue;
+        producer->absorbed_.push_back(only);
+        active_.erase(active_.begin() + long(j));
+        elided_[size_t(out_id)] = true;
+        ++num_fused_;
     }
 }
 
@@ -185,8 +222,9 @@ void FBOSession::Execute() {
         cudaGraph_t graph = nullptr;
         OGLE_RT_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
         try {
-            for (Kernel* k : active_) k->Compute();
+            RecordSequence();
         } catch (...) {
+            context_->set_stream(reinterpret_cast<ogle_stream_t>(s));
             cudaStreamEndCapture(s, &graph);
             if (graph) cudaGraphDestroy(graph);
             throw;
@@ -202,6 +240,138 @@ void FBOSession::Execute() {
     }
     for (Kernel* k : active_) k->Compute();
     ++eager_runs_;
+}
+
+namespace {
+
+struct Span { const char* lo; const char* hi; };
+
+bool Overlap(const std::vector<Span>& a, const std::vector<Span>& b) {
+    for (const Span& x : a)
+        for (const Span& y : b)
+            if (x.lo < y.hi && y.lo < x.hi) return true;
+    return false;
+}
+
+}  // namespace
+
+// Which stream each node of the steady-state sequence is recorded on, and which nodes on
+// other streams it has to wait for. Dependencies come from the memory the nodes touch
+// (a reshape that aliases its input shares its span): node i depends on an earlier node j
+// when j writes what i reads or writes, or reads what i writes. A node continues the stream
+// whose last node it depends on (the most recent such); otherwise it starts a branch on the
+// stream that has been idle longest.
+void FBOSession::PlanStreams() {
+    const int n = int(active_.size());
+    lane_.assign(size_t(n), 0);
+    waits_.assign(size_t(n), std::vector<int>());
+    signals_.assign(size_t(n), false);
+    num_branches_ = 0;
+    if (streams_ <= 1 || n == 0) return;
+    std::vector<std::vector<Span>> reads{size_t(n)}, writes{size_t(n)};
+    auto add = [](std::vector<Span>& v, const Tensor* t) {
+        if (!t || !t->device()) return;
+        const char* lo = static_cast<const char*>(t->device());
+        v.push_back(Span{lo, lo + t->AllocatedSize()});
+    };
+    for (int i = 0; i < n; ++i) {
+        std::vector<Kernel*> parts{active_[size_t(i)]};
+        for (Kernel* k : active_[size_t(i)]->absorbed_) parts.push_back(k);
+        for (Kernel* k : parts) {
+            for (const Tensor* t : k->input_tensors_) add(reads[size_t(i)], t);
+            for (const Tensor* t : k->output_tensors_) add(writes[size_t(i)], t);
+        }
+    }
+    // direct dependencies, then without those already implied by a later one
+    std::vector<std::vector<bool>> anc(size_t(n), std::vector<bool>(size_t(n), false));
+    std::vector<std::vector<int>> deps{size_t(n)};
+    for (int i = 0; i < n; ++i) {
+        std::vector<int> all;
+        for (int j = 0; j < i; ++j)
+            if (Overlap(writes[size_t(j)], reads[size_t(i)]) || Overlap(writes[size_t(j)], writes[size_t(i)]) ||
+                Overlap(reads[size_t(j)], writes[size_t(i)]))
+                all.push_back(j);
+        for (int j : all) {
+            anc[size_t(i)][size_t(j)] = true;
+            for (int a = 0; a < j; ++a)
+                if (anc[size_t(j)][size_t(a)]) anc[size_t(i)][size_t(a)] = true;
+        }
+        for (int j : all) {
+            bool implied = false;
+            for (int k : all)
+                if (k > j && anc[size_t(k)][size_t(j)]) { implied = true; break; }
+            if (!implied) deps[size_t(i)].push_back(j);
+        }
+    }
+    std::vector<int> tail(size_t(streams_), -1);
+    for (int i = 0; i < n; ++i) {
+        int best = -1;
+        for (int l = 0; l < streams_; ++l) {
+            bool is_dep = false;
+            for (int j : deps[size_t(i)]) is_dep = is_dep || j == tail[size_t(l)];
+            if (is_dep && (best < 0 || tail[size_t(l)] > tail[size_t(best)])) best = l;
+        }
+        if (best < 0) {
+            best = 0;
+            for (int l = 1; l < streams_; ++l)
+                if (tail[size_t(l)] < tail[size_t(best)]) best = l;
+            if (i > 0) ++num_branches_;
+        }
+        lane_[size_t(i)] = best;
+        for (int j : deps[size_t(i)]) {
+            // same stream: ordered by the stream itself
+            if (lane_[size_t(j)] == best) continue;
+            waits_[size_t(i)].push_back(j);
+            signals_[size_t(j)] = true;
+        }
+        tail[size_t(best)] = i;
+    }
+}
+
+// Records the steady-state sequence on the capturing stream of the context and its side
+// streams, as planned by PlanStreams.
+void FBOSession::RecordSequence() {
+    PlanStreams();
+    cudaStream_t s0 = reinterpret_cast<cudaStream_t>(context_->stream());
+    const int n = int(active_.size());
+    bool linear = true;
+    for (int l : lane_) linear = linear && l == 0;
+    if (linear) {
+        for (Kernel* k : active_) k->Compute();
+        return;
+    }
+    while (int(side_streams_.size()) < streams_ - 1) {
+        cudaStream_t st;
+        OGLE_RT_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+        side_streams_.push_back(st);
+    }
+    const size_t n_events = size_t(n) + size_t(streams_) + 1;
+    while (events_.size() < n_events) {
+        cudaEvent_t e;
+        OGLE_RT_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        events_.push_back(e);
+    }
+    auto event = [&](size_t i) { return reinterpret_cast<cudaEvent_t>(events_[i]); };
+    auto stream = [&](int lane) { return lane == 0 ? s0 : reinterpret_cast<cudaStream_t>(side_streams_[size_t(lane - 1)]); };
+    // fork: the side streams join the capture
+    OGLE_RT_CUDA(cudaEventRecord(event(size_t(n)), s0));
+    for (int l = 1; l < streams_; ++l) OGLE_RT_CUDA(cudaStreamWaitEvent(stream(l), event(size_t(n)), 0));
+    struct Restore {
+        Context* c; ogle_stream_t s;
+        ~Restore() { c->set_stream(s); }
+    } restore{context_, context_->stream()};
+    for (int i = 0; i < n; ++i) {
+        cudaStream_t ls = stream(lane_[size_t(i)]);
+        for (int j : waits_[size_t(i)]) OGLE_RT_CUDA(cudaStreamWaitEvent(ls, event(size_t(j)), 0));
+        context_->set_stream(reinterpret_cast<ogle_stream_t>(ls));
+        active_[size_t(i)]->Compute();
+        if (signals_[size_t(i)]) OGLE_RT_CUDA(cudaEventRecord(event(size_t(i)), ls));
+    }
+    // join: everything recorded on a side stream ends before the graph does
+    for (int l = 1; l < streams_; ++l) {
+        OGLE_RT_CUDA(cudaEventRecord(event(size_t(n + l)), stream(l)));
+        OGLE_RT_CUDA(cudaStreamWaitEvent(s0, event(size_t(n + l)), 0));
+    }
 }
 
 void FBOSession::Run(const NamedTensorList& inputs_cpu) {
@@ -251,6 +421,10 @@ void FBOSession::GetOutputs(const TensorNameList& output_names, const StringList
     for (size_t i = 0; i < output_names.size(); ++i) {
         Tensor* gpu_tensor = FindTensorByName(output_names[i]);
         OGLE_CHECK(gpu_tensor != nullptr) << "tensor " << output_names[i] << " was never produced";
+        const int id = tensor_name_index_[output_names[i]];
+        OGLE_CHECK(!(id < int(elided_.size()) && elided_[size_t(id)]))
+            << "tensor " << output_names[i] << " is not materialised: its only reader, an activation, runs in the "
+            << "producer's pass (session option fuse_activations = 0 or OGLE_FUSE_ACTIVATIONS=0 keeps it)";
         const DataFormat dformat = StrToFormat(output_dformats[i]);
         if (outputs->at(i) == nullptr)
             outputs->at(i) = new Tensor(Tensor::DT_FLOAT, gpu_tensor->shape(), Tensor::HOST_MEMORY, dformat);

@@ -62,6 +62,21 @@ public:
     // the first Run.
     void set_fuse_siblings(bool flag) { fuse_siblings_ = flag; }
     int num_fused() const { return num_fused_; }
+    // Activation fusion: a Relu or Clip that is the only reader of an Add's result is applied
+    // in the Add's pass (a residual block's tail). The Add's own output tensor is then not
+    // produced; GetOutputs on it fails with a message naming this switch (default on;
+    // OGLE_FUSE_ACTIVATIONS=0 disables). Set before the first Run.
+    void set_fuse_activations(bool flag) { fuse_activations_ = flag; }
+    // Branch overlap: the captured graph keeps only the true data dependencies between
+    // nodes, recorded over up to `n` streams, so that independent branches (the SSD heads
+    // of one feature map against the layers that continue from it) may run side by side
+    // and fill each other's partly empty last rounds. 1 = a linear chain in file order, as
+    // the reference executes (fbo_session.cc:127-156). Default 4; OGLE_STREAMS overrides.
+    // Eager runs and Profile() are always linear. Set before the graph is captured.
+    void set_streams(int n);
+    int streams() const { return streams_; }
+    // Number of graph branches that did not continue the stream of a predecessor (0 = chain).
+    int num_branches() const { return num_branches_; }
     // Nodes executed per Run (not pre-computed, not aliases).
     int num_active_kernels() const;
     // One eager pass with an event pair around every node; the per-node table the
@@ -76,8 +91,11 @@ private:
     void UploadInputs(const NamedTensorList& inputs_cpu);
     void Finalize();
     void FuseSiblings();
+    void FuseActivations();
     void Execute();
     void DropGraph();
+    void PlanStreams();
+    void RecordSequence();
 
     Context* context_;
     OwnedKernelList kernels_;
@@ -92,8 +110,17 @@ private:
     IntList default_input_sizes_;
     bool use_graph_ = true;
     bool fuse_siblings_ = true;
+    bool fuse_activations_ = true;
+    std::vector<bool> elided_;                // tensors no node produces any more (activation fusion)
     int num_fused_ = 0;
     int eager_runs_ = 0;
+    int streams_ = 4;
+    int num_branches_ = 0;
+    std::vector<int> lane_;                   // stream of each node of active_
+    std::vector<std::vector<int>> waits_;     // nodes on other streams it must wait for
+    std::vector<bool> signals_;               // some node on another stream waits for it
+    std::vector<void*> side_streams_;         // streams 1..n-1 (stream 0 is the context's)
+    std::vector<void*> events_;               // one per signalling node, plus fork / join
     CUgraphExec_st* graph_exec_ = nullptr;
     size_t device_bytes_ = 0;
     friend class Kernel;

@@ -49,8 +49,16 @@ public:
     // (this kernel's Compute then also writes that node's outputs, and the session drops
     // the later node from the sequence).
     virtual bool AbsorbSibling(Kernel* later) { return false; }
+    // Offered the only consumer of this kernel's output: return true to apply that node's
+    // work in the same pass (this kernel's Compute then writes the consumer's output instead
+    // of its own, which is no longer produced; the session drops the consumer).
+    virtual bool AbsorbConsumer(Kernel* consumer) { return false; }
+    // For AbsorbConsumer implementations: the activation a node applies, if it is one.
+    virtual bool AsActivation(int* act, float* lo, float* hi) const { return false; }
 
 protected:
+    // another node's output tensors, for AbsorbSibling / AbsorbConsumer implementations
+    static const std::vector<Tensor*>& ConsumerOutputs(const Kernel* k) { return k->output_tensors_; }
     Context* context_;
     std::string kernel_fname_;
     std::vector<Tensor*> input_tensors_;    // not owned
@@ -58,6 +66,7 @@ protected:
     std::vector<int> input_tensor_indexes_;
     std::vector<int> output_tensor_indexes_;
     std::vector<DataFormat> output_tensor_dformats_;
+    std::vector<Kernel*> absorbed_;         // later nodes whose work this kernel took over (AbsorbSibling)
     friend class FBOSession;
     std::string kernel_name_;
     std::string kernel_type_;

@@ -280,6 +280,10 @@ public:
         OGLE_CUDA_OK(ogle_cuda_relu(in[0]->device<float>(), out[0]->device<float>(), long(in[0]->AllocatedElements()),
                                     context_->stream()));
     }
+    bool AsActivation(int* act, float* lo, float* hi) const override {
+        *act = OGLE_ACT_RELU; *lo = 0.f; *hi = 0.f;
+        return true;
+    }
 };
 REGISTER_KERNEL_WITH_NAME(ReluKernel, "Relu");
 
@@ -302,6 +306,10 @@ public:
         OGLE_CUDA_OK(ogle_cuda_clip(in[0]->device<float>(), out[0]->device<float>(), long(in[0]->AllocatedElements()),
                                     min_, max_, context_->stream()));
     }
+    bool AsActivation(int* act, float* lo, float* hi) const override {
+        *act = OGLE_ACT_CLIP; *lo = min_; *hi = max_;
+        return true;
+    }
 private:
     float min_ = 0.f, max_ = 0.f;
 };
@@ -323,9 +331,27 @@ public:
         out.assign(1, in[0]);
     }
     void Compute(TensorList& in, TensorList& out) override {
-        OGLE_CUDA_OK(ogle_cuda_add(in[0]->device<float>(), in[1]->device<float>(), out[0]->device<float>(),
-                                   long(in[0]->AllocatedElements()), context_->stream()));
+        float* y = act_out_ ? act_out_->device<float>() : out[0]->device<float>();
+        OGLE_CUDA_OK(ogle_cuda_add_act(in[0]->device<float>(), in[1]->device<float>(), y, long(in[0]->AllocatedElements()),
+                                       act_, act_lo_, act_hi_, context_->stream()));
     }
+    // a residual block's Add -> Relu (or Clip) as one pass
+    bool AbsorbConsumer(Kernel* consumer) override {
+        if (act_out_ || consumer == this) return false;
+        int act; float lo, hi;
+        if (!consumer->AsActivation(&act, &lo, &hi)) return false;
+        const TensorList& co = ConsumerOutputs(consumer);
+        if (co.size() != 1 || co[0]->AllocatedSize() != output_tensors_[0]->AllocatedSize()) return false;
+        act_ = act; act_lo_ = lo; act_hi_ = hi;
+        act_out_ = co[0];
+        kernel_fname_ = act == OGLE_ACT_RELU ? "binary_add_relu" : "binary_add_clip";
+        kernel_name_ += "+" + consumer->kernel_name();
+        return true;
+    }
+private:
+    int act_ = OGLE_ACT_NONE;
+    float act_lo_ = 0.f, act_hi_ = 0.f;
+    Tensor* act_out_ = nullptr;      // the absorbed activation's output; not owned
 };
 REGISTER_KERNEL_WITH_NAME(BinaryKernel, "Add");
 

@@ -170,6 +170,13 @@ def add(a4, b4):
     return out
 
 
+def add_act(a4, b4, act=ACT_RELU, lo=0.0, hi=0.0):
+    """act(a + b) in one pass (a residual block's Add -> Relu / Clip)."""
+    out = torch.empty_like(a4)
+    check(_lib.cuda_lib().ogle_cuda_add_act(_p(a4), _p(b4), _p(out), a4.numel(), act, lo, hi, _stream()), "add_act")
+    return out
+
+
 def gemm(A4, B4, C4, M, K, N, transB=0, alpha=1.0, beta=1.0, bias_mode=0, math_mode=MATH_FP32):
     """A4 [M, up4(K)], B4 [K, up4(N)] or [N, up4(K)] when transB; C4 [M, up4(N)] or [up4(N)]."""
     _require_cuda(A4, B4, C4)

@@ -31,6 +31,7 @@ RT_SYMBOLS = {
     "ogle_session_tensor_info": (C.c_int, [_vp, _cp, _ip, _ip, _ip, C.POINTER(_vp)]),
     "ogle_session_get_output": (C.c_int, [_vp, _cp, _cp, _vp, C.c_size_t]),
     "ogle_session_num_active_kernels": (C.c_int, [_vp]),
+    "ogle_session_num_branches": (C.c_int, [_vp]),
     "ogle_session_graph_captured": (C.c_int, [_vp]),
     "ogle_session_device_bytes": (C.c_size_t, [_vp]),
     "ogle_session_profile": (C.c_int, [_vp, C.c_int, C.POINTER(_cp), _fpp, _ipp, _ip, _ip, _cp, C.c_size_t]),
@@ -185,6 +186,9 @@ class FBOSession:
 
     def num_active_kernels(self):
         return self._lib.ogle_session_num_active_kernels(self._h)
+
+    def num_branches(self):
+        return self._lib.ogle_session_num_branches(self._h)
 
     def graph_captured(self):
         return bool(self._lib.ogle_session_graph_captured(self._h))

@@ -362,6 +362,19 @@ def test_layout_round_trip_reference_loop():
     assert np.array_equal(y[..., :3], x.transpose(0, 2, 3, 1)) and not y[..., 3:].any()
 
 
+def test_add_with_activation_equals_two_passes():
+    """Fused Add -> Relu / Clip against the separate kernels: bit-identical."""
+    import torch
+    from ogle_b200 import ops
+    g = torch.Generator().manual_seed(53)
+    for shape in [(2, 56, 56, 64), (1, 7, 7, 512), (3, 5, 9, 4)]:
+        a = torch.randn(shape, generator=g).cuda()
+        b = torch.randn(shape, generator=g).cuda()
+        assert torch.equal(ops.add_act(a, b, ops.ACT_RELU), ops.relu(ops.add(a, b)))
+        assert torch.equal(ops.add_act(a, b, ops.ACT_CLIP, -0.5, 1.25), ops.clip(ops.add(a, b), -0.5, 1.25))
+        assert torch.equal(ops.add_act(a, b, ops.ACT_NONE), ops.add(a, b))
+
+
 def test_preprocess_bgr8_bit_exact(oracle_port):
     """The device front end (BGR8 -> RGB, 8-bit bilinear resize, float, mean) against the CPU
     restatement: integer arithmetic, so bit-exact, for shrinking, enlarging and odd sizes."""

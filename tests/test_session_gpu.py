@@ -129,6 +129,35 @@ def test_sibling_fusion_is_transparent():
                 assert np.abs(a - b).max() <= 1e-5 * max(1.0, np.abs(b).max())
 
 
+def test_branch_overlap_is_transparent():
+    """The captured graph records independent branches (SSD heads against the layers that continue
+    from their feature map) on side streams; the tensors are bit-identical to a graph recorded as one
+    chain, run after run (every node does the same arithmetic; only the order in time changes)."""
+    from ogle_b200 import models, session
+    model, _ = models.mobilenet_v1_ssd(batch=3, num_classes=21, seed=8, weight_std="he")
+    rng = np.random.default_rng(38)
+    xs = [((rng.random((3, 300, 300, 3), dtype=np.float32) - 0.5) / 0.5).astype(np.float32) for _ in range(2)]
+    outs, branches = {}, {}
+    for streams in (1, 3, 8):
+        sess = session.FBOSession()
+        sess.set_option("streams", streams)
+        sess.LoadGraph(model)
+        got = []
+        for rep in range(4):                       # eager, capture, two replays
+            sess.Run({"input": xs[rep & 1]})
+            got.append(sess.GetOutputs(["cls_logits", "box_preds"], ["ANY", "ANY"]))
+        assert sess.graph_captured()
+        outs[streams], branches[streams] = got, sess.num_branches()
+        sess.close()
+    assert branches[1] == 0 and branches[3] >= 2 and branches[8] >= 2
+    for streams in (3, 8):
+        for rep in range(4):
+            for a, b in zip(outs[streams][rep], outs[1][rep]):
+                assert np.array_equal(a, b), (streams, rep)
+    for a, b in zip(outs[3][0], outs[3][2]):       # same input, eager pass vs replay
+        assert np.array_equal(a, b)
+
+
 def test_mobilenet_ssd_config0_batch1_two_classes(oracle_port):
     """The reference's own CPU-runnable case: batch 1, 2 classes, N(0,0.02) weights."""
     from ogle_b200 import models, session
@@ -163,6 +192,33 @@ def test_resnet18_logits(oracle_port):
         assert got.shape == (2, 1000)
         assert _norm_err(got, ref) <= (5e-5 if mode == 0 else 5e-4), f"{_mode_name(mode)}: {_norm_err(got, ref):.3e}"
         sess.close()
+
+
+def test_activation_fusion_is_transparent():
+    """ResNet's eight Add -> Relu tails run as eight passes instead of sixteen; the logits are
+    bit-identical with the fusion off, and reading an Add result that is no longer produced fails
+    with a message instead of returning stale memory."""
+    from ogle_b200 import models, session
+    model, _ = models.resnet18(batch=2, seed=4, weight_std="he")
+    x = np.random.default_rng(39).standard_normal((2, 224, 224, 3), dtype=np.float32)
+    add_out = next(model.tensor_names[n.output_index[0]] for n in model.nodes if n.type == "Add")
+    outs, counts = [], []
+    for fuse in (1, 0):
+        sess = session.FBOSession()
+        sess.set_option("fuse_activations", fuse)
+        sess.LoadGraph(model)
+        for _ in range(3):                        # eager, capture, replay
+            sess.Run({"input": x})
+        outs.append(sess.GetOutputs(["logits"], ["ANY"])[0])
+        counts.append(sess.num_active_kernels())
+        if fuse:
+            with pytest.raises(session.OgleError, match="not materialised"):
+                sess.GetOutputs([add_out], ["ANY"])
+        else:
+            assert sess.GetOutputs([add_out], ["ANY"])[0].shape[0] == 2
+        sess.close()
+    assert counts[1] - counts[0] == 8
+    assert np.array_equal(outs[0], outs[1])
 
 
 def test_detector_end_to_end_matches_oracle_post_process(oracle_port):

@@ -23,6 +23,7 @@ namespace {
 using namespace tc;
 
 constexpr int kStemSmemMax = 100 * 1024;
+constexpr int kStemStages = 3;          // input tiles in flight or in use per block
 
 struct StemTiles {
     int kgroups, pl;                 // channel groups of 8; pixel lanes per warp
@@ -30,89 +31,123 @@ struct StemTiles {
     int seg_px;                      // output pixels per warp = pl * PXT
     int tiles_x, tiles_y;
     int iw, ih;                      // input window of a tile
-    long total;
+    int total;                       // tiles; 32-bit so that the per-tile index arithmetic is
 };
 
-template <int S, int PXT, int CIN>
+// Two fp32 values in one 64-bit register, and the packed multiply-add of sm_100.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+// KP: the padded output channel count when it is known at compile time (32, the usual stem), so that
+// every shared-memory offset inside the tap loops is an immediate; 0 = read it from the arguments.
+template <int S, int PXT, int CIN, int KP>
 __global__ void __launch_bounds__(256, 2)
 conv3x3_smallc_kernel(const __grid_constant__ CUtensorMap tmX, const float* __restrict__ w, const float* __restrict__ bias,
                       float* __restrict__ y, const ConvArgs a, const StemTiles tl, int* err_flag) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bar_full[2];
+    __shared__ __align__(8) uint64_t bar_full[kStemStages];
     // weights [9][CIN][Kp] + bias [Kp], then the two input stages (128-byte aligned)
     float* s_w = reinterpret_cast<float*>(smem_raw);
-    const int wn = 9 * CIN * a.Kp;
-    const uint32_t w_bytes = (uint32_t)((wn + a.Kp) * 4 + 127) & ~127u;
+    const int Kp = KP ? KP : a.Kp;
+    const int kgroups = KP ? KP / 8 : tl.kgroups;
+    const int pls = KP ? 32 / (KP / 8) : tl.pl;           // pixel lanes per warp
+    const int wn = 9 * CIN * Kp;
+    const uint32_t w_bytes = (uint32_t)((wn + Kp) * 4 + 127) & ~127u;
     const uint32_t stage_bytes = (uint32_t)(tl.ih * tl.iw * 16);      // what one TMA box delivers
     const uint32_t stage_pitch = (stage_bytes + 127u) & ~127u;        // TMA destinations are 128-byte aligned
     const uint32_t base = smem_u32(smem_raw) + w_bytes;
     const float4* stage0 = reinterpret_cast<const float4*>(smem_raw + w_bytes);
 
     for (int i = threadIdx.x; i < wn; i += blockDim.x) {
-        const int k = i % a.Kp, c = (i / a.Kp) % CIN, tap = i / (a.Kp * CIN);
-        s_w[i] = c < a.C ? w[(tap * a.Cp + c) * a.Kp + k] : 0.f;     // tap-major packed filter
+        const int k = i % Kp, c = (i / Kp) % CIN, tap = i / (Kp * CIN);
+        s_w[i] = c < a.C ? w[(tap * a.Cp + c) * Kp + k] : 0.f;     // tap-major packed filter
     }
-    for (int i = threadIdx.x; i < a.Kp; i += blockDim.x) s_w[wn + i] = (a.has_bias && i < a.K) ? bias[i] : 0.f;
+    for (int i = threadIdx.x; i < Kp; i += blockDim.x) s_w[wn + i] = (a.has_bias && i < a.K) ? bias[i] : 0.f;
     if (threadIdx.x == 0) {
-        mbar_init(&bar_full[0], 1);
-        mbar_init(&bar_full[1], 1);
+        for (int i = 0; i < kStemStages; ++i) mbar_init(&bar_full[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int kg = lane % tl.kgroups, pl = lane / tl.kgroups;
+    const int kg = lane % kgroups, pl = lane / kgroups;
     const int seg = warp % tl.segs, row = warp / tl.segs;
     const bool active = row < tl.rows;
     const float* wk = s_w + kg * 8;
     const int tile_px = tl.segs * tl.seg_px;        // output columns per tile
 
-    auto issue = [&](long tile, int stage) {
-        long t = tile;
-        const int tx = (int)(t % tl.tiles_x); t /= tl.tiles_x;
-        const int ty = (int)(t % tl.tiles_y); t /= tl.tiles_y;
+    // tile index -> (column tile, row tile, image), 32-bit (a 64-bit division costs as much as
+    // a tenth of a tile's multiply-adds)
+    const uint32_t tiles_x = (uint32_t)tl.tiles_x, tiles_y = (uint32_t)tl.tiles_y;
+    auto issue = [&](uint32_t tile, int stage) {
+        const uint32_t q = tile / tiles_x, tx = tile - q * tiles_x;
+        const uint32_t n = q / tiles_y, ty = q - n * tiles_y;
         mbar_expect_tx(&bar_full[stage], stage_bytes);
-        tma_load_4d(base + (uint32_t)stage * stage_pitch, &tmX, &bar_full[stage], 0, tx * tile_px * S - a.pad,
-                    ty * tl.rows * S - a.pad, (int)t);
+        tma_load_4d(base + (uint32_t)stage * stage_pitch, &tmX, &bar_full[stage], 0, (int)tx * tile_px * S - a.pad,
+                    (int)ty * tl.rows * S - a.pad, (int)n);
     };
 
-    if (threadIdx.x == 0 && (long)blockIdx.x < tl.total) issue(blockIdx.x, 0);
-    long it = 0;
-    for (long tile = blockIdx.x; tile < tl.total; tile += gridDim.x, ++it) {
-        const int stage = (int)(it & 1);
-        // the other stage was last read by tile it-1, finished before the barrier below
-        if (threadIdx.x == 0 && tile + gridDim.x < tl.total) issue(tile + gridDim.x, stage ^ 1);
-        long t = tile;
-        const int tx = (int)(t % tl.tiles_x); t /= tl.tiles_x;
-        const int ty = (int)(t % tl.tiles_y); t /= tl.tiles_y;
-        const int n = (int)t;
-        if (!mbar_wait(&bar_full[stage], (uint32_t)((it >> 1) & 1))) {
+    const uint32_t total = (uint32_t)tl.total;
+    const bool full_k = kg * 8 + 8 <= a.K;           // every lane of this thread's eight is a real channel
+    // ring of kStemStages input tiles: the tiles of the next kStemStages - 1 rounds are in flight
+    // while one is being used
+    if (threadIdx.x == 0)
+        for (int i = 0; i < kStemStages - 1; ++i)
+            if (blockIdx.x + (uint32_t)i * gridDim.x < total) issue(blockIdx.x + (uint32_t)i * gridDim.x, i);
+    uint32_t it = 0;
+    int stage = 0;
+    uint32_t phase = 0;
+    for (uint32_t tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
+        // the stage refilled here was last read by tile it-1, finished before the barrier at the loop's end
+        {
+            const uint32_t ahead = tile + (uint32_t)(kStemStages - 1) * gridDim.x;
+            int refill = stage + kStemStages - 1;
+            if (refill >= kStemStages) refill -= kStemStages;
+            if (threadIdx.x == 0 && ahead < total) issue(ahead, refill);
+        }
+        const uint32_t tq = tile / tiles_x;
+        const int tx = (int)(tile - tq * tiles_x);
+        const int n = (int)(tq / tiles_y);
+        const int ty = (int)(tq - (uint32_t)n * tiles_y);
+        if (!mbar_wait(&bar_full[stage], phase)) {
             if (threadIdx.x == 0) record_error(err_flag, 8);
             break;   // uniform: every thread waits on the same barrier with the same bound
         }
         if (active) {
             const float4* tile_s = stage0 + (size_t)stage * (stage_pitch / 16);
-            float acc[PXT][8];
+            // accumulators and filter taps as pairs of adjacent channels: one fma.rn.f32x2 does two of the
+            // multiply-adds (same IEEE fma per lane, same order of accumulation as the scalar form)
+            unsigned long long acc2[PXT][4];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float b = s_w[wn + kg * 8 + j];
+            for (int m = 0; m < 4; ++m) {
+                const unsigned long long b = pack2(s_w[wn + kg * 8 + 2 * m], s_w[wn + kg * 8 + 2 * m + 1]);
 #pragma unroll
-                for (int i = 0; i < PXT; ++i) acc[i][j] = b;
+                for (int i = 0; i < PXT; ++i) acc2[i][m] = b;
             }
             const int lc = seg * tl.seg_px + pl;                      // first local output column of this thread
             const float4* prow = tile_s + (size_t)(row * S) * tl.iw + lc * S;
-            const int step = tl.pl * S;                               // input columns between this thread's pixels
+            const int step = pls * S;                                 // input columns between this thread's pixels
 #pragma unroll
             for (int ky = 0; ky < 3; ++ky) {
 #pragma unroll
                 for (int kx = 0; kx < 3; ++kx) {
-                    float f[CIN][8];
+                    unsigned long long f2[CIN][4];
 #pragma unroll
                     for (int c = 0; c < CIN; ++c) {
-                        const float4 f0 = *reinterpret_cast<const float4*>(wk + ((ky * 3 + kx) * CIN + c) * a.Kp);
-                        const float4 f1 = *reinterpret_cast<const float4*>(wk + ((ky * 3 + kx) * CIN + c) * a.Kp + 4);
-                        f[c][0] = f0.x; f[c][1] = f0.y; f[c][2] = f0.z; f[c][3] = f0.w;
-                        f[c][4] = f1.x; f[c][5] = f1.y; f[c][6] = f1.z; f[c][7] = f1.w;
+                        const ulonglong2 f0 = *reinterpret_cast<const ulonglong2*>(wk + ((ky * 3 + kx) * CIN + c) * Kp);
+                        const ulonglong2 f1 = *reinterpret_cast<const ulonglong2*>(wk + ((ky * 3 + kx) * CIN + c) * Kp + 4);
+                        f2[c][0] = f0.x; f2[c][1] = f0.y; f2[c][2] = f1.x; f2[c][3] = f1.y;
                     }
                     const float4* p = prow + ky * tl.iw + kx;
 #pragma unroll
@@ -120,24 +155,33 @@ conv3x3_smallc_kernel(const __grid_constant__ CUtensorMap tmX, const float* __re
                         const float4 q = p[i * step];
                         const float u[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-                        for (int c = 0; c < CIN; ++c)
+                        for (int c = 0; c < CIN; ++c) {
+                            const unsigned long long uu = pack2(u[c], u[c]);
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(f[c][j], u[c], acc[i][j]);
+                            for (int m = 0; m < 4; ++m) acc2[i][m] = fma2(f2[c][m], uu, acc2[i][m]);
+                        }
                     }
                 }
             }
+            float acc[PXT][8];
+#pragma unroll
+            for (int i = 0; i < PXT; ++i)
+#pragma unroll
+                for (int m = 0; m < 4; ++m) unpack2(acc2[i][m], acc[i][2 * m], acc[i][2 * m + 1]);
             const int oy = ty * tl.rows + row;
             if (oy < a.Ho) {
                 float* yrow = y + (((long)n * a.Ho + oy) * a.Wo) * a.Ks + a.koff + kg * 8;
 #pragma unroll
                 for (int i = 0; i < PXT; ++i) {
-                    const int ox = tx * tile_px + lc + i * tl.pl;
+                    const int ox = tx * tile_px + lc + i * pls;
                     if (ox >= a.Wo) continue;
                     float v[8];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        v[j] = apply_act(acc[i][j], a.act, a.lo, a.hi);
-                        if (kg * 8 + j >= a.K) v[j] = 0.f;           // padded lanes stay zero
+                    for (int j = 0; j < 8; ++j) v[j] = apply_act(acc[i][j], a.act, a.lo, a.hi);
+                    if (!full_k) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (kg * 8 + j >= a.K) v[j] = 0.f;       // padded lanes stay zero
                     }
                     float* dst = yrow + (long)ox * a.Ks;
                     *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
@@ -146,6 +190,7 @@ conv3x3_smallc_kernel(const __grid_constant__ CUtensorMap tmX, const float* __re
             }
         }
         __syncthreads();
+        if (++stage == kStemStages) { stage = 0; phase ^= 1u; }
     }
 }
 
@@ -167,8 +212,10 @@ bool choose_shape(const ConvArgs& a, int pxt, StemTiles* t) {
     t->tiles_y = (a.Ho + t->rows - 1) / t->rows;
     t->iw = (t->segs * t->seg_px - 1) * S + 3;
     t->ih = (t->rows - 1) * S + 3;
-    t->total = (long)t->tiles_x * t->tiles_y * a.N;
-    const size_t smem = 2 * (((size_t)t->ih * t->iw * 16 + 127) / 128 * 128) + (size_t)(9 * 4 * a.Kp + a.Kp) * 4 + 256;
+    const long total = (long)t->tiles_x * t->tiles_y * a.N;
+    if (total > 0x7fffffffL - 2 * kNumSMs) return false;     // tile + grid stays below 2^31
+    t->total = (int)total;
+    const size_t smem = kStemStages * (((size_t)t->ih * t->iw * 16 + 127) / 128 * 128) + (size_t)(9 * 4 * a.Kp + a.Kp) * 4 + 256;
     return t->iw <= 256 && t->ih <= 256 && smem <= (size_t)kStemSmemMax;
 }
 
@@ -186,7 +233,7 @@ int choose_pxt(const ConvArgs& a, StemTiles* t) {
     return best;
 }
 
-template <int S, int PXT, int CIN>
+template <int S, int PXT, int CIN, int KP>
 int launch(const ConvArgs& a, const StemTiles& tl, const float* x, const float* w, const float* bias, float* y, cudaStream_t s) {
     CUtensorMap mX;
     const cuuint64_t dims[4] = {4, (cuuint64_t)a.W, (cuuint64_t)a.H, (cuuint64_t)a.N};
@@ -195,25 +242,29 @@ int launch(const ConvArgs& a, const StemTiles& tl, const float* x, const float* 
     const cuuint32_t es[4] = {1, 1, 1, 1};
     if (!make_map_sw(CU_TENSOR_MAP_SWIZZLE_NONE, &mX, x, 4, dims, str, box, es)) return OGLE_ERR_CUDA;
     const size_t w_bytes = ((size_t)(9 * CIN * a.Kp + a.Kp) * 4 + 127) / 128 * 128;
-    const size_t smem = w_bytes + 2 * (((size_t)tl.ih * tl.iw * 16 + 127) / 128 * 128) + 128;
+    const size_t smem = w_bytes + kStemStages * (((size_t)tl.ih * tl.iw * 16 + 127) / 128 * 128) + 128;
     static thread_local int attr_device = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (attr_device != dev) {
-        cudaError_t e = cudaFuncSetAttribute(conv3x3_smallc_kernel<S, PXT, CIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStemSmemMax);
+        cudaError_t e = cudaFuncSetAttribute(conv3x3_smallc_kernel<S, PXT, CIN, KP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStemSmemMax);
         if (e != cudaSuccess) { set_last_error(e); return OGLE_ERR_CUDA; }
         attr_device = dev;
     }
-    long blocks = (long)kNumSMs * 2;
+    int blocks = kNumSMs * 2;
     if (blocks > tl.total) blocks = tl.total;
-    conv3x3_smallc_kernel<S, PXT, CIN><<<(unsigned)blocks, 256, smem, s>>>(mX, w, bias, y, a, tl, error_flag_ptr());
+    conv3x3_smallc_kernel<S, PXT, CIN, KP><<<(unsigned)blocks, 256, smem, s>>>(mX, w, bias, y, a, tl, error_flag_ptr());
     return finish_launch();
 }
 
 template <int S, int PXT>
 int launch_c(const ConvArgs& a, const StemTiles& tl, const float* x, const float* w, const float* bias, float* y, cudaStream_t s) {
-    if (a.C == 3) return launch<S, PXT, 3>(a, tl, x, w, bias, y, s);
-    return launch<S, PXT, 4>(a, tl, x, w, bias, y, s);
+    if (a.Kp == 32) {
+        if (a.C == 3) return launch<S, PXT, 3, 32>(a, tl, x, w, bias, y, s);
+        return launch<S, PXT, 4, 32>(a, tl, x, w, bias, y, s);
+    }
+    if (a.C == 3) return launch<S, PXT, 3, 0>(a, tl, x, w, bias, y, s);
+    return launch<S, PXT, 4, 0>(a, tl, x, w, bias, y, s);
 }
 
 }  // namespace

@@ -12,7 +12,7 @@ __global__ void pad4_kernel(const float* __restrict__ src, float* __restrict__ d
     const long total = rows * q;
     for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total;
          i += (long)gridDim.x * blockDim.x) {
-        const long r = i / q;
+        const long r = q == 1 ? i : i / q;      // RGB -> RGB0: one vector per row, no division
         const int c = int(i - r * q) * 4;
         const float* s = src + r * last + c;
         float4 v;

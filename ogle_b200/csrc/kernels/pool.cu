@@ -24,15 +24,17 @@ __device__ __forceinline__ float4 f4add(float4 a, float4 b) {
     return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
 }
 
-template <int K, int S, int TY, int TX, bool MAX>
+// Index: the type the item index is split in (32-bit when the item count allows: the three
+// divisions per item cost more in 64 bits than the patch's max/add work).
+template <int K, int S, int TY, int TX, bool MAX, typename Index>
 __global__ void pool_patch_kernel(const float4* __restrict__ x, float4* __restrict__ y, PoolArgs a) {
     constexpr int PH = (TY - 1) * S + K, PW = (TX - 1) * S + K;
     const int gy = (a.Ho + TY - 1) / TY, gx = (a.Wo + TX - 1) / TX;
-    const long total = (long)a.N * gy * gx * a.C4;
+    const Index total = (Index)a.N * gy * gx * a.C4;
     const float init = MAX ? -FLT_MAX : 0.f;
-    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total;
-         i += (long)gridDim.x * blockDim.x) {
-        long t = i;
+    const Index step = (Index)gridDim.x * blockDim.x;
+    for (Index i = blockIdx.x * (Index)blockDim.x + threadIdx.x; i < total; i += step) {
+        Index t = i;
         const int c4 = int(t % a.C4); t /= a.C4;
         const int px = int(t % gx); t /= gx;
         const int py = int(t % gy); t /= gy;
@@ -199,12 +201,20 @@ int ogle_cuda_pool(const OglePoolParams* p, const float* x, float* y, ogle_strea
         pool_global_kernel<<<grid_for(warps * 32, 256), 256, 0, s>>>(xi, yo, a);
     } else if (q.kernel == 3 && q.stride == 2) {
         const long items = (long)a.N * ((a.Ho + 1) / 2) * ((a.Wo + 1) / 2) * a.C4;
-        if (q.type == 0) pool_patch_kernel<3, 2, 2, 2, true><<<grid_for(items, 128, 16), 128, 0, s>>>(xi, yo, a);
-        else pool_patch_kernel<3, 2, 2, 2, false><<<grid_for(items, 128, 16), 128, 0, s>>>(xi, yo, a);
+        const bool small = items < (1L << 30);
+        const int grid = grid_for(items, 128, 16);
+        if (q.type == 0 && small) pool_patch_kernel<3, 2, 2, 2, true, unsigned><<<grid, 128, 0, s>>>(xi, yo, a);
+        else if (q.type == 0) pool_patch_kernel<3, 2, 2, 2, true, long><<<grid, 128, 0, s>>>(xi, yo, a);
+        else if (small) pool_patch_kernel<3, 2, 2, 2, false, unsigned><<<grid, 128, 0, s>>>(xi, yo, a);
+        else pool_patch_kernel<3, 2, 2, 2, false, long><<<grid, 128, 0, s>>>(xi, yo, a);
     } else if (q.kernel == 2 && q.stride == 2) {
         const long items = (long)a.N * a.Ho * ((a.Wo + 1) / 2) * a.C4;
-        if (q.type == 0) pool_patch_kernel<2, 2, 1, 2, true><<<grid_for(items, 128, 16), 128, 0, s>>>(xi, yo, a);
-        else pool_patch_kernel<2, 2, 1, 2, false><<<grid_for(items, 128, 16), 128, 0, s>>>(xi, yo, a);
+        const bool small = items < (1L << 30);
+        const int grid = grid_for(items, 128, 16);
+        if (q.type == 0 && small) pool_patch_kernel<2, 2, 1, 2, true, unsigned><<<grid, 128, 0, s>>>(xi, yo, a);
+        else if (q.type == 0) pool_patch_kernel<2, 2, 1, 2, true, long><<<grid, 128, 0, s>>>(xi, yo, a);
+        else if (small) pool_patch_kernel<2, 2, 1, 2, false, unsigned><<<grid, 128, 0, s>>>(xi, yo, a);
+        else pool_patch_kernel<2, 2, 1, 2, false, long><<<grid, 128, 0, s>>>(xi, yo, a);
     } else {
         const long items = (long)a.N * a.Ho * a.Wo * a.C4;
         pool_generic_kernel<<<grid_for(items, 256), 256, 0, s>>>(xi, yo, a);

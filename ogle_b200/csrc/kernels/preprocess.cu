@@ -14,7 +14,7 @@ namespace {
 struct Tap { int i0, i1, w0, w1; };
 
 __device__ __forceinline__ Tap make_tap(int d, int dst, int src) {
-    const double scale = double(src) / dst;
+    const double scale = src == dst ? 1.0 : double(src) / dst;     // frames already at the network's size skip the fp64 division
     float f = float((d + 0.5) * scale - 0.5);
     int s = int(floorf(f));
     f -= s;

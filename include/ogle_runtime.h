@@ -90,6 +90,16 @@ int ogle_detector_wait(OgleDetector* d, float* score, int* anchor, int* cls, flo
 int ogle_detector_info(OgleDetector* d, int* num_anchors, int* num_classes, int* rows, size_t* h2d_bytes, size_t* d2h_bytes);
 OgleSession* ogle_detector_session(OgleDetector* d);
 
+/* The session's stream planner on its own (pure host logic; option "streams"): nodes in
+ * execution order, each with the memory spans [lo, hi) it reads and writes, given as n_spans
+ * records (span_node[i], span_lo[i], span_hi[i], span_is_write[i]). Writes lane[n_nodes] (the
+ * stream of each node) and, when waits is not NULL, waits[i * n_nodes + j] = 1 where node i
+ * must wait for node j recorded on another stream. Returns the number of branches, -1 on bad
+ * arguments. */
+int ogle_rt_plan_streams(int n_nodes, int n_spans, const int* span_node, const unsigned long long* span_lo,
+                         const unsigned long long* span_hi, const int* span_is_write, int streams, int* lane,
+                         unsigned char* waits);
+
 /* Host placement for one process (or thread) per GPU. No counterpart in the reference, which
  * runs one GL context on one thread (ogl_runtime/opengl/core/init.cc:21-43).
  * ogle_host_bind_to_device: narrows the calling thread's CPU affinity to the CPUs of the

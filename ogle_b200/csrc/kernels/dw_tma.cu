@@ -188,12 +188,16 @@ int launch(const ConvArgs& a, const DwTiles& shape, const float* x, const float*
     return finish_launch();
 }
 
-// Tile shape for a map: full-width tiles when the map is at most 32 wide; the rows per
+// Tile shape for a map: full-width tiles when the map is at most 16 wide, equal parts up to 48; the rows per
 // thread (one of the compiled RPG values) that leaves the fewest idle output rows.
 // Returns the chosen RPG, or 0 when no shape fits two stages in kDwSmemMax.
 int choose_shape(const ConvArgs& a, DwTiles* t) {
     const int S = a.stride;
     int tw = a.Wo <= 32 ? a.Wo : (S == 1 ? 32 : 16);
+    // Widths that would leave many of the 32 pixel slots of a block idle are cut into equal parts
+    // (measured at batch 256: 19 -> 2 x 10 is 6 % faster, 38 -> 3 x 13 is 18 % faster than 32 + 6)
+    if (a.Wo >= 17 && a.Wo <= 32) tw = (a.Wo + 1) / 2;
+    else if (a.Wo > 32 && a.Wo <= 48) tw = (a.Wo + 2) / 3;
     if (const char* e = getenv("OGLE_DW_TW")) { const int v = atoi(e); if (v >= 1 && v <= 32) tw = v < a.Wo ? v : a.Wo; }
     const int force_rpg = getenv("OGLE_DW_RPG") ? atoi(getenv("OGLE_DW_RPG")) : 0;
     const int groups = 32 / tw;

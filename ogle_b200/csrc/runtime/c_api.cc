@@ -6,6 +6,7 @@
 
 #include "detector.h"
 #include "host_placement.h"
+#include "stream_plan.h"
 #include "fbo_session.h"
 #include "kernel_registry.h"
 #include "ogle_runtime.h"
@@ -265,6 +266,28 @@ int ogle_host_bind_to_device(int device, int* numa_node, int* cpus_bound, int* m
     if (cpus_bound) *cpus_bound = r.cpus_bound;
     if (memory_preferred) *memory_preferred = r.memory_preferred ? 1 : 0;
     return 0;
+}
+
+int ogle_rt_plan_streams(int n_nodes, int n_spans, const int* span_node, const unsigned long long* span_lo,
+                         const unsigned long long* span_hi, const int* span_is_write, int streams, int* lane,
+                         unsigned char* waits) {
+    if (n_nodes < 0 || n_spans < 0 || (n_nodes && !lane) || (n_spans && (!span_node || !span_lo || !span_hi || !span_is_write)))
+        return -1;
+    std::vector<ogle::NodeAccess> nodes{size_t(n_nodes)};
+    for (int i = 0; i < n_spans; ++i) {
+        if (span_node[i] < 0 || span_node[i] >= n_nodes) return -1;
+        ogle::NodeAccess& a = nodes[size_t(span_node[i])];
+        (span_is_write[i] ? a.writes : a.reads).push_back(ogle::MemSpan{uintptr_t(span_lo[i]), uintptr_t(span_hi[i])});
+    }
+    const ogle::StreamPlan plan = ogle::PlanStreamsFor(nodes, streams);
+    for (int i = 0; i < n_nodes; ++i) {
+        lane[i] = plan.lane[size_t(i)];
+        if (waits) {
+            for (int j = 0; j < n_nodes; ++j) waits[size_t(i) * n_nodes + j] = 0;
+            for (int j : plan.waits[size_t(i)]) waits[size_t(i) * n_nodes + j] = 1;
+        }
+    }
+    return plan.branches;
 }
 
 int ogle_host_parse_cpulist(const char* text, int* cpus, int capacity) {

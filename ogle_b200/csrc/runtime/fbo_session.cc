@@ -4,6 +4,7 @@
 #include <cstdlib>
 
 #include "kernel_registry.h"
+#include "stream_plan.h"
 
 namespace ogle {
 
@@ -242,90 +243,30 @@ void FBOSession::Execute() {
     ++eager_runs_;
 }
 
-namespace {
-
-struct Span { const char* lo; const char* hi; };
-
-bool Overlap(const std::vector<Span>& a, const std::vector<Span>& b) {
-    for (const Span& x : a)
-        for (const Span& y : b)
-            if (x.lo < y.hi && y.lo < x.hi) return true;
-    return false;
-}
-
-}  // namespace
-
-// Which stream each node of the steady-state sequence is recorded on, and which nodes on
-// other streams it has to wait for. Dependencies come from the memory the nodes touch
-// (a reshape that aliases its input shares its span): node i depends on an earlier node j
-// when j writes what i reads or writes, or reads what i writes. A node continues the stream
-// whose last node it depends on (the most recent such); otherwise it starts a branch on the
-// stream that has been idle longest.
+// The stream plan of the steady-state sequence (stream_plan.h), from the memory every node
+// touches: a reshape that aliases its input shares its span, and a node counts with the nodes
+// it absorbed.
 void FBOSession::PlanStreams() {
-    const int n = int(active_.size());
-    lane_.assign(size_t(n), 0);
-    waits_.assign(size_t(n), std::vector<int>());
-    signals_.assign(size_t(n), false);
-    num_branches_ = 0;
-    if (streams_ <= 1 || n == 0) return;
-    std::vector<std::vector<Span>> reads{size_t(n)}, writes{size_t(n)};
-    auto add = [](std::vector<Span>& v, const Tensor* t) {
+    const size_t n = active_.size();
+    std::vector<NodeAccess> nodes(n);
+    auto add = [](std::vector<MemSpan>& v, const Tensor* t) {
         if (!t || !t->device()) return;
-        const char* lo = static_cast<const char*>(t->device());
-        v.push_back(Span{lo, lo + t->AllocatedSize()});
+        const uintptr_t lo = reinterpret_cast<uintptr_t>(t->device());
+        v.push_back(MemSpan{lo, lo + uintptr_t(t->AllocatedSize())});
     };
-    for (int i = 0; i < n; ++i) {
-        std::vector<Kernel*> parts{active_[size_t(i)]};
-        for (Kernel* k : active_[size_t(i)]->absorbed_) parts.push_back(k);
+    for (size_t i = 0; i < n; ++i) {
+        std::vector<Kernel*> parts{active_[i]};
+        for (Kernel* k : active_[i]->absorbed_) parts.push_back(k);
         for (Kernel* k : parts) {
-            for (const Tensor* t : k->input_tensors_) add(reads[size_t(i)], t);
-            for (const Tensor* t : k->output_tensors_) add(writes[size_t(i)], t);
+            for (const Tensor* t : k->input_tensors_) add(nodes[i].reads, t);
+            for (const Tensor* t : k->output_tensors_) add(nodes[i].writes, t);
         }
     }
-    // direct dependencies, then without those already implied by a later one
-    std::vector<std::vector<bool>> anc(size_t(n), std::vector<bool>(size_t(n), false));
-    std::vector<std::vector<int>> deps{size_t(n)};
-    for (int i = 0; i < n; ++i) {
-        std::vector<int> all;
-        for (int j = 0; j < i; ++j)
-            if (Overlap(writes[size_t(j)], reads[size_t(i)]) || Overlap(writes[size_t(j)], writes[size_t(i)]) ||
-                Overlap(reads[size_t(j)], writes[size_t(i)]))
-                all.push_back(j);
-        for (int j : all) {
-            anc[size_t(i)][size_t(j)] = true;
-            for (int a = 0; a < j; ++a)
-                if (anc[size_t(j)][size_t(a)]) anc[size_t(i)][size_t(a)] = true;
-        }
-        for (int j : all) {
-            bool implied = false;
-            for (int k : all)
-                if (k > j && anc[size_t(k)][size_t(j)]) { implied = true; break; }
-            if (!implied) deps[size_t(i)].push_back(j);
-        }
-    }
-    std::vector<int> tail(size_t(streams_), -1);
-    for (int i = 0; i < n; ++i) {
-        int best = -1;
-        for (int l = 0; l < streams_; ++l) {
-            bool is_dep = false;
-            for (int j : deps[size_t(i)]) is_dep = is_dep || j == tail[size_t(l)];
-            if (is_dep && (best < 0 || tail[size_t(l)] > tail[size_t(best)])) best = l;
-        }
-        if (best < 0) {
-            best = 0;
-            for (int l = 1; l < streams_; ++l)
-                if (tail[size_t(l)] < tail[size_t(best)]) best = l;
-            if (i > 0) ++num_branches_;
-        }
-        lane_[size_t(i)] = best;
-        for (int j : deps[size_t(i)]) {
-            // same stream: ordered by the stream itself
-            if (lane_[size_t(j)] == best) continue;
-            waits_[size_t(i)].push_back(j);
-            signals_[size_t(j)] = true;
-        }
-        tail[size_t(best)] = i;
-    }
+    StreamPlan plan = PlanStreamsFor(nodes, streams_);
+    lane_ = plan.lane;
+    waits_ = plan.waits;
+    signals_ = plan.signals;
+    num_branches_ = plan.branches;
 }
 
 // Records the steady-state sequence on the capturing stream of the context and its side

@@ -44,6 +44,8 @@ RT_SYMBOLS = {
     "ogle_detector_wait": (C.c_int, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "ogle_detector_info": (C.c_int, [_vp, _ip, _ip, _ip, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "ogle_detector_session": (_vp, [_vp]),
+    "ogle_rt_plan_streams": (C.c_int, [C.c_int, C.c_int, _ip, C.POINTER(C.c_ulonglong), C.POINTER(C.c_ulonglong), _ip, C.c_int,
+                                       _ip, C.POINTER(C.c_ubyte)]),
     "ogle_host_bind_to_device": (C.c_int, [C.c_int, _ip, _ip, _ip]),
     "ogle_host_parse_cpulist": (C.c_int, [_cp, _ip, C.c_int]),
 }
@@ -78,6 +80,24 @@ def bind_host_to_device(device):
     node, cpus, mem = C.c_int(-1), C.c_int(0), C.c_int(0)
     rt_lib().ogle_host_bind_to_device(int(device), C.byref(node), C.byref(cpus), C.byref(mem))
     return {"numa_node": node.value, "cpus_bound": cpus.value, "memory_preferred": bool(mem.value)}
+
+
+def plan_streams(nodes, streams):
+    """The session's stream planner on its own. nodes: list of (reads, writes), each a list of (lo, hi) spans.
+    Returns (lanes, waits, branches): waits[i] = nodes on other streams that node i waits for."""
+    n = len(nodes)
+    rec = [(i, lo, hi, w) for i, (rd, wr) in enumerate(nodes) for (spans, w) in ((rd, 0), (wr, 1)) for (lo, hi) in spans]
+    m = len(rec)
+    node = (C.c_int * max(m, 1))(*[r[0] for r in rec])
+    lo = (C.c_ulonglong * max(m, 1))(*[r[1] for r in rec])
+    hi = (C.c_ulonglong * max(m, 1))(*[r[2] for r in rec])
+    wr = (C.c_int * max(m, 1))(*[r[3] for r in rec])
+    lane = (C.c_int * max(n, 1))()
+    waits = (C.c_ubyte * max(n * n, 1))()
+    branches = rt_lib().ogle_rt_plan_streams(n, m, node, lo, hi, wr, streams, lane, waits)
+    if branches < 0:
+        raise OgleError("plan_streams: bad arguments")
+    return list(lane[:n]), [[j for j in range(n) if waits[i * n + j]] for i in range(n)], branches
 
 
 def parse_cpulist(text):

@@ -215,13 +215,14 @@ def test_conv_pair_equals_two_convs(oracle_port):
 
 def test_depthwise_tile_shapes(oracle_port):
     """Depthwise 3x3 over the map sizes of the SSD-300 backbone and some ragged ones: every tile
-    shape of the TMA kernel (full-width tiles of 19 and 10 columns, 32/16-column tiles with ragged
+    shape of the TMA kernel (full-width tiles, maps cut into two or three equal parts, 32/16-column tiles with ragged
     edges, stride 1 and 2, with and without padding) and the register-tiled fallback."""
     from gpu_ops import run_case_cuda
     rng = np.random.default_rng(41)
     for (N, H, W, C, s, p) in [(2, 19, 19, 64, 1, 1), (2, 38, 38, 32, 2, 1), (3, 10, 10, 96, 1, 1), (2, 19, 19, 32, 2, 1),
                                (1, 150, 150, 32, 1, 1), (1, 150, 150, 64, 2, 1), (2, 33, 45, 32, 1, 1), (2, 70, 41, 64, 2, 1),
-                               (2, 21, 12, 32, 1, 0), (2, 9, 8, 32, 1, 1), (1, 40, 40, 36, 1, 1)]:
+                               (2, 21, 12, 32, 1, 0), (2, 9, 8, 32, 1, 1), (1, 40, 40, 36, 1, 1), (2, 38, 38, 64, 1, 1),
+                               (1, 17, 17, 32, 1, 1), (1, 48, 47, 32, 1, 1), (1, 75, 75, 32, 2, 1)]:
         x = rng.standard_normal((N, H, W, C), dtype=np.float32)
         w = rng.standard_normal((C, 1, 3, 3), dtype=np.float32) * np.float32(0.3)
         b = rng.standard_normal(C, dtype=np.float32)

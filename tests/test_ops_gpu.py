@@ -118,6 +118,26 @@ def test_conv_tensor_core_modes(oracle_port):
     assert _lib.cuda_lib().ogle_cuda_device_status() == 0
 
 
+def test_conv_small_channel_kernel_shapes(oracle_port):
+    """3x3 convolutions over 1-4 input channels on the CUDA-core kernel (the RGB stem): stride 2 with 32
+    output channels takes the duplicated-input form, the others the plain one; ragged widths and heights,
+    3 and 4 input channels, output channel counts that are not multiples of 8."""
+    from gpu_ops import run_case_cuda
+    from ogle_b200 import _lib, ops
+    rng = np.random.default_rng(35)
+    shapes = [(2, 300, 300, 3, 32, 2, 1, 2), (1, 97, 131, 3, 32, 2, 1, 1), (2, 64, 50, 4, 32, 2, 0, 0), (1, 33, 21, 1, 30, 2, 1, 2),
+              (2, 40, 40, 3, 32, 1, 1, 2), (1, 75, 60, 3, 16, 2, 1, 0), (1, 50, 50, 4, 64, 1, 1, 1), (1, 19, 23, 2, 8, 1, 0, 2)]
+    for (N, H, W, C, K, s_, p_, act) in shapes:
+        prm = ops.conv_params(N, H, W, C, K, 3, s_, p_, 1, 1, True, act, 0.0, 6.0, ops.MATH_FP32)
+        assert _lib.cuda_lib().ogle_cuda_conv2d_kernel_name(C_byref(prm)) == b"conv3x3_smallc_kernel", (H, W, C, K)
+        x = rng.standard_normal((N, H, W, C), dtype=np.float32)
+        w = rng.standard_normal((K, C, 3, 3), dtype=np.float32) * np.float32(0.3)
+        b = rng.standard_normal(K, dtype=np.float32)
+        case = dict(op="conv2d", x=x, w=w, bias=b, stride=s_, pad=p_, dilation=1, group=1, act=act, lo=0.0, hi=6.0)
+        close(run_case_cuda(case), oracle_port.conv2d(x, w, b, s_, p_, 1, 1, act, 0.0, 6.0), atol=1e-5, rtol=1e-5)
+    assert _lib.cuda_lib().ogle_cuda_device_status() == 0
+
+
 @pytest.mark.skipif(os.environ.get("OGLE_TC_GATHER") != "1", reason="gather form is opt-in (OGLE_TC_GATHER=1)")
 def test_conv_stem_gather_form(oracle_port):
     """3x3 convolutions over 1-3 input channels (the RGB stem) in the tensor-core modes: the operand

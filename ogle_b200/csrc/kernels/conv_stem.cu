@@ -51,10 +51,7 @@ __device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigne
 
 // KP: the padded output channel count when it is known at compile time (32, the usual stem), so that
 // every shared-memory offset inside the tap loops is an immediate; 0 = read it from the arguments.
-// DUP (stride 2, KP = 32 only): every input tile is first rewritten in shared memory with each value
-// twice in a row, (r,r,g,g | b,b,a,a) per pixel, so that the packed multiply-adds read their broadcast
-// operand as it lies instead of building it with a move per value; two raw stages instead of three.
-template <int S, int PXT, int CIN, int KP, bool DUP>
+template <int S, int PXT, int CIN, int KP>
 __global__ void __launch_bounds__(256, 2)
 conv3x3_smallc_kernel(const __grid_constant__ CUtensorMap tmX, const float* __restrict__ w, const float* __restrict__ bias,
                       float* __restrict__ y, const ConvArgs a, const StemTiles tl, int* err_flag) {
@@ -71,8 +68,6 @@ conv3x3_smallc_kernel(const __grid_constant__ CUtensorMap tmX, const float* __re
     const uint32_t stage_pitch = (stage_bytes + 127u) & ~127u;        // TMA destinations are 128-byte aligned
     const uint32_t base = smem_u32(smem_raw) + w_bytes;
     const float4* stage0 = reinterpret_cast<const float4*>(smem_raw + w_bytes);
-    constexpr int NS = DUP ? 2 : kStemStages;                         // raw input stages
-    float4* dup = reinterpret_cast<float4*>(smem_raw + w_bytes + NS * stage_pitch);   // DUP: 32 bytes per pixel
 
     for (int i = threadIdx.x; i < wn; i += blockDim.x) {
         const int k = i % Kp, c = (i / Kp) % CIN, tap = i / (Kp * CIN);
@@ -105,19 +100,20 @@ conv3x3_smallc_kernel(const __grid_constant__ CUtensorMap tmX, const float* __re
 
     const uint32_t total = (uint32_t)tl.total;
     const bool full_k = kg * 8 + 8 <= a.K;           // every lane of this thread's eight is a real channel
-    // ring of NS input tiles: the tiles of the next rounds are in flight while one is being used
+    // ring of kStemStages input tiles: the tiles of the next kStemStages - 1 rounds are in flight
+    // while one is being used
     if (threadIdx.x == 0)
-        for (int i = 0; i < (DUP ? NS : NS - 1); ++i)
+        for (int i = 0; i < kStemStages - 1; ++i)
             if (blockIdx.x + (uint32_t)i * gridDim.x < total) issue(blockIdx.x + (uint32_t)i * gridDim.x, i);
     uint32_t it = 0;
     int stage = 0;
     uint32_t phase = 0;
     for (uint32_t tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
-        if (!DUP) {
-            // the stage refilled here was last read by tile it-1, finished before the barrier at the loop's end
-            const uint32_t ahead = tile + (uint32_t)(NS - 1) * gridDim.x;
-            int refill = stage + NS - 1;
-            if (refill >= NS) refill -= NS;
+        // the stage refilled here was last read by tile it-1, finished before the barrier at the loop's end
+        {
+            const uint32_t ahead = tile + (uint32_t)(kStemStages - 1) * gridDim.x;
+            int refill = stage + kStemStages - 1;
+            if (refill >= kStemStages) refill -= kStemStages;
             if (threadIdx.x == 0 && ahead < total) issue(ahead, refill);
         }
         const uint32_t tq = tile / tiles_x;
@@ -127,22 +123,6 @@ conv3x3_smallc_kernel(const __grid_constant__ CUtensorMap tmX, const float* __re
         if (!mbar_wait(&bar_full[stage], phase)) {
             if (threadIdx.x == 0) record_error(err_flag, 8);
             break;   // uniform: every thread waits on the same barrier with the same bound
-        }
-        if (DUP) {
-            // pixel p -> 16-byte chunks 2p and 2p+1, their two low index bits XORed with bits 3-4 so that
-            // the stride-2 pixels a warp reads together fall into different banks
-            const float4* raw = stage0 + (size_t)stage * (stage_pitch / 16);
-            const int npx = tl.ih * tl.iw;
-            for (int p = threadIdx.x; p < npx; p += blockDim.x) {
-                const float4 q = raw[p];
-                const int c = 2 * p, t = (c >> 3) & 3;
-                dup[c ^ t] = make_float4(q.x, q.x, q.y, q.y);
-                dup[(c + 1) ^ t] = make_float4(q.z, q.z, q.w, q.w);
-            }
-            __syncthreads();
-            // the raw stage is free again: the tile two rounds ahead goes into it
-            const uint32_t ahead = tile + (uint32_t)NS * gridDim.x;
-            if (threadIdx.x == 0 && ahead < total) issue(ahead, stage);
         }
         if (active) {
             const float4* tile_s = stage0 + (size_t)stage * (stage_pitch / 16);
@@ -168,29 +148,6 @@ conv3x3_smallc_kernel(const __grid_constant__ CUtensorMap tmX, const float* __re
                         const ulonglong2 f0 = *reinterpret_cast<const ulonglong2*>(wk + ((ky * 3 + kx) * CIN + c) * Kp);
                         const ulonglong2 f1 = *reinterpret_cast<const ulonglong2*>(wk + ((ky * 3 + kx) * CIN + c) * Kp + 4);
                         f2[c][0] = f0.x; f2[c][1] = f0.y; f2[c][2] = f1.x; f2[c][3] = f1.y;
-                    }
-                    if (DUP) {
-                        // this thread's pixels are 16 apart (32 chunks): the swizzle term is the same for all
-                        const int p0 = (row * S + ky) * tl.iw + lc * S + kx;
-                        const int c0 = (2 * p0) ^ ((p0 >> 2) & 3);
-                        const float4* d0 = dup + c0;
-                        const float4* d1 = dup + (c0 ^ 1);
-#pragma unroll
-                        for (int i = 0; i < PXT; ++i) {
-                            const ulonglong2 u01 = *reinterpret_cast<const ulonglong2*>(d0 + i * (2 * 8 * S));
-                            unsigned long long uu[4] = {u01.x, u01.y, 0ull, 0ull};
-                            if (CIN == 3) {
-                                uu[2] = *reinterpret_cast<const unsigned long long*>(d1 + i * (2 * 8 * S));
-                            } else {
-                                const ulonglong2 u23 = *reinterpret_cast<const ulonglong2*>(d1 + i * (2 * 8 * S));
-                                uu[2] = u23.x; uu[3] = u23.y;
-                            }
-#pragma unroll
-                            for (int c = 0; c < CIN; ++c)
-#pragma unroll
-                                for (int m = 0; m < 4; ++m) acc2[i][m] = fma2(f2[c][m], uu[c], acc2[i][m]);
-                        }
-                        continue;
                     }
                     const float4* p = prow + ky * tl.iw + kx;
 #pragma unroll
@@ -233,7 +190,7 @@ conv3x3_smallc_kernel(const __grid_constant__ CUtensorMap tmX, const float* __re
             }
         }
         __syncthreads();
-        if (++stage == NS) { stage = 0; phase ^= 1u; }
+        if (++stage == kStemStages) { stage = 0; phase ^= 1u; }
     }
 }
 
@@ -276,14 +233,7 @@ int choose_pxt(const ConvArgs& a, StemTiles* t) {
     return best;
 }
 
-// The duplicated-input form needs four stage-sized buffers next to the weights.
-bool stem_dup_fits(const ConvArgs& a, const StemTiles& tl) {
-    static const bool off = [] { const char* e = getenv("OGLE_STEM_DUP"); return e && e[0] == '0'; }();
-    const size_t w_bytes = ((size_t)(9 * 4 * a.Kp + a.Kp) * 4 + 127) / 128 * 128;
-    return !off && w_bytes + 4 * (((size_t)tl.ih * tl.iw * 16 + 127) / 128 * 128) + 128 <= (size_t)kStemSmemMax;
-}
-
-template <int S, int PXT, int CIN, int KP, bool DUP>
+template <int S, int PXT, int CIN, int KP>
 int launch(const ConvArgs& a, const StemTiles& tl, const float* x, const float* w, const float* bias, float* y, cudaStream_t s) {
     CUtensorMap mX;
     const cuuint64_t dims[4] = {4, (cuuint64_t)a.W, (cuuint64_t)a.H, (cuuint64_t)a.N};
@@ -292,34 +242,29 @@ int launch(const ConvArgs& a, const StemTiles& tl, const float* x, const float* 
     const cuuint32_t es[4] = {1, 1, 1, 1};
     if (!make_map_sw(CU_TENSOR_MAP_SWIZZLE_NONE, &mX, x, 4, dims, str, box, es)) return OGLE_ERR_CUDA;
     const size_t w_bytes = ((size_t)(9 * CIN * a.Kp + a.Kp) * 4 + 127) / 128 * 128;
-    // DUP: two raw stages and the rewritten tile (twice the size of a stage)
-    const size_t smem = w_bytes + (DUP ? 4 : kStemStages) * (((size_t)tl.ih * tl.iw * 16 + 127) / 128 * 128) + 128;
+    const size_t smem = w_bytes + kStemStages * (((size_t)tl.ih * tl.iw * 16 + 127) / 128 * 128) + 128;
     static thread_local int attr_device = -1;
     int dev = 0;
     cudaGetDevice(&dev);
     if (attr_device != dev) {
-        cudaError_t e = cudaFuncSetAttribute(conv3x3_smallc_kernel<S, PXT, CIN, KP, DUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStemSmemMax);
+        cudaError_t e = cudaFuncSetAttribute(conv3x3_smallc_kernel<S, PXT, CIN, KP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStemSmemMax);
         if (e != cudaSuccess) { set_last_error(e); return OGLE_ERR_CUDA; }
         attr_device = dev;
     }
     int blocks = kNumSMs * 2;
     if (blocks > tl.total) blocks = tl.total;
-    conv3x3_smallc_kernel<S, PXT, CIN, KP, DUP><<<(unsigned)blocks, 256, smem, s>>>(mX, w, bias, y, a, tl, error_flag_ptr());
+    conv3x3_smallc_kernel<S, PXT, CIN, KP><<<(unsigned)blocks, 256, smem, s>>>(mX, w, bias, y, a, tl, error_flag_ptr());
     return finish_launch();
 }
 
 template <int S, int PXT>
 int launch_c(const ConvArgs& a, const StemTiles& tl, const float* x, const float* w, const float* bias, float* y, cudaStream_t s) {
     if (a.Kp == 32) {
-        if (S == 2 && stem_dup_fits(a, tl)) {
-            if (a.C == 3) return launch<S, PXT, 3, 32, S == 2>(a, tl, x, w, bias, y, s);
-            return launch<S, PXT, 4, 32, S == 2>(a, tl, x, w, bias, y, s);
-        }
-        if (a.C == 3) return launch<S, PXT, 3, 32, false>(a, tl, x, w, bias, y, s);
-        return launch<S, PXT, 4, 32, false>(a, tl, x, w, bias, y, s);
+        if (a.C == 3) return launch<S, PXT, 3, 32>(a, tl, x, w, bias, y, s);
+        return launch<S, PXT, 4, 32>(a, tl, x, w, bias, y, s);
     }
-    if (a.C == 3) return launch<S, PXT, 3, 0, false>(a, tl, x, w, bias, y, s);
-    return launch<S, PXT, 4, 0, false>(a, tl, x, w, bias, y, s);
+    if (a.C == 3) return launch<S, PXT, 3, 0>(a, tl, x, w, bias, y, s);
+    return launch<S, PXT, 4, 0>(a, tl, x, w, bias, y, s);
 }
 
 }  // namespace

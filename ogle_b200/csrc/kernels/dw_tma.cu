@@ -201,9 +201,9 @@ int choose_shape(const ConvArgs& a, DwTiles* t) {
     if (const char* e = getenv("OGLE_DW_TW")) { const int v = atoi(e); if (v >= 1 && v <= 32) tw = v < a.Wo ? v : a.Wo; }
     const int force_rpg = getenv("OGLE_DW_RPG") ? atoi(getenv("OGLE_DW_RPG")) : 0;
     const int groups = 32 / tw;
-    static const int kRpg1[] = {10, 8, 5, 4, 2}, kRpg2[] = {5, 4, 2};
+    static const int kRpg1[] = {10, 8, 7, 5, 4, 2}, kRpg2[] = {7, 5, 4, 2};
     const int* cand = S == 1 ? kRpg1 : kRpg2;
-    const int ncand = S == 1 ? 5 : 3;
+    const int ncand = S == 1 ? 6 : 4;
     int best = 0;
     long best_cost = -1;
     for (int i = 0; i < ncand; ++i) {
@@ -247,12 +247,14 @@ int launch_dw_tma(const ConvArgs& a, const float* x, const float* w, const float
         switch (rpg) {
             case 10: return launch<1, 10>(a, t, x, w, bias, y, s);
             case 8: return launch<1, 8>(a, t, x, w, bias, y, s);
+            case 7: return launch<1, 7>(a, t, x, w, bias, y, s);
             case 5: return launch<1, 5>(a, t, x, w, bias, y, s);
             case 4: return launch<1, 4>(a, t, x, w, bias, y, s);
             case 2: return launch<1, 2>(a, t, x, w, bias, y, s);
         }
     } else {
         switch (rpg) {
+            case 7: return launch<2, 7>(a, t, x, w, bias, y, s);
             case 5: return launch<2, 5>(a, t, x, w, bias, y, s);
             case 4: return launch<2, 4>(a, t, x, w, bias, y, s);
             case 2: return launch<2, 2>(a, t, x, w, bias, y, s);

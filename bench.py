@@ -50,8 +50,8 @@ def parse_args():
     ap.add_argument("--math", default="tf32x3", choices=list(MATH))
     ap.add_argument("--mode", type=int, default=1, help="0 reference Detector rule, 1 per-class top-k")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--host-hugepages", action="store_true",
-                    help="input batches in 2 MB-page memory registered with CUDA instead of cudaHostAlloc memory")
+    ap.add_argument("--host-alloc", default="ogle", choices=["ogle", "torch"],
+                    help="pinned input batches from ogle_host_alloc_pinned (2 MB pages, default) or torch's cudaHostAlloc")
     ap.add_argument("--no-host-binding", action="store_true",
                     help="leave this process's CPU affinity and memory policy alone (default: bind to the GPU's NUMA node)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="target CPU time of the baseline sample")
@@ -144,31 +144,6 @@ def conv_costs(model, batch):
             byts = 4 * (batch * H * W * C + batch * Ho * Wo * K + K * Cg * k * k + K)
             costs[n.name] = (flops, byts)
     return costs
-
-
-_keep_alive = []
-
-
-def hugepage_pinned(array):
-    """A copy of `array` in anonymous memory advised to use 2 MB pages and registered with CUDA as pinned:
-    fewer IOMMU translations per upload than 4 KB pages where the host grants transparent huge pages."""
-    import ctypes
-    import mmap
-    import numpy as np
-    import torch
-    huge = 2 << 20
-    m = mmap.mmap(-1, array.nbytes + 2 * huge, flags=mmap.MAP_PRIVATE | mmap.MAP_ANONYMOUS)
-    if hasattr(mmap, "MADV_HUGEPAGE"):
-        m.madvise(mmap.MADV_HUGEPAGE)
-    addr = ctypes.addressof(ctypes.c_char.from_buffer(m))
-    off = (-addr) % huge
-    buf = np.frombuffer(m, dtype=np.uint8, count=array.nbytes, offset=off)
-    buf[:] = array.reshape(-1).view(np.uint8)                     # touches every page
-    rc = torch.cuda.cudart().cudaHostRegister(addr + off, array.nbytes, 0)
-    if int(rc) != 0:
-        raise SystemExit("cudaHostRegister failed: %s" % rc)
-    _keep_alive.append(m)
-    return torch.from_numpy(buf.view(array.dtype).reshape(array.shape))
 
 
 def cpu_baseline(model_builder, classes, target_seconds, kind=None):
@@ -264,10 +239,16 @@ def main():
     sess = det.session()
 
     # two different pinned host batches, alternated, so no step re-reads what the last left in L2
-    if args.host_hugepages:
-        host = [hugepage_pinned(make_inputs(B, 1000 * (rank + 1) + j * B)) for j in range(2)]
-    else:
-        host = [torch.from_numpy(make_inputs(B, 1000 * (rank + 1) + j * B)).pin_memory() for j in range(2)]
+    def pinned(array):
+        if args.host_alloc == "torch":
+            return torch.from_numpy(array).pin_memory()
+        buf = session.PinnedArray(array.shape, array.dtype)
+        buf.array[...] = array
+        pinned_buffers.append(buf)
+        return torch.from_numpy(buf.array)
+
+    pinned_buffers = []
+    host = [pinned(make_inputs(B, 1000 * (rank + 1) + j * B)) for j in range(2)]
     det.detect_async(host[0].data_ptr(), B, 300, 300)   # sizes the session (weight packing included); eager pass
     det.wait(fetch=False)
     launches0 = ops.launch_count()
@@ -335,8 +316,8 @@ def main():
 
     # the same pipeline fed the way the reference's Detector::Detect is (8-bit BGR frames; resize and
     # mean subtraction on the device): a quarter of the upload bytes. Reported beside `e2e`, not in its place.
-    frames = [torch.randint(0, 256, (B, 300, 300, 3), dtype=torch.uint8,
-                            generator=torch.Generator().manual_seed(7000 + 10 * rank + j)).pin_memory() for j in range(2)]
+    frames = [pinned(torch.randint(0, 256, (B, 300, 300, 3), dtype=torch.uint8,
+                                   generator=torch.Generator().manual_seed(7000 + 10 * rank + j)).numpy()) for j in range(2)]
 
     def frames_step(i):
         det.detect_bgr8_frames_async(frames[i & 1].data_ptr(), B, 300, 300, 300, 300)
@@ -417,7 +398,7 @@ def main():
                    "global_batch": B * world, "math_mode": args.math, "gflop_per_image": info["flops_per_image"] / 1e9,
                    "l2": "inputs larger than L2 (%.0f MB per step, two batches alternated)" % (B * 300 * 300 * 16 / 1e6),
                    "parallelism": "image-sharded x%d, no collective" % world, "cuda_graph": graph_captured,
-                   "host_placement": placement},
+                   "host_placement": placement, "host_alloc": args.host_alloc},
         "e2e": e2e, "e2e_bgr8_frames": e2e_frames, "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step,
         "clocks": clocks, "roofline": roof, "cpu_baseline": cpu}), flush=True)
 

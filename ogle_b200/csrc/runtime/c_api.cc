@@ -290,6 +290,9 @@ int ogle_rt_plan_streams(int n_nodes, int n_spans, const int* span_node, const u
     return plan.branches;
 }
 
+void* ogle_host_alloc_pinned(size_t bytes) { return ogle::AllocPinnedHost(bytes); }
+void ogle_host_free_pinned(void* p) { ogle::FreePinnedHost(p); }
+
 int ogle_host_parse_cpulist(const char* text, int* cpus, int capacity) {
     if (!text) return -1;
     const std::vector<int> v = ogle::ParseCpuList(text);

@@ -5,7 +5,12 @@
 #include <sys/syscall.h>
 #include <unistd.h>
 
+#include <sys/mman.h>
+
 #include <cctype>
+#include <cstring>
+#include <map>
+#include <mutex>
 #include <cstdlib>
 #include <fstream>
 
@@ -87,6 +92,47 @@ HostPlacement BindHostToDevice(int device) {
         if (syscall(SYS_set_mempolicy, 1, mask, 1024ul) == 0) r.memory_preferred = true;
     }
     return r;
+}
+
+namespace {
+struct Mapping { void* base; size_t length; };
+std::mutex g_pinned_mutex;
+std::map<void*, Mapping> g_pinned;
+}  // namespace
+
+void* AllocPinnedHost(size_t bytes) {
+    if (bytes == 0) return nullptr;
+    const size_t huge = size_t(2) << 20;
+    const size_t length = (bytes + huge - 1) / huge * huge + huge;      // room to align the start
+    void* base = mmap(nullptr, length, PROT_READ | PROT_WRITE, MAP_PRIVATE | MAP_ANONYMOUS, -1, 0);
+    if (base == MAP_FAILED) return nullptr;
+#ifdef MADV_HUGEPAGE
+    madvise(base, length, MADV_HUGEPAGE);                               // best effort
+#endif
+    char* p = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(base) + huge - 1) / huge * huge);
+    std::memset(p, 0, bytes);                                           // the pages exist before they are pinned
+    if (cudaHostRegister(p, bytes, cudaHostRegisterDefault) != cudaSuccess) {
+        cudaGetLastError();
+        munmap(base, length);
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(g_pinned_mutex);
+    g_pinned[p] = Mapping{base, length};
+    return p;
+}
+
+void FreePinnedHost(void* p) {
+    if (!p) return;
+    Mapping m{nullptr, 0};
+    {
+        std::lock_guard<std::mutex> lock(g_pinned_mutex);
+        auto it = g_pinned.find(p);
+        if (it == g_pinned.end()) return;
+        m = it->second;
+        g_pinned.erase(it);
+    }
+    cudaHostUnregister(p);
+    munmap(m.base, m.length);
 }
 
 }  // namespace ogle

@@ -46,6 +46,8 @@ RT_SYMBOLS = {
     "ogle_detector_session": (_vp, [_vp]),
     "ogle_rt_plan_streams": (C.c_int, [C.c_int, C.c_int, _ip, C.POINTER(C.c_ulonglong), C.POINTER(C.c_ulonglong), _ip, C.c_int,
                                        _ip, C.POINTER(C.c_ubyte)]),
+    "ogle_host_alloc_pinned": (_vp, [C.c_size_t]),
+    "ogle_host_free_pinned": (None, [_vp]),
     "ogle_host_bind_to_device": (C.c_int, [C.c_int, _ip, _ip, _ip]),
     "ogle_host_parse_cpulist": (C.c_int, [_cp, _ip, C.c_int]),
 }
@@ -80,6 +82,32 @@ def bind_host_to_device(device):
     node, cpus, mem = C.c_int(-1), C.c_int(0), C.c_int(0)
     rt_lib().ogle_host_bind_to_device(int(device), C.byref(node), C.byref(cpus), C.byref(mem))
     return {"numa_node": node.value, "cpus_bound": cpus.value, "memory_preferred": bool(mem.value)}
+
+
+class PinnedArray:
+    """numpy view of pinned host memory from ogle_host_alloc_pinned (2 MB pages where the host grants them).
+    Keep the object alive while views of .array are in use; close() (or deletion) releases the memory."""
+
+    def __init__(self, shape, dtype=np.float32):
+        self.shape = tuple(int(d) for d in shape)
+        self.nbytes = int(np.prod(self.shape)) * np.dtype(dtype).itemsize
+        self.ptr = rt_lib().ogle_host_alloc_pinned(self.nbytes)
+        if not self.ptr:
+            raise OgleError("ogle_host_alloc_pinned(%d) failed" % self.nbytes)
+        buf = (C.c_char * self.nbytes).from_address(self.ptr)
+        self.array = np.frombuffer(buf, dtype=dtype).reshape(self.shape)
+
+    def close(self):
+        if getattr(self, "ptr", None):
+            self.array = None
+            rt_lib().ogle_host_free_pinned(self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 def plan_streams(nodes, streams):

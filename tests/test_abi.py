@@ -81,3 +81,13 @@ def test_host_binding_is_harmless_without_a_gpu():
     r = session.bind_host_to_device(0)
     assert r == {"numa_node": -1, "cpus_bound": 0, "memory_preferred": False}
     assert os.sched_getaffinity(0) == before
+
+
+def test_pinned_allocation_fails_cleanly_without_a_gpu():
+    import torch
+    from ogle_b200 import session
+    if torch.cuda.is_available():
+        pytest.skip("covers the no-GPU answer")
+    with pytest.raises(session.OgleError):
+        session.PinnedArray((4, 4))
+    session.rt_lib().ogle_host_free_pinned(None)          # no-op

@@ -194,6 +194,23 @@ def test_resnet18_logits(oracle_port):
         sess.close()
 
 
+def test_pinned_host_array_round_trip():
+    """Upload buffers from the runtime's pinned allocator: writable from numpy, usable as the source of an
+    asynchronous upload, released without a trace."""
+    import torch
+    from ogle_b200 import session
+    buf = session.PinnedArray((3, 300, 300, 3), np.float32)
+    assert buf.ptr % (2 << 20) == 0 and not buf.array.any()
+    rng = np.random.default_rng(40)
+    buf.array[...] = rng.random(buf.shape, dtype=np.float32)
+    dev = torch.empty(buf.shape, dtype=torch.float32, device="cuda")
+    dev.copy_(torch.from_numpy(buf.array), non_blocking=True)
+    torch.cuda.synchronize()
+    assert np.array_equal(dev.cpu().numpy(), buf.array)
+    buf.close()
+    buf.close()                                         # idempotent
+
+
 def test_activation_fusion_is_transparent():
     """ResNet's eight Add -> Relu tails run as eight passes instead of sixteen; the logits are
     bit-identical with the fusion off, and reading an Add result that is no longer produced fails

@@ -1,8 +1,10 @@
 // Image front end of the detector (Detector::Preprocess,
 // ogl_runtime/opengl/examples/ssd/detector.cc:99-109) on the device: an 8-bit BGR image
 // becomes the network's float input in one pass - channel swap, bilinear resize with the
-// 8-bit fixed-point arithmetic of OpenCV's default cv::resize (pixel-centre alignment, edge
-// taps clamped, 11-bit weights, 32-bit row blend rounded to nearest), conversion to float,
+// 8-bit fixed-point arithmetic of OpenCV's default cv::resize (pixel-centre alignment, 11-bit
+// weights, 32-bit row blend rounded to nearest; a horizontal tap outside the row becomes the
+// edge pixel with weight 2048, a vertical tap outside the image keeps its fractional weights
+// on the clamped row), conversion to float,
 // mean subtraction - written straight into the padded NHWC4 layout. One thread per output
 // pixel; the source is read through the read-only cache (each source pixel is used by at
 // most four outputs when shrinking).
@@ -13,16 +15,19 @@ namespace {
 
 struct Tap { int i0, i1, w0, w1; };
 
+template <bool kClampWeights>
 __device__ __forceinline__ Tap make_tap(int d, int dst, int src) {
     const double scale = src == dst ? 1.0 : double(src) / dst;     // frames already at the network's size skip the fp64 division
     float f = float((d + 0.5) * scale - 0.5);
     int s = int(floorf(f));
     f -= s;
-    if (s < 0) { s = 0; f = 0.f; }
-    if (s >= src - 1) { s = src - 1; f = 0.f; }
+    if (kClampWeights) {
+        if (s < 0) { s = 0; f = 0.f; }
+        if (s >= src - 1) { s = src - 1; f = 0.f; }
+    }
     Tap t;
-    t.i0 = s;
-    t.i1 = min(s + 1, src - 1);
+    t.i0 = min(max(s, 0), src - 1);
+    t.i1 = min(max(s + 1, 0), src - 1);
     t.w0 = __float2int_rn((1.f - f) * 2048.f);
     t.w1 = __float2int_rn(f * 2048.f);
     return t;
@@ -31,7 +36,7 @@ __device__ __forceinline__ Tap make_tap(int d, int dst, int src) {
 __device__ __forceinline__ void preprocess_pixel(const unsigned char* __restrict__ src, int src_h, int src_w,
                                                  int src_row_bytes, float4* __restrict__ dst, int dst_h, int dst_w,
                                                  float3 mean, int x, int y) {
-    const Tap tx = make_tap(x, dst_w, src_w), ty = make_tap(y, dst_h, src_h);
+    const Tap tx = make_tap<true>(x, dst_w, src_w), ty = make_tap<false>(y, dst_h, src_h);
     const unsigned char* r0 = src + (size_t)ty.i0 * src_row_bytes;
     const unsigned char* r1 = src + (size_t)ty.i1 * src_row_bytes;
     float out[3];

@@ -4,11 +4,14 @@
 // the product library never does.
 //
 // Pinning: the reference holds no golden vectors for this path; every function
-// below is checked bit for bit (tests/test_oracle_vs_reference.py) against
-// oracle/_ref/libogle_ref.so, which is the reference's own shader and functor
-// source compiled for the CPU. ogle_oracle_detect and ogle_oracle_topk_per_class
-// have no compiled counterpart (the reference's needs OpenCV): PARITY UNPINNED
-// for those two, which follow the cited source by reading only.
+// below is checked bit for bit (tests/test_oracle.py) against
+// oracle/_ref/libogle_ref.so, which is the reference's own shader, functor and
+// detector source compiled for the CPU, and against that library's outputs
+// committed under tests/golden/. ogle_oracle_detect is pinned against the
+// reference's Detector::GenerateBoxInfo / GetTopK / NMS; ogle_oracle_preprocess_bgr8
+// against OpenCV (cv2). ogle_oracle_topk_per_class is an extension the reference
+// does not contain: its softmax is pinned against the reference's, its selection
+// rule (threshold, order by score then anchor, first k) has no counterpart to pin to.
 //
 // Device layouts of the reference, restated:
 //   NHWC4 / ANY4 : last dimension padded with zeros to a multiple of 4;
@@ -361,12 +364,15 @@ int ogle_oracle_detect(const float* boxes, const float* logits, int A, int C,
     std::vector<Cand> cands;
     for (int i = 0; i < A; ++i) {
         // detector.cc:176-214
+        // `exp` there is the C library's double function (the float argument is promoted,
+        // the result rounded back to float): what the reference's file gives when compiled
+        // by oracle/ref_detector.cc, against which this function is pinned bit for bit
         const float* s = logits + size_t(i) * C;
-        float total = std::exp(s[0]);
+        float total = float(std::exp(double(s[0])));
         int max_id = 0;
         float max_prob = 0.f;
         for (int j = 1; j < C; ++j) {
-            const float e = std::exp(s[j]);
+            const float e = float(std::exp(double(s[j])));
             total += e;
             if (max_prob < e) { max_prob = e; max_id = j; }
         }
@@ -439,8 +445,13 @@ int ogle_oracle_topk_per_class(const float* logits, int A, int C, float score_th
 // Detector::Preprocess (examples/ssd/detector.cc:99-109) with OpenCV's 8-bit bilinear
 // resize restated (see oracle.h). Horizontal pass in integers scaled by 2^11, vertical
 // blend ((b0 * (r0 >> 4)) >> 16) + ((b1 * (r1 >> 4)) >> 16), then (+2) >> 2.
+// The two axes treat the border differently: a horizontal tap that falls outside the row
+// moves onto the edge pixel with weights (2048, 0); a vertical tap keeps its fractional
+// weights and only its row indices are clamped, so both weights then multiply the same
+// edge row (the two truncated products can sum to one less than the single product).
+// Pinned against cv2.resize in tests/test_oracle.py.
 namespace {
-void resize_taps(int dst, int src, std::vector<int>* index, std::vector<short>* coef) {
+void resize_taps(int dst, int src, bool clamp_weights, std::vector<int>* index, std::vector<short>* coef) {
     const double scale = double(src) / dst;
     index->resize(dst);
     coef->resize(size_t(dst) * 2);
@@ -448,8 +459,10 @@ void resize_taps(int dst, int src, std::vector<int>* index, std::vector<short>* 
         float f = float((d + 0.5) * scale - 0.5);
         int s = int(std::floor(f));
         f -= s;
-        if (s < 0) { s = 0; f = 0.f; }
-        if (s >= src - 1) { s = src - 1; f = 0.f; }
+        if (clamp_weights) {
+            if (s < 0) { s = 0; f = 0.f; }
+            if (s >= src - 1) { s = src - 1; f = 0.f; }
+        }
         (*index)[d] = s;
         const float w0 = (1.f - f) * 2048.f, w1 = f * 2048.f;
         (*coef)[d * 2] = short(std::lrintf(w0));       // round half to even, as cvRound does
@@ -463,10 +476,10 @@ int ogle_oracle_preprocess_bgr8(const unsigned char* bgr, int src_h, int src_w, 
     if (!bgr || !dst || src_h <= 0 || src_w <= 0 || dst_h <= 0 || dst_w <= 0 || src_row_bytes < src_w * 3) return -1;
     std::vector<int> xi, yi;
     std::vector<short> xa, ya;
-    resize_taps(dst_w, src_w, &xi, &xa);
-    resize_taps(dst_h, src_h, &yi, &ya);
+    resize_taps(dst_w, src_w, true, &xi, &xa);
+    resize_taps(dst_h, src_h, false, &yi, &ya);
     for (int y = 0; y < dst_h; ++y) {
-        const int y0 = yi[y], y1 = std::min(y0 + 1, src_h - 1);
+        const int y0 = std::min(std::max(yi[y], 0), src_h - 1), y1 = std::min(std::max(yi[y] + 1, 0), src_h - 1);
         const unsigned char* r0 = bgr + size_t(y0) * src_row_bytes;
         const unsigned char* r1 = bgr + size_t(y1) * src_row_bytes;
         const int b0 = ya[y * 2], b1 = ya[y * 2 + 1];

@@ -86,8 +86,9 @@ int ogle_oracle_unpack_filter(const float* packed, float* w_oihw, int O, int I, 
  * ogl_runtime/opengl/examples/ssd/detector.cc:114-228, common.cc:57-77.
  * boxes [A,4] normalised corners, logits [A,C]. Outputs hold up to top_k rows:
  * out_rect (x,y,w,h ints), out_score, out_class, out_anchor. Returns the number
- * of detections kept, or a negative value. Only liboracle.so implements this
- * (the reference's version needs OpenCV types). */
+ * of detections kept, or a negative value. Only liboracle.so implements this;
+ * _ref/libogle_ref.so exports the reference's own compiled post-process as
+ * ogle_ref_detect (oracle/ref_detector.cc), against which this one is pinned. */
 int ogle_oracle_detect(const float* boxes, const float* logits, int A, int C,
                        int image_w, int image_h, float score_thr, int top_k, float nms_thr,
                        int* out_rect, float* out_score, int* out_class, int* out_anchor);
@@ -105,9 +106,12 @@ int ogle_oracle_topk_per_class(const float* logits, int A, int C, float score_th
  * minus mean (R, G, B). The resize is OpenCV's (a third-party dependency that is
  * not in the reference tree; the reference pins no version): cv::resize with the
  * default INTER_LINEAR on 8-bit data, restated here from its published
- * behaviour - pixel-centre alignment ((d + 0.5) * scale - 0.5), edge taps clamped,
- * weights rounded to 11 fractional bits, rows blended in 32-bit fixed point with
- * rounding to nearest. PARITY UNPINNED: not checked against OpenCV itself.
+ * behaviour - pixel-centre alignment ((d + 0.5) * scale - 0.5), weights rounded to
+ * 11 fractional bits, rows blended in 32-bit fixed point with rounding to nearest;
+ * horizontal taps outside the row become the edge pixel, vertical ones keep their
+ * weights on the clamped row. PINNED: bit-exact against cv2.cvtColor + cv2.resize
+ * (OpenCV 4.13) outputs committed under tests/golden/ and against the installed
+ * OpenCV where there is one (tests/test_oracle.py).
  * Output: dst_h x dst_w x 3 floats (NHWC, unpadded). Only liboracle.so implements this. */
 int ogle_oracle_preprocess_bgr8(const unsigned char* bgr, int src_h, int src_w, int src_row_bytes,
                                 float* dst, int dst_h, int dst_w, const float mean_rgb[3]);

@@ -67,6 +67,10 @@ class Oracle:
         L.ogle_oracle_detect.argtypes = [_fp, _fp] + [C.c_int] * 4 + [C.c_float, C.c_int, C.c_float, _ip, _fp, _ip, _ip]
         L.ogle_oracle_topk_per_class.argtypes = [_fp, C.c_int, C.c_int, C.c_float, C.c_int, _fp, _ip, _ip]
         L.ogle_oracle_preprocess_bgr8.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, _fp, C.c_int, C.c_int, _fp]
+        if kind == "reference":
+            # the reference's own examples/ssd/detector.cc + common.cc (oracle/ref_detector.cc)
+            L.ogle_ref_detect.argtypes = [_fp, _fp] + [C.c_int] * 4 + [C.c_float, C.c_int, C.c_float, _ip, _fp, _ip]
+            L.ogle_ref_softmax.argtypes = [_fp, _fp, C.c_int]
 
     def threads(self):
         return self.lib.ogle_oracle_threads()
@@ -216,6 +220,26 @@ class Oracle:
                                         _i(rect), _f(score), _i(cls), _i(anchor))
         self._check(n, "detect")
         return {"rect": rect[:n], "score": score[:n], "cls": cls[:n], "anchor": anchor[:n]}
+
+    def ref_detect(self, boxes, logits, image_w, image_h, score_thr=0.3, top_k=100, nms_thr=0.45):
+        """kind "reference" only: Detector::GenerateBoxInfo -> GetTopK -> NMS as the reference compiled them.
+        Returns dict of rect [n,4] int, score [n], cls [n] (the reference records no anchor index)."""
+        boxes, logits = _c(boxes), _c(logits)
+        A, Cc = logits.shape
+        rect = np.zeros((max(top_k, 1), 4), np.int32)
+        score = np.zeros(max(top_k, 1), np.float32)
+        cls = np.zeros(max(top_k, 1), np.int32)
+        n = self.lib.ogle_ref_detect(_f(boxes), _f(logits), A, Cc, image_w, image_h, score_thr, top_k, nms_thr,
+                                     _i(rect), _f(score), _i(cls))
+        self._check(n, "ref_detect")
+        return {"rect": rect[:n], "score": score[:n], "cls": cls[:n]}
+
+    def ref_softmax(self, row):
+        """kind "reference" only: softmax of examples/ssd/common.cc:86-97 on one row."""
+        row = _c(row).reshape(-1)
+        out = np.empty_like(row)
+        self.lib.ogle_ref_softmax(_f(row), _f(out), row.size)
+        return out
 
     def preprocess_bgr8(self, image_bgr, dst_h, dst_w, mean_rgb=(123.0, 117.0, 104.0)):
         """image_bgr: uint8 [H, W, 3] -> float32 [dst_h, dst_w, 3] RGB, resized, mean-subtracted."""

@@ -1,6 +1,7 @@
-// Test infrastructure only: the few glog macros the reference's CPU functors
-// use (CHECK, CHECK_EQ, CHECK_GE), so that ogl_runtime/opengl/core/cpu_functor.cc
-// compiles without the glog library. A failed check aborts, as glog's does.
+// Test infrastructure only: the few glog macros the reference's CPU functors and its SSD
+// example use, so that ogl_runtime/opengl/core/cpu_functor.cc and examples/ssd/*.cc
+// compile without the glog library. A failed check aborts, as glog's does; LOG and VLOG
+// messages are dropped.
 #ifndef ORACLE_REF_SHIM_GLOG_LOGGING_H_
 #define ORACLE_REF_SHIM_GLOG_LOGGING_H_
 #include <cstdio>
@@ -14,6 +15,9 @@ struct FatalStream {
 };
 }  // namespace ref_shim
 #define CHECK(cond) (cond) ? (void)0 : ref_shim::Voidify() & ref_shim::FatalStream().stream() << "Check failed: " #cond " "
+#define CHECK_NOTNULL(p) CHECK((p) != nullptr)
+#define LOG(severity) true ? (void)0 : ref_shim::Voidify() & std::cerr
+#define VLOG(level) true ? (void)0 : ref_shim::Voidify() & std::cerr
 #define CHECK_EQ(a, b) CHECK((a) == (b))
 #define CHECK_NE(a, b) CHECK((a) != (b))
 #define CHECK_GE(a, b) CHECK((a) >= (b))

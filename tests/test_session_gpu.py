@@ -8,8 +8,13 @@ plus a tighter normalised bound that fp32 arithmetic actually meets.
 import os
 import tempfile
 
+import sys
+
 import numpy as np
 import pytest
+
+sys.path.insert(0, os.path.dirname(__file__))
+import detect_checks  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 
@@ -240,7 +245,7 @@ def test_activation_fusion_is_transparent():
 
 def test_detector_end_to_end_matches_oracle_post_process(oracle_port):
     """Detector::Detect (detector.cc:275-295): network, decode, softmax / threshold / top-k / NMS."""
-    from ogle_b200 import models, session
+    from ogle_b200 import models, ops, session
     from oracle import graph_oracle
     model, info = models.mobilenet_v1_ssd(batch=3, num_classes=21, seed=5, weight_std="he")
     x = ((np.random.default_rng(35).random((3, 300, 300, 3), dtype=np.float32) - 0.5) / 0.5).astype(np.float32)
@@ -251,26 +256,23 @@ def test_detector_end_to_end_matches_oracle_post_process(oracle_port):
         model.save(path)
         det = session.Detector(path, mode=0, score_thr=0.3, top_k=100, nms_thr=0.45, math_mode=0)
         out = det.detect(x)
+        sess = det.session()
+        logits, preds = sess.GetOutputs(["cls_logits", "box_preds"], ["ANY", "ANY"])
+        gpu_boxes = ops.ssd_decode(ops.dense_to_device(preds), ops.dense_to_device(ref["anchors"])).cpu().numpy()
         for n in range(3):
-            r = oracle_port.detect(boxes[n], ref["cls_logits"][n], 300, 300, 0.3, 100, 0.45)
-            k = len(r["anchor"])
-            # indices and classes are exact where scores are not tied within tolerance
-            if np.array_equal(out["anchor"][n, :k], r["anchor"]) and out["count"][n] == k:
-                assert np.array_equal(out["cls"][n, :k], r["cls"])
-                assert np.abs(out["score"][n, :k] - r["score"]).max() <= 1e-4
-                assert np.abs(out["box"][n, :k] - r["rect"]).max() <= 1
-            else:
-                a, b = set(out["anchor"][n, :out["count"][n]].tolist()), set(r["anchor"].tolist())
-                assert len(a ^ b) <= max(2, k // 20), f"image {n}: kept sets differ by {len(a ^ b)} of {k}"
+            # kept anchors and classes are exact; a difference must trace to a near tie (scores within 1e-4,
+            # or a rectangle edge within 0.05 px of the integer it truncates to)
+            detect_checks.reference_rule(oracle_port, out, n, gpu_boxes[n], logits[n], boxes[n], ref["cls_logits"][n],
+                                         (300, 300), 0.3, 100, 0.45, 1e-4)
         det.close()
         det = session.Detector(path, mode=1, score_thr=0.01, top_k=200, math_mode=0)
         out = det.detect(x)
         for n in range(3):
             s_ref, a_ref, c_ref = oracle_port.topk_per_class(ref["cls_logits"][n], 0.01, 200)
-            assert np.abs(out["count"][n] - c_ref).max() <= 2
-            assert np.abs(out["score"][n].reshape(20, 200) - s_ref).max() <= 1e-4
-            same = (out["anchor"][n].reshape(20, 200) == a_ref).mean()
-            assert same >= 0.98, f"image {n}: only {same:.3f} of per-class indices agree"
+            got_s, got_a = out["score"][n].reshape(20, 200), out["anchor"][n].reshape(20, 200)
+            assert np.abs(got_s - s_ref).max() <= 1e-4
+            detect_checks.near_tie_only(got_a, a_ref, s_ref, 1e-4)
+            detect_checks.per_class_counts_differ_only_at_threshold(out["count"][n], c_ref, got_s, s_ref, 0.01, 1e-4, f"image {n}")
         det.close()
 
 

@@ -69,6 +69,14 @@ int ogle_cuda_clear_device_status(void);
 /* The raw status word: which wait gave up (1 producer, 2 MMA issuer, 3 operand split,
  * 4 epilogue, 5 accumulator hand-back); 0 when none did. Synchronises the device. */
 int ogle_cuda_device_status_detail(void);
+/* How many times a role of the tensor-core kernels polls for its turn before it gives up, for
+ * the launches that follow on any stream (process-wide). polls < 0 restores the default (2^22,
+ * tens of milliseconds); 0 makes every such wait give up at once. It exists to exercise the
+ * give-up path without a fault: a launch whose waits run out writes no valid output, sets the
+ * status word, waits for its own copies and multiplies in flight (those waits keep the full
+ * bound), frees its tensor memory and returns, and the device stays usable. No counterpart in
+ * the reference, whose only failure handling is glGetError -> abort (utils/macros.cc:21-28). */
+int ogle_cuda_set_wait_limit(long polls);
 
 /* ------------------------------------------------------------------ conv2d */
 /* Mirrors the uniform set of Conv2DKernel::Compute,
@@ -216,7 +224,8 @@ int ogle_cuda_gemm_static(const OgleGemmParams* p, const float* A, const float* 
 /* ConcatKernel::Compute, nn/kernels/concat.cc:53-96 + concat_multi.glsl.
  * Shapes are 4-D (left-padded with 1s, as AmendShape does); last dimension of
  * every tensor is stored padded to a multiple of 4. One pass, each input read
- * once and written once. */
+ * once and written once. A NULL entry of the input array means that slice is already in
+ * place (its producer wrote it there): it is neither read nor written. */
 #define OGLE_MAX_CONCAT_INPUTS 16
 typedef struct {
     int n_inputs;
@@ -267,6 +276,13 @@ int ogle_cuda_transpose(const float* x, float* y, const int in_shape[4], const i
  * same logical element order, different padded last dimension. */
 int ogle_cuda_reshape(const float* x, float* y, long n_elements, int in_last, int out_last,
                       ogle_stream_t stream);
+/* The same copy with its output rows laid out for a consumer that concatenates: output row r
+ * is written at y + (r / rows_per_block) * block_stride + (r % rows_per_block) * round_up(out_last,4)
+ * (floats; block_stride % 4 == 0). With rows_per_block = the rows one image contributes and
+ * block_stride = the floats of one image in the concatenated tensor, the copy lands in its
+ * slice of that tensor and the concat pass for it (concat.cc:73-96) is not needed. */
+int ogle_cuda_reshape_placed(const float* x, float* y, long n_elements, int in_last, int out_last,
+                             long rows_per_block, long block_stride, ogle_stream_t stream);
 
 /* --------------------------------------------------------------------- SSD */
 /* functor::SSDBBoxDecoder (ogl_runtime/opengl/core/functor.cc:96-143 +
@@ -297,6 +313,12 @@ typedef struct {
     int top_k;       /* <= 256 */
     float nms_thr;   /* mode 0 only; <= 0 disables NMS */
     int image_w, image_h; /* mode 0: scale to pixels */
+    /* mode 0, optional (NULL = every image is image_w x image_h): device table of n
+     * entries whose width/height give the pixel size of image n's ORIGINAL frame. The
+     * reference scales boxes by the raw frame it was handed, not by the network input
+     * (origin_input_sizes_, detector.cc:102,179-180), so frames of different sizes in one
+     * batch need their own scale. Only width and height of an entry are read. */
+    const OgleImageDesc* frame_sizes;
 } OgleDetectParams;
 int ogle_cuda_ssd_detect(const OgleDetectParams* p, const float* logits, const float* boxes,
                          float* out_score, int* out_anchor, int* out_class, float* out_box,

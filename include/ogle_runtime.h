@@ -36,7 +36,10 @@ OgleSession* ogle_session_create(int device, ogle_stream_t stream);
 void ogle_session_destroy(OgleSession* s);
 /* "math_mode" (OgleMathMode), "use_graph" (0/1), "fuse_siblings" (0/1: sibling convolutions
  * of one input as one pass), "fuse_activations" (0/1: a Relu/Clip that is the only reader of an
- * Add runs in the Add's pass; the Add's own tensor is then not readable), "streams" (1..8: streams the captured graph's independent
+ * Add runs in the Add's pass; the Add's own tensor is then not readable), "fuse_concats" (0/1: a Conv
+ * or re-padding Reshape whose result only a Concat reads writes into its slice of the Concat's tensor; a
+ * Concat with every slice written that way is dropped; the producers' own tensors are then not readable),
+ * "streams" (1..8: streams the captured graph's independent
  * branches are recorded on; 1 = file order, as the reference runs). Set before the first run. */
 int ogle_session_set_option(OgleSession* s, const char* key, int value);
 /* FBOSession::LoadGraph(path) / LoadGraph(ModelProto), fbo_session.cc:62-124. */
@@ -56,6 +59,8 @@ int ogle_session_tensor_info(OgleSession* s, const char* name, int* shape8, int*
  * "NCHW", "ANY", "NHWC4", "ANY4" or "HWN4C4". Synchronises. */
 int ogle_session_get_output(OgleSession* s, const char* name, const char* dformat, float* out_host, size_t capacity_floats);
 int ogle_session_num_active_kernels(OgleSession* s);
+/* Concat inputs that their producers write in place (option "fuse_concats"). */
+int ogle_session_num_placed(OgleSession* s);
 /* Branches of the captured graph that run beside the stream of their predecessors
  * (option "streams" > 1); 0 before the capture or for a chain. */
 int ogle_session_num_branches(OgleSession* s);
@@ -89,6 +94,20 @@ int ogle_detector_detect_device_async(OgleDetector* d, const float* images_nhwc4
 int ogle_detector_wait(OgleDetector* d, float* score, int* anchor, int* cls, float* box, int* count);
 int ogle_detector_info(OgleDetector* d, int* num_anchors, int* num_classes, int* rows, size_t* h2d_bytes, size_t* d2h_bytes);
 OgleSession* ogle_detector_session(OgleDetector* d);
+/* Result memory of the caller's for the detector's two pipeline slots (pinned or
+ * CUDA-registered host memory, 16-byte aligned, bytes_each >= the total of
+ * ogle_detector_result_layout for the batch): detections are copied from the device
+ * straight into it, and ogle_detector_wait still blocks until they are there. With the
+ * slots inside a region from ogle_host_shared_open, the process that owns a batch sharded
+ * over several per-GPU processes reads every shard's detections in place, where the
+ * reference's single process reads its one read-back (detector.cc:242-273). Call before
+ * the first detect call. */
+int ogle_detector_use_result_buffers(OgleDetector* d, void* slot0_host, void* slot1_host, size_t bytes_each);
+/* Byte offsets of score [N][rows] f32, anchor [N][rows] i32, class [N][rows] i32,
+ * box [N][rows][4] f32, count [N][counts_per_image] i32 inside one result block, and its
+ * total size: offsets6 = {score, anchor, class, box, count, total}. */
+int ogle_detector_result_layout(int mode, int num_classes, int top_k, int N, size_t* offsets6, int* rows,
+                                int* counts_per_image);
 
 /* The session's stream planner on its own (pure host logic; option "streams"): nodes in
  * execution order, each with the memory spans [lo, hi) it reads and writes, given as n_spans
@@ -115,6 +134,19 @@ int ogle_host_bind_to_device(int device, int* numa_node, int* cpus_bound, int* m
  * current; free only with ogle_host_free_pinned. */
 void* ogle_host_alloc_pinned(size_t bytes);
 void ogle_host_free_pinned(void* p);
+/* Bytes of the mapping holding p that the kernel backs with 2 MB pages right now (0 = none
+ * were granted, or unknown). */
+size_t ogle_host_huge_page_bytes(const void* p);
+/* A named region of host memory shared by the per-GPU processes of one box (POSIX shared
+ * memory; name starts with '/'). create != 0 makes and zero-fills it, otherwise an existing
+ * one is mapped; pin != 0 registers the mapping with CUDA in the calling process (device
+ * context current), so that uploads from it and result copies into it are asynchronous.
+ * One batch is then written once by its owner, uploaded slice by slice by every process, and
+ * the detections land where the owner reads them: the host-side scatter and gather of an
+ * image-sharded batch without a copy between processes. NULL on failure
+ * (ogle_rt_last_error). ogle_host_shared_close unmaps; unlink != 0 also removes the name. */
+void* ogle_host_shared_open(const char* name, size_t bytes, int create, int pin);
+void ogle_host_shared_close(void* p, int unlink);
 /* Parses a sysfs CPU list ("0-3,8,10-11"); writes up to `capacity` entries, returns the count. */
 int ogle_host_parse_cpulist(const char* text, int* cpus, int capacity);
 

@@ -50,7 +50,7 @@ class DetectParams(C.Structure):
     _fields_ = [
         ("N", C.c_int), ("A", C.c_int), ("C", C.c_int), ("logit_stride", C.c_int), ("mode", C.c_int),
         ("score_thr", C.c_float), ("top_k", C.c_int), ("nms_thr", C.c_float),
-        ("image_w", C.c_int), ("image_h", C.c_int),
+        ("image_w", C.c_int), ("image_h", C.c_int), ("frame_sizes", C.c_void_p),
     ]
 
 
@@ -58,6 +58,7 @@ class DetectParams(C.Structure):
 _vp = C.c_void_p
 CUDA_SYMBOLS = {
     "ogle_cuda_status_string": (C.c_char_p, [C.c_int]),
+    "ogle_cuda_set_wait_limit": (C.c_int, [C.c_long]),
     "ogle_cuda_build_info": (C.c_char_p, []),
     "ogle_cuda_launch_count": (C.c_uint64, []),
     "ogle_cuda_last_error": (C.c_char_p, []),
@@ -93,6 +94,7 @@ CUDA_SYMBOLS = {
     "ogle_cuda_nchw_to_nhwc4": (C.c_int, [_vp, _vp] + [C.c_int] * 4 + [_vp]),
     "ogle_cuda_transpose": (C.c_int, [_vp, _vp, C.POINTER(C.c_int), C.POINTER(C.c_int), _vp]),
     "ogle_cuda_reshape": (C.c_int, [_vp, _vp, C.c_long, C.c_int, C.c_int, _vp]),
+    "ogle_cuda_reshape_placed": (C.c_int, [_vp, _vp, C.c_long, C.c_int, C.c_int, C.c_long, C.c_long, _vp]),
     "ogle_cuda_ssd_decode": (C.c_int, [_vp, _vp, _vp, C.c_int, C.c_int, C.POINTER(C.c_float), _vp]),
     "ogle_cuda_ssd_detect": (C.c_int, [C.POINTER(DetectParams)] + [_vp] * 8),
 }

@@ -4,6 +4,7 @@
 namespace ogle {
 int read_tc_error();
 int clear_tc_error();
+void set_role_wait_limit(long polls);
 std::atomic<uint64_t> g_launch_count{0};
 static thread_local char g_last_error[256] = "";
 void set_last_error(cudaError_t e) {
@@ -49,6 +50,11 @@ int ogle_cuda_device_status(void) {
 int ogle_cuda_device_status_detail(void) {
     if (cudaDeviceSynchronize() != cudaSuccess) return OGLE_ERR_CUDA;
     return ogle::read_tc_error();
+}
+
+int ogle_cuda_set_wait_limit(long polls) {
+    ogle::set_role_wait_limit(polls);
+    return OGLE_OK;
 }
 
 int ogle_cuda_clear_device_status(void) { return ogle::clear_tc_error() == 0 ? OGLE_OK : OGLE_ERR_CUDA; }

@@ -18,6 +18,7 @@
 // [a_hi | a_lo] x [b_lo | b_hi] (eight mantissa bits are ample for terms that are
 // themselves 2^-11 of the result). The filter parts are made when it is packed; the
 // activation parts in shared memory while the pipeline runs.
+#include <atomic>
 #include <cmath>
 #include <cstdlib>
 
@@ -339,6 +340,15 @@ int launch_gemm_tc_packed(const OgleGemmParams& p, const float* A, const float* 
     const long Cp32 = (p.K + 31) / 32 * 32;
     const long rows = (p.N + 127) / 128 * 128;
     return launch_gemm_common(p, A, Bhi, Blo, Cp32, rows, C, Y, s, p.math_mode == OGLE_MATH_TF32X3 ? 3 : 1);
+}
+
+namespace {
+std::atomic<uint32_t> g_role_wait_limit{tc::kSpinLimit};
+}
+uint32_t tc::role_wait_limit() { return g_role_wait_limit.load(std::memory_order_relaxed); }
+void set_role_wait_limit(long polls) {
+    g_role_wait_limit.store(polls < 0 ? tc::kSpinLimit : (polls > long(tc::kSpinLimit) ? tc::kSpinLimit : uint32_t(polls)),
+                            std::memory_order_relaxed);
 }
 
 int read_tc_error() {

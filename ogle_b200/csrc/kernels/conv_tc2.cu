@@ -21,8 +21,12 @@
 //
 // HBM traffic per tile is the algorithmic minimum: the activation tile is read
 // once, the output tile written once; filters come from L2.
-// All mbarrier waits are bounded and abort the block cleanly (status word set,
-// in-flight copies drained, tensor memory freed).
+// All mbarrier waits are bounded and abort the block cleanly: the role records a code in
+// the status word and raises the block's abort flag, the other roles leave at their next
+// wait, the MMA issuer waits for the multiplies it has issued, the teardown waits for the
+// operand copies still in flight, and only then is tensor memory freed and the block retired.
+// The number of polls of the role waits can be shortened at run time (ogle_cuda_set_wait_limit,
+// for tests of this path); the waits of the abort path itself always use the full bound.
 #include <cuda_bf16.h>
 
 #include <cstdlib>
@@ -38,10 +42,11 @@ constexpr int kThreads2 = 608;
 constexpr int kMaxStages = 8;
 constexpr int kStagingBytes = kTileM * 128;   // one 128-row x 32-column fp32 slab
 
-// Bounded wait that also gives up early when another role of the block has aborted.
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+// Bounded wait of a role for its turn; also gives up early when another role of the block has
+// aborted. `limit` is the number of polls (kSpinLimit unless the host shortened it).
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t limit) {
     const uint32_t addr = smem_u32(bar);
-    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    for (uint32_t spin = 0; spin < limit; ++spin) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -60,22 +65,6 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t sr
     asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
                  ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
-
-#ifdef OGLE_TC_TRACE
-// Debug build only: per-role clock stamps of block 0, [tile][slot].
-__device__ long long g_trace[64 * 16];
-#define TRACE(tile_iter, slot) do { if (blockIdx.x == 0 && (tile_iter) < 64) g_trace[(tile_iter) * 16 + (slot)] = clock64(); } while (0)
-#else
-#define TRACE(tile_iter, slot) do {} while (0)
-#endif
-#ifdef OGLE_TC_TRACE_CHUNKS
-// Debug build only: stamps per reduction chunk of block 0's first tile instead of per tile.
-#undef TRACE
-#define TRACE(tile_iter, slot) do {} while (0)
-#define TRACEC(chunk, slot) do { if (blockIdx.x == 0 && (chunk) < 64) g_trace[(chunk) * 16 + (slot)] = clock64(); } while (0)
-#else
-#define TRACEC(chunk, slot) do {} while (0)
-#endif
 
 __device__ __forceinline__ void tmem_ld32(uint32_t (&r)[32], uint32_t taddr) {
     asm volatile(
@@ -140,8 +129,10 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[kMaxStages], bar_xf[kMaxStages], bar_empty[kMaxStages];
     __shared__ __align__(8) uint64_t bar_acc_full[4], bar_acc_empty[4];
+    __shared__ __align__(8) uint64_t bar_drain;     // abort path: the MMAs issued so far have finished
     __shared__ uint32_t tmem_slot;
     __shared__ int s_abort;
+    __shared__ int s_issued[2];                     // operand copies issued by the two producers (abort path)
     __shared__ __align__(16) float s_bias[2][256];
     __shared__ __align__(8) short s_goff[kMaxGatherK];   // gather form: window offset of each reduction index
 
@@ -184,7 +175,9 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             mbar_init(&bar_acc_full[i], 1);
             mbar_init(&bar_acc_empty[i], 128);
         }
+        mbar_init(&bar_drain, 1);
         s_abort = 0;
+        s_issued[0] = 0; s_issued[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (a.gather) {
@@ -220,8 +213,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             uint32_t wrap = 0;         // how many times the ring has wrapped
             int issued = 0;            // chunks in flight bookkeeping for the abort path
             bool ok = true;
-            int pti = 0;
-            for (int w = blockIdx.x; w < a.total_work && ok; w += gridDim.x, ++pti) {
+            for (int w = blockIdx.x; w < a.total_work && ok; w += gridDim.x) {
                 const WorkItem wi = work_item<kSplit>(a, w, chunks);
                 const TileCoord tc_ = tile_coord(a, wi.tile);
                 const int ax = a.flat ? tc_.w0 : tc_.w0 * a.stride - a.pad;
@@ -235,11 +227,8 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     c0 = (wi.c_begin - tap0 * a.chunks_per_tap) * kChunk;
                 }
                 for (int it = wi.c_begin; it < wi.c_end; ++it) {
-                    if (it == wi.c_begin) TRACE(pti, 0);
-                    if (wrap > 0) ok = wait_or_abort(&bar_empty[s], (wrap - 1) & 1u, abort_flag);
+                    if (wrap > 0) ok = wait_or_abort(&bar_empty[s], (wrap - 1) & 1u, abort_flag, a.spin_limit);
                     if (!ok) { record_error(err_flag, 1); break; }
-                    if (it == wi.c_begin) TRACE(pti, 1);
-                    TRACEC(pti * chunks + it, 0);
                     if (a.gather) {
                         mbar_expect_tx(&bar_full[s], (uint32_t)(a.g_iw * a.g_ih * 16));
                         tma_load_4d(sWin(s), &tmA, &bar_full[s], 0, ax, ay, tc_.n0);
@@ -247,7 +236,6 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         mbar_expect_tx(&bar_full[s], tx);
                         tma_load_4d(sA(s), &tmA, &bar_full[s], c0, ax + kx * a.dil, ay + ky * a.dil, tc_.n0);
                     }
-                    TRACEC(pti * chunks + it, 1);
                     ++issued;
                     if (++s == a.stages) { s = 0; ++wrap; }
                     // next chunk: channels fastest, then filter column, then filter row
@@ -255,12 +243,8 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     if (c0 == a.Cp32) { c0 = 0; if (++kx == a.kernel) { kx = 0; ++ky; } }
                 }
             }
-            if (!ok) {
-                // let the copies already in flight land before the block retires
-                s_abort = 1;
-                for (int i = (issued > a.stages ? issued - a.stages : 0); i < issued; ++i)
-                    mbar_wait(&bar_full[i % a.stages], (uint32_t)((i / a.stages) & 1));
-            }
+            if (!ok) s_abort = 1;
+            s_issued[0] = issued;      // the teardown waits for these copies if the block aborts
         }
     } else if (warp == 18) {
         // ------------------------------------------------ TMA producer, filter tiles
@@ -275,7 +259,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const int bcol = (wi.tile % a.n_tiles) * a.BN;
                 int brow = wi.c_begin * kChunk;
                 for (int it = wi.c_begin; it < wi.c_end; ++it) {
-                    if (wrap > 0) ok = wait_or_abort(&bar_empty[s], (wrap - 1) & 1u, abort_flag);
+                    if (wrap > 0) ok = wait_or_abort(&bar_empty[s], (wrap - 1) & 1u, abort_flag, a.spin_limit);
                     if (!ok) { record_error(err_flag, 7); break; }
                     mbar_expect_tx(&bar_full[s], tx);
                     tma_load_2d(sBhi(s), &tmBhi, &bar_full[s], brow, bcol);
@@ -285,11 +269,8 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     brow += kChunk;       // packed filter rows follow the chunk order
                 }
             }
-            if (!ok) {
-                s_abort = 1;
-                for (int i = (issued > a.stages ? issued - a.stages : 0); i < issued; ++i)
-                    mbar_wait(&bar_full[i % a.stages], (uint32_t)((i / a.stages) & 1));
-            }
+            if (!ok) s_abort = 1;
+            s_issued[1] = issued;
         }
     } else if (warp == 1) {
         // -------------------------------------------------------------- MMA issuer
@@ -304,17 +285,14 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             for (int w = blockIdx.x; w < a.total_work && ok; w += gridDim.x, ++ti) {
                 const WorkItem wi = work_item<kSplit>(a, w, chunks);
                 const int as = a.n_acc == 4 ? (ti & 3) : (ti & 1), use = a.n_acc == 4 ? (ti >> 2) : (ti >> 1);
-                if (use > 0) ok = wait_or_abort(&bar_acc_empty[as], (uint32_t)((use - 1) & 1), abort_flag);
+                if (use > 0) ok = wait_or_abort(&bar_acc_empty[as], (uint32_t)((use - 1) & 1), abort_flag, a.spin_limit);
                 if (!ok) { record_error(err_flag, 5); s_abort = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d = tmem_d + (uint32_t)(as * acc_cols);
                 for (int it = wi.c_begin; it < wi.c_end; ++it) {
-                    if (it == wi.c_begin) TRACE(ti, 4);
                     // gather form: the operand exists only once the split warps have built it
-                    ok = wait_or_abort(a.gather ? &bar_xf[s] : &bar_full[s], ph, abort_flag);
+                    ok = wait_or_abort(a.gather ? &bar_xf[s] : &bar_full[s], ph, abort_flag, a.spin_limit);
                     if (!ok) { record_error(err_flag, 2); s_abort = 1; break; }
-                    if (it == wi.c_begin) TRACE(ti, 5);
-                    TRACEC(ti * chunks + it, 2);
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t ad = umma_desc(sA(s)), bd = umma_desc(sBhi(s));
                     const uint32_t acc_flag = it > (kSplit ? wi.c_begin : 0) ? 1u : 0u;     // the first chunk overwrites
@@ -323,18 +301,22 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         // cross terms [a_hi | a_lo] x [b_lo | b_hi] in BF16, once the split role has
                         // written the activation parts
                         if (!a.gather) {
-                            ok = wait_or_abort(&bar_xf[s], ph, abort_flag);
+                            ok = wait_or_abort(&bar_xf[s], ph, abort_flag, a.spin_limit);
                             if (!ok) { record_error(err_flag, 2); s_abort = 1; break; }
                             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         }
                         umma_bf16_chunk(d, ad + (kABytes >> 4), bd + (b_bytes >> 4), idesc_bf16, 1u);
                     }
                     umma_commit(&bar_empty[s]);
-                    TRACEC(ti * chunks + it, 3);
                     if (++s == a.stages) { s = 0; ph ^= 1u; }
                 }
                 if (ok) umma_commit(&bar_acc_full[as]);
-                TRACE(ti, 6);
+            }
+            if (!ok) {
+                // abort: the multiplies already issued still read shared memory and write tensor
+                // memory; the block may free neither before they are done
+                umma_commit(&bar_drain);
+                mbar_wait(&bar_drain, 0u);
             }
         }
     } else if (warp >= 10) {
@@ -350,7 +332,6 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const int t = threadIdx.x - 320;       // 0 .. nthr-1
             int s = 0;
             uint32_t ph = 0;
-            int xti = 0;
             bool ok = true;
             // gather form: a thread always builds the same 16-byte piece (t & 7) of the same rows, so the
             // rows' offsets into the input window are computed once: g_row[q] for row (t >> 3) + q * nthr / 8.
@@ -363,12 +344,11 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     g_row[q] = ((ry * a.stride) * a.g_iw + rx * a.stride) * 4;
                 }
             }
-            for (int w = blockIdx.x; w < a.total_work && ok; w += gridDim.x, ++xti) {
+            for (int w = blockIdx.x; w < a.total_work && ok; w += gridDim.x) {
                 const WorkItem wi = work_item<kSplit>(a, w, chunks);
                 for (int it = wi.c_begin; it < wi.c_end; ++it) {
-                    ok = wait_or_abort(&bar_full[s], ph, abort_flag);
+                    ok = wait_or_abort(&bar_full[s], ph, abort_flag, a.spin_limit);
                     if (!ok) { record_error(err_flag, 3); s_abort = 1; break; }
-                    if (t == 0 && it == wi.c_begin) TRACE(xti, 2);
                     float4* pa = reinterpret_cast<float4*>(base_ptr + (size_t)s * stage_bytes);
                     float4* pl = pa + kABytes / 16;
                     uint2* p2 = reinterpret_cast<uint2*>(pl);                 // 8-byte pieces of the BF16 tile
@@ -425,7 +405,6 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     mbar_arrive(&bar_xf[s]);
-                    if (t == 0 && it == wi.c_begin) TRACE(xti, 3);
                     if (++s == a.stages) { s = 0; ph ^= 1u; }
                 }
             }
@@ -470,10 +449,8 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         my_bias[i] = (a.bias_mode == 2 && (!kSplit || wi.ks == 0) && nbase + i < a.K) ? a.beta * bias[nbase + i] : 0.f;
                     staged_nbase = bias_key;
                 }
-                if (t == 0) TRACE(ti, 7);
-                ok = wait_or_abort(&bar_acc_full[as], (uint32_t)(use & 1), abort_flag);
+                ok = wait_or_abort(&bar_acc_full[as], (uint32_t)(use & 1), abort_flag, a.spin_limit);
                 if (!ok) { record_error(err_flag, 4); s_abort = 1; break; }
-                if (t == 0) TRACE(ti, 8);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 // one 32-column slab per round through a ring of one or two staging slabs: a slab
                 // is reused once the store issued from it (one or two rounds ago) has read it, so
@@ -486,7 +463,6 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                     }
                     group_sync(bar_id);
-                    if (t == 0 && g0 == 0) TRACE(ti, 9);
                     {
                         const int b = 0;
                         const int col = g0 * 32;
@@ -494,7 +470,6 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         const uint32_t taddr = tmem_d + ((uint32_t)(q * 32) << 16) + (uint32_t)(as * acc_cols + col);
                         tmem_ld32(r, taddr);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                        if (t == 0 && g0 == 0 && b == 0) TRACE(ti, 14);
                         if (g0 + b == groups - 1) {
                             // this thread's part of the accumulator is in registers: hand the buffer back
                             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -552,13 +527,9 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                                 dst[c4 ^ (row & 7)] = make_float4(v[0], v[1], v[2], v[3]);
                             }
                         }
-                        if (t == 0 && g0 == 0 && b == 0) TRACE(ti, 15);
                     }
-                    if (t == 0 && g0 == 0) TRACE(ti, 10);
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    if (t == 0 && g0 == 0) TRACE(ti, 11);
                     group_sync(bar_id);
-                    if (t == 0 && g0 == 0) TRACE(ti, 12);
                     if (t == 0) {
                         {
                             const uint32_t src = base + my_staging + (uint32_t)sb * (uint32_t)kStagingBytes;
@@ -575,7 +546,6 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                             }
                         }
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                        if (g0 + 1 >= groups) TRACE(ti, 13);
                     }
                 }
             }
@@ -587,6 +557,22 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     // ------------------------------------------------------------------ teardown
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (s_abort) {
+        // Some role gave up. Every role has left its loop (a role that was not waiting finished
+        // what it had issued), but operand copies may still be in flight towards this block's
+        // shared memory, and the block must not retire before they have landed. A ring stage's
+        // barrier completes when BOTH producers have announced their copy and the bytes are in;
+        // the producers may have stopped up to a ring apart, so first supply the announcement
+        // the other one never made, then wait (full bound) for the last ring of stages.
+        if (threadIdx.x == 0) {
+            const int na = s_issued[0], nb = s_issued[1];
+            const int lo = na < nb ? na : nb, hi = na < nb ? nb : na;
+            for (int i = lo; i < hi; ++i) mbar_arrive(&bar_full[i % a.stages]);
+            for (int i = (hi > a.stages ? hi - a.stages : 0); i < hi; ++i)
+                mbar_wait(&bar_full[i % a.stages], (uint32_t)((i / a.stages) & 1));
+        }
+        __syncthreads();
+    }
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)a.tmem_cols));
     }
@@ -606,13 +592,6 @@ int num_sms() {
 }
 
 }  // namespace
-
-#ifdef OGLE_TC_TRACE
-extern "C" int ogle_debug_read_trace(long long* out) {
-    cudaDeviceSynchronize();
-    return cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 64 * 16) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, const CUtensorMap& mBlo,
                  const CUtensorMap& mY, const CUtensorMap& mY2, long m_tiles, const float* bias, int* err_flag,
@@ -659,6 +638,7 @@ int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, cons
     const long total = m_tiles * t.n_tiles;
     if (total <= 0 || total > 0x7fffffffL) return OGLE_ERR_UNSUPPORTED;
     t.total_tiles = (int)total;
+    t.spin_limit = role_wait_limit();
     if (t.split_k < 1) t.split_k = 1;
     if (total * t.split_k > 0x7fffffffL) return OGLE_ERR_UNSUPPORTED;
     t.total_work = (int)(total * t.split_k);

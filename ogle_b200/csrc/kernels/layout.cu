@@ -85,9 +85,11 @@ __global__ void transpose_kernel(const float* __restrict__ x, float* __restrict_
 
 // Same logical order, different padded last dimension. One thread per output float4
 // (four consecutive elements of an output row; lanes past out_last are written as zero).
+// rows_per_block > 0: output row r goes to block r / rows_per_block at block_stride_q float4s
+// per block (a slice of a wider tensor); 0: dense.
 template <typename Index>
 __global__ void reshape_kernel(const float* __restrict__ x, float4* __restrict__ y,
-                               Index n, int in_last, int out_last) {
+                               Index n, int in_last, int out_last, Index rows_per_block, long block_stride_q) {
     const int ip = (in_last + 3) & ~3, oq = ((out_last + 3) & ~3) >> 2;
     const Index total = n / out_last * oq;
     for (Index i = blockIdx.x * (Index)blockDim.x + threadIdx.x; i < total; i += (Index)gridDim.x * blockDim.x) {
@@ -102,7 +104,12 @@ __global__ void reshape_kernel(const float* __restrict__ x, float4* __restrict__
             v[l] = c + l < out_last ? x[q * ip + rem] : 0.f;
             if (++rem == in_last) { rem = 0; ++q; }
         }
-        y[i] = make_float4(v[0], v[1], v[2], v[3]);
+        long dst = (long)i;
+        if (rows_per_block) {
+            const Index b = r / rows_per_block;
+            dst = (long)b * block_stride_q + (long)(r - b * rows_per_block) * oq + (c >> 2);
+        }
+        y[dst] = make_float4(v[0], v[1], v[2], v[3]);
     }
 }
 
@@ -119,8 +126,9 @@ struct ConcatArgs {
 // One thread per output float4; each input is read once and the output written once.
 // Four independent 16-byte loads are issued before the first store, and the index
 // arithmetic is 32-bit when the tensor allows it (64-bit divisions cost more than the copy).
+// False when the element belongs to a slice that is already in place (null input): not stored.
 template <typename Index>
-__device__ __forceinline__ float4 concat_fetch(const ConcatArgs& a, Index i, int q) {
+__device__ __forceinline__ bool concat_fetch(const ConcatArgs& a, Index i, int q, float4* out) {
     Index t = i;
     int o[4];
     o[3] = int(t % q) * 4; t /= q;
@@ -133,11 +141,13 @@ __device__ __forceinline__ float4 concat_fetch(const ConcatArgs& a, Index i, int
     int s[4] = {a.os[0], a.os[1], a.os[2], a.os[3]};
     s[a.axis] = a.in_axis[k];
     o[a.axis] = pos - a.axis_start[k];
+    if (a.in[k] == nullptr) return false;
     const int s3p = (s[3] + 3) & ~3;
     const long off = (((long)o[0] * s[1] + o[1]) * s[2] + o[2]) * s3p + o[3];
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (o[3] < s3p) v = __ldg(reinterpret_cast<const float4*>(a.in[k] + off));
-    return v;
+    *out = v;
+    return true;
 }
 
 template <typename Index>
@@ -148,12 +158,17 @@ __global__ void __launch_bounds__(256) concat_vec_kernel(ConcatArgs a, float4* _
     Index i = blockIdx.x * (Index)blockDim.x + threadIdx.x;
     for (; i + 3 * step < total; i += 4 * step) {
         float4 v[4];
+        bool ok[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) v[u] = concat_fetch<Index>(a, i + u * step, q);
+        for (int u = 0; u < 4; ++u) ok[u] = concat_fetch<Index>(a, i + u * step, q, &v[u]);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) y[i + u * step] = v[u];
+        for (int u = 0; u < 4; ++u)
+            if (ok[u]) y[i + u * step] = v[u];
     }
-    for (; i < total; i += step) y[i] = concat_fetch<Index>(a, i, q);
+    for (; i < total; i += step) {
+        float4 v;
+        if (concat_fetch<Index>(a, i, q, &v)) y[i] = v;
+    }
 }
 
 // General path (channel-axis slices not multiples of 4): one thread per output float.
@@ -240,20 +255,38 @@ int ogle_cuda_transpose(const float* x, float* y, const int in_shape[4], const i
     return finish_launch();
 }
 
-int ogle_cuda_reshape(const float* x, float* y, long n_elements, int in_last, int out_last,
-                      ogle_stream_t stream) {
+static int launch_reshape(const float* x, float* y, long n_elements, int in_last, int out_last, long rows_per_block,
+                          long block_stride, ogle_stream_t stream) {
     if (!x || !y || n_elements <= 0 || in_last <= 0 || out_last <= 0) return OGLE_ERR_INVALID;
     if (n_elements % in_last || n_elements % out_last) return OGLE_ERR_INVALID;
-    const long items = n_elements / out_last * up4(out_last);
+    const long rows = n_elements / out_last;
+    const long items = rows * up4(out_last);
     if (!aligned16(y)) return OGLE_ERR_ALIGNMENT;
+    long extent = items;              // floats of the destination that may be addressed
+    if (rows_per_block) {
+        if (rows_per_block < 0 || rows % rows_per_block || (block_stride & 3) || block_stride < rows_per_block * up4(out_last))
+            return OGLE_ERR_INVALID;
+        extent = rows / rows_per_block * block_stride;
+    }
     const long vecs = items / 4;
-    if (n_elements < 0x7fffffffL && items < 0x7fffffffL)     // 32-bit index arithmetic when it fits (the usual case)
+    if (n_elements < 0x7fffffffL && items < 0x7fffffffL && extent < 0x7fffffffL)     // 32-bit index arithmetic when it fits (the usual case)
         reshape_kernel<unsigned><<<grid_for(vecs, 256), 256, 0, (cudaStream_t)stream>>>(
-            x, reinterpret_cast<float4*>(y), (unsigned)n_elements, in_last, out_last);
+            x, reinterpret_cast<float4*>(y), (unsigned)n_elements, in_last, out_last, (unsigned)rows_per_block, block_stride / 4);
     else
         reshape_kernel<long><<<grid_for(vecs, 256), 256, 0, (cudaStream_t)stream>>>(
-            x, reinterpret_cast<float4*>(y), n_elements, in_last, out_last);
+            x, reinterpret_cast<float4*>(y), n_elements, in_last, out_last, rows_per_block, block_stride / 4);
     return finish_launch();
+}
+
+int ogle_cuda_reshape(const float* x, float* y, long n_elements, int in_last, int out_last,
+                      ogle_stream_t stream) {
+    return launch_reshape(x, y, n_elements, in_last, out_last, 0, 0, stream);
+}
+
+int ogle_cuda_reshape_placed(const float* x, float* y, long n_elements, int in_last, int out_last,
+                             long rows_per_block, long block_stride, ogle_stream_t stream) {
+    if (rows_per_block <= 0) return OGLE_ERR_INVALID;
+    return launch_reshape(x, y, n_elements, in_last, out_last, rows_per_block, block_stride, stream);
 }
 
 int ogle_cuda_concat(const OgleConcatParams* p, const float* const* inputs, float* y,
@@ -266,21 +299,24 @@ int ogle_cuda_concat(const OgleConcatParams* p, const float* const* inputs, floa
     a.axis = p->axis;
     for (int d = 0; d < 4; ++d) a.os[d] = p->in_shapes[0][d];
     a.os[p->axis] = 0;
-    bool vec_ok = aligned16(y);
+    bool vec_ok = aligned16(y), any_input = false, any_placed = false;
     for (int i = 0; i < p->n_inputs; ++i) {
         for (int d = 0; d < 4; ++d) {
             if (p->in_shapes[i][d] <= 0) return OGLE_ERR_INVALID;
             if (d != p->axis && p->in_shapes[i][d] != p->in_shapes[0][d]) return OGLE_ERR_INVALID;
         }
-        if (!inputs[i]) return OGLE_ERR_INVALID;
-        a.in[i] = inputs[i];
+        a.in[i] = inputs[i];              // null: the slice is already in place
         a.in_axis[i] = p->in_shapes[i][p->axis];
         a.axis_start[i] = a.os[p->axis];
         a.os[p->axis] += a.in_axis[i];
-        if (!aligned16(inputs[i])) vec_ok = false;
+        if (inputs[i]) any_input = true;
+        else any_placed = true;
+        if (inputs[i] && !aligned16(inputs[i])) vec_ok = false;
         if (p->axis == 3 && (a.in_axis[i] & 3) && i + 1 < p->n_inputs) vec_ok = false;
     }
     a.axis_start[p->n_inputs] = a.os[p->axis];
+    if (!any_input) return OGLE_OK;                       // every slice in place: nothing to copy
+    if (any_placed && !vec_ok) return OGLE_ERR_UNSUPPORTED;   // in-place slices need the 16-byte path
     const int op = up4(a.os[3]);
     const long rows = (long)a.os[0] * a.os[1] * a.os[2];
     if (vec_ok) {

@@ -215,6 +215,7 @@ struct DetectArgs {
     float score_thr, nms_thr;
     int classes_per_pass;   // mode 1: foreground classes whose scores fit in shared memory at once
     int parts;              // mode 1: blocks per image, each taking a contiguous range of the foreground classes
+    const OgleImageDesc* frames;   // mode 0: per-image frame sizes, or null
 };
 
 // Dynamic shared memory layout:
@@ -329,12 +330,15 @@ ssd_detect_kernel(const float* __restrict__ logits, const float4* __restrict__ b
     }
     __syncthreads();
     const int cnt = s_cnt;
-    // integer pixel rectangles: cv::Rect members are int, so float -> int truncates
+    // integer pixel rectangles of the frame the image came from (detector.cc:179-180,199-214):
+    // cv::Rect members are int, so float -> int truncates
+    const int image_w = a.frames ? a.frames[n].width : a.image_w;
+    const int image_h = a.frames ? a.frames[n].height : a.image_h;
     for (int r = tid; r < cnt; r += blockDim.x) {
         const int an = (int)(0xffffffffu - (unsigned)(list[r] & 0xffffffffull));
         const float4 b = bx[an];
-        const float xmin = b.x * a.image_w, ymin = b.y * a.image_h;
-        const float xmax = b.z * a.image_w, ymax = b.w * a.image_h;
+        const float xmin = b.x * image_w, ymin = b.y * image_h;
+        const float xmax = b.z * image_w, ymax = b.w * image_h;
         rect[r * 4 + 0] = (int)xmin; rect[r * 4 + 1] = (int)ymin;
         rect[r * 4 + 2] = (int)(xmax - xmin); rect[r * 4 + 3] = (int)(ymax - ymin);
     }
@@ -419,6 +423,8 @@ int ogle_cuda_ssd_detect(const OgleDetectParams* p, const float* logits, const f
     DetectArgs a;
     a.N = p->N; a.A = p->A; a.C = p->C; a.logit_stride = ls; a.mode = p->mode; a.top_k = p->top_k;
     a.image_w = p->image_w; a.image_h = p->image_h; a.score_thr = p->score_thr; a.nms_thr = p->nms_thr;
+    a.frames = p->mode == 0 ? p->frame_sizes : nullptr;
+    if (a.frames && (reinterpret_cast<uintptr_t>(a.frames) & 7)) return OGLE_ERR_ALIGNMENT;
     static const size_t kSmemBudget = 200 * 1024;
     int threads;
     size_t smem;

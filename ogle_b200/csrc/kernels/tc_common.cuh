@@ -53,7 +53,11 @@ struct TcArgs {
     // (chunks_per_tap chunks; kernel = 1 in this form). g_C = input channels, g_k = filter
     // size, g_bytes = window bytes rounded up to 1 KB (its slot at the end of every stage).
     int gather, g_iw, g_ih, g_C, g_bytes, g_k;
+    uint32_t spin_limit;      // polls a role waits for its turn before it gives up (kSpinLimit by default)
 };
+
+// Polls of the role waits for the launches that follow (see ogle_cuda_set_wait_limit).
+uint32_t role_wait_limit();
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

@@ -95,6 +95,8 @@ int ogle_session_set_option(OgleSession* s, const char* key, int value) {
             s->session->set_fuse_siblings(value != 0);
         } else if (k == "fuse_activations") {
             s->session->set_fuse_activations(value != 0);
+        } else if (k == "fuse_concats") {
+            s->session->set_fuse_concats(value != 0);
         } else if (k == "streams") {
             s->session->set_streams(value);
         } else {
@@ -168,6 +170,7 @@ int ogle_session_get_output(OgleSession* s, const char* name, const char* dforma
 }
 
 int ogle_session_num_active_kernels(OgleSession* s) { return s ? s->session->num_active_kernels() : -1; }
+int ogle_session_num_placed(OgleSession* s) { return s ? s->session->num_placed() : -1; }
 int ogle_session_num_branches(OgleSession* s) { return s ? s->session->num_branches() : -1; }
 int ogle_session_graph_captured(OgleSession* s) { return s ? int(s->session->graph_captured()) : -1; }
 size_t ogle_session_device_bytes(OgleSession* s) { return s ? s->session->device_bytes() : 0; }
@@ -292,6 +295,31 @@ int ogle_rt_plan_streams(int n_nodes, int n_spans, const int* span_node, const u
 
 void* ogle_host_alloc_pinned(size_t bytes) { return ogle::AllocPinnedHost(bytes); }
 void ogle_host_free_pinned(void* p) { ogle::FreePinnedHost(p); }
+size_t ogle_host_huge_page_bytes(const void* p) { return ogle::HugePageBytes(p); }
+
+void* ogle_host_shared_open(const char* name, size_t bytes, int create, int pin) {
+    if (!name) return nullptr;
+    std::string err;
+    void* p = ogle::OpenSharedHost(name, bytes, create != 0, pin != 0, &err);
+    if (!p) g_error = err;
+    return p;
+}
+void ogle_host_shared_close(void* p, int unlink) { ogle::CloseSharedHost(p, unlink != 0); }
+
+int ogle_detector_use_result_buffers(OgleDetector* d, void* slot0, void* slot1, size_t bytes_each) {
+    if (!d) return -1;
+    return guarded([&] { d->detector->UseResultBuffers(slot0, slot1, bytes_each); });
+}
+
+int ogle_detector_result_layout(int mode, int num_classes, int top_k, int N, size_t* offsets6, int* rows, int* counts_per_image) {
+    if (mode < 0 || mode > 1 || num_classes < 2 || top_k <= 0 || N <= 0 || !offsets6) return -1;
+    const ogle::Detector::ResultLayout L = ogle::Detector::LayoutFor(mode, num_classes, top_k, N);
+    offsets6[0] = L.score; offsets6[1] = L.anchor; offsets6[2] = L.cls; offsets6[3] = L.box; offsets6[4] = L.count;
+    offsets6[5] = L.total;
+    if (rows) *rows = L.rows;
+    if (counts_per_image) *counts_per_image = L.counts_per_image;
+    return 0;
+}
 
 int ogle_host_parse_cpulist(const char* text, int* cpus, int capacity) {
     if (!text) return -1;

@@ -42,8 +42,8 @@ void Detector::Release() {
         if (s.desc_host) cudaFreeHost(s.desc_host);
         s.desc_host = nullptr; s.desc_capacity = 0;
         if (s.out_dev) cudaFree(s.out_dev);
-        if (s.out_host) cudaFreeHost(s.out_host);
-        s.stage = nullptr; s.out_dev = nullptr; s.out_host = nullptr;
+        if (s.out_host && !s.out_host_external) cudaFreeHost(s.out_host);
+        s.stage = nullptr; s.out_dev = nullptr; s.out_host = nullptr; s.out_host_external = false;
     }
 }
 
@@ -65,22 +65,50 @@ void Detector::Allocate(int N, int H, int W) {
     OGLE_CHECK(pending_.empty()) << "the batch shape may only change with no call in flight";
     OGLE_RT_CUDA(cudaDeviceSynchronize());
     Release();
-    rows_ = options_.mode == 0 ? options_.topk : (num_classes_ - 1) * options_.topk;
-    counts_per_image_ = options_.mode == 0 ? 1 : num_classes_ - 1;
-    const size_t n = size_t(N) * rows_;
-    off_anchor_ = n * 4;
-    off_cls_ = off_anchor_ + n * 4;
-    off_box_ = (off_cls_ + n * 4 + 15) / 16 * 16;
-    off_count_ = off_box_ + n * 16;
-    out_bytes_ = off_count_ + size_t(N) * counts_per_image_ * 4;
+    const ResultLayout L = LayoutFor(options_.mode, num_classes_, options_.topk, N);
+    rows_ = L.rows;
+    counts_per_image_ = L.counts_per_image;
+    off_anchor_ = L.anchor; off_cls_ = L.cls; off_box_ = L.box; off_count_ = L.count;
+    out_bytes_ = L.total;
     OGLE_RT_CUDA(cudaMalloc(&boxes_, size_t(N) * num_anchors_ * 16));
-    for (Slot& s : slots_) {
+    for (int i = 0; i < kDepth; ++i) {
+        Slot& s = slots_[i];
         OGLE_RT_CUDA(cudaMalloc(&s.stage, stage_bytes));
         OGLE_RT_CUDA(cudaMalloc(&s.out_dev, out_bytes_));
-        OGLE_RT_CUDA(cudaMallocHost(&s.out_host, out_bytes_));
+        if (external_result_[i]) {
+            OGLE_CHECK_GE(external_result_bytes_, out_bytes_) << "result buffers given to UseResultBuffers are too small";
+            s.out_host = external_result_[i];
+            s.out_host_external = true;
+        } else {
+            OGLE_RT_CUDA(cudaMallocHost(&s.out_host, out_bytes_));
+        }
     }
     batch_ = N;
     stage_bytes_ = stage_bytes;
+}
+
+Detector::ResultLayout Detector::LayoutFor(int mode, int num_classes, int topk, int N) {
+    ResultLayout L;
+    L.rows = mode == 0 ? topk : (num_classes - 1) * topk;
+    L.counts_per_image = mode == 0 ? 1 : num_classes - 1;
+    const size_t n = size_t(N) * size_t(L.rows);
+    L.score = 0;
+    L.anchor = n * 4;
+    L.cls = L.anchor + n * 4;
+    L.box = (L.cls + n * 4 + 15) / 16 * 16;
+    L.count = L.box + n * 16;
+    L.total = L.count + size_t(N) * size_t(L.counts_per_image) * 4;
+    return L;
+}
+
+void Detector::UseResultBuffers(void* slot0, void* slot1, size_t bytes_each) {
+    OGLE_CHECK(batch_ == 0 && pending_.empty()) << "UseResultBuffers must come before the first Detect call";
+    OGLE_CHECK(slot0 && slot1 && slot0 != slot1 && bytes_each > 0);
+    OGLE_CHECK((reinterpret_cast<uintptr_t>(slot0) & 15) == 0 && (reinterpret_cast<uintptr_t>(slot1) & 15) == 0)
+        << "result buffers must be 16-byte aligned";
+    external_result_[0] = slot0;
+    external_result_[1] = slot1;
+    external_result_bytes_ = bytes_each;
 }
 
 void Detector::EnsureSession(int N, int H, int W, const float* images_nhwc) {
@@ -162,7 +190,9 @@ void Detector::DetectBGR8Async(const unsigned char* const* images, const int* he
                                                  in->device<float>(), H, W, mean_rgb, context_->stream()));
     OGLE_RT_CUDA(cudaEventRecord(E(slot.ev_pad), compute));
     session_->RunDevice({});
-    PostProcess(slot, N, H, W);
+    // the reference scales each frame's boxes by that frame's own size (detector.cc:102,179-180);
+    // the table at the head of the byte buffer holds them
+    PostProcess(slot, N, H, W, reinterpret_cast<const OgleImageDesc*>(slot.bytes));
     OGLE_RT_CUDA(cudaStreamWaitEvent(S(copy_out_), E(slot.ev_done), 0));
     OGLE_RT_CUDA(cudaMemcpyAsync(slot.out_host, slot.out_dev, out_bytes_, cudaMemcpyDeviceToHost, S(copy_out_)));
     OGLE_RT_CUDA(cudaEventRecord(E(slot.ev_d2h), S(copy_out_)));
@@ -188,7 +218,7 @@ void Detector::DetectAsync(const float* images_nhwc, int N, int H, int W) {
     OGLE_CUDA_OK(ogle_cuda_pad4(slot.stage, in->device<float>(), long(N) * H * W, 3, 0, context_->stream()));
     OGLE_RT_CUDA(cudaEventRecord(E(slot.ev_pad), compute));
     session_->RunDevice({});
-    PostProcess(slot, N, H, W);
+    PostProcess(slot, N, H, W, nullptr);      // preprocessed input: the frame is the network input
     // copy the detections back on their own stream
     OGLE_RT_CUDA(cudaStreamWaitEvent(S(copy_out_), E(slot.ev_done), 0));
     OGLE_RT_CUDA(cudaMemcpyAsync(slot.out_host, slot.out_dev, out_bytes_, cudaMemcpyDeviceToHost, S(copy_out_)));
@@ -207,7 +237,7 @@ void Detector::DetectDeviceAsync(const float* images_nhwc4_device, int N, int H,
     session_->RunDevice({{options_.input_names[0], images_nhwc4_device}});
     h2d_bytes_ = 0;
     Slot& slot = slots_[next_slot_];
-    PostProcess(slot, N, H, W);
+    PostProcess(slot, N, H, W, nullptr);
     d2h_bytes_ = 0;
     if (!copy_back) return;    // stream-ordered on the compute stream; nothing for Wait() to retire
     OGLE_RT_CUDA(cudaMemcpyAsync(slot.out_host, slot.out_dev, out_bytes_, cudaMemcpyDeviceToHost, S(context_->stream())));
@@ -217,7 +247,7 @@ void Detector::DetectDeviceAsync(const float* images_nhwc4_device, int N, int H,
     next_slot_ = (next_slot_ + 1) % kDepth;
 }
 
-void Detector::PostProcess(Slot& slot, int N, int H, int W) {
+void Detector::PostProcess(Slot& slot, int N, int H, int W, const OgleImageDesc* frames_device) {
     cudaStream_t compute = S(context_->stream());
     Tensor* cls_logits = session_->FindTensorByName(options_.output_names[0]);
     Tensor* box_preds = session_->FindTensorByName(options_.output_names[1]);
@@ -239,6 +269,7 @@ void Detector::PostProcess(Slot& slot, int N, int H, int W) {
     p.top_k = options_.topk;
     p.nms_thr = options_.nms_threshold;
     p.image_w = W; p.image_h = H;
+    p.frame_sizes = options_.mode == 0 ? frames_device : nullptr;
     // this slot's output buffer must have been copied out by its previous user
     OGLE_RT_CUDA(cudaStreamWaitEvent(compute, E(slot.ev_d2h), 0));
     char* d = static_cast<char*>(slot.out_dev);

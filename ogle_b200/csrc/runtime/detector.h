@@ -63,6 +63,17 @@ public:
     void DetectDeviceAsync(const float* images_nhwc4_device, int N, int H, int W, bool copy_back);
     // Retires the OLDEST call in flight: blocks until its detections are on the host.
     const DetectionBatch& Wait();
+    // Result memory of the caller's: the detections of the two pipeline slots are copied to
+    // slot0 / slot1 (pinned or CUDA-registered host memory of at least ResultBytes(N) each)
+    // instead of buffers the detector allocates - e.g. this process's part of a region that
+    // several per-GPU processes share, so that the process collecting a sharded batch reads
+    // every shard's detections in place. Call before the first Detect*; the memory must
+    // outlive the detector.
+    void UseResultBuffers(void* slot0, void* slot1, size_t bytes_each);
+    // Byte layout of one call's result block for N images: offsets of score, anchor, class,
+    // box and count, and the total (what Wait() hands out as DetectionBatch views).
+    struct ResultLayout { size_t score, anchor, cls, box, count, total; int rows, counts_per_image; };
+    static ResultLayout LayoutFor(int mode, int num_classes, int topk, int N);
     int in_flight() const { return int(pending_.size()); }
     static constexpr int kDepth = 2;
 
@@ -82,6 +93,7 @@ private:
         size_t desc_capacity = 0;    // entries
         void* out_dev = nullptr;     // score | anchor | cls | box | count, contiguous
         void* out_host = nullptr;    // pinned mirror
+        bool out_host_external = false;   // the caller's memory (UseResultBuffers): not freed here
         void* ev_h2d = nullptr;      // upload landed (copy-in stream)
         void* ev_pad = nullptr;      // staging buffer consumed (compute stream)
         void* ev_done = nullptr;     // post-process finished (compute stream)
@@ -90,7 +102,7 @@ private:
     void EnsureSession(int N, int H, int W, const float* images_nhwc);
     void Allocate(int N, int H, int W);
     void Release();
-    void PostProcess(Slot& slot, int N, int H, int W);
+    void PostProcess(Slot& slot, int N, int H, int W, const OgleImageDesc* frames_device);
     DetectorOptions options_;
     Context* context_;
     std::unique_ptr<FBOSession> session_;
@@ -104,6 +116,8 @@ private:
     size_t out_bytes_ = 0, off_anchor_ = 0, off_cls_ = 0, off_box_ = 0, off_count_ = 0;
     size_t h2d_bytes_ = 0, d2h_bytes_ = 0, stage_bytes_ = 0;
     DetectionBatch result_;
+    void* external_result_[kDepth] = {nullptr, nullptr};
+    size_t external_result_bytes_ = 0;
 };
 
 }  // namespace ogle

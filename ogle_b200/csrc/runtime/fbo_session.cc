@@ -18,6 +18,7 @@ FBOSession::FBOSession(Context* context) : context_(context) {
     if (const char* g = std::getenv("OGLE_USE_GRAPH")) use_graph_ = std::atoi(g) != 0;
     if (const char* g = std::getenv("OGLE_FUSE_SIBLINGS")) fuse_siblings_ = std::atoi(g) != 0;
     if (const char* g = std::getenv("OGLE_FUSE_ACTIVATIONS")) fuse_activations_ = std::atoi(g) != 0;
+    if (const char* g = std::getenv("OGLE_FUSE_CONCATS")) fuse_concats_ = std::atoi(g) != 0;
     if (const char* g = std::getenv("OGLE_STREAMS")) set_streams(std::atoi(g));
 }
 
@@ -153,7 +154,10 @@ void FBOSession::Finalize() {
     }
     if (fuse_siblings_) FuseSiblings();
     elided_.assign(total_tensors_.size(), false);
+    elided_why_.assign(total_tensors_.size(), std::string());
     if (fuse_activations_) FuseActivations();
+    num_placed_ = 0;
+    if (fuse_concats_) FuseConcats();
     context_->Synchronize();
     finalized_ = true;
 }
@@ -195,7 +199,66 @@ void FBOSession::FuseActivations() {
         producer->absorbed_.push_back(only);
         active_.erase(active_.begin() + long(j));
         elided_[size_t(out_id)] = true;
+        elided_why_[size_t(out_id)] = "its only reader, an activation, runs in the producer's pass (session option "
+                                      "fuse_activations = 0 or OGLE_FUSE_ACTIVATIONS=0 keeps it)";
         ++num_fused_;
+    }
+}
+
+void FBOSession::FuseConcats() {
+    // Readers of a tensor: every node that lists it as an input, pre-computed ones and aliases included.
+    auto readers = [&](int id) {
+        int n = 0;
+        for (const auto& k : kernels_)
+            for (int in : k->input_tensor_indexes_) n += in == id;
+        return n;
+    };
+    // The node of the steady-state sequence that writes the memory behind tensor `id`: its producer, or
+    // for an alias (identity transpose, same-bytes reshape) the producer of what it aliases, as long as
+    // every tensor on the way has one reader.
+    auto writer_of = [&](int id, std::vector<int>* chain) -> Kernel* {
+        for (int hops = 0; hops < 8; ++hops) {
+            if (readers(id) != 1 || elided_[size_t(id)]) return nullptr;
+            chain->push_back(id);
+            Kernel* producer = nullptr;
+            for (const auto& k : kernels_)
+                if (!k->output_tensor_indexes_.empty() && k->output_tensor_indexes_[0] == id) producer = k.get();
+            if (!producer || producer->output_tensors_.size() != 1) return nullptr;
+            if (!producer->IsNoOp()) {
+                for (Kernel* a : active_)
+                    if (a == producer) return producer;
+                return nullptr;                       // pre-computed, or absorbed by a sibling
+            }
+            if (producer->input_tensor_indexes_.empty()) return nullptr;
+            id = producer->input_tensor_indexes_[0];
+        }
+        return nullptr;
+    };
+    for (size_t c = 0; c < active_.size();) {
+        Kernel* cat = active_[c];
+        long outer, chunk, stride, offset;
+        if (cat->output_tensors_.size() != 1 || !cat->ConcatPlacement(0, &outer, &chunk, &stride, &offset)) { ++c; continue; }
+        size_t placed = 0;
+        const size_t n_in = cat->input_tensor_indexes_.size();
+        for (size_t i = 0; i < n_in; ++i) {
+            if (!cat->ConcatPlacement(int(i), &outer, &chunk, &stride, &offset)) continue;
+            std::vector<int> chain;
+            Kernel* w = writer_of(cat->input_tensor_indexes_[i], &chain);
+            if (!w || w == cat) continue;
+            // the writer must come before the concat in the sequence (file order guarantees it)
+            if (!w->PlaceOutput(cat->output_tensors_[0], outer, chunk, stride, offset)) continue;
+            w->extra_writes_.push_back(cat->output_tensors_[0]);
+            cat->InputPlaced(int(i));
+            for (int id : chain) {
+                elided_[size_t(id)] = true;
+                elided_why_[size_t(id)] = "its producer writes straight into the Concat that reads it (session option "
+                                          "fuse_concats = 0 or OGLE_FUSE_CONCATS=0 keeps it)";
+            }
+            ++placed;
+            ++num_placed_;
+        }
+        if (placed == n_in) active_.erase(active_.begin() + long(c));     // nothing left to copy
+        else ++c;
     }
 }
 
@@ -260,6 +323,7 @@ void FBOSession::PlanStreams() {
         for (Kernel* k : parts) {
             for (const Tensor* t : k->input_tensors_) add(nodes[i].reads, t);
             for (const Tensor* t : k->output_tensors_) add(nodes[i].writes, t);
+            for (const Tensor* t : k->extra_writes_) add(nodes[i].writes, t);
         }
     }
     StreamPlan plan = PlanStreamsFor(nodes, streams_);
@@ -364,8 +428,7 @@ void FBOSession::GetOutputs(const TensorNameList& output_names, const StringList
         OGLE_CHECK(gpu_tensor != nullptr) << "tensor " << output_names[i] << " was never produced";
         const int id = tensor_name_index_[output_names[i]];
         OGLE_CHECK(!(id < int(elided_.size()) && elided_[size_t(id)]))
-            << "tensor " << output_names[i] << " is not materialised: its only reader, an activation, runs in the "
-            << "producer's pass (session option fuse_activations = 0 or OGLE_FUSE_ACTIVATIONS=0 keeps it)";
+            << "tensor " << output_names[i] << " is not materialised: " << elided_why_[size_t(id)];
         const DataFormat dformat = StrToFormat(output_dformats[i]);
         if (outputs->at(i) == nullptr)
             outputs->at(i) = new Tensor(Tensor::DT_FLOAT, gpu_tensor->shape(), Tensor::HOST_MEMORY, dformat);

@@ -67,6 +67,14 @@ public:
     // produced; GetOutputs on it fails with a message naming this switch (default on;
     // OGLE_FUSE_ACTIVATIONS=0 disables). Set before the first Run.
     void set_fuse_activations(bool flag) { fuse_activations_ = flag; }
+    // Concat in place: a Conv (channel axis) or a re-padding Reshape (any other axis) whose result
+    // only a Concat reads writes straight into its slice of the Concat's tensor, and a Concat
+    // whose slices are all written that way is dropped from the sequence, where the reference
+    // draws one full-output pass per input (nn/kernels/concat.cc:73-96). The producers' own
+    // tensors are then not produced; GetOutputs on them fails with a message naming this
+    // switch (default on; OGLE_FUSE_CONCATS=0 disables). Set before the first Run.
+    void set_fuse_concats(bool flag) { fuse_concats_ = flag; }
+    int num_placed() const { return num_placed_; }
     // Branch overlap: the captured graph keeps only the true data dependencies between
     // nodes, recorded over up to `n` streams, so that independent branches (the SSD heads
     // of one feature map against the layers that continue from it) may run side by side
@@ -92,6 +100,7 @@ private:
     void Finalize();
     void FuseSiblings();
     void FuseActivations();
+    void FuseConcats();
     void Execute();
     void DropGraph();
     void PlanStreams();
@@ -111,7 +120,10 @@ private:
     bool use_graph_ = true;
     bool fuse_siblings_ = true;
     bool fuse_activations_ = true;
-    std::vector<bool> elided_;                // tensors no node produces any more (activation fusion)
+    bool fuse_concats_ = true;
+    int num_placed_ = 0;
+    std::vector<bool> elided_;                // tensors no node produces any more (activation / concat fusion)
+    std::vector<std::string> elided_why_;     // per tensor: the switch that keeps it
     int num_fused_ = 0;
     int eager_runs_ = 0;
     int streams_ = 4;

@@ -5,9 +5,15 @@
 #include <sys/syscall.h>
 #include <unistd.h>
 
+#include <fcntl.h>
 #include <sys/mman.h>
+#include <sys/stat.h>
+
+#include <cerrno>
+#include <sstream>
 
 #include <cctype>
+#include <cstdio>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -95,7 +101,7 @@ HostPlacement BindHostToDevice(int device) {
 }
 
 namespace {
-struct Mapping { void* base; size_t length; };
+struct Mapping { void* base; size_t length; bool pinned = true; std::string shared_name; };
 std::mutex g_pinned_mutex;
 std::map<void*, Mapping> g_pinned;
 }  // namespace
@@ -117,17 +123,106 @@ void* AllocPinnedHost(size_t bytes) {
         return nullptr;
     }
     std::lock_guard<std::mutex> lock(g_pinned_mutex);
-    g_pinned[p] = Mapping{base, length};
+    Mapping m;
+    m.base = base; m.length = length;
+    g_pinned[p] = m;
     return p;
+}
+
+size_t HugePageBytes(const void* p) {
+    // /proc/self/smaps: a header line "lo-hi perms ..." per mapping, then "Key:   value kB" lines
+    std::ifstream f("/proc/self/smaps");
+    if (!f) return 0;
+    const uintptr_t addr = reinterpret_cast<uintptr_t>(p);
+    std::string line;
+    bool inside = false;
+    size_t kb = 0;
+    while (std::getline(f, line)) {
+        unsigned long lo = 0, hi = 0;
+        if (std::sscanf(line.c_str(), "%lx-%lx ", &lo, &hi) == 2 && line.find(':') > line.find(' ')) {
+            if (inside) break;
+            inside = addr >= lo && addr < hi;
+            continue;
+        }
+        if (!inside) continue;
+        unsigned long v = 0;
+        if (std::sscanf(line.c_str(), "AnonHugePages: %lu kB", &v) == 1) kb += v;
+        else if (std::sscanf(line.c_str(), "ShmemPmdMapped: %lu kB", &v) == 1) kb += v;
+    }
+    return kb * 1024;
+}
+
+void* OpenSharedHost(const std::string& name, size_t bytes, bool create, bool pin, std::string* error) {
+    auto fail = [&](const std::string& what) -> void* {
+        if (error) *error = what + ": " + std::strerror(errno);
+        return nullptr;
+    };
+    if (bytes == 0 || name.empty() || name[0] != '/') {
+        if (error) *error = "shared region needs a name that starts with '/' and a size";
+        return nullptr;
+    }
+    const int fd = create ? shm_open(name.c_str(), O_CREAT | O_RDWR | O_TRUNC, 0600) : shm_open(name.c_str(), O_RDWR, 0600);
+    if (fd < 0) return fail("shm_open(" + name + ")");
+    if (create) {
+        if (ftruncate(fd, off_t(bytes)) != 0) { close(fd); return fail("ftruncate"); }
+    } else {
+        struct stat st;
+        if (fstat(fd, &st) != 0 || size_t(st.st_size) < bytes) {
+            close(fd);
+            if (error) *error = "shared region " + name + " is smaller than the size asked for";
+            return nullptr;
+        }
+    }
+    void* p = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+    close(fd);
+    if (p == MAP_FAILED) return fail("mmap");
+#ifdef MADV_HUGEPAGE
+    madvise(p, bytes, MADV_HUGEPAGE);                                   // best effort (shmem huge pages)
+#endif
+    if (create) std::memset(p, 0, bytes);                               // the pages exist before they are pinned
+    if (pin) {
+        // every process touches its own page tables before the registration walks them
+        volatile const char* q = static_cast<const char*>(p);
+        char sink = 0;
+        for (size_t i = 0; i < bytes; i += 4096) sink ^= q[i];
+        (void)sink;
+        const cudaError_t e = cudaHostRegister(p, bytes, cudaHostRegisterPortable);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            munmap(p, bytes);
+            if (error) *error = std::string("cudaHostRegister: ") + cudaGetErrorString(e);
+            return nullptr;
+        }
+    }
+    std::lock_guard<std::mutex> lock(g_pinned_mutex);
+    Mapping m;
+    m.base = p; m.length = bytes; m.pinned = pin; m.shared_name = name;
+    g_pinned[p] = m;
+    return p;
+}
+
+void CloseSharedHost(void* p, bool unlink) {
+    if (!p) return;
+    Mapping m;
+    {
+        std::lock_guard<std::mutex> lock(g_pinned_mutex);
+        auto it = g_pinned.find(p);
+        if (it == g_pinned.end() || it->second.shared_name.empty()) return;
+        m = it->second;
+        g_pinned.erase(it);
+    }
+    if (m.pinned) cudaHostUnregister(p);
+    munmap(m.base, m.length);
+    if (unlink) shm_unlink(m.shared_name.c_str());
 }
 
 void FreePinnedHost(void* p) {
     if (!p) return;
-    Mapping m{nullptr, 0};
+    Mapping m;
     {
         std::lock_guard<std::mutex> lock(g_pinned_mutex);
         auto it = g_pinned.find(p);
-        if (it == g_pinned.end()) return;
+        if (it == g_pinned.end() || !it->second.shared_name.empty()) return;
         m = it->second;
         g_pinned.erase(it);
     }

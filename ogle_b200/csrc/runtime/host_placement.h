@@ -29,11 +29,27 @@ HostPlacement BindHostToDevice(int device);
 
 // Pinned host memory for upload buffers: anonymous memory advised to use 2 MB pages
 // (transparent huge pages, where the host grants them), touched, then registered with CUDA.
-// Uploads from it need far fewer IOMMU translations than from 4 KB pages: with four GPUs
-// uploading at once on one host, 122 k instead of 93 k images/s end to end. Returns nullptr
-// when the mapping or the registration fails. Free with FreePinnedHost only.
+// Uploads from it need fewer IOMMU translations than from 4 KB pages. Whether the host
+// granted 2 MB pages is reported by HugePageBytes. Returns nullptr when the mapping or the
+// registration fails. Free with FreePinnedHost only.
 void* AllocPinnedHost(size_t bytes);
 void FreePinnedHost(void* p);
+// Bytes of the mapping that holds `p` which the kernel backs with 2 MB pages right now
+// (AnonHugePages + ShmemPmdMapped of its /proc/self/smaps entry); 0 when none or unknown.
+size_t HugePageBytes(const void* p);
+
+// A named region of host memory shared by the processes of one box (POSIX shared memory),
+// for one-process-per-GPU serving of ONE batch: the process that owns the batch writes the
+// images once, every process uploads its own images straight from the region, and every
+// process's detections are copied from its GPU straight into the region, where the owner
+// reads them - no copy between processes, no collective. `create` makes (or truncates) the
+// object and zero-fills it, otherwise an existing one of at least `bytes` is mapped. With
+// `pin` the mapping is registered with CUDA in the calling process (its device context must
+// be current), which makes copies from and to it asynchronous. Returns nullptr on failure
+// (the reason in *error when given). Close with CloseSharedHost; `unlink` removes the name
+// (the creator does that once every process has opened it or at shutdown).
+void* OpenSharedHost(const std::string& name, size_t bytes, bool create, bool pin, std::string* error = nullptr);
+void CloseSharedHost(void* p, bool unlink);
 
 }  // namespace ogle
 

@@ -55,6 +55,17 @@ public:
     virtual bool AbsorbConsumer(Kernel* consumer) { return false; }
     // For AbsorbConsumer implementations: the activation a node applies, if it is one.
     virtual bool AsActivation(int* act, float* lo, float* hi) const { return false; }
+    // Concat in place. A concat-like node describes where its input i lies inside its output:
+    // the input is `outer` rows of `chunk` floats, and row r belongs at
+    // output + r * row_stride + offset (floats, padded layouts on both sides). False when the
+    // node is no concat or the slice cannot be described that way.
+    virtual bool ConcatPlacement(int input, long* outer, long* chunk, long* row_stride, long* offset) const { return false; }
+    // Told that input i is written in place by its producer: Compute leaves that slice alone.
+    virtual void InputPlaced(int input) {}
+    // Offered to the producer of a tensor whose only reader is a concat: write the result into
+    // `dst` with the geometry above instead of into this node's own output tensor (which is
+    // then never written). Return true to accept.
+    virtual bool PlaceOutput(Tensor* dst, long outer, long chunk, long row_stride, long offset) { return false; }
 
 protected:
     // another node's output tensors, for AbsorbSibling / AbsorbConsumer implementations
@@ -67,6 +78,7 @@ protected:
     std::vector<int> output_tensor_indexes_;
     std::vector<DataFormat> output_tensor_dformats_;
     std::vector<Kernel*> absorbed_;         // later nodes whose work this kernel took over (AbsorbSibling)
+    std::vector<Tensor*> extra_writes_;     // tensors of other nodes this kernel writes into (PlaceOutput); not owned
     friend class FBOSession;
     std::string kernel_name_;
     std::string kernel_type_;

@@ -202,6 +202,25 @@ public:
         return true;
     }
 
+    // Channel-axis concat in place: the pixels of this conv are the rows, its channels the chunk
+    // (the out_channel_offset / out_channel_stride fields of the conv call; replaces one
+    // copy pass of concat.cc:73-96).
+    bool PlaceOutput(Tensor* dst, long outer, long chunk, long row_stride, long offset) override {
+        if (sibling_ || placed_ || output_tensors_.empty()) return false;
+        const long pixels = long(params_.N) * params_.out_hwc[0] * params_.out_hwc[1];
+        if (outer != pixels || chunk != UpRound4(params_.out_hwc[2]) || (row_stride & 3) || (offset & 3)) return false;
+        if (offset + chunk > row_stride || params_.out_channel_stride || params_.out_channel_offset) return false;
+        OgleConvParams q = params_;
+        q.out_channel_stride = int(row_stride);
+        q.out_channel_offset = int(offset);
+        if (ogle_cuda_conv2d_infer(&q) != OGLE_OK) return false;
+        params_ = q;
+        placed_ = dst;
+        const size_t colon = kernel_fname_.find(':');
+        kernel_fname_ = kernel_fname_.substr(0, colon) + ":" + ogle_cuda_conv2d_kernel_name(&params_);
+        return true;
+    }
+
     void Compute(TensorList& inputs, TensorList& outputs) override {
         if (sibling_) {
             OGLE_CUDA_OK(ogle_cuda_conv2d_pair(&pair_params_, inputs[0]->device<float>(), pair_packed_, pair_bias_, pair_k1_,
@@ -212,8 +231,8 @@ public:
         if (!filter_is_constant_)
             OGLE_CUDA_OK(ogle_cuda_conv2d_prepack(&params_, inputs[1]->device<float>(), packed_, context_->stream()));
         const float* bias = inputs.size() > 2 ? inputs[2]->device<float>() : nullptr;
-        OGLE_CUDA_OK(ogle_cuda_conv2d(&params_, inputs[0]->device<float>(), packed_, bias, outputs[0]->device<float>(),
-                                      context_->stream()));
+        float* y = placed_ ? placed_->device<float>() : outputs[0]->device<float>();
+        OGLE_CUDA_OK(ogle_cuda_conv2d(&params_, inputs[0]->device<float>(), packed_, bias, y, context_->stream()));
     }
 
 private:
@@ -224,6 +243,7 @@ private:
     void* packed_ = nullptr;
     bool filter_is_constant_ = false;
     Conv2DKernel* sibling_ = nullptr;       // absorbed later node (not owned)
+    Tensor* placed_ = nullptr;              // a concat's tensor this conv writes into (not owned)
     OgleConvParams pair_params_;
     void* pair_packed_ = nullptr;
     float* pair_bias_ = nullptr;
@@ -516,11 +536,34 @@ public:
     }
     void Compute(TensorList& in, TensorList& out) override {
         const float* ptrs[OGLE_MAX_CONCAT_INPUTS];
-        for (size_t i = 0; i < in.size(); ++i) ptrs[i] = in[i]->device<float>();
+        for (size_t i = 0; i < in.size(); ++i) ptrs[i] = (placed_mask_ >> i) & 1u ? nullptr : in[i]->device<float>();
         OGLE_CUDA_OK(ogle_cuda_concat(&params_, ptrs, out[0]->device<float>(), context_->stream()));
     }
+    bool ConcatPlacement(int input, long* outer, long* chunk, long* row_stride, long* offset) const override {
+        const int n = params_.n_inputs, a = params_.axis;
+        if (input < 0 || input >= n) return false;
+        long before = 1, inner = 1, start = 0, total = 0;
+        for (int d = 0; d < a; ++d) before *= params_.in_shapes[0][d];
+        for (int d = a + 1; d < 4; ++d) inner *= d == 3 ? UpRound4(params_.in_shapes[0][3]) : params_.in_shapes[0][d];
+        for (int i = 0; i < n; ++i) {
+            if (i == input) start = total;
+            total += params_.in_shapes[i][a];
+        }
+        const long extent = params_.in_shapes[input][a];
+        if (a == 3) {
+            // slices start on a multiple of four channels; only the last may end off one
+            if ((start & 3) || ((extent & 3) && input + 1 < n)) return false;
+            *chunk = UpRound4(int(extent)); *row_stride = UpRound4(int(total)); *offset = start;
+        } else {
+            *chunk = extent * inner; *row_stride = total * inner; *offset = start * inner;
+        }
+        *outer = before;
+        return true;
+    }
+    void InputPlaced(int input) override { placed_mask_ |= 1u << input; }
 private:
     int axis_ = 0;
+    unsigned placed_mask_ = 0;
     OgleConcatParams params_;
 };
 REGISTER_KERNEL_WITH_NAME(ConcatKernel, "Concat");
@@ -623,13 +666,31 @@ public:
     bool IsNoOp() const override { return alias_; }
     void Compute(TensorList& in, TensorList& out) override {
         if (alias_) return;
+        if (placed_) {
+            OGLE_CUDA_OK(ogle_cuda_reshape_placed(in[0]->device<float>(), placed_->device<float>() + place_offset_, n_, in_last_,
+                                                  out_last_, rows_per_block_, block_stride_, context_->stream()));
+            return;
+        }
         OGLE_CUDA_OK(ogle_cuda_reshape(in[0]->device<float>(), out[0]->device<float>(), n_, in_last_, out_last_,
                                        context_->stream()));
+    }
+    // The re-padding copy writes its rows where the concat wants them (the SSD class heads:
+    // [N, h*w*a, C] slices of [N, anchors, C]).
+    bool PlaceOutput(Tensor* dst, long outer, long chunk, long row_stride, long offset) override {
+        if (alias_ || placed_) return false;
+        const long row = UpRound4(out_last_);
+        const long rows = n_ / out_last_;
+        if (chunk % row || outer <= 0 || rows % outer || rows / outer != chunk / row || (row_stride & 3) || (offset & 3))
+            return false;
+        placed_ = dst; place_offset_ = offset; rows_per_block_ = chunk / row; block_stride_ = row_stride;
+        return true;
     }
 private:
     long n_ = 0;
     int in_last_ = 1, out_last_ = 1;
     bool alias_ = false;
+    Tensor* placed_ = nullptr;          // a concat's tensor this copy writes into (not owned)
+    long place_offset_ = 0, rows_per_block_ = 0, block_stride_ = 0;
 };
 REGISTER_KERNEL_WITH_NAME(ReshapeKernel, "Reshape");
 

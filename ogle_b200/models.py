@@ -111,13 +111,17 @@ MOBILENET_V1 = [  # (out_channels, stride) of the 13 depthwise-separable blocks
 SSD_EXTRAS = [(256, 512), (128, 256), (128, 256), (64, 128)]   # (1x1 width, 3x3-s2 width)
 
 
-def mobilenet_v1_ssd(batch=1, num_classes=2, image_size=300, seed=0, weight_std=0.02):
+def mobilenet_v1_ssd(batch=1, num_classes=2, image_size=300, seed=0, weight_std=0.02, exported_shape_ops=False):
     """MobileNet-v1-SSD 300x300: stem 3x3 s2 32ch; 13 depthwise-separable blocks
     (depthwise 3x3 + 1x1 pointwise, BN+ReLU folded) up to 1024ch at 10x10; 4 extra
     1x1 / 3x3-s2 blocks giving 5x5, 3x3, 2x2, 1x1 maps; 3x3 loc/conf heads with
     3/6/6/6/6/6 anchors on the six maps (1917 anchors). Outputs "box_preds"
     [N,1917,4], "cls_logits" [N,1917,C] and the constant "anchors" [1917,4].
-    Returns (dlx.Model, info dict)."""
+    exported_shape_ops: build every head's Reshape target the way an ONNX export of
+    `y.view(y.size(0), -1, width)` does - Shape -> Gather(index 0) -> Unsqueeze(axes [0]) ->
+    Concat with the constants [-1] and [width] - instead of one constant
+    (converter/converter/onnx/ops/shape.cc, gather.cc, unsqueeze.cc emit those nodes as they are).
+    Same weights either way. Returns (dlx.Model, info dict)."""
     b = _Builder(seed, weight_std)
     s = b.s
     x = s.add_input("input", [batch, 3, image_size, image_size])
@@ -143,7 +147,15 @@ def mobilenet_v1_ssd(batch=1, num_classes=2, image_size=300, seed=0, weight_std=
         for width, bucket in ((4, locs), (num_classes, confs)):
             y, _ = b.conv(src, c, a * width, 3, 1, 1, bn=False, act="", bias=True, hw=fhw)
             t = s.add_node(b.name(), "Transpose", [y], {"transpose_attr": {"perm": [0, 2, 3, 1]}})
-            shape = s.add_const(b.name(), np.array([batch, -1, width], np.float32), dlx.ANY, dlx.ANY4)
+            if exported_shape_ops:
+                dims = s.add_node(b.name(), "Shape", [y], {"shape_attr": {}})
+                index = s.add_const(b.name(), np.array(0, np.float32), dlx.ANY, dlx.ANY4)      # scalar: x.size(0)
+                n = s.add_node(b.name(), "Gather", [dims, index], {"gather_attr": {"axis": 0}})
+                n = s.add_node(b.name(), "Unsqueeze", [n], {"unsqueeze_attr": {"axes": [0]}})
+                rest = [s.add_const(b.name(), np.array([v], np.float32), dlx.ANY, dlx.ANY4) for v in (-1, width)]
+                shape = s.add_node(b.name(), "Concat", [n] + rest, {"concat_attr": {"axis": 0}})
+            else:
+                shape = s.add_const(b.name(), np.array([batch, -1, width], np.float32), dlx.ANY, dlx.ANY4)
             bucket.append(s.add_node(b.name(), "Reshape", [t, shape], {"reshape_attr": {}}))
     s.add_node("box_preds", "Concat", locs, {"concat_attr": {"axis": 1}})
     s.add_node("cls_logits", "Concat", confs, {"concat_attr": {"axis": 1}})
@@ -187,6 +199,50 @@ def resnet18(batch=1, num_classes=1000, image_size=224, seed=0, weight_std=0.02)
     s.add_node("logits", "Gemm", [x, w, bias], {"gemm_attr": {"alpha": 1.0, "beta": 1.0, "transB": 1}})
     s.add_output_name("logits")
     return s.model, dict(flops_per_image=b.flops, conv_nodes=b.conv_nodes, batch=batch, image_size=image_size)
+
+
+def box_decoder_graph(map_h, map_w, seed=0):
+    """The Decoder operator as a graph node (nn/kernels/decoder.cc:12-92): an input of box deltas
+    [1, 4, map_h, map_w] (stored NHWC), reshaped to [1, map_h*map_w, 4], decoded against a constant
+    anchor tensor [1, map_h, map_w, 4] (cx, cy, w, h) with the kernel's fixed variances. Output "boxes".
+    Returns (dlx.Model, anchors array [map_h*map_w, 4])."""
+    s = dlx.Scope()
+    rng = np.random.default_rng(seed)
+    anchors = np.concatenate([rng.random((map_h * map_w, 2), dtype=np.float32),
+                              rng.random((map_h * map_w, 2), dtype=np.float32) * np.float32(0.4) + np.float32(0.05)], axis=1)
+    x = s.add_input("input", [1, 4, map_h, map_w])
+    shape = s.add_const("deltas.shape", np.array([1, -1, 4], np.float32), dlx.ANY, dlx.ANY4)
+    pred = s.add_node("deltas", "Reshape", [x, shape], {"reshape_attr": {}})
+    a = s.add_const("anchors", anchors.reshape(1, map_h, map_w, 4), dlx.ANY, dlx.ANY4)
+    s.add_node("boxes", "Decoder", [pred, a], {})
+    s.add_output_name("boxes")
+    return s.model, anchors
+
+
+def concat_of_convs(x_shape, widths, seed=0, kernel=1, consumer=True):
+    """input -> len(widths) convolutions of the same window -> Concat on the channel axis (ONNX axis 1)
+    [-> 1x1 conv "output"]: the graph shape where producers can write a concat in place. Output "cat"
+    (and "output"). Returns dlx.Model."""
+    s = dlx.Scope()
+    rng = np.random.default_rng(seed)
+    N, H, W, C = x_shape
+    x = s.add_input("input", [N, C, H, W])
+    parts = []
+    for i, k_out in enumerate(widths):
+        w = (rng.standard_normal((k_out, C, kernel, kernel), dtype=np.float32) * np.float32(0.2)).astype(np.float32)
+        b = rng.standard_normal(k_out, dtype=np.float32)
+        wid = s.add_const(f"branch{i}.weight", w, dlx.ANY, dlx.HWN4C4)
+        bid = s.add_const(f"branch{i}.bias", b, dlx.ANY, dlx.ANY4)
+        parts.append(s.add_conv(f"branch{i}", x, wid, bid, kernel, 1, kernel // 2, 1, 1, "Relu" if i % 2 == 0 else "", 0.0, 0.0))
+    cat = s.add_node("cat", "Concat", parts, {"concat_attr": {"axis": 1}})
+    s.add_output_name("cat")
+    if consumer:
+        total = sum(widths)
+        w = (rng.standard_normal((8, total, 1, 1), dtype=np.float32) * np.float32(0.1)).astype(np.float32)
+        wid = s.add_const("output.weight", w, dlx.ANY, dlx.HWN4C4)
+        s.add_conv("output", cat, wid, None, 1, 1, 0, 1, 1, "", 0.0, 0.0)
+        s.add_output_name("output")
+    return s.model
 
 
 def single_conv(x_shape, w, bias=None, stride=1, pad=0, dilation=1, group=1, activation="", min_=0.0, max_=0.0):

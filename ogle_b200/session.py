@@ -31,6 +31,7 @@ RT_SYMBOLS = {
     "ogle_session_tensor_info": (C.c_int, [_vp, _cp, _ip, _ip, _ip, C.POINTER(_vp)]),
     "ogle_session_get_output": (C.c_int, [_vp, _cp, _cp, _vp, C.c_size_t]),
     "ogle_session_num_active_kernels": (C.c_int, [_vp]),
+    "ogle_session_num_placed": (C.c_int, [_vp]),
     "ogle_session_num_branches": (C.c_int, [_vp]),
     "ogle_session_graph_captured": (C.c_int, [_vp]),
     "ogle_session_device_bytes": (C.c_size_t, [_vp]),
@@ -48,6 +49,11 @@ RT_SYMBOLS = {
                                        _ip, C.POINTER(C.c_ubyte)]),
     "ogle_host_alloc_pinned": (_vp, [C.c_size_t]),
     "ogle_host_free_pinned": (None, [_vp]),
+    "ogle_host_huge_page_bytes": (C.c_size_t, [_vp]),
+    "ogle_host_shared_open": (_vp, [_cp, C.c_size_t, C.c_int, C.c_int]),
+    "ogle_host_shared_close": (None, [_vp, C.c_int]),
+    "ogle_detector_use_result_buffers": (C.c_int, [_vp, _vp, _vp, C.c_size_t]),
+    "ogle_detector_result_layout": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_size_t), _ip, _ip]),
     "ogle_host_bind_to_device": (C.c_int, [C.c_int, _ip, _ip, _ip]),
     "ogle_host_parse_cpulist": (C.c_int, [_cp, _ip, C.c_int]),
 }
@@ -234,6 +240,10 @@ class FBOSession:
 
     def num_active_kernels(self):
         return self._lib.ogle_session_num_active_kernels(self._h)
+
+    def num_placed(self):
+        """Concat inputs written in place by their producers (option "fuse_concats")."""
+        return self._lib.ogle_session_num_placed(self._h)
 
     def num_branches(self):
         return self._lib.ogle_session_num_branches(self._h)

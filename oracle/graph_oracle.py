@@ -74,6 +74,25 @@ def run_graph(model, inputs, lib, stop_after=None, keep=None):
                 axis = {0: 0, 1: 3, 2: 1, 3: 2}[axis]
             out = lib.concat(ins, axis)
             out_fmt = "plain"
+        elif t == "Shape":
+            # nn/kernels/shape.cc:32-47: the stored dims (NHWC order for image tensors), as floats
+            out = np.asarray(ins[0].shape, dtype=np.float32)
+            out_fmt = "plain"
+        elif t == "Gather":
+            # nn/glsl/gather.glsl:7-18: a scalar index into the first texel of a shape tensor, the ONNX
+            # (NCHW) index mapped onto the stored order: 0 -> x, 1 -> w, 2 -> y, anything else -> z
+            sel = int(np.asarray(ins[1]).reshape(-1)[0])
+            lane = {0: 0, 1: 3, 2: 1}.get(sel, 2)
+            data = np.asarray(ins[0], dtype=np.float32).reshape(-1)
+            out = np.full(np.asarray(ins[1]).shape, data[lane] if lane < data.size else 0.0, np.float32)
+            out_fmt = "plain"
+        elif t == "Unsqueeze":
+            out = np.expand_dims(ins[0], int(a["unsqueeze_attr"]["axes"][0]))
+            out_fmt = "plain"
+        elif t == "Decoder":
+            # nn/kernels/decoder.cc:12-92: prediction [1,A,4], anchors [1,h,w,4] with h*w == A
+            out = lib.decode(ins[0], np.ascontiguousarray(ins[1]).reshape(-1, 4))
+            out_fmt = "plain"
         else:
             raise NotImplementedError(t)
         vals[node.output_index[0]] = out

@@ -500,6 +500,81 @@ def test_detect_reference_rule(oracle_port):
         assert (anchor[n, k:] == -1).all()
 
 
+def test_reshape_placed_and_concat_with_slices_in_place():
+    """The two halves of a row-axis concat written in place: the re-padding copy puts its rows at its image's
+    slice of the wider tensor (ogle_cuda_reshape_placed), and the concat pass leaves a slice alone whose input
+    pointer is null. Together they equal the plain reshape followed by the full concat, bit for bit."""
+    import ctypes as C
+    import torch
+    from ogle_b200 import _lib, ops
+    lib = _lib.cuda_lib()
+    rng = np.random.default_rng(54)
+    N = 3
+    a = rng.standard_normal((N, 5, 5, 63)).astype(np.float32)       # -> [N, 75, 21]
+    b = rng.standard_normal((N, 2, 2, 126)).astype(np.float32)      # -> [N, 24, 21]
+    a4, b4 = ops.upload(a), ops.upload(b)
+    ra = ops.reshape(a4, a.shape, (N, 75, 21))
+    rb = ops.reshape(b4, b.shape, (N, 24, 21))
+    want, shape = ops.concat([ra, rb], [(N, 75, 21), (N, 24, 21)], 1)
+    assert tuple(shape) == (N, 99, 21)
+    out = torch.full((N, 99, 24), float("nan"), dtype=torch.float32, device="cuda")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    # slice a written in place (75 rows per image, image stride 99 * 24 floats); slice b through the concat pass
+    rc = lib.ogle_cuda_reshape_placed(C.c_void_p(a4.data_ptr()), C.c_void_p(out.data_ptr()), a.size, 63, 21, 75, 99 * 24, stream)
+    assert rc == 0
+    p = ops.ConcatParams()
+    p.n_inputs, p.axis = 2, 2
+    for i, sh in enumerate([(1, N, 75, 21), (1, N, 24, 21)]):
+        p.in_shapes[i][:] = list(sh)
+    ptrs = (C.c_void_p * 2)(None, rb.data_ptr())
+    assert lib.ogle_cuda_concat(C.byref(p), ptrs, C.c_void_p(out.data_ptr()), stream) == 0
+    assert torch.equal(out, want)
+    # every slice in place: nothing is launched
+    before = ops.launch_count()
+    ptrs = (C.c_void_p * 2)(None, None)
+    assert lib.ogle_cuda_concat(C.byref(p), ptrs, C.c_void_p(out.data_ptr()), stream) == 0
+    assert ops.launch_count() == before
+    # a block stride too small for the rows it must hold is refused
+    assert lib.ogle_cuda_reshape_placed(C.c_void_p(a4.data_ptr()), C.c_void_p(out.data_ptr()), a.size, 63, 21, 75, 74 * 24, stream) == -1
+
+
+def test_bounded_waits_run_out_cleanly(oracle_port):
+    """Failure detection without a fault: with the roles' wait limit set to zero polls, every wait inside the
+    tensor-core kernel gives up at once. The launch must return (the block waits for its own operand copies,
+    frees its tensor memory and retires), the status word must name the wait that gave up, and - after the limit
+    is restored and the word cleared - the same convolutions must be served correctly by the next launches."""
+    from gpu_ops import run_case_cuda
+    from ogle_b200 import _lib, ops
+    lib = _lib.cuda_lib()
+    rng = np.random.default_rng(55)
+    cases = []
+    for (N, H, C, K, k, p) in [(2, 19, 64, 64, 1, 0),      # two reduction chunks: the ring never wraps
+                               (2, 19, 256, 96, 3, 1),     # 72 chunks: the producers reach their own wait
+                               (4, 38, 128, 256, 1, 0)]:   # several tiles per block
+        x = rng.standard_normal((N, H, H, C), dtype=np.float32)
+        w = rng.standard_normal((K, C, k, k), dtype=np.float32) * np.float32(1.0 / np.sqrt(C * k * k))
+        b = rng.standard_normal(K, dtype=np.float32)
+        cases.append(dict(op="conv2d", x=x, w=w, bias=b, stride=1, pad=p, dilation=1, group=1, act=2, lo=0.0, hi=0.0))
+    assert lib.ogle_cuda_device_status() == 0
+    try:
+        for case in cases:
+            for mode in (ops.MATH_TF32, ops.MATH_TF32X3):
+                assert lib.ogle_cuda_set_wait_limit(0) == 0
+                run_case_cuda(case, mode)                           # returns: no hang, no fault
+                assert lib.ogle_cuda_device_status() == -6          # OGLE_ERR_TIMEOUT
+                assert 1 <= lib.ogle_cuda_device_status_detail() <= 7
+                assert lib.ogle_cuda_clear_device_status() == 0
+                lib.ogle_cuda_set_wait_limit(-1)
+                got = run_case_cuda(case, mode)
+                assert lib.ogle_cuda_device_status() == 0
+                ref = oracle_port.conv2d(case["x"], case["w"], case["bias"], 1, case["pad"], 1, 1, 2)
+                tol = 3e-4 if mode == ops.MATH_TF32X3 else 2e-3 * np.abs(ref).max()
+                assert np.abs(got - ref).max() <= tol
+    finally:
+        lib.ogle_cuda_set_wait_limit(-1)
+        lib.ogle_cuda_clear_device_status()
+
+
 def test_empty_and_error_paths():
     import torch
     from ogle_b200 import _lib, ops

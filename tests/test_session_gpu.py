@@ -276,6 +276,161 @@ def test_detector_end_to_end_matches_oracle_post_process(oracle_port):
         det.close()
 
 
+def test_concat_in_place_is_transparent(oracle_port):
+    """Convolutions whose results only a channel Concat reads write straight into their slices of its tensor
+    (widths 8, 12, 16 and a ragged last one of 6) and the Concat leaves the sequence; the tensors downstream are
+    bit-identical to the copying Concat, in the CUDA-core and the tensor-core modes, eager and replayed."""
+    from ogle_b200 import models, session
+    from oracle import graph_oracle
+    x = np.random.default_rng(41).standard_normal((3, 19, 17, 32)).astype(np.float32)
+    for kernel in (1, 3):
+        model = models.concat_of_convs(x.shape, [8, 12, 16, 6], seed=9, kernel=kernel)
+        ref = graph_oracle.run_graph(model, {"input": x}, oracle_port, keep={"cat", "output"})
+        for mode in (0, 2):
+            outs, counts = [], []
+            for fuse in (1, 0):
+                sess = session.FBOSession()
+                sess.set_option("math_mode", mode)
+                sess.set_option("fuse_concats", fuse)
+                sess.LoadGraph(model)
+                for _ in range(3):                        # eager, capture, replay
+                    sess.Run({"input": x})
+                outs.append(sess.GetOutputs(["cat", "output"], ["NHWC", "NHWC"]))
+                counts.append(sess.num_active_kernels())
+                assert sess.num_placed() == (4 if fuse else 0)
+                if fuse:
+                    with pytest.raises(session.OgleError, match="fuse_concats"):
+                        sess.GetOutputs(["branch1"], ["NHWC"])
+                sess.close()
+            assert counts[1] - counts[0] == 1             # the Concat itself
+            for a, b in zip(*outs):
+                assert np.array_equal(a, b), (kernel, mode)
+            bound = 1e-5 if mode == 0 else 2e-4
+            assert _norm_err(outs[0][0], ref["cat"]) <= bound and _norm_err(outs[0][1], ref["output"]) <= bound
+
+
+def test_ssd_class_heads_write_their_concat_in_place():
+    """MobileNet-SSD: the six class heads end in a re-padding copy ([N,h,w,a*21] -> [N,h*w*a,21]); those copies
+    write into the [N,1917,21] tensor directly and the class Concat disappears. The box heads are aliases of their
+    convolutions' outputs and keep their Concat. Same bits as with the switch off."""
+    from ogle_b200 import models, session
+    model, _ = models.mobilenet_v1_ssd(batch=3, num_classes=21, seed=6, weight_std="he")
+    x = ((np.random.default_rng(42).random((3, 300, 300, 3), dtype=np.float32) - 0.5) / 0.5).astype(np.float32)
+    outs, counts = [], []
+    for fuse in (1, 0):
+        sess = session.FBOSession()
+        sess.set_option("fuse_concats", fuse)
+        sess.LoadGraph(model)
+        for _ in range(3):
+            sess.Run({"input": x})
+        outs.append(sess.GetOutputs(["cls_logits", "box_preds"], ["ANY", "ANY"]))
+        counts.append(sess.num_active_kernels())
+        assert sess.num_placed() == (6 if fuse else 0)
+        sess.close()
+    assert counts[1] - counts[0] == 1
+    for a, b in zip(*outs):
+        assert np.array_equal(a, b)
+
+
+def test_exported_shape_arithmetic_heads(oracle_port):
+    """The head plumbing as an ONNX export writes it - Shape -> Gather -> Unsqueeze -> Concat -> Reshape
+    (nn/kernels/shape.cc, gather.cc + gather.glsl:7-18, unsqueeze.cc:22-55) - runs in the setup pass and gives
+    the same tensors as constant reshape targets; none of those nodes is left in the steady-state sequence."""
+    from ogle_b200 import models, session
+    from oracle import graph_oracle
+    for batch in (1, 2):
+        plain, _ = models.mobilenet_v1_ssd(batch=batch, num_classes=5, seed=11, weight_std="he")
+        exported, _ = models.mobilenet_v1_ssd(batch=batch, num_classes=5, seed=11, weight_std="he", exported_shape_ops=True)
+        assert {n.type for n in exported.nodes} >= {"Shape", "Gather", "Unsqueeze"}
+        x = ((np.random.default_rng(43).random((batch, 300, 300, 3), dtype=np.float32) - 0.5) / 0.5).astype(np.float32)
+        ref = graph_oracle.run_graph(exported, {"input": x}, oracle_port, keep={"cls_logits", "box_preds"})
+        got = {}
+        for name, model in (("plain", plain), ("exported", exported)):
+            with tempfile.TemporaryDirectory() as d:
+                path = os.path.join(d, "ssd.dlx")
+                model.save(path)
+                sess = session.FBOSession()
+                sess.set_option("math_mode", 0)
+                sess.LoadGraph(path)
+                sess.Run({"input": x})
+                got[name] = (sess.GetOutputs(["cls_logits", "box_preds"], ["ANY", "ANY"]), sess.num_active_kernels())
+                sess.close()
+        assert got["plain"][1] == got["exported"][1]
+        for a, b, key in zip(got["plain"][0], got["exported"][0], ("cls_logits", "box_preds")):
+            assert a.shape == ref[key].shape and np.array_equal(a, b)
+            assert _norm_err(b, ref[key]) <= 2e-5
+
+
+def test_shape_gather_unsqueeze_values():
+    """Shape of a stored-NHWC tensor and Gather's index mapping (ONNX index 0, 1, 2, 3 -> N, C, H, W)."""
+    from ogle_b200 import dlx, session
+    s = dlx.Scope()
+    x = s.add_input("input", [2, 5, 7, 9])                 # N, C, H, W
+    dims = s.add_node("dims", "Shape", [x], {"shape_attr": {}})
+    for i in range(4):
+        idx = s.add_const(f"i{i}", np.array(i, np.float32), dlx.ANY, dlx.ANY4)
+        g = s.add_node(f"g{i}", "Gather", [dims, idx], {"gather_attr": {"axis": 0}})
+        s.add_node(f"u{i}", "Unsqueeze", [g], {"unsqueeze_attr": {"axes": [0]}})
+    sess = session.FBOSession()
+    sess.LoadGraph(s.model)
+    sess.Run({"input": np.zeros((2, 7, 9, 5), np.float32)})
+    assert sess.num_active_kernels() == 0
+    assert sess.GetOutputs(["dims"], ["ANY"])[0].tolist() == [2.0, 7.0, 9.0, 5.0]
+    got = [sess.GetOutputs([f"u{i}"], ["ANY"])[0] for i in range(4)]
+    assert [g.shape for g in got] == [(1,)] * 4
+    assert [float(g[0]) for g in got] == [2.0, 5.0, 7.0, 9.0]
+    sess.close()
+
+
+def test_decoder_node(oracle_port):
+    """The Decoder operator inside a graph (nn/kernels/decoder.cc:12-92): deltas [1,A,4] against anchors
+    [1,h,w,4]; the kernel's own variances; batch 1 only, as the reference defines it."""
+    from ogle_b200 import models, session
+    from oracle import graph_oracle
+    model, anchors = models.box_decoder_graph(27, 71, seed=3)
+    x = (np.random.default_rng(44).standard_normal((1, 27, 71, 4)) * 0.5).astype(np.float32)
+    ref = graph_oracle.run_graph(model, {"input": x}, oracle_port, keep={"boxes"})["boxes"]
+    sess = session.FBOSession()
+    sess.LoadGraph(model)
+    for _ in range(3):
+        sess.Run({"input": x})
+    got = sess.GetOutputs(["boxes"], ["ANY"])[0]
+    sess.close()
+    assert got.shape == (1, 27 * 71, 4) and np.abs(got - ref).max() <= 1e-5
+    two, _ = models.box_decoder_graph(3, 4)
+    two.nodes[0].attr["input_attr"]["dims"][0] = 2
+    sess = session.FBOSession()
+    sess.LoadGraph(two)
+    with pytest.raises(session.OgleError):                 # anchors are per graph, predictions for two images
+        sess.Run({"input": np.zeros((2, 3, 4, 4), np.float32)})
+    sess.close()
+
+
+def test_detector_scales_boxes_by_each_frames_own_size(oracle_port):
+    """Reference rule on raw frames of different sizes: the pixel rectangles (and with them the suppression)
+    use each frame's own rows x cols (origin_input_sizes_, detector.cc:102,179-180), not the network input size."""
+    from ogle_b200 import models, ops, session
+    rng = np.random.default_rng(45)
+    model, _ = models.mobilenet_v1_ssd(batch=3, num_classes=21, seed=12, weight_std="he")
+    sizes = [(480, 640), (300, 300), (123, 77)]
+    frames = [rng.integers(0, 256, (h, w, 3), dtype=np.uint8) for (h, w) in sizes]
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "ssd.dlx")
+        model.save(path)
+        det = session.Detector(path, mode=0, score_thr=0.3, top_k=100, nms_thr=0.45, math_mode=0)
+        det.detect_bgr8_async(frames, 300, 300)
+        out = det.wait()
+        sess = det.session()
+        logits, preds, anchors = sess.GetOutputs(["cls_logits", "box_preds", "anchors"], ["ANY", "ANY", "ANY"])
+        det.close()
+    boxes = ops.ssd_decode(ops.dense_to_device(preds), ops.dense_to_device(anchors)).cpu().numpy()
+    for n, (h, w) in enumerate(sizes):
+        r = oracle_port.detect(boxes[n], logits[n], w, h, 0.3, 100, 0.45)
+        k = len(r["anchor"])
+        assert out["count"][n] == k and np.array_equal(out["anchor"][n, :k], r["anchor"])
+        assert np.array_equal(out["box"][n, :k].astype(np.int32), r["rect"]), (h, w)
+
+
 def test_detector_raw_frames_equal_host_preprocess(oracle_port):
     """Frames of different sizes through detect_bgr8_async (upload as bytes, resize + mean on the device)
     give the same detections as the float path fed with the oracle's preprocess of the same frames -

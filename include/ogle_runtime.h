@@ -147,6 +147,11 @@ size_t ogle_host_huge_page_bytes(const void* p);
  * (ogle_rt_last_error). ogle_host_shared_close unmaps; unlink != 0 also removes the name. */
 void* ogle_host_shared_open(const char* name, size_t bytes, int create, int pin);
 void ogle_host_shared_close(void* p, int unlink);
+/* One asynchronous host-to-device copy on `stream` (the upload half of
+ * Context::CopyCPUTensorToDevice, core/context.cc:123-154, without the layout pass): what the
+ * detector issues per batch, exposed so that the bare upload rate of a host buffer can be
+ * measured beside the full pipeline. */
+int ogle_host_upload_async(void* dst_device, const void* src_host, size_t bytes, ogle_stream_t stream);
 /* Parses a sysfs CPU list ("0-3,8,10-11"); writes up to `capacity` entries, returns the count. */
 int ogle_host_parse_cpulist(const char* text, int* cpus, int capacity);
 

@@ -206,8 +206,7 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
     } else {
         t.flat = 0;
         t.N = a.N; t.Ho = a.Ho; t.Wo = a.Wo;
-        const bool may_split = v2 && a.act == OGLE_ACT_NONE && a.koff == 0 && (y2 != nullptr || a.Ks == a.Kp) &&
-                               split_k_enabled() && taps * t.chunks_per_tap >= 16;
+        const bool may_split = v2 && a.act == OGLE_ACT_NONE && split_k_enabled() && taps * t.chunks_per_tap >= 16;
         if (a.Wo >= kTileM) {
             const int parts = (a.Wo + kTileM - 1) / kTileM;
             t.tw = (a.Wo + parts - 1) / parts; t.th = 1; t.tn = 1;
@@ -262,11 +261,12 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
     if (!make_map(&mBlo, w_lo, 2, bdims, bstr, bbox, bes)) return OGLE_ERR_CUDA;
     if (v2) {
         // Split the reduction when whole tiles would leave SMs idle (few tiles) or a last round
-        // mostly empty. Needs a linear epilogue (no activation) and outputs that may be zeroed
-        // (dense tensors, not slices of a wider one): the partial tiles are added in place.
+        // mostly empty. Needs a linear epilogue (no activation); the output (a dense tensor, or
+        // this convolution's channel slice of a wider one) is zeroed first and the partial tiles
+        // are added in place.
         t.split_k = 1;
         const int chunks = t.kernel * t.kernel * t.chunks_per_tap;
-        if (a.act == OGLE_ACT_NONE && a.koff == 0 && (y2 != nullptr || a.Ks == a.Kp) && split_k_enabled()) {
+        if (a.act == OGLE_ACT_NONE && split_k_enabled()) {
             const double tiles = (double)m_tiles * t.n_tiles;
             double best = ceil(tiles / kNumSMs);
             // two ranges at most: the sum of two partial tiles onto zero does not depend on the
@@ -280,7 +280,12 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
         }
         if (t.split_k > 1) {
             const size_t rows = (size_t)a.M;
-            if (cudaMemsetAsync(y, 0, rows * (size_t)ks_a * sizeof(float), s) != cudaSuccess) return OGLE_ERR_CUDA;
+            if (ks_a == kp_a) {
+                if (cudaMemsetAsync(y + a.koff, 0, rows * (size_t)ks_a * sizeof(float), s) != cudaSuccess) return OGLE_ERR_CUDA;
+            } else if (cudaMemset2DAsync(y + a.koff, (size_t)ks_a * sizeof(float), 0, (size_t)kp_a * sizeof(float), rows, s) !=
+                       cudaSuccess) {
+                return OGLE_ERR_CUDA;
+            }
             if (y2 && cudaMemsetAsync(y2, 0, rows * (size_t)kp_b * sizeof(float), s) != cudaSuccess) return OGLE_ERR_CUDA;
         }
         return launch_tc_v2(t, mA, mBhi, mBlo, mY, y2 ? mY2 : mY, m_tiles, bias, error_flag_ptr(), s);

@@ -10,6 +10,7 @@
 #include "fbo_session.h"
 #include "kernel_registry.h"
 #include "ogle_runtime.h"
+#include <cuda_runtime.h>
 
 namespace {
 thread_local std::string g_error;
@@ -305,6 +306,13 @@ void* ogle_host_shared_open(const char* name, size_t bytes, int create, int pin)
     return p;
 }
 void ogle_host_shared_close(void* p, int unlink) { ogle::CloseSharedHost(p, unlink != 0); }
+
+int ogle_host_upload_async(void* dst_device, const void* src_host, size_t bytes, ogle_stream_t stream) {
+    if (!dst_device || !src_host) return -1;
+    const cudaError_t e = cudaMemcpyAsync(dst_device, src_host, bytes, cudaMemcpyHostToDevice, reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) { g_error = std::string("cudaMemcpyAsync: ") + cudaGetErrorString(e); return -3; }
+    return 0;
+}
 
 int ogle_detector_use_result_buffers(OgleDetector* d, void* slot0, void* slot1, size_t bytes_each) {
     if (!d) return -1;

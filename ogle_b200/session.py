@@ -52,6 +52,7 @@ RT_SYMBOLS = {
     "ogle_host_huge_page_bytes": (C.c_size_t, [_vp]),
     "ogle_host_shared_open": (_vp, [_cp, C.c_size_t, C.c_int, C.c_int]),
     "ogle_host_shared_close": (None, [_vp, C.c_int]),
+    "ogle_host_upload_async": (C.c_int, [_vp, _vp, C.c_size_t, _vp]),
     "ogle_detector_use_result_buffers": (C.c_int, [_vp, _vp, _vp, C.c_size_t]),
     "ogle_detector_result_layout": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_size_t), _ip, _ip]),
     "ogle_host_bind_to_device": (C.c_int, [C.c_int, _ip, _ip, _ip]),

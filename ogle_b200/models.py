@@ -219,21 +219,22 @@ def box_decoder_graph(map_h, map_w, seed=0):
     return s.model, anchors
 
 
-def concat_of_convs(x_shape, widths, seed=0, kernel=1, consumer=True):
-    """input -> len(widths) convolutions of the same window -> Concat on the channel axis (ONNX axis 1)
-    [-> 1x1 conv "output"]: the graph shape where producers can write a concat in place. Output "cat"
-    (and "output"). Returns dlx.Model."""
+def concat_of_convs(x_shape, widths, seed=0, kernels=(1,), consumer=True):
+    """input -> len(widths) convolutions (branch i: kernels[i % len(kernels)] x same, pad to keep the size, ReLU on the
+    first half of the branches) -> Concat on the channel axis (ONNX axis 1) [-> 1x1 conv "output"]: the graph shape
+    where producers can write a concat in place. Output "cat" (and "output"). Returns dlx.Model."""
     s = dlx.Scope()
     rng = np.random.default_rng(seed)
     N, H, W, C = x_shape
     x = s.add_input("input", [N, C, H, W])
     parts = []
     for i, k_out in enumerate(widths):
+        kernel = kernels[i % len(kernels)]
         w = (rng.standard_normal((k_out, C, kernel, kernel), dtype=np.float32) * np.float32(0.2)).astype(np.float32)
         b = rng.standard_normal(k_out, dtype=np.float32)
         wid = s.add_const(f"branch{i}.weight", w, dlx.ANY, dlx.HWN4C4)
         bid = s.add_const(f"branch{i}.bias", b, dlx.ANY, dlx.ANY4)
-        parts.append(s.add_conv(f"branch{i}", x, wid, bid, kernel, 1, kernel // 2, 1, 1, "Relu" if i % 2 == 0 else "", 0.0, 0.0))
+        parts.append(s.add_conv(f"branch{i}", x, wid, bid, kernel, 1, kernel // 2, 1, 1, "Relu" if 2 * i < len(widths) else "", 0.0, 0.0))
     cat = s.add_node("cat", "Concat", parts, {"concat_attr": {"axis": 1}})
     s.add_output_name("cat")
     if consumer:

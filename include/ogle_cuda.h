@@ -117,6 +117,18 @@ int ogle_cuda_conv2d_prepack(const OgleConvParams* p, const float* w_oihw, void*
 int ogle_cuda_conv2d(const OgleConvParams* p, const float* x, const void* packed_filter,
                      const float* bias, float* y, ogle_stream_t stream);
 
+/* The same with scratch memory lent by the caller (device memory, 16-byte aligned, at least
+ * ogle_cuda_conv2d_workspace_bytes(p), which is 0 for most layers). Layers with a long reduction
+ * and few output tiles - 3x3 heads on small feature maps, the whole network at batch 1 - then split
+ * their reduction over up to 16 blocks per tile: each block stores its partial tile into its own
+ * slice of the scratch and a second small kernel adds the slices in a fixed order, then bias and
+ * activation (bit-reproducible; any activation). Without scratch such layers split in two at
+ * most, and only without an activation. The scratch may be reused as soon as the stream has
+ * passed this call. */
+size_t ogle_cuda_conv2d_workspace_bytes(const OgleConvParams* p);
+int ogle_cuda_conv2d_ws(const OgleConvParams* p, const float* x, const void* packed_filter, const float* bias,
+                        float* y, void* workspace, size_t workspace_bytes, ogle_stream_t stream);
+
 /* Name of the device kernel that ogle_cuda_conv2d launches for these parameters
  * (for profiles and reports; "" when the parameters are invalid). */
 const char* ogle_cuda_conv2d_kernel_name(const OgleConvParams* p);
@@ -130,14 +142,19 @@ const char* ogle_cuda_conv2d_kernel_name(const OgleConvParams* p);
  * zero, packs it with ogle_cuda_conv2d_prepack under the same params, and stacks
  * the biases the same way. y_first receives channels [0, K1) as a tensor of K1
  * channels (padded to 4), y_second channels [second_offset, out_hwc[2]) as a tensor
- * of K2 channels. The arithmetic per output value is that of ogle_cuda_conv2d
- * (bit-identical in OGLE_MATH_TF32; in OGLE_MATH_TF32X3 the three partial sums
- * may be added in a different order). Tensor-core modes only: ogle_cuda_conv2d_pair_supported says
+ * of K2 channels. The arithmetic per output value is that of ogle_cuda_conv2d,
+ * up to the order in which partial sums are added (the two forms may split a
+ * long reduction into different numbers of ranges). Tensor-core modes only: ogle_cuda_conv2d_pair_supported says
  * whether these params are served (else run the two convolutions separately). */
 int ogle_cuda_conv2d_pair_supported(const OgleConvParams* p);
 int ogle_cuda_conv2d_pair(const OgleConvParams* p, const float* x, const void* packed_filter, const float* bias,
                           int first_channels, int second_offset, float* y_first, float* y_second,
                           ogle_stream_t stream);
+/* ogle_cuda_conv2d_pair with scratch memory, as ogle_cuda_conv2d_ws. */
+size_t ogle_cuda_conv2d_pair_workspace_bytes(const OgleConvParams* p, int first_channels, int second_offset);
+int ogle_cuda_conv2d_pair_ws(const OgleConvParams* p, const float* x, const void* packed_filter, const float* bias,
+                             int first_channels, int second_offset, float* y_first, float* y_second, void* workspace,
+                             size_t workspace_bytes, ogle_stream_t stream);
 
 /* -------------------------------------------------------------------- pool */
 /* PoolKernel::Compute, ogl_runtime/opengl/nn/kernels/pool.cc:55-79 + pool.glsl.

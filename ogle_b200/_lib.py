@@ -66,9 +66,13 @@ CUDA_SYMBOLS = {
     "ogle_cuda_conv2d_filter_bytes": (C.c_size_t, [C.POINTER(ConvParams)]),
     "ogle_cuda_conv2d_prepack": (C.c_int, [C.POINTER(ConvParams), _vp, _vp, _vp]),
     "ogle_cuda_conv2d": (C.c_int, [C.POINTER(ConvParams), _vp, _vp, _vp, _vp, _vp]),
+    "ogle_cuda_conv2d_workspace_bytes": (C.c_size_t, [C.POINTER(ConvParams)]),
+    "ogle_cuda_conv2d_ws": (C.c_int, [C.POINTER(ConvParams), _vp, _vp, _vp, _vp, _vp, C.c_size_t, _vp]),
     "ogle_cuda_conv2d_kernel_name": (C.c_char_p, [C.POINTER(ConvParams)]),
     "ogle_cuda_conv2d_pair_supported": (C.c_int, [C.POINTER(ConvParams)]),
     "ogle_cuda_conv2d_pair": (C.c_int, [C.POINTER(ConvParams), _vp, _vp, _vp, C.c_int, C.c_int, _vp, _vp, _vp]),
+    "ogle_cuda_conv2d_pair_workspace_bytes": (C.c_size_t, [C.POINTER(ConvParams), C.c_int, C.c_int]),
+    "ogle_cuda_conv2d_pair_ws": (C.c_int, [C.POINTER(ConvParams), _vp, _vp, _vp, C.c_int, C.c_int, _vp, _vp, _vp, C.c_size_t, _vp]),
     "ogle_cuda_pool_infer": (C.c_int, [C.POINTER(PoolParams)]),
     "ogle_cuda_pool": (C.c_int, [C.POINTER(PoolParams), _vp, _vp, _vp]),
     "ogle_cuda_batchnorm": (C.c_int, [_vp] * 6 + [C.c_long, C.c_int, C.c_int, C.c_float, _vp]),

@@ -7,7 +7,8 @@ namespace ogle {
 
 int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x,
                    const float* w_hi, const float* w_lo, const float* bias, float* y, cudaStream_t s,
-                   float* y2 = nullptr, int K1 = 0, int split_col = 0);
+                   float* y2 = nullptr, int K1 = 0, int split_col = 0, void* ws = nullptr, size_t ws_bytes = 0,
+                   size_t* ws_needed = nullptr);
 bool conv_tc_supported(const ConvArgs& a, int variant);
 bool conv_tc_gather_supported(const ConvArgs& a, int variant);
 bool dw_tma_supported(const ConvArgs& a);
@@ -169,33 +170,51 @@ int ogle_cuda_conv2d_prepack(const OgleConvParams* p, const float* w_oihw, void*
     return rc;
 }
 
-int ogle_cuda_conv2d(const OgleConvParams* p, const float* x, const void* packed_filter,
-                     const float* bias, float* y, ogle_stream_t stream) {
+static bool served_by_tc(const OgleConvParams* p, const ConvArgs& a, int variant) {
+    return p->math_mode != OGLE_MATH_FP32 && (variant == CONV_GENERAL || variant == CONV_POINTWISE) &&
+           (conv_tc_supported(a, variant) || conv_tc_gather_supported(a, variant));
+}
+
+int ogle_cuda_conv2d_ws(const OgleConvParams* p, const float* x, const void* packed_filter, const float* bias, float* y,
+                        void* workspace, size_t workspace_bytes, ogle_stream_t stream) {
     ConvArgs a; int variant;
     int rc = fill_args(p, &a, &variant);
     if (rc != OGLE_OK) return rc;
     if (a.Ho != p->out_hwc[0] || a.Wo != p->out_hwc[1]) return OGLE_ERR_INVALID;
     if (!x || !packed_filter || !y || (a.has_bias && !bias)) return OGLE_ERR_INVALID;
-    if (!aligned16(x) || !aligned16(y) || !aligned16(packed_filter))
+    if (!aligned16(x) || !aligned16(y) || !aligned16(packed_filter) || (workspace && !aligned16(workspace)))
         return OGLE_ERR_ALIGNMENT;
     if (p->math_mode < OGLE_MATH_FP32 || p->math_mode > OGLE_MATH_TF32X3) return OGLE_ERR_INVALID;
     const char* base = static_cast<const char*>(packed_filter);
     cudaStream_t s = (cudaStream_t)stream;
-    if (p->math_mode != OGLE_MATH_FP32 && (variant == CONV_GENERAL || variant == CONV_POINTWISE) &&
-        (conv_tc_supported(a, variant) || conv_tc_gather_supported(a, variant))) {
+    if (served_by_tc(p, a, variant)) {
         const FilterLayout L = filter_layout(a.K, a.C / a.group, a.kernel, a.group, a.Cp);
         return launch_conv_tc(a, variant, p->math_mode, x, reinterpret_cast<const float*>(base + L.off_hi),
-                              reinterpret_cast<const float*>(base + L.off_lo), bias, y, s);
+                              reinterpret_cast<const float*>(base + L.off_lo), bias, y, s, nullptr, 0, 0, workspace,
+                              workspace ? workspace_bytes : 0);
     }
     return launch_conv_simt(a, variant, x, reinterpret_cast<const float*>(base), bias, y, s);
+}
+
+int ogle_cuda_conv2d(const OgleConvParams* p, const float* x, const void* packed_filter,
+                     const float* bias, float* y, ogle_stream_t stream) {
+    return ogle_cuda_conv2d_ws(p, x, packed_filter, bias, y, nullptr, 0, stream);
+}
+
+size_t ogle_cuda_conv2d_workspace_bytes(const OgleConvParams* p) {
+    ConvArgs a; int variant;
+    if (fill_args(p, &a, &variant) != OGLE_OK || !served_by_tc(p, a, variant)) return 0;
+    size_t need = 0;
+    if (launch_conv_tc(a, variant, p->math_mode, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 0, 0, nullptr, 0,
+                       &need) != OGLE_OK)
+        return 0;
+    return need;
 }
 
 const char* ogle_cuda_conv2d_kernel_name(const OgleConvParams* p) {
     ConvArgs a; int variant;
     if (fill_args(p, &a, &variant) != OGLE_OK) return "";
-    if (p->math_mode != OGLE_MATH_FP32 && (variant == CONV_GENERAL || variant == CONV_POINTWISE) &&
-        (conv_tc_supported(a, variant) || conv_tc_gather_supported(a, variant)))
-        return "conv_tc2_kernel";
+    if (served_by_tc(p, a, variant)) return "conv_tc2_kernel";
     if (variant == CONV_DEPTHWISE) {
         if (dw_tma_supported(a)) return "dw3x3_tma_kernel";
         return (a.kernel == 3 && a.dil == 1 && (a.stride == 1 || a.stride == 2)) ? "dw3x3_kernel" : "dw_generic_kernel";
@@ -213,15 +232,17 @@ int ogle_cuda_conv2d_pair_supported(const OgleConvParams* p) {
     return conv_tc_supported(a, variant) ? 1 : 0;
 }
 
-int ogle_cuda_conv2d_pair(const OgleConvParams* p, const float* x, const void* packed_filter, const float* bias,
-                          int first_channels, int second_offset, float* y_first, float* y_second,
-                          ogle_stream_t stream) {
+int ogle_cuda_conv2d_pair_ws(const OgleConvParams* p, const float* x, const void* packed_filter, const float* bias,
+                             int first_channels, int second_offset, float* y_first, float* y_second, void* workspace,
+                             size_t workspace_bytes, ogle_stream_t stream) {
     ConvArgs a; int variant;
     int rc = fill_args(p, &a, &variant);
     if (rc != OGLE_OK) return rc;
     if (a.Ho != p->out_hwc[0] || a.Wo != p->out_hwc[1]) return OGLE_ERR_INVALID;
     if (!x || !packed_filter || !y_first || !y_second || (a.has_bias && !bias)) return OGLE_ERR_INVALID;
-    if (!aligned16(x) || !aligned16(y_first) || !aligned16(y_second) || !aligned16(packed_filter)) return OGLE_ERR_ALIGNMENT;
+    if (!aligned16(x) || !aligned16(y_first) || !aligned16(y_second) || !aligned16(packed_filter) ||
+        (workspace && !aligned16(workspace)))
+        return OGLE_ERR_ALIGNMENT;
     if (first_channels <= 0 || second_offset != (first_channels + 31) / 32 * 32 || second_offset >= a.K)
         return OGLE_ERR_INVALID;
     if (!ogle_cuda_conv2d_pair_supported(p)) return OGLE_ERR_UNSUPPORTED;
@@ -229,7 +250,26 @@ int ogle_cuda_conv2d_pair(const OgleConvParams* p, const float* x, const void* p
     const FilterLayout L = filter_layout(a.K, a.C / a.group, a.kernel, a.group, a.Cp);
     return launch_conv_tc(a, variant, p->math_mode, x, reinterpret_cast<const float*>(base + L.off_hi),
                           reinterpret_cast<const float*>(base + L.off_lo), bias, y_first, (cudaStream_t)stream,
-                          y_second, first_channels, second_offset);
+                          y_second, first_channels, second_offset, workspace, workspace ? workspace_bytes : 0);
+}
+
+int ogle_cuda_conv2d_pair(const OgleConvParams* p, const float* x, const void* packed_filter, const float* bias,
+                          int first_channels, int second_offset, float* y_first, float* y_second,
+                          ogle_stream_t stream) {
+    return ogle_cuda_conv2d_pair_ws(p, x, packed_filter, bias, first_channels, second_offset, y_first, y_second, nullptr, 0,
+                                    stream);
+}
+
+size_t ogle_cuda_conv2d_pair_workspace_bytes(const OgleConvParams* p, int first_channels, int second_offset) {
+    ConvArgs a; int variant;
+    if (fill_args(p, &a, &variant) != OGLE_OK || !ogle_cuda_conv2d_pair_supported(p)) return 0;
+    if (first_channels <= 0 || second_offset != (first_channels + 31) / 32 * 32 || second_offset >= a.K) return 0;
+    size_t need = 0;
+    float dummy = 0.f;      // only its being non-null matters to the planner (two-output form)
+    if (launch_conv_tc(a, variant, p->math_mode, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, &dummy, first_channels,
+                       second_offset, nullptr, 0, &need) != OGLE_OK)
+        return 0;
+    return need;
 }
 
 }  // extern "C"

@@ -134,9 +134,55 @@ bool conv_tc_gather_supported(const ConvArgs& a, int variant) {
            encode_fn() != nullptr;
 }
 
+// Adds the slices of a split reduction in slice order, then bias and activation, and writes the
+// output tensor(s). One thread per four channels of a pixel. ws: [slices][rows_stride rows][ws_cols];
+// y: stride Ks, first channel koff, K real channels (lanes K..up4(K)-1 written as zero); with y2 the
+// columns from split_col on go to the second tensor (dense, K2 channels).
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float4* __restrict__ ws, int slices, long slice_q, int ws_cols_q, long rows,
+                     const float* __restrict__ bias, int act, float lo, float hi,
+                     float4* __restrict__ y, int Ks_q, int koff_q, int K, int out_q,
+                     float4* __restrict__ y2, int split_col, int K2, int out2_q) {
+    const int per_row = out_q + out2_q;
+    const long total = rows * per_row;
+    for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long m = i / per_row;
+        int c = int(i - m * per_row);
+        const bool second = c >= out_q;
+        if (second) c -= out_q;
+        const int col = (second ? split_col : 0) + c * 4;          // column in the stacked accumulator order
+        const int real = second ? K2 : K;
+        const float4* src = ws + m * ws_cols_q + (col >> 2);
+        float4 acc = src[0];
+        for (int s = 1; s < slices; ++s) {
+            const float4 v = src[(long)s * slice_q];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        float r[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            const int n = c * 4 + l;
+            if (n < real) {
+                if (bias) r[l] += bias[col + l];
+                r[l] = apply_act(r[l], act, lo, hi);
+            } else {
+                r[l] = 0.f;                                         // padded lanes stay zero
+            }
+        }
+        const float4 o = make_float4(r[0], r[1], r[2], r[3]);
+        if (second) y2[m * out2_q + c] = o;
+        else y[m * Ks_q + koff_q + c] = o;
+    }
+}
+
+// ws / ws_bytes: scratch for a split reduction of more than two ranges (or of a layer with an
+// activation), may be null. ws_needed != null: plan only - no tensor maps, no launch - and report the
+// scratch size this layer would like.
 int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x, const float* w_hi,
                    const float* w_lo, const float* bias, float* y, cudaStream_t s, float* y2, int K1,
-                   int split_col) {
+                   int split_col, void* ws, size_t ws_bytes, size_t* ws_needed) {
+    const bool plan_only = ws_needed != nullptr;
+    if (plan_only) *ws_needed = 0;
     TcArgs t = {};
     if (y2) {
         if (split_col <= 0 || (split_col & 31) || K1 <= 0 || K1 > split_col || split_col >= a.K ||
@@ -160,6 +206,13 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
 
     CUtensorMap mA, mBhi, mBlo, mY, mY2;
     long m_tiles;
+    // planning needs the tile geometry only
+    auto make_map = [&](CUtensorMap* m, const void* p, int rank, const cuuint64_t* d, const cuuint64_t* st, const cuuint32_t* b,
+                        const cuuint32_t* e) { return plan_only ? true : ogle::make_map(m, p, rank, d, st, b, e); };
+    auto make_map_sw = [&](CUtensorMapSwizzle sw, CUtensorMap* m, const void* p, int rank, const cuuint64_t* d,
+                           const cuuint64_t* st, const cuuint32_t* b, const cuuint32_t* e) {
+        return plan_only ? true : ogle::make_map_sw(sw, m, p, rank, d, st, b, e);
+    };
     if (variant == CONV_POINTWISE) {
         t.flat = 1;
         t.N = 1; t.Ho = 1; t.Wo = (int)a.M;
@@ -261,22 +314,84 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
     if (!make_map(&mBlo, w_lo, 2, bdims, bstr, bbox, bes)) return OGLE_ERR_CUDA;
     if (v2) {
         // Split the reduction when whole tiles would leave SMs idle (few tiles) or a last round
-        // mostly empty. Needs a linear epilogue (no activation); the output (a dense tensor, or
-        // this convolution's channel slice of a wider one) is zeroed first and the partial tiles
-        // are added in place.
+        // mostly empty. Two forms:
+        //  - through scratch memory (the caller lent some): any number of ranges and any activation;
+        //    each range stores its partial tile into its own slice and a small second kernel adds the
+        //    slices in slice order, then bias and activation - bit-reproducible whatever the order in
+        //    which blocks finish;
+        //  - in place, two ranges, no activation: the output (a dense tensor, or this convolution's
+        //    channel slice of a wider one) is zeroed first and the two partial tiles are added to it by
+        //    TMA reduce stores; a sum of two addends onto zero does not depend on their order either.
         t.split_k = 1;
         const int chunks = t.kernel * t.kernel * t.chunks_per_tap;
-        if (a.act == OGLE_ACT_NONE && split_k_enabled()) {
-            const double tiles = (double)m_tiles * t.n_tiles;
-            double best = ceil(tiles / kNumSMs);
-            // two ranges at most: the sum of two partial tiles onto zero does not depend on the
-            // order in which they arrive, so results stay bit-reproducible; three or more would not
-            for (int k = 2; k <= 2 && chunks / k >= 8; ++k) {
-                const double cost = ceil(tiles * k / kNumSMs) / k + 0.03 * (k - 1);   // + per-item fill/drain
-                if (cost < 0.9 * best) { best = cost; t.split_k = k; }
+        const double tiles = (double)m_tiles * t.n_tiles;
+        const int ws_cols = t.n_tiles * t.BN;
+        // rows (flat form) or images between consecutive slices: whole tiles, so that a tile that
+        // hangs over the end of its slice writes padding, not the next slice
+        const long slice_units = t.flat ? m_tiles * kTileM : (long)((a.N + t.tn - 1) / t.tn) * t.tn;
+        const size_t slice_bytes = (size_t)(t.flat ? slice_units : slice_units * a.Ho * a.Wo) * ws_cols * sizeof(float);
+        if (split_k_enabled() && chunks >= 8) {
+            // cost of the layer in units of one reduction chunk of one tile: rounds of one work item per SM,
+            // each item paying its chunks plus a fixed fill / drain of about four chunks
+            auto cost_of = [&](int k) {
+                const int cps = (chunks + k - 1) / k;
+                return ceil(tiles * k / kNumSMs) * (cps + 4.0);
+            };
+            double best = cost_of(1);
+            int best_k = 1;
+            bool best_ws = false;
+            if (a.act == OGLE_ACT_NONE && chunks / 2 >= 8 && cost_of(2) + 2.0 < 0.9 * best) { best = cost_of(2) + 2.0; best_k = 2; }
+            const bool ws_usable = plan_only || (ws != nullptr && aligned16(ws));
+            if (ws_usable && !t.gather) {
+                static const int cand[] = {2, 3, 4, 6, 8, 12, 16};
+                for (int k : cand) {
+                    if (chunks / k < 4) break;
+                    if (!plan_only && slice_bytes * k > ws_bytes) break;
+                    if (slice_bytes * k > ((size_t)192 << 20)) break;
+                    // + the second kernel: a launch and a pass over k slices
+                    const double c = cost_of(k) + 10.0 + 0.5 * k;
+                    if (c < 0.85 * best) { best = c; best_k = k; best_ws = true; }
+                }
             }
+            t.split_k = best_k;
+            t.ws_mode = best_ws ? 1 : 0;
             const int cps = (chunks + t.split_k - 1) / t.split_k;
             while (t.split_k > 1 && (t.split_k - 1) * cps >= chunks) --t.split_k;     // no empty ranges
+            if (t.split_k == 1) t.ws_mode = 0;
+        }
+        if (plan_only) {
+            *ws_needed = t.ws_mode ? slice_bytes * t.split_k : 0;
+            return OGLE_OK;
+        }
+        if (t.ws_mode) {
+            t.ws_cols = ws_cols;
+            t.ws_slice = (int)slice_units;
+            const int act = t.act;
+            const float lo = t.lo, hi = t.hi;
+            t.act = OGLE_ACT_NONE;                 // the raw sums go to the scratch tensor
+            const cuuint32_t es[4] = {1, 1, 1, 1};
+            if (t.flat) {
+                const cuuint64_t wd[4] = {(cuuint64_t)ws_cols, (cuuint64_t)slice_units * t.split_k, 1, 1};
+                const cuuint64_t wst[3] = {(cuuint64_t)ws_cols * 4, (cuuint64_t)ws_cols * 4 * wd[1], (cuuint64_t)ws_cols * 4 * wd[1]};
+                const cuuint32_t wb[4] = {kChunk, kTileM, 1, 1};
+                if (!ogle::make_map(&mY, ws, 4, wd, wst, wb, es)) return OGLE_ERR_CUDA;
+            } else {
+                const cuuint64_t wd[4] = {(cuuint64_t)ws_cols, (cuuint64_t)a.Wo, (cuuint64_t)a.Ho, (cuuint64_t)slice_units * t.split_k};
+                const cuuint64_t wst[3] = {(cuuint64_t)ws_cols * 4, (cuuint64_t)ws_cols * 4 * a.Wo, (cuuint64_t)ws_cols * 4 * a.Wo * a.Ho};
+                const cuuint32_t wb[4] = {kChunk, (cuuint32_t)t.tw, (cuuint32_t)t.th, (cuuint32_t)t.tn};
+                if (!ogle::make_map(&mY, ws, 4, wd, wst, wb, es)) return OGLE_ERR_CUDA;
+            }
+            int rc = launch_tc_v2(t, mA, mBhi, mBlo, mY, mY, m_tiles, nullptr, error_flag_ptr(), s);
+            if (rc != OGLE_OK) return rc;
+            const long rows = a.M;
+            const long slice_q = (long)(slice_bytes / 16);
+            const int out_q = kp_a / 4, out2_q = y2 ? kp_b / 4 : 0;
+            const long items = rows * (out_q + out2_q);
+            splitk_reduce_kernel<<<grid_for(items, 256), 256, 0, s>>>(
+                reinterpret_cast<const float4*>(ws), t.split_k, slice_q, ws_cols / 4, rows, a.has_bias ? bias : nullptr, act, lo, hi,
+                reinterpret_cast<float4*>(y), ks_a / 4, a.koff / 4, y2 ? K1 : a.K, out_q,
+                reinterpret_cast<float4*>(y2), split_col, y2 ? a.K - split_col : 0, out2_q);
+            return finish_launch();
         }
         if (t.split_k > 1) {
             const size_t rows = (size_t)a.M;

@@ -446,7 +446,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 const int bias_key = kSplit ? nbase * 2 + (wi.ks == 0 ? 1 : 0) : nbase;
                 if (bias_key != staged_nbase) {
                     for (int i = t; i < a.BN; i += 128)
-                        my_bias[i] = (a.bias_mode == 2 && (!kSplit || wi.ks == 0) && nbase + i < a.K) ? a.beta * bias[nbase + i] : 0.f;
+                        my_bias[i] = (a.bias_mode == 2 && (!kSplit || (wi.ks == 0 && !a.ws_mode)) && nbase + i < a.K) ? a.beta * bias[nbase + i] : 0.f;
                     staged_nbase = bias_key;
                 }
                 ok = wait_or_abort(&bar_acc_full[as], (uint32_t)(use & 1), abort_flag, a.spin_limit);
@@ -477,9 +477,11 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         }
                         float4* dst = reinterpret_cast<float4*>(staging + (size_t)sb * kStagingBytes + (size_t)row * 128);
                         // which output this slab belongs to, and its first column there
-                        const bool second = a.split_col > 0 && nbase + col >= a.split_col;
+                        // (a partial tile bound for the workspace keeps the stacked column order of the accumulator)
+                        const bool to_ws = kSplit && a.ws_mode;
+                        const bool second = !to_ws && a.split_col > 0 && nbase + col >= a.split_col;
                         const int lcol = second ? nbase + col - a.split_col : nbase + col;
-                        const int kout = second ? a.K - a.split_col : (a.split_col > 0 ? a.K1 : a.K);
+                        const int kout = to_ws ? a.ws_cols : (second ? a.K - a.split_col : (a.split_col > 0 ? a.K1 : a.K));
                         const bool fast = a.bias_mode != 1 && lcol + 32 <= kout;
                         if (fast) {
                             // every column is a real channel and the bias is per column:
@@ -535,8 +537,13 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                             const uint32_t src = base + my_staging + (uint32_t)sb * (uint32_t)kStagingBytes;
                             int col = nbase + g0 * 32;
                             const CUtensorMap* my = &tmY;
-                            if (a.split_col > 0 && col >= a.split_col) { col -= a.split_col; my = &tmY2; }
-                            if (kSplit) {
+                            const bool to_ws = kSplit && a.ws_mode;
+                            if (!to_ws && a.split_col > 0 && col >= a.split_col) { col -= a.split_col; my = &tmY2; }
+                            if (to_ws) {
+                                // slice ks of the scratch tensor; the reduce kernel adds the slices
+                                if (a.flat) tma_store_4d(&tmY, src, col, tc_.w0 + wi.ks * a.ws_slice, 0, 0);
+                                else tma_store_4d(&tmY, src, col, tc_.w0, tc_.h0, tc_.n0 + wi.ks * a.ws_slice);
+                            } else if (kSplit) {
                                 if (a.flat) tma_reduce_add_4d(my, src, col, tc_.w0, 0, 0);
                                 else tma_reduce_add_4d(my, src, col, tc_.w0, tc_.h0, tc_.n0);
                             } else if (a.flat) {

@@ -45,6 +45,13 @@ struct TcArgs {
     // stores into an output the host zeroed. Used (activation none only) when the tiles alone
     // would leave most SMs idle or a last round mostly empty. total_work = total_tiles * split_k.
     int split_k, chunks_per_split, total_work;
+    // Split reduction through a workspace (ws_mode = 1; any number of ranges, any activation): work item
+    // (tile, ks) stores its raw partial tile - no bias, no activation - into slice ks of a scratch tensor
+    // of ws_cols columns through the first output map (which then describes the scratch tensor: slices
+    // follow one another along its outermost extent, ws_slice rows (flat form) or images apart), and
+    // a second, small kernel adds the slices in a fixed order, then bias and activation. Results do not
+    // depend on which block finishes first.
+    int ws_mode, ws_cols, ws_slice;
     // Gather form (k x k convolution over at most four input channels, e.g. an RGB stem): the
     // activation "tile" that TMA delivers is the tile's input window of 16-byte pixels
     // (g_iw x g_ih of them, halo included), once per reduction chunk; the operand-split warps

@@ -76,6 +76,7 @@ class Conv2DKernel : public Kernel {
 public:
     explicit Conv2DKernel(Context* c) : Kernel(c) {}
     ~Conv2DKernel() override {
+        if (workspace_) cudaFree(workspace_);
         if (packed_) cudaFree(packed_);
         if (pair_packed_) cudaFree(pair_packed_);
         if (pair_bias_) cudaFree(pair_bias_);
@@ -123,6 +124,19 @@ public:
         filter_is_constant_ = session_ && session_->IsTensorReady(input_tensor_indexes_[1]);
         if (filter_is_constant_)
             OGLE_CUDA_OK(ogle_cuda_conv2d_prepack(&params_, inputs[1]->device<float>(), packed_, context_->stream()));
+        EnsureWorkspace(ogle_cuda_conv2d_workspace_bytes(&params_));
+    }
+
+    // Scratch for layers that split their reduction (long reductions over few tiles): allocated with the
+    // tensors, never in steady state.
+    void EnsureWorkspace(size_t bytes) {
+        if (bytes <= workspace_bytes_) return;
+        if (workspace_) cudaFree(workspace_);
+        workspace_ = nullptr;
+        workspace_bytes_ = 0;
+        cudaError_t e = cudaMalloc(&workspace_, bytes);
+        OGLE_CHECK(e == cudaSuccess) << "cudaMalloc(" << bytes << "): " << cudaGetErrorString(e);
+        workspace_bytes_ = bytes;
     }
 
     void InferOutputShape(TensorShapeList& input_shapes, TensorShapeList& output_shapes) override {
@@ -197,6 +211,7 @@ public:
         pair_params_ = f;
         pair_k1_ = K1;
         pair_split_ = split;
+        EnsureWorkspace(ogle_cuda_conv2d_pair_workspace_bytes(&f, K1, split));
         sibling_ = o;
         kernel_name_ += "+" + o->kernel_name_;
         return true;
@@ -223,16 +238,18 @@ public:
 
     void Compute(TensorList& inputs, TensorList& outputs) override {
         if (sibling_) {
-            OGLE_CUDA_OK(ogle_cuda_conv2d_pair(&pair_params_, inputs[0]->device<float>(), pair_packed_, pair_bias_, pair_k1_,
-                                               pair_split_, outputs[0]->device<float>(),
-                                               sibling_->output_tensors_[0]->device<float>(), context_->stream()));
+            OGLE_CUDA_OK(ogle_cuda_conv2d_pair_ws(&pair_params_, inputs[0]->device<float>(), pair_packed_, pair_bias_, pair_k1_,
+                                                  pair_split_, outputs[0]->device<float>(),
+                                                  sibling_->output_tensors_[0]->device<float>(), workspace_, workspace_bytes_,
+                                                  context_->stream()));
             return;
         }
         if (!filter_is_constant_)
             OGLE_CUDA_OK(ogle_cuda_conv2d_prepack(&params_, inputs[1]->device<float>(), packed_, context_->stream()));
         const float* bias = inputs.size() > 2 ? inputs[2]->device<float>() : nullptr;
         float* y = placed_ ? placed_->device<float>() : outputs[0]->device<float>();
-        OGLE_CUDA_OK(ogle_cuda_conv2d(&params_, inputs[0]->device<float>(), packed_, bias, y, context_->stream()));
+        OGLE_CUDA_OK(ogle_cuda_conv2d_ws(&params_, inputs[0]->device<float>(), packed_, bias, y, workspace_, workspace_bytes_,
+                                         context_->stream()));
     }
 
 private:
@@ -241,6 +258,8 @@ private:
     float min_ = 0.f, max_ = 0.f;
     OgleConvParams params_;
     void* packed_ = nullptr;
+    void* workspace_ = nullptr;
+    size_t workspace_bytes_ = 0;
     bool filter_is_constant_ = false;
     Conv2DKernel* sibling_ = nullptr;       // absorbed later node (not owned)
     Tensor* placed_ = nullptr;              // a concat's tensor this conv writes into (not owned)

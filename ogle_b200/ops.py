@@ -87,19 +87,30 @@ def conv2d_prepack(p, w_oihw):
     return packed
 
 
-def conv2d(p, x4, packed, bias=None, out=None):
+def conv_workspace(p):
+    """Scratch tensor of the size ogle_cuda_conv2d_workspace_bytes asks for (None when the layer wants none)."""
+    n = int(_lib.cuda_lib().ogle_cuda_conv2d_workspace_bytes(C.byref(p)))
+    return torch.empty(n // 4, dtype=torch.float32, device="cuda") if n else None
+
+
+def conv2d(p, x4, packed, bias=None, out=None, workspace="auto"):
+    """workspace: "auto" lends the scratch the layer asks for (what the session does), None lends none,
+    or a float32 device tensor."""
     _require_cuda(x4, packed, bias)
     Ho, Wo, K = p.out_hwc
     ks = p.out_channel_stride or up4(K)
     if out is None:
         out = torch.zeros((p.N, Ho, Wo, ks), dtype=torch.float32, device="cuda") if ks != up4(K) else \
             torch.empty((p.N, Ho, Wo, ks), dtype=torch.float32, device="cuda")
-    check(_lib.cuda_lib().ogle_cuda_conv2d(C.byref(p), _p(x4), _p(packed), _p(bias), _p(out), _stream()), "conv2d")
+    if isinstance(workspace, str):
+        workspace = conv_workspace(p)
+    check(_lib.cuda_lib().ogle_cuda_conv2d_ws(C.byref(p), _p(x4), _p(packed), _p(bias), _p(out), _p(workspace),
+                                               workspace.numel() * 4 if workspace is not None else 0, _stream()), "conv2d")
     return out
 
 
 def conv2d_pair(x4, w1, b1, w2, b2, N, H, W, Cin, kernel, stride=1, pad=0, dilation=1, act=ACT_NONE, lo=0.0, hi=0.0,
-                math_mode=MATH_TF32X3):
+                math_mode=MATH_TF32X3, use_workspace=True):
     """Two convolutions over the same input in one pass (w1/w2 dense OIHW device tensors, b1/b2 device
     vectors or None). Returns (y1, y2) as padded NHWC4 device tensors."""
     _require_cuda(x4, w1, w2, b1, b2)
@@ -121,8 +132,10 @@ def conv2d_pair(x4, w1, b1, w2, b2, N, H, W, Cin, kernel, stride=1, pad=0, dilat
     Ho, Wo, _ = p.out_hwc
     y1 = torch.full((N, Ho, Wo, up4(K1)), float("nan"), dtype=torch.float32, device="cuda")
     y2 = torch.full((N, Ho, Wo, up4(K2)), float("nan"), dtype=torch.float32, device="cuda")
-    check(lib.ogle_cuda_conv2d_pair(C.byref(p), _p(x4), _p(packed), _p(bias), K1, split, _p(y1), _p(y2), _stream()),
-          "conv2d_pair")
+    n_ws = int(lib.ogle_cuda_conv2d_pair_workspace_bytes(C.byref(p), K1, split)) if use_workspace else 0
+    ws = torch.empty(n_ws // 4, dtype=torch.float32, device="cuda") if n_ws else None
+    check(lib.ogle_cuda_conv2d_pair_ws(C.byref(p), _p(x4), _p(packed), _p(bias), K1, split, _p(y1), _p(y2), _p(ws), n_ws,
+                                       _stream()), "conv2d_pair")
     return y1, y2
 
 

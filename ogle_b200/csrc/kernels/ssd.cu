@@ -4,10 +4,10 @@
 // detect: one thread block per image. The block reads the image's logits once,
 // turns them into softmax scores kept in shared memory, and then warps select
 // the top-k per class (or per image): each lane holds its share of the class's
-// scores in registers and the k-th largest is found bit by bit (radix select over
-// shared memory for more than 2048 anchors), followed by a bitonic sort of the
-// <= 256 survivors, so logits and boxes cross HBM exactly once and nothing is
-// staged in global memory.
+// scores in registers, the k-th largest is found by a radix select and the
+// <= 256 survivors are ordered by a stable radix sort (for more than 1952 anchors:
+// radix select over shared memory and a bitonic sort), so logits and boxes cross HBM
+// exactly once and nothing is staged in global memory.
 #include "common.cuh"
 
 namespace ogle {
@@ -148,66 +148,216 @@ __device__ __noinline__ int warp_select_topk(const float* vals, int A, float thr
     return warp_sort_list(list, n);
 }
 
-// Register-resident variant for A <= 32 * kRegPer and thr >= 0: each lane keeps its
-// A/32 scores in registers (0 = not a candidate; candidates are positive floats, which
-// order like their bit patterns), finds the bits of the k-th largest one bit at a time
-// from the top (a count per bit: lane-local compares and one warp reduction, no shared
-// memory, no atomics), then compacts in index order and sorts as above.
-constexpr int kRegPer = 64;
+// Selection for up to 32 * kPer scores and thr >= 0, used by the per-class mode: radix select, then a
+// stable radix sort of the survivors, all inside one warp.
+//  - Lane l owns the contiguous index range [l * per, l * per + per) (per odd, so that the 32 lanes read
+//    different shared-memory banks) and keeps its scores in registers as keys = bits(score) - bits(thr):
+//    positive floats order like their bit patterns, a key of 0 marks "not a candidate", and the keys of
+//    (thr, 1] span only range_bits bits (26 for thr = 0.01).
+//  - The k-th largest key is found digit by digit from the top (9 bits at a time: three passes for 26 bits)
+//    with a 512-bin histogram in the warp's scratch.
+//  - Survivors (keys above the k-th, and the first few equal to it in index order) are written out in index
+//    order - each lane's range is contiguous, so two prefix sums over the lanes place them - and sorted by
+//    key, descending, with a stable LSD radix sort (8 bits at a time, elements held in registers, ranks
+//    within a group of 32 from match.any). Stability keeps equal scores in index order.
+// Scratch (kWarpScratch bytes): select: hist[512] u32 at 0; sort: keys[256] u32 at 0, idx[256] u16 at 1024,
+// digit counts[512] u32 at 1536. On return keys/idx hold the n survivors in output order.
+constexpr int kPer = 61;
+constexpr int kWarpScratch = 3584;
 
-__device__ int warp_select_topk_reg(const float* vals, int A, float thr, int k, unsigned long long* list) {
+__device__ __forceinline__ unsigned warp_excl_scan(unsigned v, unsigned* total) {
+    const int lane = threadIdx.x & 31;
+    unsigned incl = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const unsigned t = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += t;
+    }
+    *total = __shfl_sync(0xffffffffu, incl, 31);
+    return incl - v;
+}
+
+__device__ int warp_topk_radix(const float* vals, int A, float thr, int k, unsigned char* scratch) {
     const int lane = threadIdx.x & 31;
     const unsigned full = 0xffffffffu;
-    unsigned bits[kRegPer];
+    const unsigned thr_bits = __float_as_uint(thr);
+    const unsigned max_key = thr_bits < 0x3f800000u ? 0x3f800000u - thr_bits : 1u;     // scores never exceed 1
+    const int range_bits = 32 - __clz(max_key);
+    const int per = ((A + 31) >> 5) | 1;
+    const int i0 = lane * per;
+    unsigned key[kPer];
     int local = 0;
 #pragma unroll
-    for (int j = 0; j < kRegPer; ++j) {
-        const int i = j * 32 + lane;
-        const float v = i < A ? vals[i] : 0.f;
-        bits[j] = (i < A && v > thr) ? __float_as_uint(v) : 0u;
-        local += bits[j] != 0u;
+    for (int j = 0; j < kPer; ++j) {
+        const int i = i0 + j;
+        unsigned kk = 0;
+        if (j < per && i < A) {
+            const float v = vals[i];
+            if (v > thr) kk = __float_as_uint(v) - thr_bits;
+        }
+        key[j] = kk;
+        local += kk != 0u;
     }
     const int n_valid = __reduce_add_sync(full, local);
     const bool take_all = n_valid <= k;
     unsigned T = 0;
     int need_eq = 0;
     if (!take_all) {
-        unsigned prefix = 0;
+        unsigned* hist = reinterpret_cast<unsigned*>(scratch);
+        unsigned prefix = 0, mask = 0;
         int remaining = k;
-        for (int bit = 30; bit >= 0; --bit) {
-            const unsigned cand = prefix | (1u << bit);
-            const unsigned hi = ~((1u << bit) - 1u);
-            int c = 0;
+        for (int hi_bit = range_bits; hi_bit > 0;) {
+            const int w = hi_bit >= 9 ? 9 : hi_bit;
+            const int shift = hi_bit - w;
+            const unsigned dmask = (1u << w) - 1u;
+            for (int b = lane; b < 512; b += 32) hist[b] = 0;
+            __syncwarp();
 #pragma unroll
-            for (int j = 0; j < kRegPer; ++j) c += (bits[j] & hi) == cand;
-            const int total = __reduce_add_sync(full, c);
-            if (total >= remaining) prefix = cand;      // the k-th largest has this bit set
-            else remaining -= total;                    // all of those rank above it
+            for (int j = 0; j < kPer; ++j) {
+                const unsigned kk = key[j];
+                if (kk != 0u && (kk & mask) == prefix) atomicAdd(&hist[(kk >> shift) & dmask], 1u);
+            }
+            __syncwarp();
+            // lane owns bins [16 * lane, 16 * lane + 16); walk down from the top bin
+            unsigned mine[16];
+            unsigned lane_sum = 0;
+            const uint4* h4 = reinterpret_cast<const uint4*>(hist + lane * 16);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint4 v = h4[q];
+                mine[q * 4 + 0] = v.x; mine[q * 4 + 1] = v.y; mine[q * 4 + 2] = v.z; mine[q * 4 + 3] = v.w;
+                lane_sum += v.x + v.y + v.z + v.w;
+            }
+            unsigned incl = lane_sum;              // sum over this lane and all higher lanes
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const unsigned t = __shfl_down_sync(full, incl, off);
+                if (lane + off < 32) incl += t;
+            }
+            unsigned run = incl - lane_sum;        // candidates in bins above this lane's
+            int found = -1;
+            unsigned cab = 0;
+#pragma unroll
+            for (int q = 15; q >= 0; --q) {
+                if (found < 0 && run < (unsigned)remaining && run + mine[q] >= (unsigned)remaining) {
+                    found = lane * 16 + q;
+                    cab = run;
+                }
+                run += mine[q];
+            }
+            const unsigned who = __ballot_sync(full, found >= 0);
+            const int src = __ffs(who) - 1;        // exactly one lane finds it
+            const int digit = __shfl_sync(full, found, src);
+            cab = __shfl_sync(full, cab, src);
+            prefix |= (unsigned)digit << shift;
+            mask |= dmask << shift;
+            remaining -= (int)cab;
+            hi_bit = shift;
+            __syncwarp();
         }
         T = prefix;
         need_eq = remaining;
     }
-    int n = 0, eq_taken = 0;
+    // survivors in index order
+    unsigned cnt_gt = 0, cnt_eq = 0;
 #pragma unroll
-    for (int j = 0; j < kRegPer; ++j) {
-        if (j * 32 >= A) break;
-        const int i = j * 32 + lane;
-        const unsigned b = bits[j];
-        const bool ok = b != 0u;
-        const bool gt = ok && (take_all || b > T);
-        const bool eq = ok && !take_all && b == T;
-        const unsigned m_eq = __ballot_sync(full, eq);
-        const int eq_rank = eq_taken + __popc(m_eq & ((1u << lane) - 1u));
-        const bool sel = gt || (eq && eq_rank < need_eq);
-        const unsigned m_sel = __ballot_sync(full, sel);
-        if (sel) {
-            const int pos = n + __popc(m_sel & ((1u << lane) - 1u));
-            if (pos < kMaxTopK) list[pos] = ((unsigned long long)b << 32) | (unsigned long long)(0xffffffffu - (unsigned)i);
-        }
-        n += __popc(m_sel);
-        eq_taken += __popc(m_eq);
+    for (int j = 0; j < kPer; ++j) {
+        const unsigned kk = key[j];
+        cnt_gt += (kk != 0u) && (take_all || kk > T);
+        cnt_eq += (kk != 0u) && !take_all && kk == T;
     }
-    return warp_sort_list(list, n);
+    unsigned tot_eq, tot_sel;
+    const unsigned eq_before = warp_excl_scan(cnt_eq, &tot_eq);
+    unsigned take_eq = 0;
+    if ((unsigned)need_eq > eq_before) take_eq = min(cnt_eq, (unsigned)need_eq - eq_before);
+    unsigned pos = warp_excl_scan(cnt_gt + take_eq, &tot_sel);
+    const int n = (int)(tot_sel < (unsigned)kMaxTopK ? tot_sel : (unsigned)kMaxTopK);
+    unsigned* keys = reinterpret_cast<unsigned*>(scratch);
+    unsigned short* idx = reinterpret_cast<unsigned short*>(scratch + 1024);
+    unsigned* counts = reinterpret_cast<unsigned*>(scratch + 1536);
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+        const unsigned kk = key[j];
+        const bool gt = (kk != 0u) && (take_all || kk > T);
+        const bool eq = (kk != 0u) && !take_all && kk == T;
+        bool sel = gt;
+        if (eq && take_eq > 0) { sel = true; --take_eq; }
+        if (sel) {
+            if (pos < (unsigned)kMaxTopK) { keys[pos] = kk; idx[pos] = (unsigned short)(i0 + j); }
+            ++pos;
+        }
+    }
+    __syncwarp();
+    // stable LSD radix sort, descending: eight elements per lane in registers, position p = c * 32 + lane
+    unsigned e_key[8], e_idx[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        const int p = c * 32 + lane;
+        e_key[c] = p < n ? keys[p] : 0u;
+        e_idx[c] = p < n ? idx[p] : 0u;
+    }
+    const int n_chunks = (n + 31) >> 5;
+    for (int shift = 0; shift < range_bits; shift += 9) {
+        for (int b = lane; b < 512; b += 32) counts[b] = 0;
+        __syncwarp();
+        for (int c = 0; c < n_chunks; ++c) {
+            const bool ok = c * 32 + lane < n;
+            const unsigned d = 511u - ((e_key[c] >> shift) & 511u);
+            const unsigned act = __ballot_sync(full, ok);
+            if (ok) {
+                const unsigned peers = __match_any_sync(act, d);
+                if (lane == __ffs(peers) - 1) counts[d] += (unsigned)__popc(peers);
+            }
+            __syncwarp();
+        }
+        // exclusive prefix over the 512 digits (digit 0 = largest key digit comes first)
+        {
+            unsigned v[16], sum = 0;
+            uint4* c4 = reinterpret_cast<uint4*>(counts + lane * 16);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint4 t = c4[q];
+                v[q * 4 + 0] = t.x; v[q * 4 + 1] = t.y; v[q * 4 + 2] = t.z; v[q * 4 + 3] = t.w;
+                sum += t.x + t.y + t.z + t.w;
+            }
+            unsigned tot;
+            unsigned run = warp_excl_scan(sum, &tot);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint4 t;
+                t.x = run; run += v[q * 4 + 0];
+                t.y = run; run += v[q * 4 + 1];
+                t.z = run; run += v[q * 4 + 2];
+                t.w = run; run += v[q * 4 + 3];
+                c4[q] = t;
+            }
+        }
+        __syncwarp();
+        for (int c = 0; c < n_chunks; ++c) {
+            const bool ok = c * 32 + lane < n;
+            const unsigned d = 511u - ((e_key[c] >> shift) & 511u);
+            const unsigned act = __ballot_sync(full, ok);
+            unsigned peers = 0, base = 0;
+            if (ok) {
+                peers = __match_any_sync(act, d);
+                base = counts[d];
+                const unsigned dst = base + (unsigned)__popc(peers & ((1u << lane) - 1u));
+                keys[dst] = e_key[c];
+                idx[dst] = (unsigned short)e_idx[c];
+            }
+            __syncwarp();
+            if (ok && lane == __ffs(peers) - 1) counts[d] = base + (unsigned)__popc(peers);
+            __syncwarp();
+        }
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const int p = c * 32 + lane;
+            if (p < n) { e_key[c] = keys[p]; e_idx[c] = idx[p]; }
+        }
+        __syncwarp();
+    }
+    return n;
 }
 
 struct DetectArgs {
@@ -236,15 +386,20 @@ ssd_detect_kernel(const float* __restrict__ logits, const float4* __restrict__ b
         float* scores = reinterpret_cast<float*>(smem);
         unsigned char* wbase = smem + (size_t)a.classes_per_pass * a.A * sizeof(float);
         wbase += (16 - (reinterpret_cast<uintptr_t>(wbase) & 15)) & 15;
-        unsigned long long* list = reinterpret_cast<unsigned long long*>(wbase + (size_t)warp * 2048);
+        unsigned char* my_scratch = wbase + (size_t)warp * kWarpScratch;
+        unsigned long long* list = reinterpret_cast<unsigned long long*>(my_scratch);
         unsigned* hist = reinterpret_cast<unsigned*>(list);
+        // the radix path: one lane range of at most kPer scores each, 16-bit anchor indices, thr >= 0
+        const bool radix = (((a.A + 31) >> 5) | 1) <= kPer && a.A <= 65535 && a.score_thr >= 0.f;
+        const unsigned thr_bits = __float_as_uint(a.score_thr);
         const int rows = (a.C - 1) * a.top_k;
         const int per_part = (a.C - 1 + parts - 1) / parts;
         const int c_lo = 1 + part * per_part, c_hi = min(a.C, c_lo + per_part);     // this block's classes
         for (int c0 = c_lo; c0 < c_hi; c0 += a.classes_per_pass) {
             const int nc = min(a.classes_per_pass, c_hi - c0);
-            // softmax exactly as the reference post-process does: exp of the raw
-            // logits, summed in class order, then one divide per class
+            // softmax as the reference post-process does it - exp of the raw logits, summed in class
+            // order - with the per-class divide replaced by one IEEE reciprocal of the sum and a
+            // multiply per class (scores within one ulp of the reference's quotient)
             if (nc == c_hi - c_lo && a.C <= 32 && (a.logit_stride & 3) == 0 && a.logit_stride <= 32) {
                 // the whole row in registers: 128-bit loads, every exponential taken once
                 for (int i = tid; i < a.A; i += blockDim.x) {
@@ -260,32 +415,40 @@ ssd_detect_kernel(const float* __restrict__ logits, const float4* __restrict__ b
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
                         if (j < a.C) { e[j] = expf(e[j]); total += e[j]; }
+                    const float inv = 1.0f / total;
 #pragma unroll
                     for (int j = 1; j < 32; ++j)
-                        if (j >= c0 && j < c0 + nc) scores[(j - c0) * a.A + i] = e[j] / total;
+                        if (j >= c0 && j < c0 + nc) scores[(j - c0) * a.A + i] = fminf(e[j] * inv, 1.0f);
                 }
             } else {
                 for (int i = tid; i < a.A; i += blockDim.x) {
                     const float* row = lg + (long)i * a.logit_stride;
                     float total = 0.f;
                     for (int j = 0; j < a.C; ++j) total += expf(row[j]);
-                    for (int j = 0; j < nc; ++j) scores[j * a.A + i] = expf(row[c0 + j]) / total;
+                    const float inv = 1.0f / total;
+                    for (int j = 0; j < nc; ++j) scores[j * a.A + i] = fminf(expf(row[c0 + j]) * inv, 1.0f);
                 }
             }
             __syncthreads();
             for (int j = warp; j < nc; j += nwarps) {
                 const int cls = c0 + j;
-                const int cnt = (a.A <= 32 * kRegPer && a.score_thr >= 0.f)
-                                    ? warp_select_topk_reg(scores + j * a.A, a.A, a.score_thr, a.top_k, list)
-                                    : warp_select_topk(scores + j * a.A, a.A, a.score_thr, a.top_k, list, hist);
+                const int cnt = radix ? warp_topk_radix(scores + j * a.A, a.A, a.score_thr, a.top_k, my_scratch)
+                                      : warp_select_topk(scores + j * a.A, a.A, a.score_thr, a.top_k, list, hist);
+                const unsigned* r_keys = reinterpret_cast<const unsigned*>(my_scratch);
+                const unsigned short* r_idx = reinterpret_cast<const unsigned short*>(my_scratch + 1024);
                 const long base = (long)n * rows + (long)(cls - 1) * a.top_k;
                 for (int r = lane; r < a.top_k; r += 32) {
                     float sc = 0.f; int an = -1;
                     float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (r < cnt) {
-                        const unsigned long long key = list[r];
-                        sc = __uint_as_float((unsigned)(key >> 32));
-                        an = (int)(0xffffffffu - (unsigned)(key & 0xffffffffull));
+                        if (radix) {
+                            sc = __uint_as_float(r_keys[r] + thr_bits);
+                            an = (int)r_idx[r];
+                        } else {
+                            const unsigned long long key = list[r];
+                            sc = __uint_as_float((unsigned)(key >> 32));
+                            an = (int)(0xffffffffu - (unsigned)(key & 0xffffffffull));
+                        }
                         b = bx[an];
                     }
                     out_score[base + r] = sc;
@@ -425,7 +588,7 @@ int ogle_cuda_ssd_detect(const OgleDetectParams* p, const float* logits, const f
     a.image_w = p->image_w; a.image_h = p->image_h; a.score_thr = p->score_thr; a.nms_thr = p->nms_thr;
     a.frames = p->mode == 0 ? p->frame_sizes : nullptr;
     if (a.frames && (reinterpret_cast<uintptr_t>(a.frames) & 7)) return OGLE_ERR_ALIGNMENT;
-    static const size_t kSmemBudget = 200 * 1024;
+    static const size_t kSmemBudget = 224 * 1024;
     int threads;
     size_t smem;
     if (p->mode == 1) {
@@ -433,21 +596,21 @@ int ogle_cuda_ssd_detect(const OgleDetectParams* p, const float* logits, const f
         // blocks share an SM and the batch is a few rounds of SMs at most (more, smaller blocks
         // fill the last round better; for large batches the softmax done twice costs more than
         // that gains); one warp per class, ~100 registers each.
-        const size_t per_warp = 2048;
+        const size_t per_warp = kWarpScratch;
         const size_t per_class = (size_t)p->A * sizeof(float);
         const int fg = p->C - 1;
         a.parts = 1;
         if (fg >= 8 && p->N <= 4 * kNumSMs) {
             const int half = (fg + 1) / 2;
             const size_t need = (size_t)half * per_class + per_warp * (size_t)half + 16;
-            if (need <= 108 * 1024) a.parts = 2;
+            if (need <= 112 * 1024) a.parts = 2;
         }
         const int classes = (fg + a.parts - 1) / a.parts;
         int warps = classes < 20 ? classes : 20;
         if (warps < 1) warps = 1;
         threads = warps * 32;
         const size_t warp_bytes = per_warp * (size_t)warps + 16;
-        const size_t budget = a.parts == 2 ? 108 * 1024 : kSmemBudget;
+        const size_t budget = a.parts == 2 ? 112 * 1024 : kSmemBudget;
         if (per_class + warp_bytes > budget) return OGLE_ERR_UNSUPPORTED;
         size_t cpp = (budget - warp_bytes) / per_class;
         if (cpp > (size_t)classes) cpp = classes;
@@ -465,7 +628,7 @@ int ogle_cuda_ssd_detect(const OgleDetectParams* p, const float* logits, const f
     cudaGetDevice(&dev);
     if (attr_set_for_device != dev) {
         cudaError_t e = cudaFuncSetAttribute(ssd_detect_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)(kSmemBudget + 4096));
+                                             (int)(kSmemBudget + 2048));
         if (e != cudaSuccess) { set_last_error(e); return OGLE_ERR_CUDA; }
         attr_set_for_device = dev;
     }

@@ -40,6 +40,36 @@ inline int grid_for(long items, int threads, int max_per_sm = 8) {
     return int(blocks);
 }
 
+// Programmatic dependent launch. A kernel launched through launch_overlapped() may be scheduled while
+// the kernel before it on the stream is still running: its blocks start as that kernel's blocks retire,
+// do their set-up (shared-memory barriers, tensor-memory allocation, index tables) and only then wait
+// for the predecessor's results. Every kernel launched that way calls grid_dependency_wait() before its
+// first access to global memory that another kernel may write or read, and
+// grid_dependency_trigger() at its top, which lets ITS successor be scheduled early in turn. Both are
+// no-ops in a kernel launched the ordinary way. In a captured graph the dependency becomes a programmatic
+// edge; a predecessor that is not a kernel (memset, copy, event wait) keeps an ordinary, full dependency.
+// Off by default (every launch is then an ordinary one); OGLE_PDL=1 turns it on.
+__device__ __forceinline__ void grid_dependency_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+bool overlapped_launches_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = overlapped_launches_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float apply_act(float v, int act, float lo, float hi) {
     // conv2d.glsl:82-90: clip is min(max(v,lo),hi), relu is max(0,v)
     if (act == OGLE_ACT_CLIP) return fminf(fmaxf(v, lo), hi);

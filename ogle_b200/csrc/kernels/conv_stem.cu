@@ -69,15 +69,17 @@ conv3x3_smallc_kernel(const __grid_constant__ CUtensorMap tmX, const float* __re
     const uint32_t base = smem_u32(smem_raw) + w_bytes;
     const float4* stage0 = reinterpret_cast<const float4*>(smem_raw + w_bytes);
 
+    grid_dependency_trigger();
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kStemStages; ++i) mbar_init(&bar_full[i], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    grid_dependency_wait();         // nothing from global memory before this point
     for (int i = threadIdx.x; i < wn; i += blockDim.x) {
         const int k = i % Kp, c = (i / Kp) % CIN, tap = i / (Kp * CIN);
         s_w[i] = c < a.C ? w[(tap * a.Cp + c) * Kp + k] : 0.f;     // tap-major packed filter
     }
     for (int i = threadIdx.x; i < Kp; i += blockDim.x) s_w[wn + i] = (a.has_bias && i < a.K) ? bias[i] : 0.f;
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < kStemStages; ++i) mbar_init(&bar_full[i], 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
     __syncthreads();
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -253,7 +255,8 @@ int launch(const ConvArgs& a, const StemTiles& tl, const float* x, const float* 
     }
     int blocks = kNumSMs * 2;
     if (blocks > tl.total) blocks = tl.total;
-    conv3x3_smallc_kernel<S, PXT, CIN, KP><<<(unsigned)blocks, 256, smem, s>>>(mX, w, bias, y, a, tl, error_flag_ptr());
+    launch_overlapped(conv3x3_smallc_kernel<S, PXT, CIN, KP>, dim3((unsigned)blocks), dim3(256), smem, s, mX, w, bias, y, a, tl,
+                      error_flag_ptr());
     return finish_launch();
 }
 

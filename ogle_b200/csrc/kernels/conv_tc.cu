@@ -143,6 +143,8 @@ splitk_reduce_kernel(const float4* __restrict__ ws, int slices, long slice_q, in
                      const float* __restrict__ bias, int act, float lo, float hi,
                      float4* __restrict__ y, int Ks_q, int koff_q, int K, int out_q,
                      float4* __restrict__ y2, int split_col, int K2, int out2_q) {
+    grid_dependency_trigger();
+    grid_dependency_wait();
     const int per_row = out_q + out2_q;
     const long total = rows * per_row;
     for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
@@ -387,10 +389,11 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
             const long slice_q = (long)(slice_bytes / 16);
             const int out_q = kp_a / 4, out2_q = y2 ? kp_b / 4 : 0;
             const long items = rows * (out_q + out2_q);
-            splitk_reduce_kernel<<<grid_for(items, 256), 256, 0, s>>>(
-                reinterpret_cast<const float4*>(ws), t.split_k, slice_q, ws_cols / 4, rows, a.has_bias ? bias : nullptr, act, lo, hi,
-                reinterpret_cast<float4*>(y), ks_a / 4, a.koff / 4, y2 ? K1 : a.K, out_q,
-                reinterpret_cast<float4*>(y2), split_col, y2 ? a.K - split_col : 0, out2_q);
+            launch_overlapped(splitk_reduce_kernel, dim3(grid_for(items, 256)), dim3(256), 0, s,
+                              reinterpret_cast<const float4*>(ws), t.split_k, slice_q, ws_cols / 4, rows,
+                              a.has_bias ? bias : (const float*)nullptr, act, lo, hi, reinterpret_cast<float4*>(y), ks_a / 4,
+                              a.koff / 4, y2 ? K1 : a.K, out_q, reinterpret_cast<float4*>(y2), split_col,
+                              y2 ? a.K - split_col : 0, out2_q);
             return finish_launch();
         }
         if (t.split_k > 1) {

@@ -136,6 +136,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     __shared__ __align__(16) float s_bias[2][256];
     __shared__ __align__(8) short s_goff[kMaxGatherK];   // gather form: window offset of each reduction index
 
+    grid_dependency_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool split = a.passes == 3;
     const uint32_t b_bytes = (uint32_t)a.BN * 128u;
@@ -202,6 +203,8 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = tmem_slot;
+    // barriers, tensor memory and tables are set up; what follows reads and writes global memory
+    grid_dependency_wait();
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -666,8 +669,10 @@ int launch_tc_v2(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, cons
     }
     const int sms = num_sms();
     const unsigned grid = (unsigned)(t.total_work < sms ? t.total_work : sms);
-    if (t.split_k > 1) conv_tc2_kernel<true><<<grid, kThreads2, smem, s>>>(mA, mBhi, mBlo, mY, mY2, bias, t, err_flag);
-    else conv_tc2_kernel<false><<<grid, kThreads2, smem, s>>>(mA, mBhi, mBlo, mY, mY2, bias, t, err_flag);
+    if (t.split_k > 1)
+        launch_overlapped(conv_tc2_kernel<true>, dim3(grid), dim3(kThreads2), smem, s, mA, mBhi, mBlo, mY, mY2, bias, t, err_flag);
+    else
+        launch_overlapped(conv_tc2_kernel<false>, dim3(grid), dim3(kThreads2), smem, s, mA, mBhi, mBlo, mY, mY2, bias, t, err_flag);
     return finish_launch();
 }
 

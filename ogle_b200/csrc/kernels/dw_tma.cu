@@ -54,10 +54,12 @@ dw3x3_tma_kernel(const __grid_constant__ CUtensorMap tmX, const float4* __restri
     const int col = slot % TW, rg = slot / TW;
     const bool active = rg < tl.row_groups;        // slots past tw * row_groups idle
 
+    grid_dependency_trigger();
     if (threadIdx.x == 0) {
         for (int i = 0; i < kDwMaxStages; ++i) mbar_init(&bar_full[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    grid_dependency_wait();         // nothing from global memory before this point
     __syncthreads();
 
     // tile id -> (channel slab fastest, then x, y, image): neighbouring blocks share halo rows in L2
@@ -183,8 +185,8 @@ int launch(const ConvArgs& a, const DwTiles& shape, const float* x, const float*
     // a multiple of the channel-slab count: block b then always works on slab b % cblocks
     if (tl.cblocks <= blocks) blocks -= blocks % tl.cblocks;
     if (blocks > tl.total) blocks = tl.total;
-    dw3x3_tma_kernel<S, RPG><<<(unsigned)blocks, 256, smem, s>>>(mX, reinterpret_cast<const float4*>(w), bias,
-                                                               reinterpret_cast<float4*>(y), a, tl, error_flag_ptr());
+    launch_overlapped(dw3x3_tma_kernel<S, RPG>, dim3((unsigned)blocks), dim3(256), smem, s, mX, reinterpret_cast<const float4*>(w),
+                      bias, reinterpret_cast<float4*>(y), a, tl, error_flag_ptr());
     return finish_launch();
 }
 

@@ -9,6 +9,8 @@ enum { EW_RELU = 0, EW_CLIP = 1, EW_ADD = 2, EW_ADD_RELU = 3, EW_ADD_CLIP = 4 };
 template <int OP>
 __global__ void elementwise_kernel(const float4* __restrict__ a, const float4* __restrict__ b,
                                    float4* __restrict__ y, long n4, float lo, float hi) {
+    grid_dependency_trigger();
+    grid_dependency_wait();
     for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n4;
          i += (long)gridDim.x * blockDim.x) {
         float4 v = a[i];
@@ -71,9 +73,9 @@ static int launch_elementwise(const float* a, const float* b, float* y, long n, 
     if (n == 0) return OGLE_OK;
     if (!a || !y || (OP >= EW_ADD && !b)) return OGLE_ERR_INVALID;
     if (!aligned16(a) || !aligned16(y) || (b && !aligned16(b))) return OGLE_ERR_ALIGNMENT;
-    elementwise_kernel<OP><<<grid_for(n / 4, 256), 256, 0, (cudaStream_t)stream>>>(
-        reinterpret_cast<const float4*>(a), reinterpret_cast<const float4*>(b),
-        reinterpret_cast<float4*>(y), n / 4, lo, hi);
+    launch_overlapped(elementwise_kernel<OP>, dim3(grid_for(n / 4, 256)), dim3(256), 0, (cudaStream_t)stream,
+                      reinterpret_cast<const float4*>(a), reinterpret_cast<const float4*>(b), reinterpret_cast<float4*>(y), n / 4,
+                      lo, hi);
     return finish_launch();
 }
 

@@ -8,6 +8,8 @@ namespace ogle {
 // [rows][last] dense -> [rows][stride], zero fill. One thread per output float4.
 __global__ void pad4_kernel(const float* __restrict__ src, float* __restrict__ dst,
                             long rows, int last, int stride) {
+    grid_dependency_trigger();
+    grid_dependency_wait();
     const int q = stride >> 2;
     const long total = rows * q;
     for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total;
@@ -90,6 +92,8 @@ __global__ void transpose_kernel(const float* __restrict__ x, float* __restrict_
 template <typename Index>
 __global__ void reshape_kernel(const float* __restrict__ x, float4* __restrict__ y,
                                Index n, int in_last, int out_last, Index rows_per_block, long block_stride_q) {
+    grid_dependency_trigger();
+    grid_dependency_wait();
     const int ip = (in_last + 3) & ~3, oq = ((out_last + 3) & ~3) >> 2;
     const Index total = n / out_last * oq;
     for (Index i = blockIdx.x * (Index)blockDim.x + threadIdx.x; i < total; i += (Index)gridDim.x * blockDim.x) {
@@ -152,6 +156,8 @@ __device__ __forceinline__ bool concat_fetch(const ConcatArgs& a, Index i, int q
 
 template <typename Index>
 __global__ void __launch_bounds__(256) concat_vec_kernel(ConcatArgs a, float4* __restrict__ y) {
+    grid_dependency_trigger();
+    grid_dependency_wait();
     const int q = ((a.os[3] + 3) & ~3) >> 2;
     const Index total = (Index)a.os[0] * a.os[1] * a.os[2] * q;
     const Index step = (Index)gridDim.x * blockDim.x;
@@ -213,7 +219,7 @@ int ogle_cuda_pad4(const float* dense, float* padded, long rows, int last, int s
     if (!dense || !padded) return OGLE_ERR_INVALID;
     if (!aligned16(padded)) return OGLE_ERR_ALIGNMENT;
     const long items = rows * (stride / 4);
-    pad4_kernel<<<grid_for(items, 256), 256, 0, (cudaStream_t)stream>>>(dense, padded, rows, last, stride);
+    launch_overlapped(pad4_kernel, dim3(grid_for(items, 256)), dim3(256), 0, (cudaStream_t)stream, dense, padded, rows, last, stride);
     return finish_launch();
 }
 
@@ -270,11 +276,12 @@ static int launch_reshape(const float* x, float* y, long n_elements, int in_last
     }
     const long vecs = items / 4;
     if (n_elements < 0x7fffffffL && items < 0x7fffffffL && extent < 0x7fffffffL)     // 32-bit index arithmetic when it fits (the usual case)
-        reshape_kernel<unsigned><<<grid_for(vecs, 256), 256, 0, (cudaStream_t)stream>>>(
-            x, reinterpret_cast<float4*>(y), (unsigned)n_elements, in_last, out_last, (unsigned)rows_per_block, block_stride / 4);
+        launch_overlapped(reshape_kernel<unsigned>, dim3(grid_for(vecs, 256)), dim3(256), 0, (cudaStream_t)stream,
+                          x, reinterpret_cast<float4*>(y), (unsigned)n_elements, in_last, out_last, (unsigned)rows_per_block,
+                          block_stride / 4);
     else
-        reshape_kernel<long><<<grid_for(vecs, 256), 256, 0, (cudaStream_t)stream>>>(
-            x, reinterpret_cast<float4*>(y), n_elements, in_last, out_last, rows_per_block, block_stride / 4);
+        launch_overlapped(reshape_kernel<long>, dim3(grid_for(vecs, 256)), dim3(256), 0, (cudaStream_t)stream,
+                          x, reinterpret_cast<float4*>(y), n_elements, in_last, out_last, rows_per_block, block_stride / 4);
     return finish_launch();
 }
 
@@ -322,11 +329,11 @@ int ogle_cuda_concat(const OgleConcatParams* p, const float* const* inputs, floa
     if (vec_ok) {
         const long vecs = rows * (op / 4);
         if (vecs + 4L * kNumSMs * 8 * 256 < (1L << 31))
-            concat_vec_kernel<int><<<grid_for(vecs, 256), 256, 0, (cudaStream_t)stream>>>(
-                a, reinterpret_cast<float4*>(y));
+            launch_overlapped(concat_vec_kernel<int>, dim3(grid_for(vecs, 256)), dim3(256), 0, (cudaStream_t)stream, a,
+                              reinterpret_cast<float4*>(y));
         else
-            concat_vec_kernel<long><<<grid_for(vecs, 256), 256, 0, (cudaStream_t)stream>>>(
-                a, reinterpret_cast<float4*>(y));
+            launch_overlapped(concat_vec_kernel<long>, dim3(grid_for(vecs, 256)), dim3(256), 0, (cudaStream_t)stream, a,
+                              reinterpret_cast<float4*>(y));
     } else {
         concat_scalar_kernel<<<grid_for(rows * op, 256), 256, 0, (cudaStream_t)stream>>>(a, y);
     }

@@ -14,6 +14,8 @@ namespace ogle {
 
 __global__ void ssd_decode_kernel(const float4* __restrict__ pred, const float4* __restrict__ anchors,
                                   float4* __restrict__ out, long total, int A, float4 var) {
+    grid_dependency_trigger();
+    grid_dependency_wait();
     for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total;
          i += (long)gridDim.x * blockDim.x) {
         const float4 p = pred[i];
@@ -376,6 +378,8 @@ ssd_detect_kernel(const float* __restrict__ logits, const float4* __restrict__ b
                   float* __restrict__ out_score, int* __restrict__ out_anchor, int* __restrict__ out_class,
                   float4* __restrict__ out_box, int* __restrict__ out_count, DetectArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
+    grid_dependency_trigger();
+    grid_dependency_wait();
     const int parts = a.mode == 1 ? a.parts : 1;
     const int n = blockIdx.x / parts, part = blockIdx.x - n * parts;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
@@ -567,9 +571,9 @@ int ogle_cuda_ssd_decode(const float* pred, const float* anchors, float* out, in
     if (!aligned16(pred) || !aligned16(anchors) || !aligned16(out)) return OGLE_ERR_ALIGNMENT;
     const long total = (long)N * A;
     const float4 var = make_float4(variances[0], variances[1], variances[2], variances[3]);
-    ssd_decode_kernel<<<grid_for(total, 256), 256, 0, (cudaStream_t)stream>>>(
-        reinterpret_cast<const float4*>(pred), reinterpret_cast<const float4*>(anchors),
-        reinterpret_cast<float4*>(out), total, A, var);
+    launch_overlapped(ssd_decode_kernel, dim3(grid_for(total, 256)), dim3(256), 0, (cudaStream_t)stream,
+                      reinterpret_cast<const float4*>(pred), reinterpret_cast<const float4*>(anchors),
+                      reinterpret_cast<float4*>(out), total, A, var);
     return finish_launch();
 }
 
@@ -632,9 +636,9 @@ int ogle_cuda_ssd_detect(const OgleDetectParams* p, const float* logits, const f
         if (e != cudaSuccess) { set_last_error(e); return OGLE_ERR_CUDA; }
         attr_set_for_device = dev;
     }
-    ssd_detect_kernel<<<p->N * (p->mode == 1 ? a.parts : 1), threads, smem, (cudaStream_t)stream>>>(
-        logits, reinterpret_cast<const float4*>(boxes), out_score, out_anchor, out_class,
-        reinterpret_cast<float4*>(out_box), out_count, a);
+    launch_overlapped(ssd_detect_kernel, dim3(p->N * (p->mode == 1 ? a.parts : 1)), dim3(threads), smem, (cudaStream_t)stream,
+                      logits, reinterpret_cast<const float4*>(boxes), out_score, out_anchor, out_class,
+                      reinterpret_cast<float4*>(out_box), out_count, a);
     return finish_launch();
 }
 

@@ -94,6 +94,14 @@ typedef struct {
     int out_channel_stride;  /* floats per output pixel; 0 = round_up(K,4)  */
     int out_channel_offset;  /* first output channel lands here (mult of 4) */
     int math_mode;           /* OgleMathMode */
+    int n_tile;              /* tensor-core path: output channels per tile (a multiple of 32, at most
+                                256 and round_up(K,32)); 0 = chosen by the library. Results do not
+                                depend on it bit for bit (each output value sums its reduction in the
+                                same order); a caller may time the candidates and keep the fastest. */
+    int split;               /* tensor-core path: ranges the reduction is split into (1 = not split, up to
+                                16; more than 2, or any with an activation, needs the scratch of
+                                ogle_cuda_conv2d_ws); 0 = chosen by the library. Unlike n_tile this changes the
+                                order in which a value's partial sums are added. */
 } OgleConvParams;
 
 /* Output size rule of Conv2DKernel::InferOutputShape (conv2d.cc:169-195).

@@ -39,6 +39,9 @@ void ogle_session_destroy(OgleSession* s);
  * Add runs in the Add's pass; the Add's own tensor is then not readable), "fuse_concats" (0/1: a Conv
  * or re-padding Reshape whose result only a Concat reads writes into its slice of the Concat's tensor; a
  * Concat with every slice written that way is dropped; the producers' own tensors are then not readable),
+ * "tune" (0/1: after set-up every convolution served by the tensor cores times its tile widths on its own
+ * tensors and keeps the fastest; the reduction of a layer may then be split differently from session to
+ * session, i.e. results can differ in the last bits between sessions, never between runs of one),
  * "streams" (1..8: streams the captured graph's independent
  * branches are recorded on; 1 = file order, as the reference runs). Set before the first run. */
 int ogle_session_set_option(OgleSession* s, const char* key, int value);

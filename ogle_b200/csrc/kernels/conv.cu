@@ -107,6 +107,10 @@ static int fill_args(const OgleConvParams* p, ConvArgs* a, int* variant) {
     a->Kp = up4(K);
     a->has_bias = p->has_bias ? 1 : 0;
     a->M = (long)p->N * Ho * Wo;
+    if (p->n_tile < 0 || p->n_tile > 256 || (p->n_tile & 31)) return OGLE_ERR_INVALID;
+    a->n_tile = p->n_tile;
+    if (p->split < 0 || p->split > 16) return OGLE_ERR_INVALID;
+    a->split = p->split;
     // activation, with the per-shader differences of the reference kept:
     //   pointwise clip clamps to [0, max] (conv2d_pw.glsl:85);
     //   grouped relu is max(min_value, v) (conv2d_grp.glsl:121).

@@ -15,6 +15,8 @@ struct ConvArgs {
     float lo, hi;
     int has_bias;
     long M;                    // N*Ho*Wo output pixels
+    int n_tile;                // requested output channels per tile of the tensor-core path (0 = choose)
+    int split;                 // requested number of reduction ranges (0 = choose)
 };
 
 // Packed filter blob, in this order (all sections 256-byte aligned):

@@ -57,7 +57,7 @@ using namespace tc;
 // tile's time modelled by its tensor-core instructions: one instruction costs about 100
 // cycles up to ~180 columns (bound by the shared-memory fetch of its 128-row A operand)
 // and 0.55 cycles per column beyond.
-void choose_n_tiling_v2(int Kp, long m_tiles, TcArgs* t) {
+void choose_n_tiling_v2(int Kp, long m_tiles, TcArgs* t, int requested = 0) {
     const int kmax = (Kp + 31) / 32 * 32;
     auto mma = [](int n) { const double c = 0.55 * n; return c < 100.0 ? 100.0 : c; };
     int best_bn = 32;
@@ -78,6 +78,7 @@ void choose_n_tiling_v2(int Kp, long m_tiles, TcArgs* t) {
         const int v = atoi(e);
         if (v >= 32 && v <= 256 && v % 32 == 0 && v <= kmax) best_bn = v;
     }
+    if (requested >= 32 && requested <= 256 && requested % 32 == 0 && requested <= kmax) best_bn = requested;
     t->BN = best_bn;
     t->n_tiles = (Kp + best_bn - 1) / best_bn;
 }
@@ -305,7 +306,7 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
             }
         }
     }
-    choose_n_tiling_v2(a.Kp, m_tiles, &t);
+    choose_n_tiling_v2(a.Kp, m_tiles, &t, a.n_tile);
     const int Kp128 = (a.K + 127) / 128 * 128;
     const cuuint64_t bcols = t.gather ? (cuuint64_t)t.Cp32 : (cuuint64_t)taps * t.Cp32;
     const cuuint64_t bdims[2] = {bcols, (cuuint64_t)Kp128};
@@ -354,6 +355,17 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
                     const double c = cost_of(k) + 10.0 + 0.5 * k;
                     if (c < 0.85 * best) { best = c; best_k = k; best_ws = true; }
                 }
+            }
+            if (a.split >= 1) {
+                // the caller's choice, as far as it can be served: the in-place form for two ranges without an
+                // activation, else the scratch form when scratch of the right size was lent
+                int k = a.split;
+                while (k > 1 && chunks / k < 1) --k;
+                const bool fits = ws_usable && !t.gather && (plan_only || slice_bytes * k <= ws_bytes) &&
+                                  slice_bytes * k <= ((size_t)192 << 20);
+                if (k == 1) { best_k = 1; best_ws = false; }
+                else if (k == 2 && a.act == OGLE_ACT_NONE && !fits) { best_k = 2; best_ws = false; }
+                else if (fits) { best_k = k; best_ws = true; }
             }
             t.split_k = best_k;
             t.ws_mode = best_ws ? 1 : 0;

@@ -98,6 +98,8 @@ int ogle_session_set_option(OgleSession* s, const char* key, int value) {
             s->session->set_fuse_activations(value != 0);
         } else if (k == "fuse_concats") {
             s->session->set_fuse_concats(value != 0);
+        } else if (k == "tune") {
+            s->session->set_tune(value != 0);
         } else if (k == "streams") {
             s->session->set_streams(value);
         } else {

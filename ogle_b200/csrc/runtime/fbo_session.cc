@@ -19,6 +19,7 @@ FBOSession::FBOSession(Context* context) : context_(context) {
     if (const char* g = std::getenv("OGLE_FUSE_SIBLINGS")) fuse_siblings_ = std::atoi(g) != 0;
     if (const char* g = std::getenv("OGLE_FUSE_ACTIVATIONS")) fuse_activations_ = std::atoi(g) != 0;
     if (const char* g = std::getenv("OGLE_FUSE_CONCATS")) fuse_concats_ = std::atoi(g) != 0;
+    if (const char* g = std::getenv("OGLE_TUNE")) tune_ = std::atoi(g) != 0;
     if (const char* g = std::getenv("OGLE_STREAMS")) set_streams(std::atoi(g));
 }
 
@@ -158,6 +159,9 @@ void FBOSession::Finalize() {
     if (fuse_activations_) FuseActivations();
     num_placed_ = 0;
     if (fuse_concats_) FuseConcats();
+    context_->Synchronize();
+    if (tune_)
+        for (Kernel* k : active_) k->Tune();
     context_->Synchronize();
     finalized_ = true;
 }

@@ -74,6 +74,10 @@ public:
     // tensors are then not produced; GetOutputs on them fails with a message naming this
     // switch (default on; OGLE_FUSE_CONCATS=0 disables). Set before the first Run.
     void set_fuse_concats(bool flag) { fuse_concats_ = flag; }
+    // Launch tuning: after set-up every node may time variants of its launch that give identical results
+    // and keep the fastest (convolutions on the tensor cores: the tile width). Default on; OGLE_TUNE=0
+    // disables. Set before the first Run.
+    void set_tune(bool flag) { tune_ = flag; }
     int num_placed() const { return num_placed_; }
     // Branch overlap: the captured graph keeps only the true data dependencies between
     // nodes, recorded over up to `n` streams, so that independent branches (the SSD heads
@@ -121,6 +125,7 @@ private:
     bool fuse_siblings_ = true;
     bool fuse_activations_ = true;
     bool fuse_concats_ = true;
+    bool tune_ = true;
     int num_placed_ = 0;
     std::vector<bool> elided_;                // tensors no node produces any more (activation / concat fusion)
     std::vector<std::string> elided_why_;     // per tensor: the switch that keeps it

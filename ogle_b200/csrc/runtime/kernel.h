@@ -55,6 +55,10 @@ public:
     virtual bool AbsorbConsumer(Kernel* consumer) { return false; }
     // For AbsorbConsumer implementations: the activation a node applies, if it is one.
     virtual bool AsActivation(int* act, float* lo, float* hi) const { return false; }
+    // Called once by the session after every tensor exists and the fusions are decided: a node may time
+    // variants of its launch that give identical results (on its real tensors, whatever they hold) and keep
+    // the fastest. Default: nothing to choose.
+    virtual void Tune() {}
     // Concat in place. A concat-like node describes where its input i lies inside its output:
     // the input is `outer` rows of `chunk` floats, and row r belongs at
     // output + r * row_stride + offset (floats, padded layouts on both sides). False when the

@@ -236,6 +236,61 @@ public:
         return true;
     }
 
+    // The tensor-core path's tile width (output channels per tile) decides how many tiles a layer has, how
+    // deep its operand ring is and how long a tile's epilogue takes; which width wins depends on the batch
+    // (rounds of tiles over the SMs) in ways a cost model only approximates. Every width gives the same bits,
+    // so the layer simply times the candidates on its own tensors and keeps the fastest; then, at that width, the
+    // number of ranges its reduction is split into (which does change the order of the partial sums).
+    void Tune() override {
+        OgleConvParams& p = sibling_ ? pair_params_ : params_;
+        if (!filter_is_constant_ || std::string(ogle_cuda_conv2d_kernel_name(&p)) != "conv_tc2_kernel") return;
+        cudaStream_t s = reinterpret_cast<cudaStream_t>(context_->stream());
+        cudaEvent_t e0, e1;
+        if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return;
+        const int kmax = (p.out_hwc[2] + 31) / 32 * 32;
+        auto workspace_for = [&] {
+            EnsureWorkspace(sibling_ ? ogle_cuda_conv2d_pair_workspace_bytes(&p, pair_k1_, pair_split_)
+                                     : ogle_cuda_conv2d_workspace_bytes(&p));
+        };
+        auto time_it = [&](float* ms) {
+            workspace_for();
+            Kernel::Compute();                                          // warm-up
+            cudaEventRecord(e0, s);
+            for (int r = 0; r < 3; ++r) Kernel::Compute();
+            cudaEventRecord(e1, s);
+            if (cudaEventSynchronize(e1) != cudaSuccess) return false;
+            return cudaEventElapsedTime(ms, e0, e1) == cudaSuccess;
+        };
+        float auto_ms = 0.f, best_ms = 0.f;
+        p.n_tile = 0;
+        p.split = 0;
+        if (time_it(&auto_ms)) {
+            best_ms = auto_ms;
+            int best_tile = 0, best_split = 0;
+            for (int bn = 32; bn <= 256 && bn <= kmax; bn += 32) {          // tile widths, the library's split rule
+                float ms;
+                p.n_tile = bn;
+                if (time_it(&ms) && ms < best_ms) { best_ms = ms; best_tile = bn; }
+            }
+            p.n_tile = best_tile;
+            static const int splits[] = {1, 2, 3, 4, 6, 8, 12, 16};          // then the reduction split at that width
+            for (int k : splits) {
+                float ms;
+                p.split = k;
+                if (time_it(&ms) && ms < best_ms) { best_ms = ms; best_split = k; }
+            }
+            if (best_ms > 0.97f * auto_ms) { best_tile = 0; best_split = 0; }   // within noise of the defaults: keep them
+            p.n_tile = best_tile;
+            p.split = best_split;
+            tuned_tile_ = best_tile;
+            tuned_split_ = best_split;
+        }
+        workspace_for();
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+    }
+    int tuned_tile() const { return tuned_tile_; }
+
     void Compute(TensorList& inputs, TensorList& outputs) override {
         if (sibling_) {
             OGLE_CUDA_OK(ogle_cuda_conv2d_pair_ws(&pair_params_, inputs[0]->device<float>(), pair_packed_, pair_bias_, pair_k1_,
@@ -263,6 +318,7 @@ private:
     bool filter_is_constant_ = false;
     Conv2DKernel* sibling_ = nullptr;       // absorbed later node (not owned)
     Tensor* placed_ = nullptr;              // a concat's tensor this conv writes into (not owned)
+    int tuned_tile_ = 0, tuned_split_ = 0;
     OgleConvParams pair_params_;
     void* pair_packed_ = nullptr;
     float* pair_bias_ = nullptr;

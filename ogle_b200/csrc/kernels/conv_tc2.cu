@@ -166,6 +166,14 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int rows_in_tile = a.flat ? kTileM : a.tn * a.th * a.tw;
     volatile int* abort_flag = &s_abort;
 
+    if (threadIdx.x == 32 * 18) {
+        // the copy descriptors are fetched while the barriers and tensor memory are being set up
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmA)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmBhi)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmBlo)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmY)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmY2)) : "memory");
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
             mbar_init(&bar_full[s], 2);     // one arrive.expect_tx from each producer
@@ -559,8 +567,9 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     }
                 }
             }
-            // the staging slabs must outlive the stores that read them
-            if (t == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            // the staging slabs must outlive the stores that read them (their writes to global memory are
+            // complete, like every write of the grid, when the grid is)
+            if (t == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         }
     }
 

@@ -102,6 +102,10 @@ typedef struct {
                                 16; more than 2, or any with an activation, needs the scratch of
                                 ogle_cuda_conv2d_ws); 0 = chosen by the library. Unlike n_tile this changes the
                                 order in which a value's partial sums are added. */
+    int sm_pair;             /* tensor-core path: 2 = compute tiles of 256 pixels on pairs of SMs (each SM of a
+                                pair loads half of the filter tile; needs n_tile a multiple of 64 and an unsplit
+                                reduction, else ignored), 1 = one SM per tile, 0 = chosen by the library.
+                                Results do not depend on it bit for bit. */
 } OgleConvParams;
 
 /* Output size rule of Conv2DKernel::InferOutputShape (conv2d.cc:169-195).

@@ -111,6 +111,8 @@ static int fill_args(const OgleConvParams* p, ConvArgs* a, int* variant) {
     a->n_tile = p->n_tile;
     if (p->split < 0 || p->split > 16) return OGLE_ERR_INVALID;
     a->split = p->split;
+    if (p->sm_pair < 0 || p->sm_pair > 2) return OGLE_ERR_INVALID;
+    a->pair = p->sm_pair;
     // activation, with the per-shader differences of the reference kept:
     //   pointwise clip clamps to [0, max] (conv2d_pw.glsl:85);
     //   grouped relu is max(min_value, v) (conv2d_grp.glsl:121).

@@ -30,6 +30,9 @@ namespace ogle {
 int launch_tc_v2(tc::TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, const CUtensorMap& mBlo,
                  const CUtensorMap& mY, const CUtensorMap& mY2, long m_tiles, const float* bias, int* err_flag,
                  cudaStream_t s);
+int launch_tc_pair(tc::TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, const CUtensorMap& mBlo,
+                   const CUtensorMap& mY, const CUtensorMap& mY2, long m_tiles, const float* bias, int* err_flag,
+                   cudaStream_t s);
 
 __device__ int g_tc_error = 0;   // first error seen by any block (0 = none)
 
@@ -83,9 +86,27 @@ void choose_n_tiling_v2(int Kp, long m_tiles, TcArgs* t, int requested = 0) {
     t->n_tiles = (Kp + best_bn - 1) / best_bn;
 }
 
+// Two-SM form (conv_tc2_pair.cu): 0 = the built-in rule, 1 = never, 2 = wherever it can run.
+int pair_mode_override() {
+    static const int v = [] { const char* e = getenv("OGLE_TC_PAIR"); return e ? (e[0] == '0' ? 1 : (e[0] == '1' ? 2 : 0)) : 0; }();
+    return v;
+}
+
 bool split_k_enabled() {
     static const bool v = [] { const char* e = getenv("OGLE_TC_SPLIT_K"); return !(e && e[0] == '0'); }();
     return v;
+}
+
+// Whether a launch takes the two-SM form: it can (no gather, no split reduction, a tile width that
+// halves into multiples of 32 columns, at least one pair of tiles) and either the caller asked for it
+// or the rule holds: wide tiles, a reduction long enough that operand traffic dominates, and enough
+// pairs of tiles for two rounds of the GPU's SM pairs.
+bool want_pair(const TcArgs& t, long m_tiles, int requested) {
+    if (t.gather || t.split_k > 1 || t.ws_mode || t.BN % 64 || m_tiles < 2) return false;
+    const int mode = pair_mode_override();
+    if (mode == 1 || requested == 1) return false;
+    if (mode == 2 || requested == 2) return true;
+    return false;
 }
 
 }  // namespace
@@ -417,6 +438,13 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
                 return OGLE_ERR_CUDA;
             }
             if (y2 && cudaMemsetAsync(y2, 0, rows * (size_t)kp_b * sizeof(float), s) != cudaSuccess) return OGLE_ERR_CUDA;
+        }
+        if (want_pair(t, m_tiles, a.pair)) {
+            // each block of a pair loads half of the filter tile's rows
+            const cuuint32_t hbox[2] = {kChunk, (cuuint32_t)(t.BN / 2)};
+            if (!ogle::make_map(&mBhi, w_hi, 2, bdims, bstr, hbox, bes)) return OGLE_ERR_CUDA;
+            if (!ogle::make_map(&mBlo, w_lo, 2, bdims, bstr, hbox, bes)) return OGLE_ERR_CUDA;
+            return launch_tc_pair(t, mA, mBhi, mBlo, mY, y2 ? mY2 : mY, m_tiles, bias, error_flag_ptr(), s);
         }
         return launch_tc_v2(t, mA, mBhi, mBlo, mY, y2 ? mY2 : mY, m_tiles, bias, error_flag_ptr(), s);
     }

@@ -240,7 +240,8 @@ public:
     // deep its operand ring is and how long a tile's epilogue takes; which width wins depends on the batch
     // (rounds of tiles over the SMs) in ways a cost model only approximates. Every width gives the same bits,
     // so the layer simply times the candidates on its own tensors and keeps the fastest; then, at that width, the
-    // number of ranges its reduction is split into (which does change the order of the partial sums).
+    // number of ranges its reduction is split into (which does change the order of the partial sums); last, for
+    // an unsplit reduction, whether pairs of SMs should share the filter tiles (same bits again).
     void Tune() override {
         OgleConvParams& p = sibling_ ? pair_params_ : params_;
         if (!filter_is_constant_ || std::string(ogle_cuda_conv2d_kernel_name(&p)) != "conv_tc2_kernel") return;
@@ -264,9 +265,10 @@ public:
         float auto_ms = 0.f, best_ms = 0.f;
         p.n_tile = 0;
         p.split = 0;
+        p.sm_pair = 0;
         if (time_it(&auto_ms)) {
             best_ms = auto_ms;
-            int best_tile = 0, best_split = 0;
+            int best_tile = 0, best_split = 0, best_pair = 0;
             for (int bn = 32; bn <= 256 && bn <= kmax; bn += 32) {          // tile widths, the library's split rule
                 float ms;
                 p.n_tile = bn;
@@ -279,11 +281,23 @@ public:
                 p.split = k;
                 if (time_it(&ms) && ms < best_ms) { best_ms = ms; best_split = k; }
             }
-            if (best_ms > 0.97f * auto_ms) { best_tile = 0; best_split = 0; }   // within noise of the defaults: keep them
+            p.split = best_split;
+            int pair_tile = best_tile;
+            for (int bn = 64; bn <= 256 && bn <= kmax; bn += 64) {           // SM pairs, unsplit, at the widths that halve
+                float ms;
+                p.n_tile = bn;
+                p.split = 1;
+                p.sm_pair = 2;
+                if (time_it(&ms) && ms < best_ms) { best_ms = ms; best_pair = 2; pair_tile = bn; }
+            }
+            if (best_pair) { best_tile = pair_tile; best_split = 1; }
+            if (best_ms > 0.97f * auto_ms) { best_tile = 0; best_split = 0; best_pair = 0; }   // within noise of the defaults: keep them
             p.n_tile = best_tile;
             p.split = best_split;
+            p.sm_pair = best_pair;
             tuned_tile_ = best_tile;
             tuned_split_ = best_split;
+            tuned_pair_ = best_pair;
         }
         workspace_for();
         cudaEventDestroy(e0);
@@ -318,7 +332,7 @@ private:
     bool filter_is_constant_ = false;
     Conv2DKernel* sibling_ = nullptr;       // absorbed later node (not owned)
     Tensor* placed_ = nullptr;              // a concat's tensor this conv writes into (not owned)
-    int tuned_tile_ = 0, tuned_split_ = 0;
+    int tuned_tile_ = 0, tuned_split_ = 0, tuned_pair_ = 0;
     OgleConvParams pair_params_;
     void* pair_packed_ = nullptr;
     float* pair_bias_ = nullptr;

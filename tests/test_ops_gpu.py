@@ -118,6 +118,61 @@ def test_conv_tensor_core_modes(oracle_port):
     assert _lib.cuda_lib().ogle_cuda_device_status() == 0
 
 
+def test_conv_on_sm_pairs_gives_the_same_bits(oracle_port):
+    """Two-SM form of the tensor-core path (sm_pair = 2: a cluster of two blocks computes 256 pixels x n_tile
+    channels, each block loading half of the filter tile): every output value sums its reduction in the same
+    order as the one-SM form, so the tensors must be identical bit for bit, and both must match the oracle.
+    Shapes: an odd number of 128-pixel tiles (the last pair has one empty half), a ragged last tile, a channel
+    count that leaves the last filter tile partly empty, a 3x3 layer (tiles of whole rows), ReLU / Clip, a
+    concat slice as destination, both tensor-core math modes."""
+    import torch
+    from ogle_b200 import _lib, ops
+    lib = _lib.cuda_lib()
+    rng = np.random.default_rng(77)
+    shapes = [  # N, H, C, K, k, s, p, act, n_tile
+        (3, 19, 512, 600, 1, 1, 0, 0, 256), (4, 19, 256, 512, 1, 1, 0, 2, 256), (5, 10, 128, 128, 1, 1, 0, 1, 128),
+        (2, 38, 64, 256, 3, 1, 1, 2, 256), (7, 10, 96, 75, 3, 2, 1, 0, 64), (1, 20, 64, 192, 1, 1, 0, 0, 192)]
+    for N, H, Cc, K, k, st, pd, act, nt in shapes:
+        x = rng.standard_normal((N, H, H, Cc), dtype=np.float32)
+        w = rng.standard_normal((K, Cc, k, k), dtype=np.float32) * np.float32(1.0 / np.sqrt(Cc * k * k))
+        b = rng.standard_normal(K, dtype=np.float32) * np.float32(0.05)
+        ref = oracle_port.conv2d(x[:2], w, b, st, pd, 1, 1, act, 0.0, 1.5)
+        x4, b4 = ops.upload(x), ops.dense_to_device(b)
+        for mode in (ops.MATH_TF32X3, ops.MATH_TF32):
+            outs = []
+            for pair in (1, 2):
+                p = ops.conv_params(N, H, H, Cc, K, k, st, pd, 1, 1, True, act, 0.0, 1.5, mode)
+                p.n_tile, p.split, p.sm_pair = nt, 1, pair
+                packed = ops.conv2d_prepack(p, ops.dense_to_device(w))
+                outs.append(ops.conv2d(p, x4, packed, b4, workspace=None))
+            assert torch.equal(outs[0], outs[1]), (N, H, Cc, K, k, mode)
+            got = ops.download(outs[1], K)[:2]
+            tol = 3e-4 if mode == ops.MATH_TF32X3 else 2e-3 * np.abs(ref).max()
+            assert np.abs(got - ref).max() <= tol, (N, H, Cc, K, mode, float(np.abs(got - ref).max()))
+            if ops.up4(K) != K:
+                assert float(outs[1][..., K:].abs().max()) == 0.0
+    # into a channel slice of a wider tensor (a concat written in place)
+    N, H, Cc, K = 3, 19, 256, 128
+    x = rng.standard_normal((N, H, H, Cc), dtype=np.float32)
+    w = rng.standard_normal((K, Cc, 1, 1), dtype=np.float32) * np.float32(0.06)
+    b = rng.standard_normal(K, dtype=np.float32)
+    x4, b4 = ops.upload(x), ops.dense_to_device(b)
+    wide = []
+    for pair in (1, 2):
+        p = ops.conv_params(N, H, H, Cc, K, 1, 1, 0, 1, 1, True, 0, 0.0, 0.0, ops.MATH_TF32X3)
+        p.out_channel_stride, p.out_channel_offset = 320, 64
+        p.n_tile, p.split, p.sm_pair = 128, 1, pair
+        packed = ops.conv2d_prepack(p, ops.dense_to_device(w))
+        out = torch.full((N, H, H, 320), -7.0, device="cuda")
+        ops.conv2d(p, x4, packed, b4, out, workspace=None)
+        wide.append(out)
+    assert torch.equal(wide[0], wide[1])
+    assert float((wide[1][..., :64] + 7.0).abs().max()) == 0.0 and float((wide[1][..., 192:] + 7.0).abs().max()) == 0.0
+    ref = oracle_port.conv2d(x, w, b, 1, 0)
+    assert np.abs(wide[1][..., 64:192].cpu().numpy() - ref).max() <= 3e-4
+    assert lib.ogle_cuda_device_status() == 0
+
+
 def test_conv_split_reduction_through_workspace(oracle_port):
     """Long reductions over few output tiles (3x3 heads on small maps, batch 1): with scratch memory lent
     (ogle_cuda_conv2d_ws) the reduction is split over several blocks per tile and a second kernel adds the slices in

@@ -129,6 +129,17 @@ int ogle_cuda_conv2d_prepack(const OgleConvParams* p, const float* w_oihw, void*
 int ogle_cuda_conv2d(const OgleConvParams* p, const float* x, const void* packed_filter,
                      const float* bias, float* y, ogle_stream_t stream);
 
+/* y = act(conv(x, w) + bias + residual): the convolution, the Add of a residual block and the activation that
+ * follows it in one pass (replaces the binary.glsl pass of nn/kernels/binary.cc and, with act != none, the relu.glsl /
+ * clip.glsl pass after it; same fp32 operations in the same order as the separate passes, so the result is bit-identical
+ * to them). residual: a tensor with the output's pixels, residual_stride floats per pixel (0 = round_up(K,4)), channel c of
+ * the convolution at residual[pixel * residual_stride + c]. Served by the tensor-core path only
+ * (ogle_cuda_conv2d_residual_supported: math_mode TF32 or TF32X3, >= 16 input channels); OGLE_ERR_UNSUPPORTED otherwise -
+ * the caller then runs ogle_cuda_conv2d and ogle_cuda_add_act. */
+int ogle_cuda_conv2d_residual_supported(const OgleConvParams* p);
+int ogle_cuda_conv2d_residual(const OgleConvParams* p, const float* x, const void* packed_filter, const float* bias,
+                              const float* residual, int residual_stride, float* y, ogle_stream_t stream);
+
 /* The same with scratch memory lent by the caller (device memory, 16-byte aligned, at least
  * ogle_cuda_conv2d_workspace_bytes(p), which is 0 for most layers). Layers with a long reduction
  * and few output tiles - 3x3 heads on small feature maps, the whole network at batch 1 - then split

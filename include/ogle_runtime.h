@@ -39,6 +39,9 @@ void ogle_session_destroy(OgleSession* s);
  * Add runs in the Add's pass; the Add's own tensor is then not readable), "fuse_concats" (0/1: a Conv
  * or re-padding Reshape whose result only a Concat reads writes into its slice of the Concat's tensor; a
  * Concat with every slice written that way is dropped; the producers' own tensors are then not readable),
+ * "fuse_residuals" (0/1: an Add one of whose operands is a convolution's result that nothing else reads runs in
+ * that convolution's pass, with the Relu the Add may have taken over; the convolution's and the Add's own tensors
+ * are then not readable),
  * "tune" (0/1: after set-up every convolution served by the tensor cores times its tile widths on its own
  * tensors and keeps the fastest; the reduction of a layer may then be split differently from session to
  * session, i.e. results can differ in the last bits between sessions, never between runs of one),
@@ -64,6 +67,8 @@ int ogle_session_get_output(OgleSession* s, const char* name, const char* dforma
 int ogle_session_num_active_kernels(OgleSession* s);
 /* Concat inputs that their producers write in place (option "fuse_concats"). */
 int ogle_session_num_placed(OgleSession* s);
+/* Residual Adds that run in a convolution's pass (option "fuse_residuals"). */
+int ogle_session_num_residuals(OgleSession* s);
 /* Branches of the captured graph that run beside the stream of their predecessors
  * (option "streams" > 1); 0 before the capture or for a chain. */
 int ogle_session_num_branches(OgleSession* s);

@@ -66,6 +66,8 @@ CUDA_SYMBOLS = {
     "ogle_cuda_conv2d_filter_bytes": (C.c_size_t, [C.POINTER(ConvParams)]),
     "ogle_cuda_conv2d_prepack": (C.c_int, [C.POINTER(ConvParams), _vp, _vp, _vp]),
     "ogle_cuda_conv2d": (C.c_int, [C.POINTER(ConvParams), _vp, _vp, _vp, _vp, _vp]),
+    "ogle_cuda_conv2d_residual_supported": (C.c_int, [C.POINTER(ConvParams)]),
+    "ogle_cuda_conv2d_residual": (C.c_int, [C.POINTER(ConvParams), _vp, _vp, _vp, _vp, C.c_int, _vp, _vp]),
     "ogle_cuda_conv2d_workspace_bytes": (C.c_size_t, [C.POINTER(ConvParams)]),
     "ogle_cuda_conv2d_ws": (C.c_int, [C.POINTER(ConvParams), _vp, _vp, _vp, _vp, _vp, C.c_size_t, _vp]),
     "ogle_cuda_conv2d_kernel_name": (C.c_char_p, [C.POINTER(ConvParams)]),

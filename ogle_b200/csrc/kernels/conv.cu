@@ -8,7 +8,7 @@ namespace ogle {
 int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x,
                    const float* w_hi, const float* w_lo, const float* bias, float* y, cudaStream_t s,
                    float* y2 = nullptr, int K1 = 0, int split_col = 0, void* ws = nullptr, size_t ws_bytes = 0,
-                   size_t* ws_needed = nullptr);
+                   size_t* ws_needed = nullptr, const float* residual = nullptr, int res_ld = 0);
 bool conv_tc_supported(const ConvArgs& a, int variant);
 bool conv_tc_gather_supported(const ConvArgs& a, int variant);
 bool dw_tma_supported(const ConvArgs& a);
@@ -200,6 +200,31 @@ int ogle_cuda_conv2d_ws(const OgleConvParams* p, const float* x, const void* pac
                               workspace ? workspace_bytes : 0);
     }
     return launch_conv_simt(a, variant, x, reinterpret_cast<const float*>(base), bias, y, s);
+}
+
+int ogle_cuda_conv2d_residual(const OgleConvParams* p, const float* x, const void* packed_filter, const float* bias,
+                              const float* residual, int residual_stride, float* y, ogle_stream_t stream) {
+    ConvArgs a; int variant;
+    int rc = fill_args(p, &a, &variant);
+    if (rc != OGLE_OK) return rc;
+    if (a.Ho != p->out_hwc[0] || a.Wo != p->out_hwc[1]) return OGLE_ERR_INVALID;
+    if (!x || !packed_filter || !y || !residual || (a.has_bias && !bias)) return OGLE_ERR_INVALID;
+    if (!aligned16(x) || !aligned16(y) || !aligned16(packed_filter) || !aligned16(residual)) return OGLE_ERR_ALIGNMENT;
+    if (p->math_mode < OGLE_MATH_FP32 || p->math_mode > OGLE_MATH_TF32X3) return OGLE_ERR_INVALID;
+    if (!ogle_cuda_conv2d_residual_supported(p)) return OGLE_ERR_UNSUPPORTED;
+    const int ld = residual_stride ? residual_stride : a.Kp;
+    if (ld < a.Kp || (ld & 3)) return OGLE_ERR_INVALID;
+    const char* base = static_cast<const char*>(packed_filter);
+    const FilterLayout L = filter_layout(a.K, a.C / a.group, a.kernel, a.group, a.Cp);
+    return launch_conv_tc(a, variant, p->math_mode, x, reinterpret_cast<const float*>(base + L.off_hi),
+                          reinterpret_cast<const float*>(base + L.off_lo), bias, y, (cudaStream_t)stream, nullptr, 0, 0, nullptr, 0,
+                          nullptr, residual, ld);
+}
+
+int ogle_cuda_conv2d_residual_supported(const OgleConvParams* p) {
+    ConvArgs a; int variant;
+    if (fill_args(p, &a, &variant) != OGLE_OK) return 0;
+    return served_by_tc(p, a, variant) ? 1 : 0;
 }
 
 int ogle_cuda_conv2d(const OgleConvParams* p, const float* x, const void* packed_filter,

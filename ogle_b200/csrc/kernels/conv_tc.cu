@@ -204,8 +204,9 @@ splitk_reduce_kernel(const float4* __restrict__ ws, int slices, long slice_q, in
 // scratch size this layer would like.
 int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x, const float* w_hi,
                    const float* w_lo, const float* bias, float* y, cudaStream_t s, float* y2, int K1,
-                   int split_col, void* ws, size_t ws_bytes, size_t* ws_needed) {
+                   int split_col, void* ws, size_t ws_bytes, size_t* ws_needed, const float* residual, int res_ld) {
     const bool plan_only = ws_needed != nullptr;
+    if (residual && (y2 || res_ld < a.Kp || (res_ld & 3))) return OGLE_ERR_UNSUPPORTED;
     if (plan_only) *ws_needed = 0;
     TcArgs t = {};
     if (y2) {
@@ -354,7 +355,7 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
         // hangs over the end of its slice writes padding, not the next slice
         const long slice_units = t.flat ? m_tiles * kTileM : (long)((a.N + t.tn - 1) / t.tn) * t.tn;
         const size_t slice_bytes = (size_t)(t.flat ? slice_units : slice_units * a.Ho * a.Wo) * ws_cols * sizeof(float);
-        if (split_k_enabled() && chunks >= 8) {
+        if (split_k_enabled() && chunks >= 8 && !residual) {      // (a residual operand is added by whole tiles only)
             // cost of the layer in units of one reduction chunk of one tile: rounds of one work item per SM,
             // each item paying its chunks plus a fixed fill / drain of about four chunks
             auto cost_of = [&](int k) {
@@ -439,7 +440,9 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
             }
             if (y2 && cudaMemsetAsync(y2, 0, rows * (size_t)kp_b * sizeof(float), s) != cudaSuccess) return OGLE_ERR_CUDA;
         }
-        if (want_pair(t, m_tiles, a.pair)) {
+        t.res = residual;
+        t.res_ld = res_ld;
+        if (!residual && want_pair(t, m_tiles, a.pair)) {
             // each block of a pair loads half of the filter tile's rows
             const cuuint32_t hbox[2] = {kChunk, (cuuint32_t)(t.BN / 2)};
             if (!ogle::make_map(&mBhi, w_hi, 2, bdims, bstr, hbox, bes)) return OGLE_ERR_CUDA;

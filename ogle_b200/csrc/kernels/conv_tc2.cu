@@ -460,6 +460,19 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                         my_bias[i] = (a.bias_mode == 2 && (!kSplit || (wi.ks == 0 && !a.ws_mode)) && nbase + i < a.K) ? a.beta * bias[nbase + i] : 0.f;
                     staged_nbase = bias_key;
                 }
+                // residual operand: this thread's pixel (its accumulator row) in the residual tensor
+                const float* res_row = nullptr;
+                if (!kSplit && a.res) {
+                    if (a.flat) {
+                        const long pixel = (long)tc_.w0 + row;
+                        if (pixel < a.Wo) res_row = a.res + pixel * a.res_ld;
+                    } else if (row < rows_in_tile) {
+                        const int rw = row % a.tw, t2 = row / a.tw;
+                        const int rh = t2 % a.th, rn = t2 / a.th;
+                        const int n = tc_.n0 + rn, h = tc_.h0 + rh, w_ = tc_.w0 + rw;
+                        if (n < a.N && h < a.Ho && w_ < a.Wo) res_row = a.res + (((long)n * a.Ho + h) * a.Wo + w_) * a.res_ld;
+                    }
+                }
                 ok = wait_or_abort(&bar_acc_full[as], (uint32_t)(use & 1), abort_flag, a.spin_limit);
                 if (!ok) { record_error(err_flag, 4); s_abort = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -509,6 +522,10 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                                 v.y = fmaf(a.alpha, __uint_as_float(r[c4 * 4 + 1]), bb.y);
                                 v.z = fmaf(a.alpha, __uint_as_float(r[c4 * 4 + 2]), bb.z);
                                 v.w = fmaf(a.alpha, __uint_as_float(r[c4 * 4 + 3]), bb.w);
+                                if (!kSplit && res_row) {
+                                    const float4 rr = __ldg(reinterpret_cast<const float4*>(res_row + lcol) + c4);
+                                    v.x += rr.x; v.y += rr.y; v.z += rr.z; v.w += rr.w;
+                                }
                                 if (a.act == OGLE_ACT_RELU) {
                                     v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f);
                                 } else if (a.act == OGLE_ACT_CLIP) {
@@ -531,6 +548,7 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                                     if (n < kout) {
                                         if (a.bias_mode == 2) acc += my_bias[col + c4 * 4 + l];
                                         else if (a.bias_mode == 1) acc = fmaf(a.beta, bias[pix * a.ldc + n], acc);
+                                        if (!kSplit && res_row) acc += __ldg(res_row + n);
                                         acc = apply_act(acc, a.act, a.lo, a.hi);
                                     } else {
                                         acc = 0.f;         // padded lanes stay zero

@@ -60,6 +60,11 @@ struct TcArgs {
     // (chunks_per_tap chunks; kernel = 1 in this form). g_C = input channels, g_k = filter
     // size, g_bytes = window bytes rounded up to 1 KB (its slot at the end of every stage).
     int gather, g_iw, g_ih, g_C, g_bytes, g_k;
+    // Residual operand (one-SM form, unsplit reduction): res[pixel * res_ld + channel] is added to the
+    // convolution's value (after the bias, before the activation) - a residual block's Add and activation in
+    // the convolution's own pass. Null = none.
+    const float* res;
+    int res_ld;
     uint32_t spin_limit;      // polls a role waits for its turn before it gives up (kSpinLimit by default)
 };
 

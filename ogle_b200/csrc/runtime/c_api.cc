@@ -98,6 +98,8 @@ int ogle_session_set_option(OgleSession* s, const char* key, int value) {
             s->session->set_fuse_activations(value != 0);
         } else if (k == "fuse_concats") {
             s->session->set_fuse_concats(value != 0);
+        } else if (k == "fuse_residuals") {
+            s->session->set_fuse_residuals(value != 0);
         } else if (k == "tune") {
             s->session->set_tune(value != 0);
         } else if (k == "streams") {
@@ -174,6 +176,7 @@ int ogle_session_get_output(OgleSession* s, const char* name, const char* dforma
 
 int ogle_session_num_active_kernels(OgleSession* s) { return s ? s->session->num_active_kernels() : -1; }
 int ogle_session_num_placed(OgleSession* s) { return s ? s->session->num_placed() : -1; }
+int ogle_session_num_residuals(OgleSession* s) { return s ? s->session->num_residuals() : -1; }
 int ogle_session_num_branches(OgleSession* s) { return s ? s->session->num_branches() : -1; }
 int ogle_session_graph_captured(OgleSession* s) { return s ? int(s->session->graph_captured()) : -1; }
 size_t ogle_session_device_bytes(OgleSession* s) { return s ? s->session->device_bytes() : 0; }

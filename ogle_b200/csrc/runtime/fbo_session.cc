@@ -19,6 +19,7 @@ FBOSession::FBOSession(Context* context) : context_(context) {
     if (const char* g = std::getenv("OGLE_FUSE_SIBLINGS")) fuse_siblings_ = std::atoi(g) != 0;
     if (const char* g = std::getenv("OGLE_FUSE_ACTIVATIONS")) fuse_activations_ = std::atoi(g) != 0;
     if (const char* g = std::getenv("OGLE_FUSE_CONCATS")) fuse_concats_ = std::atoi(g) != 0;
+    if (const char* g = std::getenv("OGLE_FUSE_RESIDUALS")) fuse_residuals_ = std::atoi(g) != 0;
     if (const char* g = std::getenv("OGLE_TUNE")) tune_ = std::atoi(g) != 0;
     if (const char* g = std::getenv("OGLE_STREAMS")) set_streams(std::atoi(g));
 }
@@ -157,6 +158,8 @@ void FBOSession::Finalize() {
     elided_.assign(total_tensors_.size(), false);
     elided_why_.assign(total_tensors_.size(), std::string());
     if (fuse_activations_) FuseActivations();
+    num_residuals_ = 0;
+    if (fuse_residuals_) FuseResiduals();
     num_placed_ = 0;
     if (fuse_concats_) FuseConcats();
     context_->Synchronize();
@@ -206,6 +209,68 @@ void FBOSession::FuseActivations() {
         elided_why_[size_t(out_id)] = "its only reader, an activation, runs in the producer's pass (session option "
                                       "fuse_activations = 0 or OGLE_FUSE_ACTIVATIONS=0 keeps it)";
         ++num_fused_;
+    }
+}
+
+void FBOSession::FuseResiduals() {
+    // An Add whose one operand is a convolution's result that nothing else reads, and whose other operand is
+    // complete before that convolution runs, moves into the convolution's pass together with the activation the
+    // Add may have taken over.
+    auto readers = [&](int id) {
+        int n = 0;
+        for (const auto& k : kernels_)
+            for (int in : k->input_tensor_indexes_) n += in == id;
+        return n;
+    };
+    auto position = [&](const Kernel* k) {
+        for (size_t i = 0; i < active_.size(); ++i)
+            if (active_[i] == k) return long(i);
+        return long(-1);
+    };
+    for (size_t j = 0; j < active_.size(); ++j) {
+        Kernel* add = active_[j];
+        int act; float lo, hi; Tensor* dst = nullptr;
+        if (add->input_tensor_indexes_.size() != 2 || !add->AsResidualAdd(&act, &lo, &hi, &dst)) continue;
+        for (int side = 0; side < 2; ++side) {
+            const int conv_id = add->input_tensor_indexes_[size_t(side)], res_id = add->input_tensor_indexes_[size_t(1 - side)];
+            if (conv_id == res_id || readers(conv_id) != 1 || elided_[size_t(conv_id)] || elided_[size_t(res_id)]) continue;
+            Kernel* conv = nullptr;
+            Kernel* res_producer = nullptr;
+            for (const auto& k : kernels_) {
+                if (k->output_tensor_indexes_.size() == 1 && k->output_tensor_indexes_[0] == conv_id) conv = k.get();
+                for (int out : k->output_tensor_indexes_)
+                    if (out == res_id) res_producer = k.get();
+            }
+            const long ci = conv ? position(conv) : -1;
+            if (ci < 0 || ci >= long(j)) continue;
+            if (res_producer) {
+                // an alias (same-bytes reshape) has no place in the sequence of its own; keep those out
+                if (res_producer->IsNoOp()) continue;
+                const long ri = position(res_producer);
+                if (ri >= ci) continue;                        // not there yet when the convolution runs
+                if (ri < 0) {
+                    bool absorbed = false;                   // its work may run inside another node, later than we know
+                    for (Kernel* a : active_)
+                        for (Kernel* b : a->absorbed_) absorbed = absorbed || b == res_producer;
+                    if (absorbed) continue;
+                }
+            }
+            if (!conv->AbsorbResidualAdd(add, total_tensors_[size_t(res_id)].get(), dst, act, lo, hi)) continue;
+            conv->absorbed_.push_back(add);
+            conv->extra_writes_.push_back(dst);
+            active_.erase(active_.begin() + long(j));
+            --j;
+            elided_[size_t(conv_id)] = true;
+            elided_why_[size_t(conv_id)] = "its only reader, a residual Add, runs in the convolution's pass (session option "
+                                            "fuse_residuals = 0 or OGLE_FUSE_RESIDUALS=0 keeps it)";
+            const int add_out = add->output_tensor_indexes_[0];
+            if (total_tensors_[size_t(add_out)].get() != dst && !elided_[size_t(add_out)]) {
+                elided_[size_t(add_out)] = true;
+                elided_why_[size_t(add_out)] = elided_why_[size_t(conv_id)];
+            }
+            ++num_residuals_;
+            break;
+        }
     }
 }
 

@@ -74,6 +74,8 @@ public:
     // tensors are then not produced; GetOutputs on them fails with a message naming this
     // switch (default on; OGLE_FUSE_CONCATS=0 disables). Set before the first Run.
     void set_fuse_concats(bool flag) { fuse_concats_ = flag; }
+    void set_fuse_residuals(bool flag) { fuse_residuals_ = flag; }
+    int num_residuals() const { return num_residuals_; }
     // Launch tuning: after set-up every node may time variants of its launch that give identical results
     // and keep the fastest (convolutions on the tensor cores: the tile width). Default on; OGLE_TUNE=0
     // disables. Set before the first Run.
@@ -104,6 +106,7 @@ private:
     void Finalize();
     void FuseSiblings();
     void FuseActivations();
+    void FuseResiduals();
     void FuseConcats();
     void Execute();
     void DropGraph();
@@ -125,6 +128,8 @@ private:
     bool fuse_siblings_ = true;
     bool fuse_activations_ = true;
     bool fuse_concats_ = true;
+    bool fuse_residuals_ = true;
+    int num_residuals_ = 0;
     bool tune_ = true;
     int num_placed_ = 0;
     std::vector<bool> elided_;                // tensors no node produces any more (activation / concat fusion)

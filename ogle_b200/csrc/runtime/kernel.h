@@ -53,6 +53,13 @@ public:
     // work in the same pass (this kernel's Compute then writes the consumer's output instead
     // of its own, which is no longer produced; the session drops the consumer).
     virtual bool AbsorbConsumer(Kernel* consumer) { return false; }
+    // Residual blocks. An elementwise Add (with the activation it may have absorbed) describes itself:
+    // the activation it applies and the tensor its result goes to.
+    virtual bool AsResidualAdd(int* act, float* lo, float* hi, Tensor** dst) const { return false; }
+    // Offered such an Add as the only reader of this kernel's output, and the Add's other operand (complete
+    // before this kernel runs): return true to add that operand and apply the activation in this kernel's own
+    // pass, writing `dst` (the session then drops the Add; this kernel's own tensor is no longer produced).
+    virtual bool AbsorbResidualAdd(Kernel* add, Tensor* residual, Tensor* dst, int act, float lo, float hi) { return false; }
     // For AbsorbConsumer implementations: the activation a node applies, if it is one.
     virtual bool AsActivation(int* act, float* lo, float* hi) const { return false; }
     // Called once by the session after every tensor exists and the fusions are decided: a node may time

@@ -236,6 +236,27 @@ public:
         return true;
     }
 
+    // A residual block's tail: y = act(conv(x) + bias + residual) in the convolution's pass
+    // (ogle_cuda_conv2d_residual; same fp32 operations in the same order as conv, binary add and activation
+    // passes, nn/kernels/binary.cc + relu.cc). Relu or no activation only: a Clip keeps its own pass, because a
+    // pointwise convolution's built-in clip clamps to [0, max] (conv2d_pw.glsl:85), not to [min, max].
+    bool AbsorbResidualAdd(Kernel* add, Tensor* residual, Tensor* dst, int act, float lo, float hi) override {
+        if (sibling_ || placed_ || residual_ || !filter_is_constant_ || output_tensors_.empty()) return false;
+        if (params_.act != OGLE_ACT_NONE || (act != OGLE_ACT_NONE && act != OGLE_ACT_RELU)) return false;
+        if (params_.out_channel_stride || params_.out_channel_offset) return false;
+        if (!ogle_cuda_conv2d_residual_supported(&params_)) return false;
+        if (residual->AllocatedSize() != output_tensors_[0]->AllocatedSize() ||
+            dst->AllocatedSize() != output_tensors_[0]->AllocatedSize())
+            return false;
+        params_.act = act;
+        params_.min_value = lo;
+        params_.max_value = hi;
+        residual_ = residual;
+        residual_dst_ = dst;
+        kernel_name_ += "+" + add->kernel_name();
+        return true;
+    }
+
     // The tensor-core path's tile width (output channels per tile) decides how many tiles a layer has, how
     // deep its operand ring is and how long a tile's epilogue takes; which width wins depends on the batch
     // (rounds of tiles over the SMs) in ways a cost model only approximates. Every width gives the same bits,
@@ -316,6 +337,11 @@ public:
         if (!filter_is_constant_)
             OGLE_CUDA_OK(ogle_cuda_conv2d_prepack(&params_, inputs[1]->device<float>(), packed_, context_->stream()));
         const float* bias = inputs.size() > 2 ? inputs[2]->device<float>() : nullptr;
+        if (residual_) {
+            OGLE_CUDA_OK(ogle_cuda_conv2d_residual(&params_, inputs[0]->device<float>(), packed_, bias, residual_->device<float>(),
+                                                   0, residual_dst_->device<float>(), context_->stream()));
+            return;
+        }
         float* y = placed_ ? placed_->device<float>() : outputs[0]->device<float>();
         OGLE_CUDA_OK(ogle_cuda_conv2d_ws(&params_, inputs[0]->device<float>(), packed_, bias, y, workspace_, workspace_bytes_,
                                          context_->stream()));
@@ -332,6 +358,8 @@ private:
     bool filter_is_constant_ = false;
     Conv2DKernel* sibling_ = nullptr;       // absorbed later node (not owned)
     Tensor* placed_ = nullptr;              // a concat's tensor this conv writes into (not owned)
+    Tensor* residual_ = nullptr;            // a residual block's other operand, added in this conv's pass (not owned)
+    Tensor* residual_dst_ = nullptr;        // where that sum (after the activation) goes (not owned)
     int tuned_tile_ = 0, tuned_split_ = 0, tuned_pair_ = 0;
     OgleConvParams pair_params_;
     void* pair_packed_ = nullptr;
@@ -443,6 +471,12 @@ public:
         float* y = act_out_ ? act_out_->device<float>() : out[0]->device<float>();
         OGLE_CUDA_OK(ogle_cuda_add_act(in[0]->device<float>(), in[1]->device<float>(), y, long(in[0]->AllocatedElements()),
                                        act_, act_lo_, act_hi_, context_->stream()));
+    }
+    bool AsResidualAdd(int* act, float* lo, float* hi, Tensor** dst) const override {
+        if (output_tensors_.empty()) return false;
+        *act = act_; *lo = act_lo_; *hi = act_hi_;
+        *dst = act_out_ ? act_out_ : output_tensors_[0];
+        return true;
     }
     // a residual block's Add -> Relu (or Clip) as one pass
     bool AbsorbConsumer(Kernel* consumer) override {

@@ -109,6 +109,17 @@ def conv2d(p, x4, packed, bias=None, out=None, workspace="auto"):
     return out
 
 
+def conv2d_residual(p, x4, packed, bias, residual4, out=None):
+    """act(conv(x) + bias + residual) in one pass (ogle_cuda_conv2d_residual); residual4 has the output's shape."""
+    _require_cuda(x4, packed, bias, residual4)
+    Ho, Wo, K = p.out_hwc
+    if out is None:
+        out = torch.empty((p.N, Ho, Wo, up4(K)), dtype=torch.float32, device="cuda")
+    check(_lib.cuda_lib().ogle_cuda_conv2d_residual(C.byref(p), _p(x4), _p(packed), _p(bias), _p(residual4),
+                                                    residual4.shape[-1], _p(out), _stream()), "conv2d_residual")
+    return out
+
+
 def conv2d_pair(x4, w1, b1, w2, b2, N, H, W, Cin, kernel, stride=1, pad=0, dilation=1, act=ACT_NONE, lo=0.0, hi=0.0,
                 math_mode=MATH_TF32X3, use_workspace=True):
     """Two convolutions over the same input in one pass (w1/w2 dense OIHW device tensors, b1/b2 device

@@ -32,6 +32,7 @@ RT_SYMBOLS = {
     "ogle_session_get_output": (C.c_int, [_vp, _cp, _cp, _vp, C.c_size_t]),
     "ogle_session_num_active_kernels": (C.c_int, [_vp]),
     "ogle_session_num_placed": (C.c_int, [_vp]),
+    "ogle_session_num_residuals": (C.c_int, [_vp]),
     "ogle_session_num_branches": (C.c_int, [_vp]),
     "ogle_session_graph_captured": (C.c_int, [_vp]),
     "ogle_session_device_bytes": (C.c_size_t, [_vp]),
@@ -245,6 +246,10 @@ class FBOSession:
     def num_placed(self):
         """Concat inputs written in place by their producers (option "fuse_concats")."""
         return self._lib.ogle_session_num_placed(self._h)
+
+    def num_residuals(self):
+        """Residual Adds computed in a convolution's pass (option "fuse_residuals")."""
+        return self._lib.ogle_session_num_residuals(self._h)
 
     def num_branches(self):
         return self._lib.ogle_session_num_branches(self._h)

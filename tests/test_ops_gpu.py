@@ -118,6 +118,50 @@ def test_conv_tensor_core_modes(oracle_port):
     assert _lib.cuda_lib().ogle_cuda_device_status() == 0
 
 
+def test_conv_with_residual_operand_equals_the_separate_passes(oracle_port):
+    """ogle_cuda_conv2d_residual: act(conv(x) + bias + residual) in the convolution's pass performs the same fp32
+    operations in the same order as ogle_cuda_conv2d followed by ogle_cuda_add_act, so the two must agree bit for
+    bit; also checked against the oracle's conv + add + relu. Pointwise and 3x3 (tiles of whole rows), a ragged
+    last tile, a channel count that is no multiple of 4 (padded lanes stay zero), Relu and no activation."""
+    import torch
+    from ogle_b200 import _lib, ops
+    rng = np.random.default_rng(91)
+    shapes = [  # N, H, C, K, k, s, p, act
+        (3, 19, 64, 64, 1, 1, 0, 2), (2, 28, 128, 128, 3, 1, 1, 2), (5, 7, 512, 510, 3, 1, 1, 0), (1, 56, 64, 64, 3, 1, 1, 2),
+        (2, 14, 256, 30, 1, 1, 0, 2)]
+    for N, H, Cc, K, k, st, pd, act in shapes:
+        x = rng.standard_normal((N, H, H, Cc), dtype=np.float32)
+        w = rng.standard_normal((K, Cc, k, k), dtype=np.float32) * np.float32(1.0 / np.sqrt(Cc * k * k))
+        b = rng.standard_normal(K, dtype=np.float32) * np.float32(0.05)
+        Ho = (H + 2 * pd - k) // st + 1
+        res = rng.standard_normal((N, Ho, Ho, K), dtype=np.float32)
+        ref = oracle_port.conv2d(x[:2], w, b, st, pd) + res[:2]
+        if act == 2:
+            ref = np.maximum(ref, 0.0)
+        x4, b4, r4 = ops.upload(x), ops.dense_to_device(b), ops.upload(res)
+        for mode in (ops.MATH_TF32X3, ops.MATH_TF32):
+            p = ops.conv_params(N, H, H, Cc, K, k, st, pd, 1, 1, True, act, 0.0, 0.0, mode)
+            p.split = 1
+            packed = ops.conv2d_prepack(p, ops.dense_to_device(w))
+            fused = ops.conv2d_residual(p, x4, packed, b4, r4)
+            q = ops.conv_params(N, H, H, Cc, K, k, st, pd, 1, 1, True, 0, 0.0, 0.0, mode)
+            q.split = 1
+            plain = ops.conv2d(q, x4, packed, b4, workspace=None)
+            two_pass = ops.add_act(plain, r4, act)
+            assert torch.equal(fused, two_pass), (N, H, Cc, K, k, mode)
+            got = ops.download(fused, K)[:2]
+            tol = 3e-4 if mode == ops.MATH_TF32X3 else 2e-3 * np.abs(ref).max()
+            assert np.abs(got - ref).max() <= tol, (N, H, Cc, K, mode, float(np.abs(got - ref).max()))
+            if ops.up4(K) != K:
+                assert float(fused[..., K:].abs().max()) == 0.0
+    # a parameter set the tensor cores do not serve is refused, not silently computed another way
+    p = ops.conv_params(1, 8, 8, 8, 8, 3, 1, 1, 1, 1, True, 0, 0.0, 0.0, ops.MATH_FP32)
+    packed = ops.conv2d_prepack(p, torch.zeros((8, 8, 3, 3), device="cuda"))
+    with pytest.raises(_lib.OgleError):
+        ops.conv2d_residual(p, torch.zeros((1, 8, 8, 8), device="cuda"), packed, torch.zeros(8, device="cuda"),
+                            torch.zeros((1, 8, 8, 8), device="cuda"))
+
+
 def test_conv_on_sm_pairs_gives_the_same_bits(oracle_port):
     """Two-SM form of the tensor-core path (sm_pair = 2: a cluster of two blocks computes 256 pixels x n_tile
     channels, each block loading half of the filter tile): every output value sums its reduction in the same

@@ -245,6 +245,40 @@ def test_activation_fusion_is_transparent():
     assert np.array_equal(outs[0], outs[1])
 
 
+def test_residual_fusion_is_transparent():
+    """ResNet's eight residual tails (conv -> Add -> Relu) run inside the second convolution of each block
+    (ogle_cuda_conv2d_residual): eight launches fewer again, the same logits as with the fusion off, and the
+    convolution's own result, which is no longer produced, cannot be read."""
+    from ogle_b200 import models, session
+    model, _ = models.resnet18(batch=2, seed=6, weight_std="he")
+    x = np.random.default_rng(41).standard_normal((2, 224, 224, 3), dtype=np.float32)
+    add = next(n for n in model.nodes if n.type == "Add")
+    conv_out = model.tensor_names[add.input_index[0]]
+    outs, counts, fused = [], [], []
+    for fuse in (1, 0):
+        sess = session.FBOSession()
+        sess.set_option("fuse_residuals", fuse)
+        sess.set_option("tune", 0)
+        sess.LoadGraph(model)
+        for _ in range(3):                        # eager, capture, replay
+            sess.Run({"input": x})
+        outs.append(sess.GetOutputs(["logits"], ["ANY"])[0])
+        counts.append(sess.num_active_kernels())
+        fused.append(sess.num_residuals())
+        if fuse:
+            with pytest.raises(session.OgleError, match="not materialised"):
+                sess.GetOutputs([conv_out], ["ANY"])
+        else:
+            assert sess.GetOutputs([conv_out], ["ANY"])[0].shape[0] == 2
+        sess.close()
+    assert fused == [8, 0]
+    assert counts[1] - counts[0] == 8
+    # the fused pass performs the separate passes' operations in their order (bit-identical at the operator level:
+    # test_conv_with_residual_operand_equals_the_separate_passes), but a convolution with a residual operand never
+    # splits its reduction, while the same layer on its own may: the partial sums can be grouped differently
+    assert np.abs(outs[0] - outs[1]).max() <= 3e-4 * max(1.0, float(np.abs(outs[1]).max()))
+
+
 def test_detector_end_to_end_matches_oracle_post_process(oracle_port):
     """Detector::Detect (detector.cc:275-295): network, decode, softmax / threshold / top-k / NMS."""
     from ogle_b200 import models, ops, session

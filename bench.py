@@ -132,7 +132,10 @@ def tf32_peak(seconds=1.5):
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons, sampled every 20 ms while the timed regions run."""
+    """nvidia-smi clocks and throttle reasons, sampled every 20 ms. The process is started ahead of the timed
+    regions (it needs a few hundred ms to produce its first line); mark() is called when they begin and stop()
+    when they end, and only the samples in between count. A region shorter than the sampling period can fall
+    between two samples: then the last sample before it and the first after it are used, and "window" says so."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -153,7 +156,21 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
+    def wait_first(self, seconds=3.0):
+        t0 = time.time()
+        while self.proc and not self.rows and time.time() - t0 < seconds:
+            time.sleep(0.01)
+
+    def mark(self):
+        self.first = len(self.rows)
+
     def stop(self):
+        window = "timed regions"
+        first = getattr(self, "first", 0)
+        if self.proc and len(self.rows) <= first:
+            time.sleep(0.05)                      # one more sample, taken right after the region
+            window = "nearest samples before and after the timed regions"
+            first = max(0, first - 1)
         if self.proc:
             self.proc.terminate()
             try:
@@ -161,7 +178,7 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self.proc.kill()
         sm, mx, reasons = [], [], set()
-        for r in self.rows:
+        for r in self.rows[first:]:
             if len(r) < 9:
                 continue
             try:
@@ -174,7 +191,7 @@ class ClockSampler:
                     reasons.add(name)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "window": window}
 
 
 def conv_costs(model, batch):
@@ -399,10 +416,12 @@ def main():
         return max_ms(e0.elapsed_time(e1))
 
     resident = lambda i: det.detect_device_async(dev_in[i & 1].data_ptr(), B, 300, 300, False)
-    for i in range(W):
-        resident(i)
     sampler = ClockSampler(local_rank)
     sampler.start()
+    for i in range(W):
+        resident(i)
+    sampler.wait_first()
+    sampler.mark()
     ms = timed(resident, K)
     value = G * K / (ms / 1000.0)
 

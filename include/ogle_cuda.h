@@ -102,6 +102,10 @@ typedef struct {
                                 16; more than 2, or any with an activation, needs the scratch of
                                 ogle_cuda_conv2d_ws); 0 = chosen by the library. Unlike n_tile this changes the
                                 order in which a value's partial sums are added. */
+    int channels_on_m;       /* tensor-core path, at most 128 output channels, unsplit reduction: 2 = keep the
+                                accumulator transposed (filters on the 128-row side of the multiply, 256 pixels per
+                                instruction), which halves the tensor-core instructions of layers with 64-128 output
+                                channels; 1 = no, 0 = chosen by the library. Ignored where it cannot run. */
     int sm_pair;             /* tensor-core path: 2 = compute tiles of 256 pixels on pairs of SMs (each SM of a
                                 pair loads half of the filter tile; needs n_tile a multiple of 64 and an unsplit
                                 reduction, else ignored), 1 = one SM per tile, 0 = chosen by the library.

@@ -22,7 +22,7 @@ class ConvParams(C.Structure):
         ("kernel", C.c_int), ("stride", C.c_int), ("pad", C.c_int), ("dilation", C.c_int), ("group", C.c_int),
         ("has_bias", C.c_int), ("act", C.c_int), ("min_value", C.c_float), ("max_value", C.c_float),
         ("in_channel_stride", C.c_int), ("out_channel_stride", C.c_int), ("out_channel_offset", C.c_int),
-        ("math_mode", C.c_int), ("n_tile", C.c_int), ("split", C.c_int), ("sm_pair", C.c_int),
+        ("math_mode", C.c_int), ("n_tile", C.c_int), ("split", C.c_int), ("channels_on_m", C.c_int), ("sm_pair", C.c_int),
     ]
 
 

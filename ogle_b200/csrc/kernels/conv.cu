@@ -111,6 +111,8 @@ static int fill_args(const OgleConvParams* p, ConvArgs* a, int* variant) {
     a->n_tile = p->n_tile;
     if (p->split < 0 || p->split > 16) return OGLE_ERR_INVALID;
     a->split = p->split;
+    if (p->channels_on_m < 0 || p->channels_on_m > 2) return OGLE_ERR_INVALID;
+    a->on_m = p->channels_on_m;
     if (p->sm_pair < 0 || p->sm_pair > 2) return OGLE_ERR_INVALID;
     a->pair = p->sm_pair;
     // activation, with the per-shader differences of the reference kept:

@@ -17,6 +17,7 @@ struct ConvArgs {
     long M;                    // N*Ho*Wo output pixels
     int n_tile;                // requested output channels per tile of the tensor-core path (0 = choose)
     int split;                 // requested number of reduction ranges (0 = choose)
+    int on_m;                  // channels-on-M form of the tensor-core path: 0 = choose (off), 1 = no, 2 = where it can run
     int pair;                  // two-SM form of the tensor-core path: 0 = choose, 1 = no, 2 = where it can run
 };
 

@@ -30,6 +30,9 @@ namespace ogle {
 int launch_tc_v2(tc::TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, const CUtensorMap& mBlo,
                  const CUtensorMap& mY, const CUtensorMap& mY2, long m_tiles, const float* bias, int* err_flag,
                  cudaStream_t s);
+int launch_tc_t(tc::TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, const CUtensorMap& mBlo,
+                const CUtensorMap& mY, const CUtensorMap& mY2, long m_tiles, const float* bias, int* err_flag,
+                cudaStream_t s);
 int launch_tc_pair(tc::TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, const CUtensorMap& mBlo,
                    const CUtensorMap& mY, const CUtensorMap& mY2, long m_tiles, const float* bias, int* err_flag,
                    cudaStream_t s);
@@ -95,6 +98,16 @@ int pair_mode_override() {
 bool split_k_enabled() {
     static const bool v = [] { const char* e = getenv("OGLE_TC_SPLIT_K"); return !(e && e[0] == '0'); }();
     return v;
+}
+
+// Whether a launch takes the channels-on-M form (conv_tc2_t.cu): at most 128 (stacked) output channels, an
+// unsplit reduction, no gather, at least two 128-pixel tiles, and the caller asked for it (2) or the
+// environment forces it for experiments.
+bool want_channels_on_m(const TcArgs& t, int Kp_total, long m_tiles, int requested) {
+    static const int mode = [] { const char* e = getenv("OGLE_TC_T"); return e ? (e[0] == '0' ? 1 : (e[0] == '1' ? 2 : 0)) : 0; }();
+    if (t.gather || t.split_k > 1 || t.ws_mode || t.bias_mode == 1 || Kp_total > 128 || m_tiles < 2) return false;
+    if (mode == 1 || requested == 1) return false;
+    return mode == 2 || requested == 2;
 }
 
 // Whether a launch takes the two-SM form: it can (no gather, no split reduction, a tile width that
@@ -442,6 +455,15 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
         }
         t.res = residual;
         t.res_ld = res_ld;
+        if (want_channels_on_m(t, a.Kp, m_tiles, a.on_m)) {
+            // the filter tile is the M-side operand: all (stacked) channels in one tile of FR rows
+            t.BN = (a.Kp + 31) / 32 * 32;
+            t.n_tiles = 1;
+            const cuuint32_t fbox[2] = {kChunk, (cuuint32_t)t.BN};
+            if (!ogle::make_map(&mBhi, w_hi, 2, bdims, bstr, fbox, bes)) return OGLE_ERR_CUDA;
+            if (!ogle::make_map(&mBlo, w_lo, 2, bdims, bstr, fbox, bes)) return OGLE_ERR_CUDA;
+            return launch_tc_t(t, mA, mBhi, mBlo, mY, y2 ? mY2 : mY, m_tiles, bias, error_flag_ptr(), s);
+        }
         if (!residual && want_pair(t, m_tiles, a.pair)) {
             // each block of a pair loads half of the filter tile's rows
             const cuuint32_t hbox[2] = {kChunk, (cuuint32_t)(t.BN / 2)};

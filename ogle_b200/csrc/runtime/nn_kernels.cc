@@ -287,6 +287,7 @@ public:
         p.n_tile = 0;
         p.split = 0;
         p.sm_pair = 0;
+        p.channels_on_m = 0;
         if (time_it(&auto_ms)) {
             best_ms = auto_ms;
             int best_tile = 0, best_split = 0, best_pair = 0;
@@ -312,10 +313,22 @@ public:
                 if (time_it(&ms) && ms < best_ms) { best_ms = ms; best_pair = 2; pair_tile = bn; }
             }
             if (best_pair) { best_tile = pair_tile; best_split = 1; }
-            if (best_ms > 0.97f * auto_ms) { best_tile = 0; best_split = 0; best_pair = 0; }   // within noise of the defaults: keep them
+            // at most 128 output channels: the accumulator kept transposed (filters on the multiply's 128-row side)
+            int best_on_m = 0;
+            if (p.out_hwc[2] <= 128) {
+                float ms;
+                p.n_tile = 0;
+                p.split = 1;
+                p.sm_pair = 1;
+                p.channels_on_m = 2;
+                if (time_it(&ms) && ms < best_ms) { best_ms = ms; best_on_m = 2; best_pair = 0; best_tile = 0; best_split = 1; }
+                p.channels_on_m = 0;
+            }
+            if (best_ms > 0.97f * auto_ms) { best_tile = 0; best_split = 0; best_pair = 0; best_on_m = 0; }   // within noise of the defaults: keep them
             p.n_tile = best_tile;
             p.split = best_split;
             p.sm_pair = best_pair;
+            p.channels_on_m = best_on_m;
             tuned_tile_ = best_tile;
             tuned_split_ = best_split;
             tuned_pair_ = best_pair;

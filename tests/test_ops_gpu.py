@@ -162,6 +162,48 @@ def test_conv_with_residual_operand_equals_the_separate_passes(oracle_port):
                             torch.zeros((1, 8, 8, 8), device="cuda"))
 
 
+def test_conv_with_channels_on_m_gives_the_same_bits(oracle_port):
+    """Channels-on-M form of the tensor-core path (channels_on_m = 2, at most 128 output channels: the filter tile
+    is the multiply's 128-row operand and two 128-pixel tiles its 256-column operand, the epilogue transposes):
+    same products summed in the same order, so the output must equal the pixels-on-M form's bit for bit, and
+    match the oracle. Shapes: an odd number of pixel tiles, a ragged last tile, 3x3 with tiles of whole rows from
+    several images, 1x1, channel counts that are no multiple of 32 or of 4, 128 channels (the staging slabs are
+    then shared in turns), Relu / Clip, with and without a residual operand, both tensor-core math modes."""
+    import torch
+    from ogle_b200 import _lib, ops
+    lib = _lib.cuda_lib()
+    rng = np.random.default_rng(93)
+    shapes = [  # N, H, C, K, k, s, p, act
+        (3, 19, 64, 75, 3, 1, 1, 0), (2, 28, 128, 128, 3, 1, 1, 2), (5, 10, 96, 30, 3, 2, 1, 1), (4, 20, 64, 64, 1, 1, 0, 2),
+        (7, 5, 256, 126, 3, 1, 1, 0), (1, 56, 64, 64, 3, 1, 1, 2)]
+    for N, H, Cc, K, k, st, pd, act in shapes:
+        x = rng.standard_normal((N, H, H, Cc), dtype=np.float32)
+        w = rng.standard_normal((K, Cc, k, k), dtype=np.float32) * np.float32(1.0 / np.sqrt(Cc * k * k))
+        b = rng.standard_normal(K, dtype=np.float32) * np.float32(0.05)
+        Ho = (H + 2 * pd - k) // st + 1
+        res = rng.standard_normal((N, Ho, Ho, K), dtype=np.float32)
+        ref = oracle_port.conv2d(x[:2], w, b, st, pd, 1, 1, act, 0.0, 1.5)
+        x4, b4, r4 = ops.upload(x), ops.dense_to_device(b), ops.upload(res)
+        for mode in (ops.MATH_TF32X3, ops.MATH_TF32):
+            outs, outs_res = [], []
+            for on_m in (1, 2):
+                p = ops.conv_params(N, H, H, Cc, K, k, st, pd, 1, 1, True, act, 0.0, 1.5, mode)
+                p.split, p.sm_pair, p.channels_on_m = 1, 1, on_m
+                packed = ops.conv2d_prepack(p, ops.dense_to_device(w))
+                outs.append(ops.conv2d(p, x4, packed, b4, workspace=None))
+                if act != 1:
+                    outs_res.append(ops.conv2d_residual(p, x4, packed, b4, r4))
+            assert torch.equal(outs[0], outs[1]), (N, H, Cc, K, k, mode)
+            if outs_res:
+                assert torch.equal(outs_res[0], outs_res[1]), (N, H, Cc, K, k, mode, "residual")
+            got = ops.download(outs[1], K)[:2]
+            tol = 3e-4 if mode == ops.MATH_TF32X3 else 2e-3 * np.abs(ref).max()
+            assert np.abs(got - ref).max() <= tol, (N, H, Cc, K, mode, float(np.abs(got - ref).max()))
+            if ops.up4(K) != K:
+                assert float(outs[1][..., K:].abs().max()) == 0.0
+    assert lib.ogle_cuda_device_status() == 0
+
+
 def test_conv_on_sm_pairs_gives_the_same_bits(oracle_port):
     """Two-SM form of the tensor-core path (sm_pair = 2: a cluster of two blocks computes 256 pixels x n_tile
     channels, each block loading half of the filter tile): every output value sums its reduction in the same
@@ -717,6 +759,48 @@ def test_bounded_waits_run_out_cleanly(oracle_port):
                 ref = oracle_port.conv2d(case["x"], case["w"], case["bias"], 1, case["pad"], 1, 1, 2)
                 tol = 3e-4 if mode == ops.MATH_TF32X3 else 2e-3 * np.abs(ref).max()
                 assert np.abs(got - ref).max() <= tol
+    finally:
+        lib.ogle_cuda_set_wait_limit(-1)
+        lib.ogle_cuda_clear_device_status()
+
+
+def test_bounded_waits_of_the_sm_pair_and_channels_on_m_forms(oracle_port):
+    """The same drill for the other two forms of the tensor-core kernel: with zero polls allowed every role's wait
+    gives up at once; the launch returns, the status word names a wait of that form (11-18: the SM-pair form,
+    where the abort flag is raised in both blocks of the pair and the pair meets at a cluster barrier before
+    either frees its tensor memory; 21-27: the channels-on-M form), and with the limit restored the same call
+    gives the same bits as the one-SM pixels-on-M form."""
+    import torch
+    from ogle_b200 import _lib, ops
+    lib = _lib.cuda_lib()
+    rng = np.random.default_rng(57)
+    N, H, Cc, K, k, pd = 4, 19, 256, 128, 3, 1
+    x = rng.standard_normal((N, H, H, Cc), dtype=np.float32)
+    w = rng.standard_normal((K, Cc, k, k), dtype=np.float32) * np.float32(1.0 / np.sqrt(Cc * k * k))
+    b = rng.standard_normal(K, dtype=np.float32)
+    x4, b4, w4 = ops.upload(x), ops.dense_to_device(b), ops.dense_to_device(w)
+    assert lib.ogle_cuda_device_status() == 0
+
+    def params(mode, sm_pair, on_m):
+        p = ops.conv_params(N, H, H, Cc, K, k, 1, pd, 1, 1, True, 2, 0.0, 0.0, mode)
+        p.n_tile, p.split, p.sm_pair, p.channels_on_m = 128, 1, sm_pair, on_m
+        return p
+
+    try:
+        for mode in (ops.MATH_TF32, ops.MATH_TF32X3):
+            packed = ops.conv2d_prepack(params(mode, 1, 1), w4)
+            want = ops.conv2d(params(mode, 1, 1), x4, packed, b4, workspace=None)
+            for sm_pair, on_m, codes in ((2, 1, range(11, 19)), (1, 2, range(21, 28))):
+                p = params(mode, sm_pair, on_m)
+                assert lib.ogle_cuda_set_wait_limit(0) == 0
+                ops.conv2d(p, x4, packed, b4, workspace=None)           # returns: no hang, no fault
+                assert lib.ogle_cuda_device_status() == -6              # OGLE_ERR_TIMEOUT
+                assert lib.ogle_cuda_device_status_detail() in codes
+                assert lib.ogle_cuda_clear_device_status() == 0
+                lib.ogle_cuda_set_wait_limit(-1)
+                got = ops.conv2d(p, x4, packed, b4, workspace=None)
+                assert lib.ogle_cuda_device_status() == 0
+                assert torch.equal(got, want)
     finally:
         lib.ogle_cuda_set_wait_limit(-1)
         lib.ogle_cuda_clear_device_status()

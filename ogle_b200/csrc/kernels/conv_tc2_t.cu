@@ -336,8 +336,26 @@ conv_tc2_t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                         const TCoord tc_ = t_coord(a, 2 * w + pt);
                         if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                         __syncwarp();
-                        // residual operand: the tile's pixels are walked in accumulator-column order
-                        // (column fastest, then row, then image); (rw, rh, rn) is the pixel of the next column
+                        // residual operand. Usually a tile's pixels are one contiguous run of the tensor's pixels
+                        // (the flat form; whole-width rows of one image; whole images): pixel = run0 + column for
+                        // the first run_n columns. Otherwise the tile's pixels are walked in accumulator-column order
+                        // (column fastest, then row, then image); (rw, rh, rn) is the pixel of the next column.
+                        long run0 = 0;
+                        int run_n = -1;                      // -1: no contiguous run, walk
+                        if (kRes) {
+                            if (a.flat) {
+                                run0 = tc_.w0;
+                                const long left = (long)a.Wo - tc_.w0;
+                                run_n = left < 0 ? 0 : (left > kTileM ? kTileM : (int)left);
+                            } else if (a.tw == a.Wo && (a.tn == 1 || a.th == a.Ho)) {
+                                run0 = ((long)tc_.n0 * a.Ho + tc_.h0) * a.Wo;
+                                long left;
+                                if (a.tn == 1) left = tc_.n0 < a.N ? (long)(a.Ho - tc_.h0 < a.th ? a.Ho - tc_.h0 : a.th) * a.Wo : 0;
+                                else left = (long)(a.N - tc_.n0 < a.tn ? a.N - tc_.n0 : a.tn) * a.Ho * a.Wo;
+                                run_n = left < 0 ? 0 : (int)left;
+                            }
+                        }
+                        const float* res_run = kRes ? a.res + run0 * a.res_ld + lcol + lane : nullptr;
                         int rw = 0, rh = 0, rn = 0;
 #pragma unroll 1
                         for (int g = 0; g < 4; ++g) {
@@ -347,18 +365,20 @@ conv_tc2_t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                             float rr[32];
                             if (kRes) {
                                 // this channel's residual values of the 32 pixels, all loads issued before any is used
+                                if (run_n >= 0) {
+                                    const float* rp = res_run + (long)(g * 32) * a.res_ld;
 #pragma unroll
-                                for (int j = 0; j < 32; ++j) {
-                                    long pixel = -1;
-                                    if (a.flat) {
-                                        const long p_ = (long)tc_.w0 + g * 32 + j;
-                                        if (p_ < a.Wo) pixel = p_;
-                                    } else {
+                                    for (int j = 0; j < 32; ++j)
+                                        rr[j] = (real && g * 32 + j < run_n) ? __ldg(rp + (long)j * a.res_ld) : 0.f;
+                                } else {
+#pragma unroll
+                                    for (int j = 0; j < 32; ++j) {
+                                        long pixel = -1;
                                         const int n = tc_.n0 + rn, h = tc_.h0 + rh, w_ = tc_.w0 + rw;
                                         if (rn < a.tn && n < a.N && h < a.Ho && w_ < a.Wo) pixel = ((long)n * a.Ho + h) * a.Wo + w_;
                                         if (++rw == a.tw) { rw = 0; if (++rh == a.th) { rh = 0; ++rn; } }
+                                        rr[j] = (real && pixel >= 0) ? __ldg(a.res + pixel * a.res_ld + lcol + lane) : 0.f;
                                     }
-                                    rr[j] = (real && pixel >= 0) ? __ldg(a.res + pixel * a.res_ld + lcol + lane) : 0.f;
                                 }
                             }
                             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");

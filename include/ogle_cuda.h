@@ -69,6 +69,14 @@ int ogle_cuda_clear_device_status(void);
 /* The raw status word: which wait gave up (1 producer, 2 MMA issuer, 3 operand split,
  * 4 epilogue, 5 accumulator hand-back); 0 when none did. Synchronises the device. */
 int ogle_cuda_device_status_detail(void);
+/* Programmatic dependent launches for the kernels launched after this call (process-wide): each kernel's
+ * prologue (barrier set-up, tensor-memory allocation, descriptor prefetch) may then run while its predecessor
+ * on the stream drains; every kernel waits for its predecessor's results before its first global access. Pays
+ * when the launches are short (5 % at one image per step), costs 1-2 % when they are long: the runtime turns it
+ * on for sessions whose tensors are small. The environment variable OGLE_PDL (0/1), when set, overrides it.
+ * Captured CUDA graphs keep what was in force when they were captured. */
+int ogle_cuda_set_overlapped_launches(int on);
+
 /* How many times a role of the tensor-core kernels polls for its turn before it gives up, for
  * the launches that follow on any stream (process-wide). polls < 0 restores the default (2^22,
  * tens of milliseconds); 0 makes every such wait give up at once. It exists to exercise the

@@ -89,6 +89,7 @@ CUDA_SYMBOLS = {
     "ogle_cuda_gemm_ws": (C.c_int, [C.POINTER(GemmParams), _vp, _vp, _vp, _vp, _vp, C.c_size_t, _vp]),
     "ogle_cuda_gemm_static_max_bytes": (C.c_size_t, []),
     "ogle_cuda_gemm_static": (C.c_int, [C.POINTER(GemmParams), _vp, _vp, _vp, _vp, _vp]),
+    "ogle_cuda_set_overlapped_launches": (C.c_int, [C.c_int]),
     "ogle_cuda_device_status": (C.c_int, []),
     "ogle_cuda_clear_device_status": (C.c_int, []),
     "ogle_cuda_device_status_detail": (C.c_int, []),

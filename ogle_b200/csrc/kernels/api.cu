@@ -1,4 +1,5 @@
 // Library-wide state and the small informational entry points of ogle_cuda.h.
+#include <atomic>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -15,11 +16,18 @@ void set_last_error(cudaError_t e) {
     for (; s[i] && i < 255; ++i) g_last_error[i] = s[i];
     g_last_error[i] = 0;
 }
-bool overlapped_launches_enabled() {
-    // off unless asked for: measured 4 % faster at one image per step, nothing at 32, 1-2 % slower at 256
-    static const bool v = [] { const char* e = getenv("OGLE_PDL"); return e && e[0] == '1'; }();
-    return v;
+namespace {
+// -1: not set by the caller. The environment, when it names a value, wins over the caller.
+std::atomic<int> g_overlapped{-1};
 }
+bool overlapped_launches_enabled() {
+    // measured 5 % faster at one image per step, nothing at 32, 1-2 % slower at 256: off unless the
+    // environment or the caller (a session whose tensors are small) turns it on
+    static const int env = [] { const char* e = getenv("OGLE_PDL"); return e ? (e[0] == '1' ? 1 : 0) : -1; }();
+    if (env >= 0) return env == 1;
+    return g_overlapped.load(std::memory_order_relaxed) == 1;
+}
+void set_overlapped_launches(int on) { g_overlapped.store(on ? 1 : 0, std::memory_order_relaxed); }
 void set_last_error(const char* s) {
     int i = 0;
     for (; s[i] && i < 255; ++i) g_last_error[i] = s[i];
@@ -57,6 +65,11 @@ int ogle_cuda_device_status(void) {
 int ogle_cuda_device_status_detail(void) {
     if (cudaDeviceSynchronize() != cudaSuccess) return OGLE_ERR_CUDA;
     return ogle::read_tc_error();
+}
+
+int ogle_cuda_set_overlapped_launches(int on) {
+    ogle::set_overlapped_launches(on);
+    return OGLE_OK;
 }
 
 int ogle_cuda_set_wait_limit(long polls) {

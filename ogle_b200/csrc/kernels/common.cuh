@@ -53,6 +53,7 @@ __device__ __forceinline__ void grid_dependency_trigger() { asm volatile("gridde
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 bool overlapped_launches_enabled();
+void set_overlapped_launches(int on);
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

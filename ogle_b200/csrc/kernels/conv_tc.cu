@@ -103,9 +103,11 @@ bool split_k_enabled() {
 // Whether a launch takes the channels-on-M form (conv_tc2_t.cu): at most 128 (stacked) output channels, an
 // unsplit reduction, no gather, at least two 128-pixel tiles, and the caller asked for it (2) or the
 // environment forces it for experiments.
-bool want_channels_on_m(const TcArgs& t, int Kp_total, long m_tiles, int requested) {
+bool want_channels_on_m(const TcArgs& t, int Kp_total, long m_tiles, int requested, bool through_scratch = false) {
     static const int mode = [] { const char* e = getenv("OGLE_TC_T"); return e ? (e[0] == '0' ? 1 : (e[0] == '1' ? 2 : 0)) : 0; }();
-    if (t.gather || t.split_k > 1 || t.ws_mode || t.bias_mode == 1 || Kp_total > 128 || m_tiles < 2) return false;
+    if (t.gather || t.bias_mode == 1 || Kp_total > 128 || m_tiles < 2) return false;
+    // a split reduction only in the form that goes through scratch
+    if (through_scratch ? !(t.ws_mode && t.split_k > 1) : (t.split_k > 1 || t.ws_mode)) return false;
     if (mode == 1 || requested == 1) return false;
     return mode == 2 || requested == 2;
 }
@@ -413,31 +415,45 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
             return OGLE_OK;
         }
         if (t.ws_mode) {
-            t.ws_cols = ws_cols;
+            // channels-on-M form: the scratch tensor is as wide as the filter tile (never wider than planned)
+            const bool on_m = want_channels_on_m(t, a.Kp, m_tiles, a.on_m, true);
+            const int wcols = on_m ? (a.Kp + 31) / 32 * 32 : ws_cols;
+            const size_t wslice_bytes = (size_t)(t.flat ? slice_units : slice_units * a.Ho * a.Wo) * wcols * sizeof(float);
+            t.ws_cols = wcols;
             t.ws_slice = (int)slice_units;
             const int act = t.act;
             const float lo = t.lo, hi = t.hi;
             t.act = OGLE_ACT_NONE;                 // the raw sums go to the scratch tensor
             const cuuint32_t es[4] = {1, 1, 1, 1};
             if (t.flat) {
-                const cuuint64_t wd[4] = {(cuuint64_t)ws_cols, (cuuint64_t)slice_units * t.split_k, 1, 1};
-                const cuuint64_t wst[3] = {(cuuint64_t)ws_cols * 4, (cuuint64_t)ws_cols * 4 * wd[1], (cuuint64_t)ws_cols * 4 * wd[1]};
+                const cuuint64_t wd[4] = {(cuuint64_t)wcols, (cuuint64_t)slice_units * t.split_k, 1, 1};
+                const cuuint64_t wst[3] = {(cuuint64_t)wcols * 4, (cuuint64_t)wcols * 4 * wd[1], (cuuint64_t)wcols * 4 * wd[1]};
                 const cuuint32_t wb[4] = {kChunk, kTileM, 1, 1};
                 if (!ogle::make_map(&mY, ws, 4, wd, wst, wb, es)) return OGLE_ERR_CUDA;
             } else {
-                const cuuint64_t wd[4] = {(cuuint64_t)ws_cols, (cuuint64_t)a.Wo, (cuuint64_t)a.Ho, (cuuint64_t)slice_units * t.split_k};
-                const cuuint64_t wst[3] = {(cuuint64_t)ws_cols * 4, (cuuint64_t)ws_cols * 4 * a.Wo, (cuuint64_t)ws_cols * 4 * a.Wo * a.Ho};
+                const cuuint64_t wd[4] = {(cuuint64_t)wcols, (cuuint64_t)a.Wo, (cuuint64_t)a.Ho, (cuuint64_t)slice_units * t.split_k};
+                const cuuint64_t wst[3] = {(cuuint64_t)wcols * 4, (cuuint64_t)wcols * 4 * a.Wo, (cuuint64_t)wcols * 4 * a.Wo * a.Ho};
                 const cuuint32_t wb[4] = {kChunk, (cuuint32_t)t.tw, (cuuint32_t)t.th, (cuuint32_t)t.tn};
                 if (!ogle::make_map(&mY, ws, 4, wd, wst, wb, es)) return OGLE_ERR_CUDA;
             }
-            int rc = launch_tc_v2(t, mA, mBhi, mBlo, mY, mY, m_tiles, nullptr, error_flag_ptr(), s);
+            int rc;
+            if (on_m) {
+                t.BN = wcols;
+                t.n_tiles = 1;
+                const cuuint32_t fbox[2] = {kChunk, (cuuint32_t)t.BN};
+                if (!ogle::make_map(&mBhi, w_hi, 2, bdims, bstr, fbox, bes)) return OGLE_ERR_CUDA;
+                if (!ogle::make_map(&mBlo, w_lo, 2, bdims, bstr, fbox, bes)) return OGLE_ERR_CUDA;
+                rc = launch_tc_t(t, mA, mBhi, mBlo, mY, mY, m_tiles, nullptr, error_flag_ptr(), s);
+            } else {
+                rc = launch_tc_v2(t, mA, mBhi, mBlo, mY, mY, m_tiles, nullptr, error_flag_ptr(), s);
+            }
             if (rc != OGLE_OK) return rc;
             const long rows = a.M;
-            const long slice_q = (long)(slice_bytes / 16);
+            const long slice_q = (long)(wslice_bytes / 16);
             const int out_q = kp_a / 4, out2_q = y2 ? kp_b / 4 : 0;
             const long items = rows * (out_q + out2_q);
             launch_overlapped(splitk_reduce_kernel, dim3(grid_for(items, 256)), dim3(256), 0, s,
-                              reinterpret_cast<const float4*>(ws), t.split_k, slice_q, ws_cols / 4, rows,
+                              reinterpret_cast<const float4*>(ws), t.split_k, slice_q, wcols / 4, rows,
                               a.has_bias ? bias : (const float*)nullptr, act, lo, hi, reinterpret_cast<float4*>(y), ks_a / 4,
                               a.koff / 4, y2 ? K1 : a.K, out_q, reinterpret_cast<float4*>(y2), split_col,
                               y2 ? a.K - split_col : 0, out2_q);

@@ -22,6 +22,8 @@
 //     TMA box - then stores the 128-pixel x 32-channel slab with one TMA tensor store of its own. No
 //     barrier between the warps of a round; when fewer slabs than active warps fit in shared memory
 //     the warps take turns in rounds.
+// A split reduction through scratch (ws_mode, as in conv_tc2.cu) is supported: work item (pair, ks) multiplies
+// the chunks of range ks and stores its raw partial tiles into slice ks of the scratch tensor.
 // Every output value is the same sum of the same products in the same order as in the other forms.
 // All waits are bounded and the abort path is the one of conv_tc2.cu.
 #include <cuda_bf16.h>
@@ -87,6 +89,17 @@ __device__ __forceinline__ TCoord t_coord(const TcArgs& a, int m_tile) {
         c.n0 = (t / a.tiles_h) * a.tn;
     }
     return c;
+}
+
+struct TItem { int pair, ks, c_begin, c_end; };
+__device__ __forceinline__ TItem t_item(const TcArgs& a, int w, int chunks) {
+    TItem it;
+    if (!a.ws_mode) { it.pair = w; it.ks = 0; it.c_begin = 0; it.c_end = chunks; return it; }
+    it.pair = w / a.split_k;
+    it.ks = w - it.pair * a.split_k;
+    it.c_begin = it.ks * a.chunks_per_split;
+    it.c_end = it.c_begin + a.chunks_per_split < chunks ? it.c_begin + a.chunks_per_split : chunks;
+    return it;
 }
 
 // a.BN holds FR (filter rows loaded per chunk, a multiple of 32, at most 128); a.total_tiles the number of
@@ -173,11 +186,18 @@ conv_tc2_t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             int issued = 0;
             bool ok = true;
             for (int w = blockIdx.x; w < a.total_work && ok; w += gridDim.x) {
-                const TCoord t0 = t_coord(a, 2 * w), t1 = t_coord(a, 2 * w + 1);
+                const TItem wi = t_item(a, w, chunks);
+                const TCoord t0 = t_coord(a, 2 * wi.pair), t1 = t_coord(a, 2 * wi.pair + 1);
                 const int ax0 = a.flat ? t0.w0 : t0.w0 * a.stride - a.pad, ay0 = a.flat ? 0 : t0.h0 * a.stride - a.pad;
                 const int ax1 = a.flat ? t1.w0 : t1.w0 * a.stride - a.pad, ay1 = a.flat ? 0 : t1.h0 * a.stride - a.pad;
                 int ky = 0, kx = 0, c0 = 0;
-                for (int it = 0; it < chunks; ++it) {
+                if (wi.c_begin != 0) {
+                    const int tap0 = wi.c_begin / a.chunks_per_tap;
+                    ky = tap0 / a.kernel;
+                    kx = tap0 - ky * a.kernel;
+                    c0 = (wi.c_begin - tap0 * a.chunks_per_tap) * kChunk;
+                }
+                for (int it = wi.c_begin; it < wi.c_end; ++it) {
                     if (wrap > 0) ok = wait_t(&bar_empty[s], (wrap - 1) & 1u, abort_flag, a.spin_limit);
                     if (!ok) { record_error(err_flag, 21); break; }
                     mbar_expect_tx(&bar_full[s], tx);
@@ -202,8 +222,9 @@ conv_tc2_t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             int issued = 0;
             bool ok = true;
             for (int w = blockIdx.x; w < a.total_work && ok; w += gridDim.x) {
-                int brow = 0;
-                for (int it = 0; it < chunks; ++it) {
+                const TItem wi = t_item(a, w, chunks);
+                int brow = wi.c_begin * kChunk;
+                for (int it = wi.c_begin; it < wi.c_end; ++it) {
                     if (wrap > 0) ok = wait_t(&bar_empty[s], (wrap - 1) & 1u, abort_flag, a.spin_limit);
                     if (!ok) { record_error(err_flag, 27); break; }
                     mbar_expect_tx(&bar_full[s], tx);
@@ -233,12 +254,13 @@ conv_tc2_t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 if (!ok) { record_error(err_flag, 25); s_abort = 1; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d = tmem_d + (uint32_t)(as * 256);
-                for (int it = 0; it < chunks; ++it) {
+                const TItem wi = t_item(a, w, chunks);
+                for (int it = wi.c_begin; it < wi.c_end; ++it) {
                     ok = wait_t(&bar_full[s], ph, abort_flag, a.spin_limit);
                     if (!ok) { record_error(err_flag, 22); s_abort = 1; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t fd = umma_desc(sF(s)), xd = umma_desc(sX(s));
-                    umma_tf32_chunk(d, fd, xd, idesc, it > 0 ? 1u : 0u);         // f_hi x x (x read as its high part)
+                    umma_tf32_chunk(d, fd, xd, idesc, it > wi.c_begin ? 1u : 0u);         // f_hi x x (x read as its high part)
                     if (split) {
                         ok = wait_t(&bar_xf[s], ph, abort_flag, a.spin_limit);
                         if (!ok) { record_error(err_flag, 22); s_abort = 1; break; }
@@ -266,7 +288,8 @@ conv_tc2_t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             uint32_t ph = 0;
             bool ok = true;
             for (int w = blockIdx.x; w < a.total_work && ok; w += gridDim.x) {
-                for (int it = 0; it < chunks; ++it) {
+                const TItem wi = t_item(a, w, chunks);
+                for (int it = wi.c_begin; it < wi.c_end; ++it) {
                     ok = wait_t(&bar_full[s], ph, abort_flag, a.spin_limit);
                     if (!ok) { record_error(err_flag, 23); s_abort = 1; break; }
                     float4* pa = reinterpret_cast<float4*>(base_ptr + (size_t)s * stage_bytes);
@@ -312,16 +335,21 @@ conv_tc2_t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int active_warps = FR >> 5;
         const int ch = q * 32 + lane;                // stacked channel (accumulator lane) of this thread
         // which output this warp's slab belongs to, and its first column there
-        const bool second = a.split_col > 0 && q * 32 >= a.split_col;
+        // (partial tiles bound for the scratch tensor keep the stacked channel order and are stored raw:
+        // no bias, no activation - the second kernel applies them after adding the slices)
+        const bool raw = a.ws_mode != 0;
+        const bool second = !raw && a.split_col > 0 && q * 32 >= a.split_col;
         const int lcol = second ? q * 32 - a.split_col : q * 32;
-        const int kout = second ? a.K - a.split_col : (a.split_col > 0 ? a.K1 : a.K);
+        const int kout = raw ? FR : (second ? a.K - a.split_col : (a.split_col > 0 ? a.K1 : a.K));
         const bool real = lcol + lane < kout;        // padded lanes are written as zeros
-        const float my_b = (a.bias_mode == 2 && real && ch < a.K) ? a.beta * bias[ch] : 0.f;
+        const float my_b = (!raw && a.bias_mode == 2 && real && ch < a.K) ? a.beta * bias[ch] : 0.f;
+        const int act = raw ? OGLE_ACT_NONE : a.act;
         const CUtensorMap* my_map = second ? &tmY2 : &tmY;
         bool ok = true;
         int ti = 0;
         for (int w = blockIdx.x; w < a.total_work && ok; w += gridDim.x, ++ti) {
             const int as = ti & 1, use = ti >> 1;
+            const TItem wi = t_item(a, w, chunks);
             ok = wait_t(&bar_acc_full[as], (uint32_t)(use & 1), abort_flag, a.spin_limit);
             if (!ok) { record_error(err_flag, 24); s_abort = 1; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -333,7 +361,7 @@ conv_tc2_t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     unsigned char* slab = base_ptr + staging_off + (size_t)(q - r0) * kSlabBytes;
                     const uint32_t slab_addr = base + staging_off + (uint32_t)(q - r0) * (uint32_t)kSlabBytes;
                     for (int pt = 0; pt < 2; ++pt) {
-                        const TCoord tc_ = t_coord(a, 2 * w + pt);
+                        const TCoord tc_ = t_coord(a, 2 * wi.pair + pt);
                         if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                         __syncwarp();
                         // residual operand. Usually a tile's pixels are one contiguous run of the tensor's pixels
@@ -388,7 +416,7 @@ conv_tc2_t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                                 if (real) {
                                     v = fmaf(a.alpha, __uint_as_float(r[j]), my_b);
                                     if (kRes) v += rr[j];
-                                    v = apply_act(v, a.act, a.lo, a.hi);
+                                    v = apply_act(v, act, a.lo, a.hi);
                                 }
                                 const int px = g * 32 + j;
                                 // row px of the slab, 16-byte piece (lane / 4) swizzled by the row, word lane % 4
@@ -399,8 +427,9 @@ conv_tc2_t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                         __syncwarp();
                         if (lane == 0) {
                             if (tc_.m_tile < m_tiles) {
-                                if (a.flat) tma_store_4d_t(my_map, slab_addr, lcol, tc_.w0, 0, 0);
-                                else tma_store_4d_t(my_map, slab_addr, lcol, tc_.w0, tc_.h0, tc_.n0);
+                                // (scratch: slice ks lies ws_slice rows resp. images further on)
+                                if (a.flat) tma_store_4d_t(my_map, slab_addr, lcol, tc_.w0 + (raw ? wi.ks * a.ws_slice : 0), 0, 0);
+                                else tma_store_4d_t(my_map, slab_addr, lcol, tc_.w0, tc_.h0, tc_.n0 + (raw ? wi.ks * a.ws_slice : 0));
                             }
                             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                         }
@@ -446,9 +475,10 @@ int launch_tc_t(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, const
                 const CUtensorMap& mY, const CUtensorMap& mY2, long m_tiles, const float* bias, int* err_flag,
                 cudaStream_t s) {
     const int FR = t.BN;
-    if (FR % 32 || FR < 32 || FR > 128 || t.n_tiles != 1 || t.gather || t.split_k > 1 || t.ws_mode || t.bias_mode == 1 ||
-        (t.res && t.split_col > 0))
+    if (FR % 32 || FR < 32 || FR > 128 || t.n_tiles != 1 || t.gather || t.bias_mode == 1 || (t.res && t.split_col > 0))
         return OGLE_ERR_UNSUPPORTED;
+    if (t.split_k < 1) t.split_k = 1;
+    if ((t.split_k > 1) != (t.ws_mode != 0) || (t.ws_mode && t.res)) return OGLE_ERR_UNSUPPORTED;   // splits go through scratch only
     const size_t stage = (size_t)(t.passes == 3 ? 2 : 1) * (2 * kABytes + (size_t)FR * 128);
     const size_t kBudget = 224 * 1024;
     t.xf_groups = t.passes == 3 ? 2 : 1;
@@ -470,9 +500,10 @@ int launch_tc_t(TcArgs& t, const CUtensorMap& mA, const CUtensorMap& mBhi, const
     if (m_tiles <= 0 || m_tiles > 0x3fffffffL) return OGLE_ERR_UNSUPPORTED;
     t.total_tiles = (int)m_tiles;
     t.spin_limit = role_wait_limit();
-    t.split_k = 1;
-    t.total_work = (int)((m_tiles + 1) / 2);
-    t.chunks_per_split = t.kernel * t.kernel * t.chunks_per_tap;
+    const int all_chunks = t.kernel * t.kernel * t.chunks_per_tap;
+    t.chunks_per_split = (all_chunks + t.split_k - 1) / t.split_k;
+    if ((long)(t.split_k - 1) * t.chunks_per_split >= all_chunks && t.split_k > 1) return OGLE_ERR_UNSUPPORTED;   // an empty range
+    t.total_work = (int)((m_tiles + 1) / 2) * t.split_k;
     static thread_local int attr_device = -1;
     int dev = 0;
     cudaGetDevice(&dev);

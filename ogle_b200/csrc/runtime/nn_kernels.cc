@@ -322,6 +322,11 @@ public:
                 p.sm_pair = 1;
                 p.channels_on_m = 2;
                 if (time_it(&ms) && ms < best_ms) { best_ms = ms; best_on_m = 2; best_pair = 0; best_tile = 0; best_split = 1; }
+                static const int t_splits[] = {2, 3, 4, 6, 8};          // and with the reduction split through scratch
+                for (int k : t_splits) {
+                    p.split = k;
+                    if (time_it(&ms) && ms < best_ms) { best_ms = ms; best_on_m = 2; best_pair = 0; best_tile = 0; best_split = k; }
+                }
                 p.channels_on_m = 0;
             }
             if (best_ms > 0.97f * auto_ms) { best_tile = 0; best_split = 0; best_pair = 0; best_on_m = 0; }   // within noise of the defaults: keep them

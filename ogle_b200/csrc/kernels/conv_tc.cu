@@ -63,7 +63,10 @@ using namespace tc;
 // tile's time modelled by its tensor-core instructions: one instruction costs about 100
 // cycles up to ~180 columns (bound by the shared-memory fetch of its 128-row A operand)
 // and 0.55 cycles per column beyond.
-void choose_n_tiling_v2(int Kp, long m_tiles, TcArgs* t, int requested = 0) {
+// wide_ties: among widths of equal cost take the wider one even when everything fits in one round - for
+// layers whose reduction can be split through scratch, which fills the SMs better than narrow tiles do (a
+// narrow tile pays the same instruction floor as a wide one).
+void choose_n_tiling_v2(int Kp, long m_tiles, TcArgs* t, int requested = 0, bool wide_ties = false) {
     const int kmax = (Kp + 31) / 32 * 32;
     auto mma = [](int n) { const double c = 0.55 * n; return c < 100.0 ? 100.0 : c; };
     int best_bn = 32;
@@ -78,7 +81,7 @@ void choose_n_tiling_v2(int Kp, long m_tiles, TcArgs* t, int requested = 0) {
         const double cost = (double)rounds * per_tile;
         // equal cost: the wider tile when there are several rounds (fewer passes over A), the
         // narrower one when everything fits in one round (more SMs busy, shorter epilogues)
-        if (best_cost < 0 || cost < best_cost || (cost == best_cost && rounds > 1)) { best_cost = cost; best_bn = bn; }
+        if (best_cost < 0 || cost < best_cost || (cost == best_cost && (rounds > 1 || wide_ties))) { best_cost = cost; best_bn = bn; }
     }
     if (const char* e = getenv("OGLE_TC_BN")) {      // experiments: force the tile width
         const int v = atoi(e);
@@ -343,7 +346,9 @@ int launch_conv_tc(const ConvArgs& a, int variant, int math_mode, const float* x
             }
         }
     }
-    choose_n_tiling_v2(a.Kp, m_tiles, &t, a.n_tile);
+    choose_n_tiling_v2(a.Kp, m_tiles, &t, a.n_tile,
+                       (plan_only || (ws != nullptr && aligned16(ws))) && !t.gather && split_k_enabled() &&
+                           taps * t.chunks_per_tap >= 16);
     const int Kp128 = (a.K + 127) / 128 * 128;
     const cuuint64_t bcols = t.gather ? (cuuint64_t)t.Cp32 : (cuuint64_t)taps * t.Cp32;
     const cuuint64_t bdims[2] = {bcols, (cuuint64_t)Kp128};

@@ -396,7 +396,11 @@ conv_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                             }
                         }
                     } else
-                    for (int i = t; i < kABytes / 16; i += nthr) {
+                    for (int i0 = t; i0 < kABytes / 16; i0 += nthr) {
+                        // rows of a group of eight are taken in the order 0,4,1,5,2,6,3,7: the four rows a warp
+                        // handles at once then put their BF16 halves into both halves of the banks (rows r and
+                        // r + 4 swizzle to different 64-byte halves), two wavefronts per store instead of four
+                        const int i = split_row_order(i0);
                         const float4 v = pa[i];
                         const int r = i >> 3, j = (i & 7) ^ (r & 7);          // row; logical 16-byte chunk = channels 4j..4j+3
                         float4 h;

@@ -373,7 +373,8 @@ conv_tc2_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                     if (!ok) { record_error(err_flag, 14); raise_abort(); break; }
                     float4* pa = reinterpret_cast<float4*>(base_ptr + (size_t)s * stage_bytes);
                     uint2* p2 = reinterpret_cast<uint2*>(pa + kABytes / 16);
-                    for (int i = t; i < kABytes / 16; i += nthr) {
+                    for (int i0 = t; i0 < kABytes / 16; i0 += nthr) {
+                        const int i = split_row_order(i0);      // see conv_tc2.cu: halves the stores' bank conflicts
                         const float4 v = pa[i];
                         const int r = i >> 3, j = (i & 7) ^ (r & 7);
                         float4 h;

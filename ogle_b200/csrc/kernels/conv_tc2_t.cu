@@ -300,12 +300,13 @@ conv_tc2_t_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     float4 v8[kPieces];
                     if (nthr == 256) {
 #pragma unroll
-                        for (int u = 0; u < kPieces; ++u) v8[u] = pa[t + u * 256];
+                        for (int u = 0; u < kPieces; ++u) v8[u] = pa[split_row_order(t + u * 256)];
                     }
 #pragma unroll
                     for (int u = 0; u < kPieces; ++u) {
                         if (nthr != 256 && u > 0) break;
-                        for (int i = t + u * 256; i < (int)(x_bytes / 16); i += (nthr == 256 ? (int)(x_bytes / 16) : nthr)) {
+                        for (int i0 = t + u * 256; i0 < (int)(x_bytes / 16); i0 += (nthr == 256 ? (int)(x_bytes / 16) : nthr)) {
+                            const int i = split_row_order(i0);      // see conv_tc2.cu: halves the stores' bank conflicts
                             const float4 v = nthr == 256 ? v8[u] : pa[i];
                             const int r = i >> 3, j = (i & 7) ^ (r & 7);
                             float4 h;

@@ -169,6 +169,14 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// Operand split: piece index (row * 8 + 16-byte piece) -> the piece a thread takes instead, with the rows of
+// every group of eight permuted to 0,4,1,5,2,6,3,7 (a bijection on the pieces of a tile).
+__device__ __forceinline__ int split_row_order(int i) {
+    const int x = i >> 3;
+    const int r = (x & ~7) | ((x & 1) << 2) | ((x >> 1) & 3);
+    return (r << 3) | (i & 7);
+}
+
 // Records the first error seen by any block in the library's device status word.
 __device__ __forceinline__ void record_error(int* flag, int code) { atomicCAS(flag, 0, code); }
 

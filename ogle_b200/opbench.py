@@ -8,7 +8,13 @@ buffer is overwritten so that nothing of the previous launch is left in the 126 
 launch has its own event pair on the launching stream; median and best are reported. Inputs
 follow the sweep's distributions (N(0,1) activations, N(0,0.05) weights), one seeded CPU
 generator per tensor. Fractions are of the measured peaks in MEASURED_PEAKS.json (HBM copy
-bandwidth; bf16/2 for one-pass TF32, bf16/6 for 3xTF32), else of the stated fallback.
+bandwidth; bf16/2 for one-pass TF32, bf16/4 for 3xTF32), else of the stated fallback.
+
+    python -m ogle_b200.opbench --one-conv N H C K kernel stride pad [--math tf32x3] [--n-tile T] [--split S]
+                                [--sm-pair 0|1|2] [--channels-on-m 0|1|2] [--reps R]
+
+runs one convolution layer with the launch variant pinned (the fields of OgleConvParams that the session's
+tuning otherwise chooses) and prints its time: for comparing variants of a layer and for profiler captures of one.
 
 This is the headless counterpart of the reference's per-op profile tool (nn/profile_main.cc):
 a table per operator type, and JSON for scripts.
@@ -81,13 +87,53 @@ def run_conv(case, mode, timer):
     return kernel, med, best
 
 
+def one_conv(args):
+    """One layer, launch variant pinned; prints median microseconds per launch (back-to-back launches)."""
+    N, H, Cc, K, k, st, pd = args.one_conv
+    mode = {"fp32": ops.MATH_FP32, "tf32": ops.MATH_TF32, "tf32x3": ops.MATH_TF32X3}[args.math]
+    x = randn((N, H, H, ops.up4(Cc)), 1)
+    w = randn((K, Cc, k, k), 2, 0.05)
+    b = randn((K,), 3, 0.05)
+    p = ops.conv_params(N, H, H, Cc, K, k, st, pd, 1, 1, True, ops.ACT_RELU, 0.0, 0.0, mode)
+    p.n_tile, p.split, p.sm_pair, p.channels_on_m = args.n_tile, args.split, args.sm_pair, args.channels_on_m
+    packed = ops.conv2d_prepack(p, w)
+    ws = ops.conv_workspace(p)
+    y = ops.conv2d(p, x, packed, b, workspace=ws)
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(max(1, args.reps)):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ops.conv2d(p, x, packed, b, y, workspace=ws)
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1) * 1000.0)
+    Ho = (H + 2 * pd - k) // st + 1
+    gflop = 2.0 * N * Ho * Ho * K * Cc * k * k / 1e9
+    med = statistics.median(times)
+    print(json.dumps({"op": "conv", "shape": args.one_conv, "math_mode": args.math,
+                      "kernel": _lib.cuda_lib().ogle_cuda_conv2d_kernel_name(C.byref(p)).decode(),
+                      "n_tile": args.n_tile, "split": args.split, "sm_pair": args.sm_pair, "channels_on_m": args.channels_on_m,
+                      "us_median": med, "us_best": min(times), "tflops": gflop / med * 1e3,
+                      "device_status": _lib.cuda_lib().ogle_cuda_device_status()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--one-conv", type=int, nargs=7, metavar=("N", "H", "C", "K", "KERNEL", "STRIDE", "PAD"))
+    ap.add_argument("--math", default="tf32x3", choices=["fp32", "tf32", "tf32x3"])
+    ap.add_argument("--n-tile", type=int, default=0)
+    ap.add_argument("--split", type=int, default=0)
+    ap.add_argument("--sm-pair", type=int, default=0)
+    ap.add_argument("--channels-on-m", type=int, default=0)
     ap.add_argument("--reps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--json", default="")
     ap.add_argument("--only", default="", help="comma-separated case names")
     args = ap.parse_args()
+    if args.one_conv:
+        one_conv(args)
+        return
     if not torch.cuda.is_available():
         raise SystemExit("opbench needs a CUDA device")
     pk = peaks()

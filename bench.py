@@ -14,9 +14,12 @@ detections into a shared result region where rank 0 reads all of them (ogle_b200
 
 Prints ONE JSON line (rank 0):
   value     images/s with each rank's images already resident on its GPU ("scaling": "strong");
-  e2e       the same through the sharded Detector call with the batch in HOST memory: uploads,
-            copy-back of the detections and rank 0's gather inside the timed region;
-  h2d_only  the bare upload of the same bytes from the same buffers, for reading e2e against;
+  e2e       the same through the sharded Detector call with the batch in HOST memory as 8-bit BGR
+            frames (what the reference's Detector::Detect is given): uploads, conversion on the
+            device, copy-back of the detections and rank 0's gather inside the timed region;
+  e2e_fp32_tensors  the same with the batch as fp32 tensors (what FBOSession::Run is given:
+            four times the upload bytes);
+  h2d_only  the bare upload of the fp32 bytes from the same buffers, for reading that against;
   roofline  the dominant kernel timed live with CUDA events, its tensor-bound and HBM-bound
             layers reported as two families;
   weak_256_per_gpu  (N > 1) the figure with 256 images on EVERY GPU instead;
@@ -360,7 +363,8 @@ def main():
     tag = "bench_%s" % os.environ.get("MASTER_PORT", str(os.getpid()))
     sd = sharding.ShardedDetector(path, G, rank, world, tag, args.classes, (300, 300), mode=args.mode, score_thr=thr,
                                   top_k=topk, nms_thr=0.45, math_mode=MATH[args.math], device=local_rank,
-                                  stream=stream.cuda_stream, barrier=(dist.barrier if world > 1 else None))
+                                  stream=stream.cuda_stream, barrier=(dist.barrier if world > 1 else None),
+                                  with_frames=True)
     det, sb = sd.det, sd.batch
     sess = det.session()
 
@@ -368,15 +372,18 @@ def main():
     if rank == 0:
         for j in range(2):
             sb.input_slot(j)[...] = make_inputs(G, 1000 + j * G)
+            sb.frame_slot(j)[...] = torch.randint(0, 256, (G, 300, 300, 3), dtype=torch.uint8,
+                                                  generator=torch.Generator().manual_seed(7000 + j)).numpy()
     barrier()
     step_no = [0]
+    feed_frames = [False]      # which host input the steps are fed from: fp32 tensors or 8-bit frames
 
     def sharded_step(_i):
         s = step_no[0]
         step_no[0] += 1
         if rank == 0:
             sb.publish(s)
-        sd.submit(s)
+        sd.submit(s, frames=feed_frames[0])
         if sd.in_flight() == 2:
             done = sd.retire()
             if rank == 0:
@@ -429,14 +436,30 @@ def main():
         sharded_step(i)
     sharded_drain()
     ms_e2e = timed(sharded_step, K, sharded_drain)
-    clocks = sampler.stop()     # sampled across both timed regions
-    inf = det.info()
-    h2d = torch.tensor([float(inf["h2d_bytes"]), float(inf["d2h_bytes"])], device="cuda")
-    if world > 1:
-        dist.all_reduce(h2d)
-    e2e = {"value": G * K / (ms_e2e / 1000.0), "unit": UNIT, "h2d_bytes_per_step": int(h2d[0].item()),
-           "d2h_bytes_per_step": int(h2d[1].item()), "ms_per_step": ms_e2e / K,
-           "gather": "rank 0 reads every rank's detections from shared pinned host memory"}
+
+    def e2e_record(ms_region, what):
+        inf = det.info()
+        h2d = torch.tensor([float(inf["h2d_bytes"]), float(inf["d2h_bytes"])], device="cuda")
+        if world > 1:
+            dist.all_reduce(h2d)
+        return {"value": G * K / (ms_region / 1000.0), "unit": UNIT, "h2d_bytes_per_step": int(h2d[0].item()),
+                "d2h_bytes_per_step": int(h2d[1].item()), "ms_per_step": ms_region / K, "input": what,
+                "gather": "rank 0 reads every rank's detections from shared pinned host memory"}
+
+    e2e_fp32 = e2e_record(ms_e2e, "fp32 RGB tensors 300x300x3, mean already subtracted (what FBOSession::Run is given)")
+    # the same steps fed the way the reference's Detector::Detect is: 8-bit BGR frames in host memory; colour order,
+    # float conversion and mean subtraction run on the device. A quarter of the upload bytes.
+    feed_frames[0] = True
+    if step_no[0] & 1:
+        sharded_step(0)         # steps alternate slots and start on an even one
+        sharded_drain()
+    for i in range(W):
+        sharded_step(i)
+    sharded_drain()
+    ms_frames = timed(sharded_step, K, sharded_drain)
+    clocks = sampler.stop()     # sampled across the timed regions
+    e2e = e2e_record(ms_frames, "8-bit BGR frames 300x300 (what Detector::Detect is given)")
+    feed_frames[0] = False
 
     # the bare upload of the same bytes from the same host buffers (no compute): the ceiling e2e can be read against
     rt = session.rt_lib()
@@ -454,34 +477,6 @@ def main():
     del sink
 
     extras = {}
-    if not args.no_extras:
-        # the same pipeline fed the way the reference's Detector::Detect is (8-bit BGR frames; resize and mean
-        # subtraction on the device): a quarter of the upload bytes. Reported beside `e2e`, not in its place.
-        frames = []
-        for j in range(2):
-            buf = session.PinnedArray((B, 300, 300, 3), np.uint8)
-            buf.array[...] = torch.randint(0, 256, (B, 300, 300, 3), dtype=torch.uint8,
-                                           generator=torch.Generator().manual_seed(7000 + 10 * rank + j)).numpy()
-            frames.append(buf)
-
-        def frames_step(i):
-            det.detect_bgr8_frames_async(frames[i & 1].ptr, B, 300, 300, 300, 300)
-            if det.in_flight() == 2:
-                det.wait(fetch=False)
-
-        def det_drain():
-            while det.in_flight():
-                det.wait(fetch=False)
-
-        for i in range(W):
-            frames_step(i)
-        det_drain()
-        ms_frames = timed(frames_step, K, det_drain)
-        inf8 = det.info()
-        extras["e2e_bgr8_frames"] = {"value": G * K / (ms_frames / 1000.0), "unit": UNIT, "input": "8-bit BGR frames 300x300",
-                                     "h2d_bytes_per_rank_step": inf8["h2d_bytes"], "d2h_bytes_per_rank_step": inf8["d2h_bytes"]}
-        for f in frames:
-            f.close()
 
     # roofline of the dominant kernel, timed live: eager passes with an event pair per node
     roof = None
@@ -644,7 +639,7 @@ def main():
                    "l2": "inputs larger than L2 (%.0f MB per GPU per step, two batches alternated)" % (B * 300 * 300 * 16 / 1e6),
                    "parallelism": "image-sharded x%d, no collective; host scatter/gather through shared pinned memory" % world,
                    "cuda_graph": graph_captured, "concat_inputs_written_in_place": placed, "host_placement": placement},
-        "e2e": e2e, "h2d_only": h2d_only, "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step,
+        "e2e": e2e, "e2e_fp32_tensors": e2e_fp32, "h2d_only": h2d_only, "gpu_launches": launches_per_step * K, "launches_per_step": launches_per_step,
         "clocks": clocks, "roofline": roof, "cpu_baseline": cpu, "tf32_peak_check": peak_check}
     line.update(extras)
     print(json.dumps(line), flush=True)

@@ -328,11 +328,14 @@ class Detector:
         """n equally sized 8-bit BGR frames stored back to back at host address frames_ptr ([n, h, w, 3] bytes;
         pinned memory makes the upload asynchronous): one upload, one preprocessing launch."""
         key = (frames_ptr, n, h, w)
-        cached = getattr(self, "_frames_args", None)
-        if cached is None or cached[0] != key:
+        cache = self.__dict__.setdefault("_frames_args", {})      # callers alternate between a few buffers
+        cached = cache.get(key)
+        if cached is None:
+            if len(cache) > 8:
+                cache.clear()
             ptrs = (C.c_void_p * n)(*[frames_ptr + i * h * w * 3 for i in range(n)])
             cached = (key, ptrs, (C.c_int * n)(*([h] * n)), (C.c_int * n)(*([w] * n)))
-            self._frames_args = cached
+            cache[key] = cached
         mean = (C.c_float * 3)(*mean_rgb)
         _check(self._lib.ogle_detector_detect_bgr8_async(self._h, cached[1], cached[2], cached[3], n, H, W, mean),
                "detect_bgr8_async")

@@ -140,7 +140,7 @@ class ShardedBatch:
     LINE = 64      # counters live on separate cache lines
 
     def __init__(self, tag, global_batch, image_shape, rank, world, mode, num_classes, top_k, pin=True, barrier=None,
-                 owner=0):
+                 owner=0, with_frames=False):
         self.rank, self.world, self.owner, self.global_batch = rank, world, owner, int(global_batch)
         self.image_shape = tuple(int(d) for d in image_shape)            # (H, W, channels) of one image, fp32
         self.mode, self.num_classes, self.top_k = mode, num_classes, top_k
@@ -153,12 +153,17 @@ class ShardedBatch:
         self.slot_bytes = off
         self.image_bytes = int(np.prod(self.image_shape)) * 4
         self.input_slot_bytes = _round_up(self.global_batch * self.image_bytes, 4096)
+        # optional second input region: the same batch as 8-bit frames (what Detector::Detect is given,
+        # detector.cc:275-295), a quarter of the bytes; a step is fed from one region or the other
+        self.frame_bytes = int(np.prod(self.image_shape))
+        self.frame_slot_bytes = _round_up(self.global_batch * self.frame_bytes, 4096)
         uid = os.getuid() if hasattr(os, "getuid") else 0
         base = f"/ogle_{uid}_{tag}"
         create = rank == owner
         if not create and barrier:
             barrier()                                  # the owner creates first
         self.inputs = SharedRegion(base + "_in", 2 * self.input_slot_bytes, create, pin)
+        self.frames = SharedRegion(base + "_u8", 2 * self.frame_slot_bytes, create, pin) if with_frames else None
         self.results = SharedRegion(base + "_out", 2 * self.slot_bytes, create, pin)
         self.control = SharedRegion(base + "_ctl", self.LINE * (world + 2), create, False)
         if create and barrier:
@@ -188,6 +193,14 @@ class ShardedBatch:
     def local_input_ptr(self, step):
         lo, _ = self.local_range()
         return self.inputs.ptr + (step & 1) * self.input_slot_bytes + lo * self.image_bytes
+
+    def frame_slot(self, step):
+        """The whole batch of step `step` as 8-bit frames: uint8 [global_batch, H, W, channels] (with_frames=True)."""
+        return self.frames.view((step & 1) * self.frame_slot_bytes, (self.global_batch,) + self.image_shape, np.uint8)
+
+    def local_frame_ptr(self, step):
+        lo, _ = self.local_range()
+        return self.frames.ptr + (step & 1) * self.frame_slot_bytes + lo * self.frame_bytes
 
     def result_ptr(self, slot, rank=None):
         return self.results.ptr + slot * self.slot_bytes + self.block_offset[self.rank if rank is None else rank]
@@ -254,8 +267,9 @@ class ShardedBatch:
 
     def close(self):
         unlink = self.rank == self.owner
-        for region in (self.inputs, self.results, self.control):
-            region.close(unlink=unlink)
+        for region in (self.inputs, self.frames, self.results, self.control):
+            if region is not None:
+                region.close(unlink=unlink)
 
 
 class ShardedDetector:
@@ -268,10 +282,11 @@ class ShardedDetector:
     dims, as the converter writes them)."""
 
     def __init__(self, model_path, global_batch, rank, world, tag, num_classes, image_hw=(300, 300), mode=1,
-                 score_thr=0.01, top_k=200, nms_thr=0.45, math_mode=-1, device=-1, stream=None, barrier=None):
+                 score_thr=0.01, top_k=200, nms_thr=0.45, math_mode=-1, device=-1, stream=None, barrier=None,
+                 with_frames=False):
         from . import session
         self.batch = ShardedBatch(tag, global_batch, (image_hw[0], image_hw[1], 3), rank, world, mode, num_classes, top_k,
-                                  pin=True, barrier=barrier)
+                                  pin=True, barrier=barrier, with_frames=with_frames)
         lo, hi = self.batch.local_range()
         self.local = hi - lo
         self.H, self.W = image_hw
@@ -285,13 +300,18 @@ class ShardedDetector:
             self._slot = 0          # the detector alternates its two result slots call by call
         self._pending = []
 
-    def submit(self, step, timeout=30.0):
-        """Upload and run this rank's images of `step` (asynchronous; at most two steps in flight)."""
+    def submit(self, step, timeout=30.0, frames=False):
+        """Upload and run this rank's images of `step` (asynchronous; at most two steps in flight). frames=True:
+        the step was published as 8-bit BGR frames of the network's input size (frame_slot); they are uploaded as
+        bytes and converted on the device (BGR -> RGB, float, mean subtraction), as Detector::Detect does on the host."""
         self.batch.wait_input(step, timeout)
         if self.det is not None:
             if (step & 1) != self._slot:
                 raise OgleError("steps must be submitted in order, starting with an even step")
-            self.det.detect_async(self.batch.local_input_ptr(step), self.local, self.H, self.W)
+            if frames:
+                self.det.detect_bgr8_frames_async(self.batch.local_frame_ptr(step), self.local, self.H, self.W, self.H, self.W)
+            else:
+                self.det.detect_async(self.batch.local_input_ptr(step), self.local, self.H, self.W)
             self._slot ^= 1
         self._pending.append(step)
 

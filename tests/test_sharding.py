@@ -68,8 +68,12 @@ SHARED_WORKER = textwrap.dedent("""
     tag = "test_%%s_%%s" %% (os.environ["MASTER_PORT"], scenario)
     # no GPU here: the regions are not registered with CUDA and a stand-in plays the detector
     sb = sharding.ShardedBatch(tag, n_images, (4, 5, 3), rank, world, mode=1, num_classes=3, top_k=2, pin=False,
-                               barrier=dist.barrier)
+                               barrier=dist.barrier, with_frames=True)
     lo, hi = sb.local_range()
+    # the 8-bit frame region: same slots and ranges, a quarter of the bytes
+    assert sb.frame_slot(0).shape == (n_images, 4, 5, 3) and sb.frame_slot(0).dtype == np.uint8
+    assert sb.local_frame_ptr(1) - sb.frames.ptr == sb.frame_slot_bytes + lo * 60
+    assert sb.local_input_ptr(1) - sb.inputs.ptr == sb.input_slot_bytes + lo * 240
 
     def fake_detector(step):
         x = sb.input_slot(step)[lo:hi]                 # this rank's images, read in place

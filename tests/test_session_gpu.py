@@ -502,6 +502,41 @@ def test_detector_raw_frames_equal_host_preprocess(oracle_port):
         det.close()
 
 
+def test_sharded_detector_fed_frames_equals_fed_tensors(oracle_port):
+    """ShardedDetector (one rank here): a step published as 8-bit BGR frames in the shared host region and run
+    with submit(frames=True) gives the detections of the same step published as the fp32 tensors that the
+    reference's host-side preprocess makes of those frames; both come back through the shared result region."""
+    from ogle_b200 import models, sharding
+    rng = np.random.default_rng(61)
+    n = 3
+    model, _ = models.mobilenet_v1_ssd(batch=n, num_classes=21, seed=9, weight_std="he")
+    frames = rng.integers(0, 256, (n, 300, 300, 3), dtype=np.uint8)
+    tensors = np.stack([oracle_port.preprocess_bgr8(f, 300, 300) for f in frames])
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "ssd.dlx")
+        model.save(path)
+        sd = sharding.ShardedDetector(path, n, 0, 1, "test_frames_%d" % os.getpid(), 21, (300, 300), mode=1,
+                                      score_thr=0.01, top_k=200, with_frames=True)
+        try:
+            got = []
+            for step, as_frames in ((0, False), (1, True)):
+                if as_frames:
+                    sd.batch.frame_slot(step)[...] = frames
+                else:
+                    sd.batch.input_slot(step)[...] = tensors
+                sd.batch.publish(step)
+                sd.submit(step, frames=as_frames)
+                assert sd.retire() == step
+                out = sd.batch.gather(step, timeout=10.0, merged=True)
+                got.append({k: v.copy() for k, v in out.items()})
+                sd.batch.release(step)
+        finally:
+            sd.close()
+    assert got[0]["count"].sum() > 0
+    for key in ("score", "anchor", "cls", "box", "count"):
+        assert np.array_equal(got[0][key], got[1][key]), key
+
+
 def test_profile_tool_reports_per_type_table(tmp_path):
     """ogle_profile (the headless counterpart of nn/profile_main.cc): loads a dlx file, runs it and
     prints the per-node-type table; --json gives the same numbers for scripts."""

@@ -7,8 +7,10 @@
 // i.e. the filter tile is the M-side operand and TWO 128-pixel activation tiles, side by side in
 // shared memory, are the N-side operand. A tcgen05.mma costs about the same 140-150 cycles for
 // any N up to ~180 columns, so a layer with 64-128 output channels pays that floor once per 256
-// pixels here instead of once per 128 pixels in the pixels-on-M form (conv_tc2.cu): the
-// 3x3 heads and 64/128-channel 3x3 layers, which sit on that floor, get up to 1.8x.
+// pixels here instead of once per 128 pixels in the pixels-on-M form (conv_tc2.cu). Measured
+// on the 3x3 heads and 64/128-channel 3x3 layers, which sit on that floor: 1.5x in one-pass
+// TF32, 1.2-1.3x in the fp32-grade mode (where the shared-memory traffic of the operand split,
+// 256 rows per chunk here, then sets the pace).
 //
 // Roles and pipeline as in conv_tc2.cu (two TMA producer threads, one MMA thread, operand-split
 // warp groups for the fp32-grade mode); what differs:

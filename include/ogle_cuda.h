@@ -72,8 +72,8 @@ int ogle_cuda_device_status_detail(void);
 /* Programmatic dependent launches for the kernels launched after this call (process-wide): each kernel's
  * prologue (barrier set-up, tensor-memory allocation, descriptor prefetch) may then run while its predecessor
  * on the stream drains; every kernel waits for its predecessor's results before its first global access. Pays
- * when the launches are short (5 % at one image per step), costs 1-2 % when they are long: the runtime turns it
- * on for sessions whose tensors are small. The environment variable OGLE_PDL (0/1), when set, overrides it.
+ * when the launches are short (5 % at one image per step, 1-4 % up to 16), costs 1-2 % when they are long: the
+ * runtime turns it on for sessions whose tensors hold less than 1 GB. The environment variable OGLE_PDL (0/1), when set, overrides it.
  * Captured CUDA graphs keep what was in force when they were captured. */
 int ogle_cuda_set_overlapped_launches(int on);
 

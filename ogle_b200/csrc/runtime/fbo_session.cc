@@ -156,7 +156,7 @@ void FBOSession::Finalize() {
     }
     // short launches (small tensors: a few images per step) gain from overlapping each kernel's prologue with
     // its predecessor's tail, long ones lose a little: decided per session from the bytes its tensors hold
-    ogle_cuda_set_overlapped_launches(device_bytes_ < (size_t(192) << 20) ? 1 : 0);
+    ogle_cuda_set_overlapped_launches(device_bytes_ < (size_t(1) << 30) ? 1 : 0);
     if (fuse_siblings_) FuseSiblings();
     elided_.assign(total_tensors_.size(), false);
     elided_why_.assign(total_tensors_.size(), std::string());

@@ -91,3 +91,33 @@ def test_pinned_allocation_fails_cleanly_without_a_gpu():
     with pytest.raises(session.OgleError):
         session.PinnedArray((4, 4))
     session.rt_lib().ogle_host_free_pinned(None)          # no-op
+
+
+def test_ctypes_mirrors_have_the_headers_layout(tmp_path):
+    """The Python front end mirrors the parameter structs of include/ogle_cuda.h by hand: a small C program
+    compiled against the header prints each struct's size and the offset of its last fields, and they must be
+    what ctypes computes for the mirror (a field added on one side only shows up here, not as a corrupted launch)."""
+    import subprocess
+    from ogle_b200 import _lib
+    pairs = [("OgleConvParams", _lib.ConvParams, ["math_mode", "n_tile", "split", "channels_on_m", "sm_pair"]),
+             ("OglePoolParams", _lib.PoolParams, ["type", "out_channel_stride"]),
+             ("OgleGemmParams", _lib.GemmParams, ["bias_mode"]),
+             ("OgleConcatParams", _lib.ConcatParams, ["axis", "in_shapes"]),
+             ("OgleDetectParams", _lib.DetectParams, ["top_k", "nms_thr"])]
+    lines = ['#include <stddef.h>', '#include <stdio.h>', '#include "ogle_cuda.h"', 'int main(void) {']
+    for cname, _, fields in pairs:
+        lines.append('printf("%s %%zu", sizeof(%s));' % (cname, cname))
+        for f in fields:
+            lines.append('printf(" %%zu", offsetof(%s, %s));' % (cname, f))
+        lines.append('printf("\\n");')
+    lines += ['return 0;', '}']
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split("\n")
+    for (cname, mirror, fields), line in zip(pairs, out):
+        got = line.split()
+        assert got[0] == cname
+        want = [ctypes.sizeof(mirror)] + [getattr(mirror, f).offset for f in fields]
+        assert [int(v) for v in got[1:]] == want, (cname, got[1:], want)
